@@ -1,0 +1,139 @@
+/* C ABI of the B200 (sm_100a) MatMulNBits library.
+ *
+ * This is the thin layer between the C++ operator class (MatMulNBitsKernel, the
+ * counterpart of the reference's KernelBase subclasses) and the hand-written CUDA kernels.
+ * Signatures use plain pointers and sizes only. Every function returns 0 on success and a
+ * non-zero mnb_status otherwise; mnb_last_error() gives the message of the calling thread's
+ * last failure. Nothing here throws, and nothing falls back to the CPU: without a CUDA
+ * device every compute entry point fails with MNB_ERR_CUDA.
+ *
+ * Operator contract (com.microsoft.MatMulNBits, fp32 activations):
+ *   B       uint8 [N, n_blocks, block_size*bits/8], n_blocks = ceil(K/block_size); element
+ *           2i of a 4-bit blob is the LOW nibble of byte i (the reference's packed-INT4
+ *           convention, onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.h:42-47)
+ *   scales  fp32 [N*n_blocks]
+ *   zero_points (optional) packed like B, one code per block, rows padded to a whole byte;
+ *           default 2^(bits-1)
+ *   bias    (optional) fp32 [N]
+ *   Y[m,n] = sum_k A[m,k] * (q[n,k] - zp[n,k/block_size]) * scale[n,k/block_size] + bias[n]
+ */
+#ifndef MATMULNBITS_B200_H_
+#define MATMULNBITS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mnb_status {
+  MNB_OK = 0,
+  MNB_ERR_INVALID_ARGUMENT = 1, /* maps to std::invalid_argument in the C++ operator class */
+  MNB_ERR_CUDA = 2,             /* maps to std::runtime_error */
+  MNB_ERR_UNSUPPORTED = 3,
+  MNB_ERR_DEVICE_TIMEOUT = 4    /* a bounded device-side wait gave up; context still usable */
+} mnb_status;
+
+/* Which kernel family runs. AUTO picks by M and accuracy_level. */
+typedef enum mnb_path {
+  MNB_PATH_AUTO = 0,
+  MNB_PATH_GEMV = 1,    /* CUDA-core fused unpack-dequant GEMV, fp32 accumulate (decode) */
+  MNB_PATH_TCGEN05 = 2, /* TMA + smem dequant to bf16 + tcgen05/TMEM MMA (prefill) */
+  MNB_PATH_INT8 = 3,    /* accuracy_level 4: per-block int8 A, int32 block dots */
+  MNB_PATH_GEMV_MMA = 4 /* decode with exact 3-way bf16 split of A on warp-level MMA */
+} mnb_path;
+
+/* Device-resident, immutable weights of one MatMulNBits node. Plays the role the reference
+ * gives its per-node plan cache (onnx_light_cpu/kernels/math/gemm_kernel.cc:100-184): built
+ * once per node from the initializer tensors, reused by every Run. */
+typedef struct mnb_weights mnb_weights;
+
+/* Message of the last failure on the calling thread (never NULL). */
+const char *mnb_last_error(void);
+
+/* Number of CUDA devices visible; 0 with MNB_OK when the driver reports none. */
+int mnb_device_count(int *count);
+
+/* Library identification: "matmulnbits_b200 <version> sm_100a". */
+const char *mnb_version(void);
+
+/* Uploads one node's constant operands from HOST memory to `device`.
+ * Replaces: the per-call operand packing of IntegerMatMul4Bit2D
+ * (onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:164-206) with a one-time
+ * constant-weight upload. zero_points and bias may be NULL. */
+int mnb_weights_create(int device, const uint8_t *b, const float *scales,
+                       const uint8_t *zero_points, const float *bias, int64_t n, int64_t k,
+                       int bits, int block_size, mnb_weights **out);
+
+/* Same, but the four operand pointers are DEVICE pointers that the caller keeps alive; no
+ * copy is made. Used by benchmarks and by sharded callers that fill device memory directly. */
+int mnb_weights_wrap_device(int device, const uint8_t *b, const float *scales,
+                            const uint8_t *zero_points, const float *bias, int64_t n, int64_t k,
+                            int bits, int block_size, mnb_weights **out);
+
+int mnb_weights_destroy(mnb_weights *weights);
+
+/* Bytes the operator must read and write once per call (weights + scales + zero points +
+ * bias + A + Y): the algorithmic traffic used for roofline figures. */
+int64_t mnb_algorithmic_bytes(int64_t m, int64_t n, int64_t k, int bits, int block_size,
+                              int has_zero_points, int has_bias);
+
+/* Y = MatMulNBits(A) with A and Y in HOST memory. Synchronous: copies A to the device,
+ * runs the selected kernel, copies Y back and waits.
+ * Replaces: the body of a KernelBase::operator() that calls IntegerMatMul2D on host
+ * tensors (onnx_light_cpu/kernels/math/integer_matmul_kernel.cc:298-339). */
+int mnb_matmul_host(mnb_weights *weights, const float *a_host, int64_t m, int accuracy_level,
+                    int path, float *y_host);
+
+/* Y = MatMulNBits(A) with A and Y in DEVICE memory, asynchronous on `stream`
+ * (a cudaStream_t passed as void*, NULL = default stream).
+ * Replaces: IntegerMatMul4Bit2D's raw-pointer entry point
+ * (onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.h:52-55). */
+int mnb_matmul_device(mnb_weights *weights, const float *a_dev, int64_t m, int accuracy_level,
+                      int path, float *y_dev, void *stream);
+
+/* Column-sharded form: writes this shard's N columns into a row-major [m, ld_y] matrix
+ * starting at column `col_offset`, so g shards tile one [m, g*N] output. */
+int mnb_matmul_device_strided(mnb_weights *weights, const float *a_dev, int64_t m,
+                              int accuracy_level, int path, float *y_dev, int64_t ld_y,
+                              int64_t col_offset, void *stream);
+
+/* Waits for the device and reads the status word that kernels with bounded waits write when
+ * they give up (0 = fine, see MNB_ERR_DEVICE_TIMEOUT). Clears it after reading. The
+ * host-buffer call checks it itself; callers of the asynchronous entry points use this. */
+int mnb_weights_poll_status(mnb_weights *weights, int *status);
+
+/* Parity hooks (device pointers) ---------------------------------------------------------- */
+
+/* out[n*K + k] = q[n,k] - zp[n,k/block_size] as int32: the integer dequantization that must
+ * be bit-exact (integer_gemm_vnni.cc:60-93 nibble order, :208-223 exact integers). */
+int mnb_dequant_int_device(mnb_weights *weights, int32_t *out_dev, void *stream);
+
+/* accuracy_level 4 stage 1: per (row, block) scale = max|A|/127, aq = clamp(rne(A/scale)). */
+int mnb_quantize_a_device(const float *a_dev, int64_t m, int64_t k, int block_size,
+                          int8_t *aq_dev, float *a_scales_dev, void *stream);
+
+/* accuracy_level 4 stage 2 exposed: dots[(m*N+n)*n_blocks+blk] = sum aq*(q-zp), int32 exact
+ * (the same modulo-2^32 integer semantics as IntegerDotU8S8Scalar,
+ * integer_gemm_vnni.cc:48-56). */
+int mnb_int8_block_dots_device(mnb_weights *weights, const int8_t *aq_dev, int64_t m,
+                               int32_t *dots_dev, void *stream);
+
+/* Number of kernels this library has launched in the calling process (for benchmarks). */
+int64_t mnb_launch_count(void);
+
+/* Name of the kernel the last mnb_matmul_* call on this thread dispatched to. */
+const char *mnb_last_kernel(void);
+
+/* Geometry accessors. */
+int64_t mnb_weights_n(const mnb_weights *weights);
+int64_t mnb_weights_k(const mnb_weights *weights);
+int mnb_weights_bits(const mnb_weights *weights);
+int mnb_weights_block_size(const mnb_weights *weights);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MATMULNBITS_B200_H_ */

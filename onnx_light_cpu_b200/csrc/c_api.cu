@@ -1,0 +1,563 @@
+// C ABI of the library (declarations and contract: include/matmulnbits_b200.h).
+// Owns the per-node device weight handle, scratch buffers and the dispatch between kernels.
+// No CPU fallback exists: every compute entry point needs a CUDA device.
+
+#include "../../include/matmulnbits_b200.h"
+
+#include "nbits_common.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+namespace mnb {
+
+namespace {
+std::atomic<std::int64_t> g_launches{0};
+thread_local std::string t_last_error = "";
+thread_local const char *t_last_kernel = "";
+} // namespace
+
+void CountLaunch(int launches) { g_launches.fetch_add(launches, std::memory_order_relaxed); }
+
+// out[n*K + k] = q - zp, one thread per element.
+__global__ void __launch_bounds__(256)
+    nbits_dequant_int_kernel(const WeightView w, std::int32_t *out) {
+  const std::int64_t total = w.n * w.k;
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+    const std::int64_t row = i / w.k;
+    const std::int64_t kk = i - row * w.k;
+    out[i] = CodeOf(w, row, kk) - ZeroPointOf(w, row, static_cast<int>(kk / w.block_size));
+  }
+}
+
+const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream) {
+  const std::int64_t total = w.n * w.k;
+  if (total <= 0) {
+    return nullptr;
+  }
+  std::int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) {
+    blocks = 148 * 16;
+  }
+  nbits_dequant_int_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(w, out);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_dequant_int_kernel";
+}
+
+} // namespace mnb
+
+using mnb::OutputView;
+using mnb::WeightView;
+
+struct mnb_weights {
+  WeightView view{};
+  int device = 0;
+  int sm_count = 148;
+  bool owns = false;
+  void *owned[4] = {nullptr, nullptr, nullptr, nullptr};
+  int *status_dev = nullptr;
+  // scratch, grown on demand (guarded by `mutex`)
+  std::mutex mutex;
+  void *scratch_a = nullptr; // bf16 activations (prefill) or int8 activations (accuracy_level 4)
+  std::size_t scratch_a_bytes = 0;
+  void *scratch_s = nullptr; // activation block scales (accuracy_level 4)
+  std::size_t scratch_s_bytes = 0;
+  // host-call staging
+  float *a_dev = nullptr;
+  float *y_dev = nullptr;
+  std::size_t a_dev_bytes = 0;
+  std::size_t y_dev_bytes = 0;
+  cudaStream_t stream = nullptr;
+};
+
+namespace {
+
+int Fail(int code, const std::string &message) {
+  mnb::t_last_error = message;
+  return code;
+}
+
+int FailCuda(const char *what, cudaError_t err) {
+  return Fail(MNB_ERR_CUDA, std::string("matmulnbits_b200: ") + what + ": " + cudaGetErrorString(err));
+}
+
+bool ValidGeometry(std::int64_t n, std::int64_t k, int bits, int block_size, std::string *why) {
+  if (n <= 0 || k <= 0) {
+    *why = "MatMulNBits requires positive N and K.";
+    return false;
+  }
+  if (bits != 4 && bits != 8) {
+    *why = "MatMulNBits supports bits = 4 or 8.";
+    return false;
+  }
+  if (block_size < 16 || (block_size & (block_size - 1)) != 0) {
+    *why = "MatMulNBits block_size must be a power of two >= 16.";
+    return false;
+  }
+  return true;
+}
+
+void FillView(WeightView *v, std::int64_t n, std::int64_t k, int bits, int block_size) {
+  v->n = n;
+  v->k = k;
+  v->bits = bits;
+  v->block_size = block_size;
+  v->n_blocks = static_cast<int>((k + block_size - 1) / block_size);
+  v->blob_bytes = block_size * bits / 8;
+  v->row_bytes = v->n_blocks * v->blob_bytes;
+  v->zp_row_bytes = (v->n_blocks * bits + 7) / 8;
+}
+
+int SetupCommon(mnb_weights *h) {
+  cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, h->device) == cudaSuccess && sms > 0) {
+    h->sm_count = sms;
+  }
+  err = cudaMalloc(&h->status_dev, sizeof(int));
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMalloc(status)", err);
+  }
+  err = cudaMemset(h->status_dev, 0, sizeof(int));
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMemset(status)", err);
+  }
+  err = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaStreamCreate", err);
+  }
+  return MNB_OK;
+}
+
+int Grow(void **ptr, std::size_t *have, std::size_t need) {
+  if (need <= *have) {
+    return MNB_OK;
+  }
+  if (*ptr != nullptr) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+    *have = 0;
+  }
+  cudaError_t err = cudaMalloc(ptr, need);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMalloc(scratch)", err);
+  }
+  *have = need;
+  return MNB_OK;
+}
+
+// Core dispatch. The caller holds h->mutex and has made h->device current.
+int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_level, int path,
+             OutputView out, cudaStream_t stream) {
+  if (accuracy_level != 0 && accuracy_level != 4) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits accuracy_level must be 0 or 4.");
+  }
+  if (m < 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits requires M >= 0.");
+  }
+  if (m == 0) {
+    mnb::t_last_kernel = "none";
+    return MNB_OK;
+  }
+  const WeightView &w = h->view;
+  int chosen = path;
+  if (chosen == MNB_PATH_AUTO) {
+    if (accuracy_level == 4) {
+      chosen = MNB_PATH_INT8;
+    } else if (m <= 16) {
+      chosen = MNB_PATH_GEMV;
+    } else {
+      chosen = mnb::GemmTcgen05Supports(w, m) ? MNB_PATH_TCGEN05 : MNB_PATH_GEMV;
+    }
+  }
+  const char *name = nullptr;
+  switch (chosen) {
+  case MNB_PATH_GEMV: {
+    if (m <= 16) {
+      name = mnb::LaunchGemvStream(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
+    if (name == nullptr) {
+      name = mnb::LaunchGemvGeneric(w, a_dev, m, out, stream);
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_MMA: {
+    name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED, "MatMulNBits: shape not supported by the MMA decode kernel.");
+    }
+    break;
+  }
+  case MNB_PATH_TCGEN05: {
+    if (!mnb::GemmTcgen05Supports(w, m)) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the tcgen05 path needs bits=4, block_size>=32, K%64==0.");
+    }
+    const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, mnb::GemmTcgen05ScratchBytes(m, w.k));
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    name = mnb::LaunchGemmTcgen05(w, a_dev, m, static_cast<std::uint16_t *>(h->scratch_a), out,
+                                  h->status_dev, stream, h->sm_count);
+    break;
+  }
+  case MNB_PATH_INT8: {
+    const std::size_t aq_bytes = static_cast<std::size_t>(m) * w.n_blocks * w.block_size;
+    int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, aq_bytes);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    rc = Grow(&h->scratch_s, &h->scratch_s_bytes, static_cast<std::size_t>(m) * w.n_blocks * sizeof(float));
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    name = mnb::LaunchQuantizeAPadded(a_dev, m, w.k, w.block_size,
+                                      static_cast<std::int8_t *>(h->scratch_a),
+                                      static_cast<float *>(h->scratch_s), stream);
+    if (name != nullptr) {
+      name = mnb::LaunchInt8Matmul(w, static_cast<const std::int8_t *>(h->scratch_a),
+                                   static_cast<const float *>(h->scratch_s), m, out, stream,
+                                   h->sm_count);
+    }
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: accuracy_level 4 needs 16-byte aligned rows and block_size >= 32 "
+                  "for 4-bit weights.");
+    }
+    break;
+  }
+  default:
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: unknown path selector.");
+  }
+  if (name == nullptr) {
+    const cudaError_t err = cudaGetLastError();
+    return Fail(MNB_ERR_CUDA, std::string("matmulnbits_b200: kernel launch failed: ") +
+                                  cudaGetErrorString(err));
+  }
+  mnb::t_last_kernel = name;
+  return MNB_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+const char *mnb_last_error(void) { return mnb::t_last_error.c_str(); }
+
+const char *mnb_version(void) { return "matmulnbits_b200 0.1.0 sm_100a"; }
+
+int mnb_device_count(int *count) {
+  if (count == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_device_count: null output.");
+  }
+  int n = 0;
+  const cudaError_t err = cudaGetDeviceCount(&n);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  *count = n;
+  return MNB_OK;
+}
+
+int64_t mnb_algorithmic_bytes(int64_t m, int64_t n, int64_t k, int bits, int block_size,
+                              int has_zero_points, int has_bias) {
+  const int64_t n_blocks = (k + block_size - 1) / block_size;
+  int64_t bytes = n * n_blocks * (static_cast<int64_t>(block_size) * bits / 8);
+  bytes += 4 * n * n_blocks;
+  if (has_zero_points) {
+    bytes += n * ((n_blocks * bits + 7) / 8);
+  }
+  if (has_bias) {
+    bytes += 4 * n;
+  }
+  bytes += 4 * m * k + 4 * m * n;
+  return bytes;
+}
+
+static int CreateImpl(int device, const uint8_t *b, const float *scales, const uint8_t *zero_points,
+                      const float *bias, int64_t n, int64_t k, int bits, int block_size, bool copy,
+                      mnb_weights **out) {
+  if (out == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_weights_create: null output handle.");
+  }
+  *out = nullptr;
+  std::string why;
+  if (!ValidGeometry(n, k, bits, block_size, &why)) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, why);
+  }
+  if (b == nullptr || scales == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits requires B and scales.");
+  }
+  int count = 0;
+  mnb_device_count(&count);
+  if (count <= 0) {
+    return Fail(MNB_ERR_CUDA, "matmulnbits_b200: no CUDA device is visible; there is no CPU path.");
+  }
+  if (device < 0 || device >= count) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "matmulnbits_b200: device index out of range.");
+  }
+  mnb_weights *h = new (std::nothrow) mnb_weights();
+  if (h == nullptr) {
+    return Fail(MNB_ERR_CUDA, "matmulnbits_b200: out of host memory.");
+  }
+  h->device = device;
+  FillView(&h->view, n, k, bits, block_size);
+  int rc = SetupCommon(h);
+  if (rc != MNB_OK) {
+    mnb_weights_destroy(h);
+    return rc;
+  }
+  if (!copy) {
+    h->view.b = b;
+    h->view.scales = scales;
+    h->view.zp = zero_points;
+    h->view.bias = bias;
+    *out = h;
+    return MNB_OK;
+  }
+  h->owns = true;
+  const std::size_t sizes[4] = {
+      static_cast<std::size_t>(n) * h->view.row_bytes,
+      static_cast<std::size_t>(n) * h->view.n_blocks * sizeof(float),
+      zero_points != nullptr ? static_cast<std::size_t>(n) * h->view.zp_row_bytes : 0,
+      bias != nullptr ? static_cast<std::size_t>(n) * sizeof(float) : 0};
+  const void *sources[4] = {b, scales, zero_points, bias};
+  for (int i = 0; i < 4; ++i) {
+    if (sizes[i] == 0) {
+      continue;
+    }
+    cudaError_t err = cudaMalloc(&h->owned[i], sizes[i]);
+    if (err == cudaSuccess) {
+      err = cudaMemcpy(h->owned[i], sources[i], sizes[i], cudaMemcpyHostToDevice);
+    }
+    if (err != cudaSuccess) {
+      rc = FailCuda("weight upload", err);
+      mnb_weights_destroy(h);
+      return rc;
+    }
+  }
+  h->view.b = static_cast<const std::uint8_t *>(h->owned[0]);
+  h->view.scales = static_cast<const float *>(h->owned[1]);
+  h->view.zp = static_cast<const std::uint8_t *>(h->owned[2]);
+  h->view.bias = static_cast<const float *>(h->owned[3]);
+  *out = h;
+  return MNB_OK;
+}
+
+int mnb_weights_create(int device, const uint8_t *b, const float *scales,
+                       const uint8_t *zero_points, const float *bias, int64_t n, int64_t k,
+                       int bits, int block_size, mnb_weights **out) {
+  return CreateImpl(device, b, scales, zero_points, bias, n, k, bits, block_size, true, out);
+}
+
+int mnb_weights_wrap_device(int device, const uint8_t *b, const float *scales,
+                            const uint8_t *zero_points, const float *bias, int64_t n, int64_t k,
+                            int bits, int block_size, mnb_weights **out) {
+  return CreateImpl(device, b, scales, zero_points, bias, n, k, bits, block_size, false, out);
+}
+
+int mnb_weights_destroy(mnb_weights *h) {
+  if (h == nullptr) {
+    return MNB_OK;
+  }
+  cudaSetDevice(h->device);
+  if (h->stream != nullptr) {
+    cudaStreamSynchronize(h->stream);
+    cudaStreamDestroy(h->stream);
+  }
+  if (h->owns) {
+    for (void *ptr : h->owned) {
+      if (ptr != nullptr) {
+        cudaFree(ptr);
+      }
+    }
+  }
+  for (void *ptr : {static_cast<void *>(h->status_dev), h->scratch_a, h->scratch_s,
+                    static_cast<void *>(h->a_dev), static_cast<void *>(h->y_dev)}) {
+    if (ptr != nullptr) {
+      cudaFree(ptr);
+    }
+  }
+  delete h;
+  return MNB_OK;
+}
+
+int mnb_matmul_device_strided(mnb_weights *h, const float *a_dev, int64_t m, int accuracy_level,
+                              int path, float *y_dev, int64_t ld_y, int64_t col_offset,
+                              void *stream) {
+  if (h == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null weights handle.");
+  }
+  if (m > 0 && (a_dev == nullptr || y_dev == nullptr)) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null A or Y.");
+  }
+  if (ld_y < h->view.n || col_offset < 0 || col_offset + h->view.n > ld_y) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: output window does not fit its row.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  OutputView out{y_dev, ld_y, col_offset};
+  return Dispatch(h, a_dev, m, accuracy_level, path, out, static_cast<cudaStream_t>(stream));
+}
+
+int mnb_matmul_device(mnb_weights *h, const float *a_dev, int64_t m, int accuracy_level, int path,
+                      float *y_dev, void *stream) {
+  if (h == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null weights handle.");
+  }
+  return mnb_matmul_device_strided(h, a_dev, m, accuracy_level, path, y_dev, h->view.n, 0, stream);
+}
+
+int mnb_matmul_host(mnb_weights *h, const float *a_host, int64_t m, int accuracy_level, int path,
+                    float *y_host) {
+  if (h == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null weights handle.");
+  }
+  if (m < 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits requires M >= 0.");
+  }
+  if (m == 0) {
+    return MNB_OK;
+  }
+  if (a_host == nullptr || y_host == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null A or Y.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  const std::size_t a_bytes = static_cast<std::size_t>(m) * h->view.k * sizeof(float);
+  const std::size_t y_bytes = static_cast<std::size_t>(m) * h->view.n * sizeof(float);
+  int rc = Grow(reinterpret_cast<void **>(&h->a_dev), &h->a_dev_bytes, a_bytes);
+  if (rc != MNB_OK) {
+    return rc;
+  }
+  rc = Grow(reinterpret_cast<void **>(&h->y_dev), &h->y_dev_bytes, y_bytes);
+  if (rc != MNB_OK) {
+    return rc;
+  }
+  err = cudaMemcpyAsync(h->a_dev, a_host, a_bytes, cudaMemcpyHostToDevice, h->stream);
+  if (err != cudaSuccess) {
+    return FailCuda("copy A to device", err);
+  }
+  OutputView out{h->y_dev, h->view.n, 0};
+  rc = Dispatch(h, h->a_dev, m, accuracy_level, path, out, h->stream);
+  if (rc != MNB_OK) {
+    return rc;
+  }
+  err = cudaMemcpyAsync(y_host, h->y_dev, y_bytes, cudaMemcpyDeviceToHost, h->stream);
+  if (err != cudaSuccess) {
+    return FailCuda("copy Y to host", err);
+  }
+  int status = 0;
+  err = cudaMemcpyAsync(&status, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream);
+  if (err == cudaSuccess) {
+    err = cudaStreamSynchronize(h->stream);
+  }
+  if (err != cudaSuccess) {
+    return FailCuda("MatMulNBits execution", err);
+  }
+  if (status != 0) {
+    cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
+    cudaStreamSynchronize(h->stream);
+    char text[96];
+    std::snprintf(text, sizeof(text), "matmulnbits_b200: device-side wait timed out (status %d).", status);
+    return Fail(MNB_ERR_DEVICE_TIMEOUT, text);
+  }
+  return MNB_OK;
+}
+
+int mnb_weights_poll_status(mnb_weights *h, int *status) {
+  if (h == nullptr || status == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_weights_poll_status: null argument.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  cudaError_t err = cudaSetDevice(h->device);
+  if (err == cudaSuccess) {
+    err = cudaDeviceSynchronize();
+  }
+  if (err == cudaSuccess) {
+    err = cudaMemcpy(status, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost);
+  }
+  if (err != cudaSuccess) {
+    return FailCuda("status read", err);
+  }
+  if (*status != 0) {
+    cudaMemset(h->status_dev, 0, sizeof(int));
+  }
+  return MNB_OK;
+}
+
+int mnb_dequant_int_device(mnb_weights *h, int32_t *out_dev, void *stream) {
+  if (h == nullptr || out_dev == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_dequant_int_device: null argument.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  if (mnb::LaunchDequantInt(h->view, out_dev, static_cast<cudaStream_t>(stream)) == nullptr) {
+    return FailCuda("dequant launch", cudaGetLastError());
+  }
+  return MNB_OK;
+}
+
+int mnb_quantize_a_device(const float *a_dev, int64_t m, int64_t k, int block_size, int8_t *aq_dev,
+                          float *a_scales_dev, void *stream) {
+  if (a_dev == nullptr || aq_dev == nullptr || a_scales_dev == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_quantize_a_device: null argument.");
+  }
+  if (m <= 0 || k <= 0 || block_size < 16 || (block_size & (block_size - 1)) != 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_quantize_a_device: bad geometry.");
+  }
+  if (mnb::LaunchQuantizeA(a_dev, m, k, block_size, aq_dev, a_scales_dev,
+                           static_cast<cudaStream_t>(stream)) == nullptr) {
+    return FailCuda("quantize launch", cudaGetLastError());
+  }
+  return MNB_OK;
+}
+
+int mnb_int8_block_dots_device(mnb_weights *h, const int8_t *aq_dev, int64_t m, int32_t *dots_dev,
+                               void *stream) {
+  if (h == nullptr || aq_dev == nullptr || dots_dev == nullptr || m <= 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_int8_block_dots_device: bad argument.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  if (mnb::LaunchInt8BlockDots(h->view, aq_dev, m, dots_dev, static_cast<cudaStream_t>(stream)) ==
+      nullptr) {
+    return FailCuda("block-dot launch", cudaGetLastError());
+  }
+  return MNB_OK;
+}
+
+int64_t mnb_launch_count(void) { return mnb::g_launches.load(std::memory_order_relaxed); }
+
+const char *mnb_last_kernel(void) { return mnb::t_last_kernel; }
+
+int64_t mnb_weights_n(const mnb_weights *h) { return h != nullptr ? h->view.n : 0; }
+int64_t mnb_weights_k(const mnb_weights *h) { return h != nullptr ? h->view.k : 0; }
+int mnb_weights_bits(const mnb_weights *h) { return h != nullptr ? h->view.bits : 0; }
+int mnb_weights_block_size(const mnb_weights *h) { return h != nullptr ? h->view.block_size : 0; }
+
+} // extern "C"

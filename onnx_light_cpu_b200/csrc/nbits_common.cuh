@@ -1,0 +1,101 @@
+// Shared device/host definitions of the sm_100a MatMulNBits kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace mnb {
+
+// Device view of one node's constant operands (all pointers are device pointers).
+//   b       [n, n_blocks, blob_bytes]   packed codes, low nibble = even element
+//   scales  [n, n_blocks]               fp32
+//   zp      [n, zp_row_bytes] or null   packed codes, one per block
+//   bias    [n] or null
+struct WeightView {
+  const std::uint8_t *b;
+  const float *scales;
+  const std::uint8_t *zp;
+  const float *bias;
+  std::int64_t n;
+  std::int64_t k;
+  int bits;
+  int block_size;
+  int n_blocks;
+  int blob_bytes;
+  int row_bytes;    // n_blocks * blob_bytes
+  int zp_row_bytes; // ceil(n_blocks * bits / 8)
+};
+
+// Where a kernel writes its [m, n] result inside a possibly wider row-major matrix.
+struct OutputView {
+  float *y;
+  std::int64_t ld;         // leading dimension in elements
+  std::int64_t col_offset; // first column written
+};
+
+// Error word written by kernels whose bounded waits gave up (0 = fine).
+enum DeviceStatus : int {
+  kDeviceOk = 0,
+  kDeviceTimeoutFullBarrier = 1,
+  kDeviceTimeoutEmptyBarrier = 2,
+  kDeviceTimeoutMmaBarrier = 3,
+  kDeviceTimeoutEpilogueBarrier = 4,
+};
+
+__host__ __device__ inline int ZeroPointOf(const WeightView &w, std::int64_t row, int block) {
+  if (w.zp == nullptr) {
+    return 1 << (w.bits - 1);
+  }
+  const std::uint8_t *zrow = w.zp + row * w.zp_row_bytes;
+  if (w.bits == 8) {
+    return zrow[block];
+  }
+  const std::uint8_t byte = zrow[block >> 1];
+  return (block & 1) ? (byte >> 4) : (byte & 0x0f);
+}
+
+__host__ __device__ inline int CodeOf(const WeightView &w, std::int64_t row, std::int64_t kk) {
+  const int block = static_cast<int>(kk / w.block_size);
+  const int within = static_cast<int>(kk - static_cast<std::int64_t>(block) * w.block_size);
+  const std::uint8_t *blob = w.b + row * w.row_bytes + static_cast<std::int64_t>(block) * w.blob_bytes;
+  if (w.bits == 8) {
+    return blob[within];
+  }
+  const std::uint8_t byte = blob[within >> 1];
+  return (within & 1) ? (byte >> 4) : (byte & 0x0f);
+}
+
+// ---- launchers (defined in the .cu files, called by the C ABI layer) ------------------------
+
+// Returns a static kernel name for diagnostics, or nullptr when the shape is outside what the
+// kernel supports (the caller then picks another one).
+const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                             int *status_word, cudaStream_t stream, int sm_count);
+const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                              cudaStream_t stream);
+const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                          int *status_word, cudaStream_t stream, int sm_count);
+
+// Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
+const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
+                              std::uint16_t *a_bf16, OutputView out, int *status_word,
+                              cudaStream_t stream, int sm_count);
+std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k);
+bool GemmTcgen05Supports(const WeightView &w, std::int64_t m);
+
+// accuracy_level 4.
+const char *LaunchQuantizeA(const float *a, std::int64_t m, std::int64_t k, int block_size,
+                            std::int8_t *aq, float *a_scales, cudaStream_t stream);
+const char *LaunchQuantizeAPadded(const float *a, std::int64_t m, std::int64_t k, int block_size,
+                                  std::int8_t *aq_padded, float *a_scales, cudaStream_t stream);
+const char *LaunchInt8BlockDots(const WeightView &w, const std::int8_t *aq, std::int64_t m,
+                                std::int32_t *dots, cudaStream_t stream);
+const char *LaunchInt8Matmul(const WeightView &w, const std::int8_t *aq, const float *a_scales,
+                             std::int64_t m, OutputView out, cudaStream_t stream, int sm_count);
+
+const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
+
+void CountLaunch(int launches = 1);
+
+} // namespace mnb

@@ -1,0 +1,182 @@
+// Inline-PTX helpers for sm_100a: mbarrier, bulk (TMA) copies, tcgen05/TMEM.
+// Every wait in this file is bounded: it returns false after `kSpinLimit` polls so that a
+// kernel can record a status word and leave instead of spinning forever.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace mnb {
+namespace ptx {
+
+constexpr std::uint32_t kSpinLimit = 1u << 21; // polls; each failed poll backs off ~64 ns
+
+__device__ __forceinline__ std::uint32_t SmemAddr(const void *ptr) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(ptr));
+}
+
+__device__ __forceinline__ void MbarInit(std::uint64_t *bar, std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count)
+               : "memory");
+}
+
+__device__ __forceinline__ void FenceMbarInit() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void FenceProxyAsyncShared() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void MbarArrive(std::uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void MbarArriveExpectTx(std::uint64_t *bar, std::uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool MbarTryWait(std::uint64_t *bar, std::uint32_t parity) {
+  std::uint32_t done;
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t"
+               "}"
+               : "=r"(done)
+               : "r"(SmemAddr(bar)), "r"(parity)
+               : "memory");
+  return done != 0;
+}
+
+// Bounded wait. Returns false when the phase did not complete within the poll budget.
+__device__ __forceinline__ bool MbarWait(std::uint64_t *bar, std::uint32_t parity) {
+  for (std::uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (MbarTryWait(bar, parity)) {
+      return true;
+    }
+    if (spin > 64) {
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void BulkLoad(void *smem_dst, const void *gmem_src, std::uint32_t bytes,
+                                         std::uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(SmemAddr(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(SmemAddr(bar))
+      : "memory");
+}
+
+// 2-D tiled TMA load (no multicast), coordinates innermost first.
+__device__ __forceinline__ void TmaLoad2D(void *smem_dst, const void *tensor_map, int x, int y,
+                                          std::uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%2, %3}], [%4];" ::"r"(SmemAddr(smem_dst)),
+               "l"(tensor_map), "r"(x), "r"(y), "r"(SmemAddr(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void PrefetchTensorMap(const void *tensor_map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
+}
+
+// ---- tcgen05 / TMEM ---------------------------------------------------------------------------
+
+// Whole-warp instruction. Writes the TMEM base address of `columns` columns to *smem_result.
+__device__ __forceinline__ void TmemAlloc(std::uint32_t *smem_result, std::uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   SmemAddr(smem_result)),
+               "r"(columns)
+               : "memory");
+}
+
+__device__ __forceinline__ void TmemRelinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void TmemDealloc(std::uint32_t taddr, std::uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+               : "memory");
+}
+
+__device__ __forceinline__ void TcFenceBefore() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void TcFenceAfter() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 x bf16 -> fp32. One thread issues.
+__device__ __forceinline__ void UmmaBf16(std::uint32_t tmem_d, std::uint64_t desc_a,
+                                         std::uint64_t desc_b, std::uint32_t idesc,
+                                         std::uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "}" ::"r"(tmem_d),
+               "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// Makes `bar` complete one arrival once every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void UmmaCommit(std::uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   SmemAddr(bar))
+               : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base+i).
+__device__ __forceinline__ void TmemLoad32x32(std::uint32_t taddr, std::uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void TmemLoadWait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with
+// the 128-byte swizzle (what a TMA box of 64 bf16 with SWIZZLE_128B produces): 8-row groups
+// are 1024 bytes apart. Field layout: start address >> 4 in bits [0,14), leading byte offset
+// >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48),
+// layout type (2 = 128-byte swizzle) in [61,64).
+__device__ __forceinline__ std::uint64_t UmmaDescKMajorSw128(std::uint32_t smem_addr) {
+  std::uint64_t desc = 0;
+  desc |= static_cast<std::uint64_t>((smem_addr & 0x3ffffu) >> 4);
+  desc |= static_cast<std::uint64_t>(1) << 16;           // leading byte offset (unused here)
+  desc |= static_cast<std::uint64_t>(1024 >> 4) << 32;   // stride between 8-row groups
+  desc |= static_cast<std::uint64_t>(1) << 46;           // descriptor version
+  desc |= static_cast<std::uint64_t>(2) << 61;           // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor for kind::f16 with bf16 A and B (both K-major), fp32 accumulate.
+// c_format [4,6) = 1 (f32), a_format [7,10) = 1 (bf16), b_format [10,13) = 1 (bf16),
+// a_major bit 15 = 0, b_major bit 16 = 0, n >> 3 in [17,23), m >> 4 in [24,29).
+__host__ __device__ constexpr std::uint32_t UmmaIdescBf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<std::uint32_t>(n >> 3) << 17) |
+         (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
+} // namespace ptx
+} // namespace mnb
