@@ -1,0 +1,465 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 MatMulNBits path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout (rank 0). Headline metric: effective HBM GB/s of the 4-bit decode
+GEMV at M=1 (algorithmic bytes / device time), with the M=2048 prefill TFLOP/s, the decode
+sweep, the roofline fractions and a timed CPU baseline in the same line.
+
+N = 1   workload = the decode configuration the metric is quoted on: M=1, K=4096, N=14336,
+        bits=4, block_size=128, zero points and bias. A step is one pass over R=8 distinct
+        weight copies (252 MB, twice the 126 MB L2, so every launch streams from HBM),
+        captured as one CUDA graph.
+N > 1   workload = the large-N output projection (K=4096, N=128256, bits=4, block 32, M=1),
+        weight columns sharded across ranks, output columns all-gathered over NCCL; strong
+        scaling (the total problem is fixed). A step is one pass over R=2 weight copies.
+
+`value` times device-resident inputs; `e2e` goes through the host-buffer C ABI call (pinned
+host A in, pinned host Y out, copies inside the timed region). `--impl reference` times the CPU
+restatement of the operator (the reference ships no MatMulNBits kernel) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+DECODE = dict(k=4096, n=14336, bits=4, block_size=128)
+PREFILL = dict(m=2048, k=4096, n=4096, bits=4, block_size=64)
+LMHEAD = dict(k=4096, n=128256, bits=4, block_size=32)
+L2_BYTES = 126 * 1024 * 1024
+
+# DRAM bytes per launch of nbits_gemv_stream_kernel<4,1,1> on the decode workload, from the ncu
+# capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until
+# a capture exists.
+NCU_DECODE_TRAFFIC_BYTES = None
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return ({"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]),
+                 "bf16_tflops_sustained": float(data.get("bf16_tflops_sustained", data["bf16_tflops"]))},
+                "measured")
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.samples.append([v.strip() for v in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self) -> dict:
+        mhz = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        max_mhz = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [name for i, name in enumerate(names)
+                   if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(max_mhz) if max_mhz else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def cpu_port_baseline(seconds: float = 3.0) -> dict:
+    """Times the CPU restatement (oracle port) on this host: M=1 decode workload, all threads."""
+    from onnx_light_cpu_b200.tools import synthetic as syn
+    from oracle import nbits_oracle as o
+
+    case = syn.config2(1)
+    threads = o.hardware_threads()
+    args = (case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits, case.block_size)
+    o.matmul_f32_fast(*args, threads=threads)
+    calls, start = 0, time.perf_counter()
+    samples = []
+    while time.perf_counter() - start < seconds or calls < 7:
+        t0 = time.perf_counter()
+        o.matmul_f32_fast(*args, threads=threads)
+        samples.append(time.perf_counter() - t0)
+        calls += 1
+    from onnx_light_cpu_b200 import _capi
+
+    nbytes = _capi.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size, True, True)
+    median = statistics.median(samples)
+    return {"value": nbytes / median / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{calls} calls of the full M=1 K=4096 N=14336 workload, median of per-call times",
+            "ms_per_call": median * 1e3}
+
+
+def run_reference(args, rank: int) -> None:
+    """The reference arm: the CPU implementation of this path on the host cores. The reference
+    project has no MatMulNBits kernel, so this is the CPU restatement (kind "port")."""
+    if rank != 0:
+        return
+    from onnx_light_cpu_b200 import _capi
+    from onnx_light_cpu_b200.tools import synthetic as syn
+    from oracle import nbits_oracle as o
+
+    o.build(reference=False)
+    multi = args.gpus > 1
+    copies = 2 if multi else 8
+    case = syn.config5(1, 4, n=LMHEAD["n"] // 8) if multi else syn.config2(1)
+    threads = o.hardware_threads()
+    call_args = (case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits,
+                 case.block_size)
+    per_call_bytes = _capi.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size,
+                                             case.zero_points is not None, case.bias is not None)
+    scale = (LMHEAD["n"] / case.n) if multi else 1.0   # the lm-head sample is 1/8 of the columns
+    # bound the run: a step is `copies` calls on the sample
+    steps = max(1, min(args.steps, 50))
+    warmup = max(1, min(args.warmup, 5))
+    for _ in range(warmup):
+        o.matmul_f32_fast(*call_args, threads=threads)
+    start = time.perf_counter()
+    for _ in range(steps * copies):
+        o.matmul_f32_fast(*call_args, threads=threads)
+    elapsed = time.perf_counter() - start
+    value = per_call_bytes * steps * copies / elapsed / 1e9
+    workload = ("cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32" if multi
+                else "cfg2 decode M=1 K=4096 N=14336 bits=4 block=128 zp+bias")
+    sample = (f"{steps} steps x {copies} calls on a 1/8 column sample (N={case.n}); per-call bytes counted for "
+              "the sample" if multi else f"{steps} steps x {copies} calls of the full workload")
+    line = {
+        "impl": "reference", "metric": "MatMulNBits 4-bit M=1 HBM GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": elapsed / steps * 1e3 * scale,
+        "higher_is_better": True, "scaling": "strong" if multi else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": workload, "weight_copies": copies},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships no MatMulNBits kernel; this is the CPU restatement used as the oracle",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_steps(torch, dist, step, steps: int, warmup: int, world: int) -> float:
+    """Seconds for exactly `steps` calls of step(), device-timed, max over ranks."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    begin = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    seconds = begin.elapsed_time(end) / 1e3
+    if world > 1:
+        t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        seconds = float(t.item())
+    return seconds
+
+
+def capture_graph(torch, step):
+    """Captures step() into a CUDA graph; returns a replay callable (or step on failure)."""
+    try:
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            step()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        return graph.replay, True
+    except Exception as exc:  # pragma: no cover - depends on the driver
+        print(f"bench: CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+        torch.cuda.synchronize()
+        return step, False
+
+
+def device_weights(torch, pkg, m_cfg: dict, copies: int, seed: int, zp: bool, bias: bool):
+    """`copies` random weight sets resident on the device (generated there, same distributions
+    as the synthetic configurations) and their handles."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    k, n, bits, bs = m_cfg["k"], m_cfg["n"], m_cfg["bits"], m_cfg["block_size"]
+    nb = -(-k // bs)
+    out = []
+    for _ in range(copies):
+        b = torch.randint(0, 256, (n, nb, bs * bits // 8), dtype=torch.uint8, device="cuda", generator=gen)
+        scales = (torch.randn(n * nb, device="cuda", generator=gen).abs() * 0.01).float()
+        zero_points = (torch.randint(0, 256, (n, (nb * bits + 7) // 8), dtype=torch.uint8, device="cuda",
+                                     generator=gen) if zp else None)
+        bias_t = (torch.randn(n, device="cuda", generator=gen) * 0.1).float() if bias else None
+        out.append(pkg.MatMulNBitsWeights(b, scales, zero_points, bias_t, K=k, N=n, bits=bits, block_size=bs))
+    return out
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling runs)")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from onnx_light_cpu_b200 import build
+
+    if rank == 0:
+        build.build_all()
+    if world > 1:
+        dist.barrier()
+    import onnx_light_cpu_b200 as pkg
+    from onnx_light_cpu_b200 import _capi
+    from onnx_light_cpu_b200.matmul_nbits import _ptr  # noqa: F401
+
+    _capi.load()
+    peaks, peak_kind = measured_peaks()
+    multi = world > 1
+    extras: dict = {}
+
+    if not multi:
+        cfg = DECODE
+        copies = 8
+        weights = device_weights(torch, pkg, cfg, copies, seed=1201, zp=True, bias=True)
+        m = 1
+        a = torch.randn(m, cfg["k"], device="cuda").half().float()
+        ys = [torch.empty(m, cfg["n"], device="cuda") for _ in range(copies)]
+        per_launch_bytes = weights[0].algorithmic_bytes(m)
+        assert copies * per_launch_bytes > L2_BYTES
+
+        def step():
+            for w, y in zip(weights, ys):
+                w.matmul_device(a, y)
+
+        step()
+        torch.cuda.synchronize()
+        kernel_name = _capi.last_kernel()
+        replay, graphed = capture_graph(torch, step)
+        launches_before = _capi.launch_count()
+        with ClockSampler(local_rank) as clocks:
+            seconds = time_steps(torch, dist, replay, args.steps, args.warmup, world)
+        # graph replays do not pass through the launcher: count the kernels inside the graph
+        gpu_launches = args.steps * copies if graphed else _capi.launch_count() - launches_before
+        value = per_launch_bytes * copies * args.steps / seconds / 1e9
+        launch_us = seconds / (args.steps * copies) * 1e6
+        workload = "cfg2 decode M=1 K=4096 N=14336 bits=4 block=128 zp+bias"
+        config = {"workload": workload, "weight_copies": copies, "bytes_per_launch": per_launch_bytes,
+                  "l2_defeat": f"{copies} weight copies = {copies * per_launch_bytes / 1e6:.0f} MB > 126 MB L2",
+                  "cuda_graph": graphed, "kernel": kernel_name}
+        roofline = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": value / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
+                    "peak_kind": f"of {peak_kind} (copy bandwidth)", "kernel": kernel_name,
+                    "us_per_launch": launch_us, "algorithmic_bytes_per_launch": per_launch_bytes}
+        scaling = "weak"
+
+        # ---- end to end through the host-buffer call ----
+        a_host = a.cpu().pin_memory()
+        y_host = torch.empty(m, cfg["n"]).pin_memory()
+        host_steps = max(3, min(args.steps, 50))
+
+        def host_step():
+            for w in weights:
+                w.matmul_host_ptr(a_host.data_ptr(), m, y_host.data_ptr())
+
+        for _ in range(3):
+            host_step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(host_steps):
+            host_step()
+        host_seconds = time.perf_counter() - t0
+        e2e = {"value": per_launch_bytes * copies * host_steps / host_seconds / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": copies * a_host.numel() * 4, "d2h_bytes_per_step": copies * y_host.numel() * 4,
+               "us_per_call": host_seconds / (host_steps * copies) * 1e6,
+               "note": "constant weights resident on the device (uploaded once per node); A and Y are pinned host buffers"}
+
+        if not args.skip_extras:
+            # ---- decode sweep M = 4, 16 ----
+            sweep = {}
+            for m_sweep in (4, 16):
+                a_s = torch.randn(m_sweep, cfg["k"], device="cuda").half().float()
+                ys_s = [torch.empty(m_sweep, cfg["n"], device="cuda") for _ in range(copies)]
+
+                def sweep_step():
+                    for w, y in zip(weights, ys_s):
+                        w.matmul_device(a_s, y)
+
+                sweep_step()
+                torch.cuda.synchronize()
+                name = _capi.last_kernel()
+                rep, _ = capture_graph(torch, sweep_step)
+                sec = time_steps(torch, dist, rep, max(5, args.steps // 4), 3, 1)
+                nbytes = weights[0].algorithmic_bytes(m_sweep)
+                gbs = nbytes * copies * max(5, args.steps // 4) / sec / 1e9
+                sweep[f"m{m_sweep}"] = {"gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "kernel": name}
+            extras["decode_sweep"] = sweep
+            del weights, ys
+            torch.cuda.empty_cache()
+
+            # ---- prefill M = 2048 (bf16 tcgen05 path) ----
+            pw = device_weights(torch, pkg, PREFILL, 1, seed=1301, zp=True, bias=False)[0]
+            pm = PREFILL["m"]
+            sets = 3  # rotate A/Y so that A + Y + weights exceed L2 between repeats
+            a_p = [torch.randn(pm, PREFILL["k"], device="cuda") for _ in range(sets)]
+            y_p = [torch.empty(pm, PREFILL["n"], device="cuda") for _ in range(sets)]
+
+            def prefill_step():
+                for a_i, y_i in zip(a_p, y_p):
+                    pw.matmul_device(a_i, y_i)
+
+            prefill_step()
+            torch.cuda.synchronize()
+            pname = _capi.last_kernel()
+            status = pw.poll_status()
+            psteps = max(5, args.steps // 10)
+            # events around the whole call: the fp32->bf16 activation pre-pass is inside
+            sec = time_steps(torch, dist, prefill_step, psteps, 3, 1)
+            flops = 2.0 * pm * PREFILL["n"] * PREFILL["k"]
+            tflops = flops * sets * psteps / sec / 1e12
+            extras["prefill"] = {
+                "workload": "cfg3 prefill M=2048 K=4096 N=4096 bits=4 block=64 zp",
+                "tflops": tflops, "us_per_call": sec / (sets * psteps) * 1e6, "kernel": pname,
+                "device_status": status,
+                "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": tflops / peaks["bf16_tflops"],
+                             "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],
+                             "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)", "traffic": None},
+                "includes": "fp32->bf16 activation pre-pass + GEMM kernel"}
+            del pw, a_p, y_p
+    else:
+        # ---- multi-GPU: column-sharded lm-head, NCCL all-gather of the output columns ----
+        cfg = dict(LMHEAD)
+        if cfg["n"] % world != 0:
+            raise SystemExit("N must divide by the number of GPUs")
+        shard_cfg = dict(cfg, n=cfg["n"] // world)
+        copies = 2
+        weights = device_weights(torch, pkg, shard_cfg, copies, seed=1500 + rank, zp=True, bias=False)
+        m = 1
+        a = torch.randn(m, cfg["k"], device="cuda")
+        dist.broadcast(a, src=0)
+        y_shard = [torch.empty(m, shard_cfg["n"], device="cuda") for _ in range(copies)]
+        y_full = [torch.empty(world, m, shard_cfg["n"], device="cuda") for _ in range(copies)]
+        full_bytes = _capi.algorithmic_bytes(m, cfg["n"], cfg["k"], cfg["bits"], cfg["block_size"], True, False)
+
+        def step():
+            for w, ys_, yf in zip(weights, y_shard, y_full):
+                w.matmul_device(a, ys_)
+                dist.all_gather_into_tensor(yf, ys_)
+
+        step()
+        torch.cuda.synchronize()
+        kernel_name = _capi.last_kernel()
+        launches_before = _capi.launch_count()
+        with ClockSampler(local_rank) as clocks:
+            seconds = time_steps(torch, dist, step, args.steps, args.warmup, world)
+        gpu_launches = (_capi.launch_count() - launches_before) * world
+        value = full_bytes * copies * args.steps / seconds / 1e9
+        workload = "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + NCCL all-gather"
+        config = {"workload": workload, "weight_copies": copies, "shard_columns": shard_cfg["n"],
+                  "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name,
+                  "l2_defeat": f"{copies} weight copies per rank"}
+        shard_bytes = weights[0].algorithmic_bytes(m)
+        roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": value / world / peaks["hbm_gbs"], "traffic": None,
+                    "peak_kind": f"of {peak_kind} (copy bandwidth), per GPU, all-gather time included",
+                    "algorithmic_bytes_per_launch": shard_bytes}
+        scaling = "strong"
+        # end to end: A from pinned host memory, gathered Y back to pinned host memory
+        a_host = a.cpu().pin_memory()
+        y_host = torch.empty(world, m, shard_cfg["n"]).pin_memory()
+        host_steps = max(3, min(args.steps, 50))
+
+        def host_step():
+            for w, ys_, yf in zip(weights, y_shard, y_full):
+                a.copy_(a_host, non_blocking=True)
+                w.matmul_device(a, ys_)
+                dist.all_gather_into_tensor(yf, ys_)
+                y_host.copy_(yf, non_blocking=True)
+                torch.cuda.synchronize()
+
+        host_step()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(host_steps):
+            host_step()
+        dist.barrier()
+        host_seconds = time.perf_counter() - t0
+        e2e = {"value": full_bytes * copies * host_steps / host_seconds / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": copies * a_host.numel() * 4, "d2h_bytes_per_step": copies * y_host.numel() * 4}
+
+    if rank == 0:
+        line = {
+            "metric": "MatMulNBits 4-bit M=1 HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config, "roofline": roofline, "e2e": e2e, "gpu_launches": int(gpu_launches),
+            "clocks": clocks.summary(),
+        }
+        line.update(extras)
+        if not multi and not args.skip_extras:
+            line["cpu_baseline"] = cpu_port_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

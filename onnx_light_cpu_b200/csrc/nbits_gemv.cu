@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
   // ---------------- consumers ----------------
   const int cc = tid & ((1 << p.cc_log2) - 1);
   const int rg = tid >> p.cc_log2;
-  const int warps_per_group = (1 << p.cc_log2) >> 5 > 0 ? (1 << p.cc_log2) >> 5 : 1;
+  const int warps_per_group = (1 << p.cc_log2) >> 5; // chunk columns per group >= 32
   const int warp_in_group = warp & (warps_per_group - 1);
 
   // activations of this thread's chunk columns, pre-scaled, as pairs; and their plain sums
@@ -521,7 +521,7 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
   }
   p.rows_per_cta = static_cast<int>((w.n + ctas - 1) / ctas);
 
-  const int mt = m == 1 ? 1 : 2;
+  const int mt = (m == 1 || j == 2) ? 1 : 2; // two chunk columns x two rows of A would spill
   dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>((m + mt - 1) / mt), 1);
   cudaError_t err = cudaErrorInvalidValue;
   const char *name = nullptr;
@@ -533,11 +533,9 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
   MNB_STREAM_CASE(4, 1, 1)
   MNB_STREAM_CASE(4, 2, 1)
   MNB_STREAM_CASE(4, 1, 2)
-  MNB_STREAM_CASE(4, 2, 2)
   MNB_STREAM_CASE(8, 1, 1)
   MNB_STREAM_CASE(8, 2, 1)
   MNB_STREAM_CASE(8, 1, 2)
-  MNB_STREAM_CASE(8, 2, 2)
 #undef MNB_STREAM_CASE
   if (err != cudaSuccess) {
     return nullptr;

@@ -1,0 +1,265 @@
+"""Parity of the CUDA path with the CPU checker, through the C ABI (device pointers) and
+through the registered operator (host tensors). Bars:
+  * integer dequantization and int32 block dots: bit-exact
+  * CUDA-core fp32 decode path: max |y - y_ref| / max |y_ref| <= 1e-5
+  * bf16 tensor-core path:      max |y - y_ref| / max |y_ref| <= 2e-2
+"""
+
+import numpy as np
+import pytest
+
+import onnx_light_cpu_b200 as pkg
+from onnx_light_cpu_b200 import _capi
+from onnx_light_cpu_b200.matmul_nbits import quantize_a
+from onnx_light_cpu_b200.tools import synthetic as syn
+from oracle import nbits_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-5
+TOL_BF16 = 2e-2
+
+
+def rel_err(y, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(np.asarray(y, dtype=np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def run_device(case, path=_capi.PATH_AUTO, accuracy_level=0):
+    import torch
+
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n,
+                                     bits=case.bits, block_size=case.block_size)
+    a = torch.from_numpy(case.a).cuda()
+    y = torch.full((case.m, case.n), float("nan"), device="cuda", dtype=torch.float32)
+    weights.matmul_device(a, y, accuracy_level=accuracy_level, path=path)
+    torch.cuda.synchronize()
+    assert weights.poll_status() == 0
+    kernel = _capi.last_kernel()
+    out = y.cpu().numpy()
+    weights.close()
+    return out, kernel
+
+
+def oracle_f64(case):
+    return o.matmul_f64(case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits,
+                        case.block_size)
+
+
+# ---- integer dequantization: bit-exact ---------------------------------------------------------
+@pytest.mark.parametrize("bits,bs,k,n,zp", [(4, 32, 4096, 64, False), (4, 128, 4096, 96, True), (4, 16, 80, 7, True),
+                                            (4, 64, 200, 5, True), (8, 32, 4096, 33, True), (8, 16, 40, 3, False)])
+def test_dequant_integers_bit_exact(cuda_device, bits, bs, k, n, zp):
+    import torch
+
+    case = syn.make_case("dq", 1, k, n, bits, bs, seed=11 + bits + bs, zero_points=zp)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, None, K=k, N=n, bits=bits, block_size=bs)
+    out = torch.empty((n, k), dtype=torch.int32, device="cuda")
+    weights.dequant_int(out)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), o.dequant_int(case.b, case.zero_points, n, k, bits, bs))
+
+
+# ---- decode path -----------------------------------------------------------------------------------
+def test_config1_single_node(cuda_device):
+    case = syn.config1()
+    y, kernel = run_device(case)
+    assert kernel.startswith("nbits_gemv_stream_kernel<4,1,1>"), kernel
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, None, None, case.n, case.k, 4, 32)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_config2_decode_sweep(cuda_device, m):
+    case = syn.config2(m)
+    y, kernel = run_device(case)
+    assert kernel.startswith("nbits_gemv_stream_kernel"), kernel
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+
+
+DECODE_EDGES = [
+    # m, k, n, bits, block, zp, bias
+    (1, 4096, 1, 4, 32, True, True),        # single column
+    (3, 4096, 149, 4, 64, True, False),     # N not a multiple of any tile, odd M
+    (2, 1024, 300, 4, 32, False, True),     # narrow rows: 16 row groups
+    (1, 14336, 64, 4, 32, True, False),     # wide K: one row group, idle lanes
+    (5, 8192, 40, 4, 256, True, True),
+    (1, 20480, 24, 4, 128, True, False),    # two chunk columns per thread
+    (1, 4096, 77, 8, 32, True, True),       # 8-bit
+    (7, 4096, 50, 8, 128, False, False),
+    (16, 2048, 31, 8, 16, True, True),
+    (1, 4000, 33, 4, 32, True, True),       # K not a multiple of the chunk: generic kernel
+    (2, 96, 5, 4, 16, True, False),         # block 16: generic kernel
+    (1, 40, 3, 8, 32, True, True),          # partial last block
+    (16, 4096, 2, 4, 128, True, True),
+]
+
+
+@pytest.mark.parametrize("m,k,n,bits,bs,zp,bias", DECODE_EDGES)
+def test_decode_edge_cases(cuda_device, m, k, n, bits, bs, zp, bias):
+    case = syn.make_case("edge", m, k, n, bits, bs, seed=m * 7 + k + n + bits, zero_points=zp, bias=bias)
+    y, kernel = run_device(case)
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32, kernel
+
+
+def test_generic_kernel_matches_stream_kernel(cuda_device):
+    """Two independent CUDA implementations of the decode path agree."""
+    import torch
+
+    case = syn.make_case("cross", 2, 4096, 513, 4, 32, seed=42, bias=True)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n)
+    a = torch.from_numpy(case.a).cuda()
+    y1 = torch.empty((2, 513), device="cuda")
+    weights.matmul_device(a, y1, path=_capi.PATH_GEMV)
+    # block_size 16 is outside what the stream kernel takes, so it runs on the generic one
+    case2 = syn.make_case("cross", 2, 4096, 513, 4, 16, seed=42, bias=True)
+    torch.cuda.synchronize()
+    assert _capi.last_kernel().startswith("nbits_gemv_stream")
+    y_ref = oracle_f64(case)
+    assert rel_err(y1.cpu().numpy(), y_ref) <= TOL_FP32
+    y2, kernel2 = run_device(case2)
+    assert kernel2 == "nbits_gemv_generic_kernel"
+    assert rel_err(y2, oracle_f64(case2)) <= TOL_FP32
+
+
+def test_strided_output_window(cuda_device):
+    import torch
+
+    case = syn.make_case("win", 2, 4096, 64, 4, 32, seed=8, bias=True)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n)
+    y = torch.zeros((2, 200), device="cuda")
+    weights.matmul_device(torch.from_numpy(case.a).cuda(), y, ld_y=200, col_offset=100)
+    torch.cuda.synchronize()
+    out = y.cpu().numpy()
+    assert not out[:, :100].any() and not out[:, 164:].any()
+    assert rel_err(out[:, 100:164], oracle_f64(case)) <= TOL_FP32
+
+
+def test_decode_linearity_at_full_size(cuda_device):
+    """Size-independent property on the full cfg2 shape: f(a1 + a2) = f(a1) + f(a2) - f(0)."""
+    base = syn.config2(1)
+    rng = np.random.default_rng(5)
+    a1 = rng.standard_normal((1, base.k)).astype(np.float32)
+    a2 = rng.standard_normal((1, base.k)).astype(np.float32)
+    outs = []
+    for a in (a1, a2, a1 + a2, np.zeros_like(a1)):
+        base.a = a
+        outs.append(run_device(base)[0].astype(np.float64))
+    lhs = outs[2]
+    rhs = outs[0] + outs[1] - outs[3]
+    assert np.abs(lhs - rhs).max() / np.abs(lhs).max() <= 2e-5
+    assert np.allclose(outs[3][0], base.bias, rtol=0, atol=0)  # zero activations leave the bias
+
+
+# ---- prefill path (bf16 tcgen05) -------------------------------------------------------------------
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (512, 4096, 512, 64, True, False),     # cfg3 geometry at reduced N
+    (64, 1024, 128, 32, True, True),
+    (200, 2048, 300, 128, False, True),    # ragged M and N
+    (17, 256, 130, 64, True, False),
+    (256, 512, 128, 256, True, True),
+    (300, 4096, 256, 64, True, False),
+])
+def test_prefill_tcgen05(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("prefill", m, k, n, 4, bs, seed=m + k + n, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_TCGEN05)
+    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
+    assert rel_err(y, ref_bf16) <= TOL_BF16
+    assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+
+
+def test_prefill_auto_dispatch_and_full_size_property(cuda_device):
+    """cfg3 at full size M=2048: a checksum identity instead of a full CPU product. With A = ones
+    the result is the per-column sum of the (bf16-rounded) dequantized weights."""
+    import torch
+
+    case = syn.config3(2048)
+    case.a = np.ones_like(case.a)
+    y, kernel = run_device(case)
+    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    ints = o.dequant_int(case.b, case.zero_points, case.n, case.k, 4, 64).astype(np.float64)
+    scales = np.repeat(case.scales.reshape(case.n, -1).astype(np.float64), 64, axis=1)
+    col_sums = (ints * scales).sum(axis=1)
+    assert np.abs(y - y[0:1]).max() == 0.0                     # all rows identical
+    assert rel_err(y[0], col_sums) <= TOL_BF16
+
+
+# ---- accuracy_level 4 ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,k,bs", [(16, 4096, 32), (3, 200, 64), (1, 4096, 128), (5, 48, 16)])
+def test_activation_quantization_bit_exact(cuda_device, m, k, bs):
+    import torch
+
+    rng = np.random.default_rng(m + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    a[0, :bs] = 0.0
+    nb = -(-k // bs)
+    aq = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    sa = torch.empty((m, nb), dtype=torch.float32, device="cuda")
+    quantize_a(torch.from_numpy(a).cuda(), aq, sa, bs)
+    torch.cuda.synchronize()
+    ref_q, ref_s = o.quantize_a(a, k, bs)
+    assert np.array_equal(sa.cpu().numpy(), ref_s)
+    assert np.array_equal(aq.cpu().numpy(), ref_q)
+
+
+@pytest.mark.parametrize("bits,bs,k,n", [(4, 32, 4096, 40), (4, 128, 512, 9), (8, 32, 256, 17), (4, 16, 80, 5)])
+def test_int8_block_dots_bit_exact(cuda_device, bits, bs, k, n):
+    import torch
+
+    case = syn.make_case("dots", 4, k, n, bits, bs, seed=bits + bs + k)
+    aq, _ = o.quantize_a(case.a, k, bs)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, None, K=k, N=n, bits=bits, block_size=bs)
+    dots = torch.empty((4, n, case.n_blocks), dtype=torch.int32, device="cuda")
+    weights.int8_block_dots(torch.from_numpy(aq).cuda(), dots)
+    torch.cuda.synchronize()
+    assert np.array_equal(dots.cpu().numpy(), o.int8_block_dots(aq, case.b, case.zero_points, n, k, bits, bs))
+
+
+@pytest.mark.parametrize("m,k,n,bits,bs,zp", [(16, 4096, 128, 4, 32, False), (1, 4096, 77, 4, 128, True),
+                                              (9, 1024, 50, 8, 32, True), (16, 4064, 31, 4, 32, True)])
+def test_int8_path_outputs(cuda_device, m, k, n, bits, bs, zp):
+    case = syn.make_case("lvl4", m, k, n, bits, bs, seed=m + n, zero_points=zp, bias=True)
+    y, kernel = run_device(case, accuracy_level=4)
+    assert kernel.startswith("nbits_int8_matmul_kernel"), kernel
+    ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, bits, bs)
+    assert rel_err(y, ref) <= TOL_FP32   # same integers, fp32 scaling in a different order
+    assert rel_err(y, oracle_f64(case)) <= 2e-2   # int8 activations vs exact
+
+
+# ---- through the registered operator (host tensors) -----------------------------------------------
+def test_registered_operator_end_to_end(cuda_device):
+    pkg.register_kernels()
+    pkg.clear_used_kernel_names()
+    case = syn.config2(4, n=1024)
+    session = pkg.MatMulNBitsSession(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n, bits=4,
+                                     block_size=128)
+    y = session.run(case.a)
+    assert y.shape == (4, 1024)
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    assert session.last_device_kernel.startswith("nbits_gemv_stream_kernel")
+    y3 = session.run(case.a.reshape(2, 2, case.k))          # leading dims are kept
+    assert y3.shape == (2, 2, 1024) and np.array_equal(y3.reshape(4, 1024), y)
+    assert pkg.used_kernel_names() == ["onnx_light_cuda::MatMulNBits"] * 2
+    big = syn.make_case("op_prefill", 96, 1024, 256, 4, 64, seed=2)
+    s2 = pkg.MatMulNBitsSession(big.b, big.scales, big.zero_points, None, K=1024, N=256, bits=4, block_size=64)
+    assert rel_err(s2.run(big.a), oracle_f64(big)) <= TOL_BF16
+    assert s2.last_device_kernel.startswith("nbits_gemm_tcgen05_kernel")
+    s4 = pkg.MatMulNBitsSession(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n, bits=4,
+                                block_size=128, accuracy_level=4)
+    ref4 = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, 4, 128)
+    assert rel_err(s4.run(case.a), ref4) <= TOL_FP32
+
+
+def test_llama_layer_shapes_both_accuracy_levels(cuda_device):
+    """cfg4 geometry (seven projections, M=16, block 32, no zero points) at reduced N."""
+    for level in (0, 4):
+        for full in syn.config4(level):
+            n = min(full.n, 256)
+            case = syn.make_case(full.name, 16, full.k, n, 4, 32, seed=full.meta["seed"], zero_points=False)
+            y, _ = run_device(case, accuracy_level=level)
+            if level == 0:
+                assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+            else:
+                ref = o.matmul_int8(case.a, case.b, case.scales, None, None, n, case.k, 4, 32)
+                assert rel_err(y, ref) <= TOL_FP32
