@@ -239,6 +239,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling runs)")
+    parser.add_argument("--no-graph", action="store_true", help="plain launches instead of a CUDA graph")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -291,7 +292,7 @@ def main() -> None:
         step()
         torch.cuda.synchronize()
         kernel_name = _capi.last_kernel()
-        replay, graphed = capture_graph(torch, step)
+        replay, graphed = (step, False) if args.no_graph else capture_graph(torch, step)
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
             seconds = time_steps(torch, dist, replay, args.steps, args.warmup, world)

@@ -9,8 +9,11 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+import os
+
 PACKAGE_DIR = Path(__file__).resolve().parent
-CUDA_LIB_PATH = PACKAGE_DIR / "libmatmulnbits_b200.so"
+# MNB_LIBRARY_PATH selects another build of the same C ABI (e.g. an instrumented one).
+CUDA_LIB_PATH = Path(os.environ.get("MNB_LIBRARY_PATH", PACKAGE_DIR / "libmatmulnbits_b200.so"))
 
 MNB_OK = 0
 MNB_ERR_INVALID_ARGUMENT = 1

@@ -3,11 +3,15 @@
 // Two kernels:
 //   * nbits_gemv_stream_kernel - persistent, one CTA per SM. A producer warp streams whole
 //     row tiles of the packed weights (plus their scales and zero points) into a ring of
-//     shared-memory stages with 1-D bulk (TMA) copies completed on mbarriers; 16 consumer
-//     warps read 128-bit chunks from shared memory, turn nibbles/bytes into fp32 with a
-//     magic-number OR (no integer->float conversion instruction), multiply-accumulate with
-//     packed fp32x2 FMAs against activations held in registers, and reduce with warp
-//     shuffles. Memory-bound by design: every weight byte is read from HBM exactly once.
+//     shared-memory stages with 1-D bulk (TMA) copies completed on mbarriers. Eight consumer
+//     warps each own a few rows of the tile: a warp walks its rows across all of K, reading
+//     128-bit chunks from shared memory, turning nibbles/bytes into fp32 with one LOP3 per
+//     code (magic-number OR, no integer->float conversion), and accumulating with packed
+//     fp32x2 add/fma against the activations, which are staged once per CTA in shared memory
+//     (pre-scaled, bank-conflict-free swizzle) and reused across the warp's rows. Warps never
+//     wait for one another: the only cross-warp objects are the stage barriers. The row sums
+//     are reduced with warp shuffles and written straight to Y.
+//     Memory-bound by design: every weight byte is read from HBM exactly once.
 //   * nbits_gemv_generic_kernel - one warp per output column, scalar code, any shape. Used
 //     for shapes the streaming kernel does not take (unaligned rows, block_size 16, ...).
 //
@@ -15,8 +19,8 @@
 // split N across workers (onnx_light_cpu/impl/math/gemm_kernel.cc:1219-1258) - with the
 // packed-INT4 conventions of onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:60-93.
 //
-// Numerics: q is exact in fp32; sum_k a_k*q_k is accumulated in fp32 per 32-element chunk,
-// then (chunk_sum - zp * sum_k a_k) * scale is added to the row accumulator. Differences
+// Numerics: q is exact in fp32; sum_k a_k*q_k is accumulated in fp32 per 16-byte chunk,
+// then scale * (chunk_sum - zp * sum_k a_k) is added to the row accumulator. Differences
 // from a sequential fp32 sum are summation-order only.
 
 #include "nbits_common.cuh"
@@ -27,12 +31,13 @@
 namespace mnb {
 namespace {
 
-constexpr int kConsumerThreads = 512;
-constexpr int kConsumerWarps = kConsumerThreads / 32;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kProducerThreads = 32;
-constexpr int kRowsPerThread = 4;
+constexpr int kThreads = kConsumerThreads + kProducerThreads;
 constexpr int kMaxStages = 4;
 constexpr int kChunkBytes = 16;
+constexpr std::uint32_t kMagicBits = 0x4b000000u; // 2^23 as fp32
 
 struct StreamParams {
   WeightView w;
@@ -40,100 +45,97 @@ struct StreamParams {
   int m_total;
   OutputView out;
   int *status;
-  int cc_log2;        // log2(chunk columns handled by one row group)
-  int row_groups;     // kConsumerThreads >> cc_log2
-  int tile_rows;      // row_groups * kRowsPerThread
-  int chunks_per_row; // row_bytes / 16
+  int chunks_per_row;   // row_bytes / 16
+  int chunk_iters;      // ceil(chunks_per_row / 32): chunk columns per lane
+  int rows_per_warp;    // 4, 2 or 1
+  int tile_rows;        // kConsumerWarps * rows_per_warp
   int rows_per_cta;
   int stages;
   int stage_b_bytes;     // tile_rows * row_bytes
   int stage_scale_bytes; // tile_rows * n_blocks * 4, rounded up to 16
   int stage_zp_bytes;    // tile_rows * zp_row_bytes rounded up to 16 (0 without zero points)
   int stage_bytes;
-  int block_shift; // log2(block_size)
+  int a_bytes;           // activation staging: MT * chunk_iters * 32 chunks * 128 B (+ sums)
+  int block_shift;       // log2(block_size)
+  std::uint32_t magic;   // kMagicBits, passed at run time so that it stays in a register
 };
 
-__device__ __forceinline__ float2 Ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 Fadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
-
-// Reduces V per-thread values over the 32 lanes of a warp with V-1 + log2(32/V) shuffles.
-// On return, value index ((lane * V) >> 5) is complete in every lane; the function returns it.
-template <int V> __device__ __forceinline__ float WarpMultiReduce(float (&v)[V], int lane) {
-  static_assert(V == 1 || V == 2 || V == 4 || V == 8 || V == 16, "V must be a power of two");
-  int width = V;
-  int offset = 16;
-#pragma unroll
-  for (int step = 0; step < 5; ++step) {
-    if (width > 1) {
-      const bool upper = (lane & offset) != 0;
-      const int half = width >> 1;
-#pragma unroll
-      for (int i = 0; i < V / 2; ++i) {
-        if (i < half) {
-          const float send = upper ? v[i] : v[i + half];
-          const float keep = upper ? v[i + half] : v[i];
-          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, offset);
-        }
-      }
-      width = half;
-    } else {
-      v[0] += __shfl_xor_sync(0xffffffffu, v[0], offset);
-    }
-    offset >>= 1;
-  }
-  return v[0];
+// d = (a & mask) | c in one LOP3 (truth table 0xEA).
+template <std::uint32_t MASK>
+__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "n"(MASK), "r"(c));
+  return d;
 }
 
-// Per-thread activation registers for one chunk column: 32 (4-bit) or 16 (8-bit) consecutive
-// k, pre-multiplied by the power of two that undoes the bit position of their code.
+// acc += ((x0, x1) - 2^23) * ap   with packed fp32x2 instructions.
+__device__ __forceinline__ void PairFma(std::uint64_t &acc, std::uint32_t x0, std::uint32_t x1,
+                                        std::uint64_t neg_magic2, std::uint64_t ap) {
+  asm("{\n\t"
+      ".reg .b64 t;\n\t"
+      "mov.b64 t, {%1, %2};\n\t"
+      "add.rn.f32x2 t, t, %3;\n\t"
+      "fma.rn.f32x2 %0, t, %4, %0;\n\t"
+      "}"
+      : "+l"(acc)
+      : "r"(x0), "r"(x1), "l"(neg_magic2), "l"(ap));
+}
+
+__device__ __forceinline__ float PairSum(std::uint64_t a, std::uint64_t b) {
+  std::uint64_t s;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(s) : "l"(a), "l"(b));
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(s));
+  return lo + hi;
+}
+
 template <int BITS> struct ChunkTraits;
 template <> struct ChunkTraits<4> {
-  static constexpr int kWeights = 32;
+  static constexpr int kWeights = 32; // codes per 16-byte chunk
+  static constexpr int kPairs = 16;   // activation pairs per chunk
+  static constexpr int kUnits = 8;    // 16-byte units of fp32 activations per chunk
 };
 template <> struct ChunkTraits<8> {
   static constexpr int kWeights = 16;
+  static constexpr int kPairs = 8;
+  static constexpr int kUnits = 4;
 };
 
-// sum_e a[e] * code[e] for one 16-byte chunk. `ap` holds the pre-scaled activations as pairs.
+// sum_e a[e] * code[e] for one 16-byte chunk; `ap` holds pre-scaled activation pairs.
 template <int BITS>
-__device__ __forceinline__ float ChunkDot(const uint4 &q, const float2 *ap) {
-  const float2 kMagic2 = make_float2(-8388608.0f, -8388608.0f);
-  float2 acc0 = make_float2(0.0f, 0.0f);
-  float2 acc1 = make_float2(0.0f, 0.0f);
+__device__ __forceinline__ float ChunkDot(const uint4 &q, const std::uint64_t *ap,
+                                          std::uint32_t magic, std::uint64_t neg_magic2) {
+  std::uint64_t acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
   const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
   if constexpr (BITS == 4) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const std::uint32_t w = words[i];
       const std::uint32_t hi = w >> 12;
-      // nibble j sits at bit 4j of w (j <= 4) or at bit 4(j-3) of hi (j >= 5)
-      const float x0 = __uint_as_float((w & 0x0000000fu) | 0x4b000000u);
-      const float x1 = __uint_as_float((w & 0x000000f0u) | 0x4b000000u);
-      const float x2 = __uint_as_float((w & 0x00000f00u) | 0x4b000000u);
-      const float x3 = __uint_as_float((w & 0x0000f000u) | 0x4b000000u);
-      const float x4 = __uint_as_float((w & 0x000f0000u) | 0x4b000000u);
-      const float x5 = __uint_as_float((hi & 0x00000f00u) | 0x4b000000u);
-      const float x6 = __uint_as_float((hi & 0x0000f000u) | 0x4b000000u);
-      const float x7 = __uint_as_float((hi & 0x000f0000u) | 0x4b000000u);
-      acc0 = Ffma2(Fadd2(make_float2(x0, x1), kMagic2), ap[4 * i + 0], acc0);
-      acc1 = Ffma2(Fadd2(make_float2(x2, x3), kMagic2), ap[4 * i + 1], acc1);
-      acc0 = Ffma2(Fadd2(make_float2(x4, x5), kMagic2), ap[4 * i + 2], acc0);
-      acc1 = Ffma2(Fadd2(make_float2(x6, x7), kMagic2), ap[4 * i + 3], acc1);
+      // code j sits at bit 4j of w (j <= 4) or at bit 4(j-3) of hi (j >= 5); the bit position
+      // is undone by the power-of-two pre-scale of the matching activation
+      PairFma(acc0, AndOr<0x0000000fu>(w, magic), AndOr<0x000000f0u>(w, magic), neg_magic2, ap[4 * i + 0]);
+      PairFma(acc1, AndOr<0x00000f00u>(w, magic), AndOr<0x0000f000u>(w, magic), neg_magic2, ap[4 * i + 1]);
+      PairFma(acc2, AndOr<0x000f0000u>(w, magic), AndOr<0x00000f00u>(hi, magic), neg_magic2, ap[4 * i + 2]);
+      PairFma(acc3, AndOr<0x0000f000u>(hi, magic), AndOr<0x000f0000u>(hi, magic), neg_magic2, ap[4 * i + 3]);
     }
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const std::uint32_t w = words[i];
-      const float x0 = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7540));
-      const float x1 = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7541));
-      const float x2 = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7542));
-      const float x3 = __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7543));
-      acc0 = Ffma2(Fadd2(make_float2(x0, x1), kMagic2), ap[2 * i + 0], acc0);
-      acc1 = Ffma2(Fadd2(make_float2(x2, x3), kMagic2), ap[2 * i + 1], acc1);
+      if (i & 1) {
+        PairFma(acc2, __byte_perm(w, magic, 0x7540), __byte_perm(w, magic, 0x7541), neg_magic2, ap[2 * i + 0]);
+        PairFma(acc3, __byte_perm(w, magic, 0x7542), __byte_perm(w, magic, 0x7543), neg_magic2, ap[2 * i + 1]);
+      } else {
+        PairFma(acc0, __byte_perm(w, magic, 0x7540), __byte_perm(w, magic, 0x7541), neg_magic2, ap[2 * i + 0]);
+        PairFma(acc1, __byte_perm(w, magic, 0x7542), __byte_perm(w, magic, 0x7543), neg_magic2, ap[2 * i + 1]);
+      }
     }
   }
-  const float2 s = Fadd2(acc0, acc1);
-  return s.x + s.y;
+  std::uint64_t s01, s23;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(s01) : "l"(acc0), "l"(acc1));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(s23) : "l"(acc2), "l"(acc3));
+  return PairSum(s01, s23);
 }
 
 // Pre-scale factor for element e of a chunk (undoes the bit position left in place by the OR).
@@ -147,24 +149,54 @@ template <int BITS> __device__ __forceinline__ float PrescaleOf(int e) {
   }
 }
 
-template <int BITS, int MT, int J>
-__global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
-    nbits_gemv_stream_kernel(const StreamParams p) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  constexpr int kW = ChunkTraits<BITS>::kWeights;
-  constexpr int kV = kRowsPerThread * MT;
+// Reduces V per-thread values over the 32 lanes of a warp with V-1 + log2(32/V) shuffles.
+// Afterwards value index (lane * V) >> 5 is complete in every lane and is returned.
+template <int V, int OFFSET = 16> __device__ __forceinline__ float WarpMultiReduce(float *v, int lane) {
+  if constexpr (OFFSET == 0) {
+    return v[0];
+  } else if constexpr (V > 1) {
+    const bool upper = (lane & OFFSET) != 0;
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      const float send = upper ? v[i] : v[i + V / 2];
+      const float keep = upper ? v[i + V / 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, OFFSET);
+    }
+    return WarpMultiReduce<V / 2, OFFSET / 2>(v, lane);
+  } else {
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], OFFSET);
+    return WarpMultiReduce<1, OFFSET / 2>(v, lane);
+  }
+}
 
-  // shared memory carve-up: [stages x (B | scales | zp)] [barriers] [reduction scratch]
+// Shared-memory position (in bytes) of 16-byte unit `unit` of the pre-scaled activations: rows
+// of 128 bytes with the unit index XOR-swizzled by the row, so that lanes reading the same
+// unit of consecutive chunks hit different banks.
+__device__ __forceinline__ int ActUnitOffset(int unit) {
+  const int row = unit >> 3;
+  return (row << 7) + (((unit & 7) ^ (row & 7)) << 4);
+}
+
+template <int BITS, int MT, int RPW>
+__global__ void __launch_bounds__(kThreads, 1) nbits_gemv_stream_kernel(const StreamParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  using Traits = ChunkTraits<BITS>;
+  constexpr int kW = Traits::kWeights;
+  constexpr int kV = RPW * MT;
+
+  // shared memory: [stages x (B | scales | zp)] [activations: MT x (units | sums)] [barriers]
   unsigned char *stage_base = smem_raw;
-  std::uint64_t *full_bar =
-      reinterpret_cast<std::uint64_t *>(smem_raw + static_cast<size_t>(p.stages) * p.stage_bytes);
+  unsigned char *act_base = smem_raw + static_cast<size_t>(p.stages) * p.stage_bytes;
+  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(act_base + p.a_bytes);
   std::uint64_t *empty_bar = full_bar + kMaxStages;
-  float *red = reinterpret_cast<float *>(empty_bar + kMaxStages); // [2][row_groups][kV][wpg]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const bool is_producer = warp == kConsumerWarps;
+  const int chunk_slots = p.chunk_iters * 32;            // chunk columns incl. padding
+  const int act_row_bytes = chunk_slots * Traits::kUnits * 16; // pre-scaled activations of one m
+  const int act_m_bytes = act_row_bytes + chunk_slots * 4; // + per-chunk plain sums
 
   const std::int64_t row_begin = static_cast<std::int64_t>(blockIdx.x) * p.rows_per_cta;
   std::int64_t rows_here = p.w.n - row_begin;
@@ -209,13 +241,11 @@ __global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
       const std::uint32_t b_bytes = static_cast<std::uint32_t>(rows) * p.w.row_bytes;
       const float *scale_src = p.w.scales + row0 * p.w.n_blocks;
       const std::uint32_t scale_bytes = static_cast<std::uint32_t>(rows) * p.w.n_blocks * 4u;
-      const bool scale_bulk =
-          ((reinterpret_cast<std::uintptr_t>(scale_src) | scale_bytes) & 15u) == 0;
+      const bool scale_bulk = ((reinterpret_cast<std::uintptr_t>(scale_src) | scale_bytes) & 15u) == 0;
       const std::uint8_t *zp_src = p.w.zp != nullptr ? p.w.zp + row0 * p.w.zp_row_bytes : nullptr;
       const std::uint32_t zp_bytes =
           p.w.zp != nullptr ? static_cast<std::uint32_t>(rows) * p.w.zp_row_bytes : 0u;
-      const bool zp_bulk =
-          zp_bytes != 0 && ((reinterpret_cast<std::uintptr_t>(zp_src) | zp_bytes) & 15u) == 0;
+      const bool zp_bulk = zp_bytes != 0 && ((reinterpret_cast<std::uintptr_t>(zp_src) | zp_bytes) & 15u) == 0;
 
       if (!scale_bulk) {
         float *dst = reinterpret_cast<float *>(ss);
@@ -229,8 +259,7 @@ __global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
         }
       }
       if (lane == 0) {
-        const std::uint32_t tx =
-            b_bytes + (scale_bulk ? scale_bytes : 0u) + (zp_bulk ? zp_bytes : 0u);
+        const std::uint32_t tx = b_bytes + (scale_bulk ? scale_bytes : 0u) + (zp_bulk ? zp_bytes : 0u);
         ptx::MbarArriveExpectTx(&full_bar[s], tx);
         ptx::BulkLoad(sb, p.w.b + row0 * p.w.row_bytes, b_bytes, &full_bar[s]);
         if (scale_bulk) {
@@ -256,46 +285,65 @@ __global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
   }
 
   // ---------------- consumers ----------------
-  const int cc = tid & ((1 << p.cc_log2) - 1);
-  const int rg = tid >> p.cc_log2;
-  const int warps_per_group = (1 << p.cc_log2) >> 5; // chunk columns per group >= 32
-  const int warp_in_group = warp & (warps_per_group - 1);
-
-  // activations of this thread's chunk columns, pre-scaled, as pairs; and their plain sums
-  float2 ap[MT][J][kW / 2];
-  float a_sum[MT][J];
-#pragma unroll
+  // Stage the activations once: pre-scaled, swizzled, zero beyond K; plus per-chunk sums.
   for (int mi = 0; mi < MT; ++mi) {
     const int m = m_base + mi;
+    unsigned char *dst = act_base + mi * act_m_bytes;
+    const int units = chunk_slots * Traits::kUnits;
+    for (int u = tid; u < units; u += kConsumerThreads) {
+      float v[4];
 #pragma unroll
-    for (int j = 0; j < J; ++j) {
-      const int c = cc + (j << p.cc_log2);
-      const std::int64_t k0 = static_cast<std::int64_t>(c) * kW;
-      float total = 0.0f;
-#pragma unroll
-      for (int e = 0; e < kW; e += 2) {
-        float v0 = 0.0f, v1 = 0.0f;
-        if (m < p.m_total && c < p.chunks_per_row) {
-          if (k0 + e < p.w.k) {
-            v0 = __ldg(p.a + static_cast<std::int64_t>(m) * p.w.k + k0 + e);
-          }
-          if (k0 + e + 1 < p.w.k) {
-            v1 = __ldg(p.a + static_cast<std::int64_t>(m) * p.w.k + k0 + e + 1);
-          }
-        }
-        total += v0 + v1;
-        ap[mi][j][e / 2] = make_float2(v0 * PrescaleOf<BITS>(e), v1 * PrescaleOf<BITS>(e + 1));
+      for (int e = 0; e < 4; ++e) {
+        const std::int64_t kk = static_cast<std::int64_t>(u) * 4 + e;
+        const float raw = (m < p.m_total && kk < p.w.k) ? __ldg(p.a + static_cast<std::int64_t>(m) * p.w.k + kk) : 0.0f;
+        v[e] = raw * PrescaleOf<BITS>(static_cast<int>(kk & 7));
       }
-      a_sum[mi][j] = total;
+      *reinterpret_cast<float4 *>(dst + ActUnitOffset(u)) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    float *sums = reinterpret_cast<float *>(dst + act_row_bytes);
+    for (int c = tid; c < chunk_slots; c += kConsumerThreads) {
+      float total = 0.0f;
+      for (int e = 0; e < kW; ++e) {
+        const std::int64_t kk = static_cast<std::int64_t>(c) * kW + e;
+        if (m < p.m_total && kk < p.w.k) {
+          total += __ldg(p.a + static_cast<std::int64_t>(m) * p.w.k + kk);
+        }
+      }
+      sums[c] = total;
     }
   }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); // consumers only
 
+  const std::uint32_t magic = p.magic;
+  std::uint64_t neg_magic2;
+  {
+    const float neg = -__uint_as_float(magic);
+    asm("mov.b64 %0, {%1, %1};" : "=l"(neg_magic2) : "f"(neg));
+  }
   const int default_zp = 1 << (BITS - 1);
   const bool has_zp = p.w.zp != nullptr;
 
   for (int t = 0; t < num_tiles; ++t) {
     const int s = t % p.stages;
     const std::uint32_t round = static_cast<std::uint32_t>(t / p.stages);
+    std::int64_t rows = rows_here - static_cast<std::int64_t>(t) * p.tile_rows;
+    if (rows > p.tile_rows) {
+      rows = p.tile_rows;
+    }
+    const int r0 = warp * RPW; // first tile row of this warp
+    const std::int64_t row0 = row_begin + static_cast<std::int64_t>(t) * p.tile_rows;
+
+    // the lane that will write result `value_index` fetches its bias now, behind the math
+    const int value_index = (lane * kV) >> 5; // = r * MT + mi
+    const bool writer_lane = (lane & (32 / kV - 1)) == 0;
+    const int out_r = r0 + value_index / MT;
+    const int out_m = m_base + value_index % MT;
+    const bool out_valid = writer_lane && out_r < rows && out_m < p.m_total;
+    float bias = 0.0f;
+    if (out_valid && p.w.bias != nullptr) {
+      bias = __ldg(p.w.bias + row0 + out_r);
+    }
+
     if (!ptx::MbarWait(&full_bar[s], round & 1u)) {
       atomicExch(p.status, kDeviceTimeoutFullBarrier);
       return;
@@ -303,93 +351,73 @@ __global__ void __launch_bounds__(kConsumerThreads + kProducerThreads, 1)
     const unsigned char *sb = stage_base + static_cast<size_t>(s) * p.stage_bytes;
     const float *ss = reinterpret_cast<const float *>(sb + p.stage_b_bytes);
     const unsigned char *sz = sb + p.stage_b_bytes + p.stage_scale_bytes;
-    std::int64_t rows = rows_here - static_cast<std::int64_t>(t) * p.tile_rows;
-    if (rows > p.tile_rows) {
-      rows = p.tile_rows;
-    }
 
     float acc[kV];
 #pragma unroll
     for (int v = 0; v < kV; ++v) {
       acc[v] = 0.0f;
     }
+    if (r0 < rows) {
+      // Rows of this warp that lie beyond the tile read the warp's first row instead (their
+      // sums are never written), which keeps the row loop free of branches so that the
+      // independent rows interleave in the instruction stream.
+      int row_of[RPW];
 #pragma unroll
-    for (int i = 0; i < kRowsPerThread; ++i) {
-      const int r = rg * kRowsPerThread + i;
-      if (r < rows) {
+      for (int r = 0; r < RPW; ++r) {
+        row_of[r] = r0 + r < rows ? r0 + r : r0;
+      }
+#ifndef MNB_GEMV_SKIP_COMPUTE
+#pragma unroll 1
+      for (int j = 0; j < p.chunk_iters; ++j) {
+        const int c = lane + 32 * j;
+        const int c_read = c < p.chunks_per_row ? c : 0; // padded chunk columns have zero activations
+        const int block = (c_read * kW) >> p.block_shift;
+        std::uint64_t ap[MT][Traits::kPairs];
+        float a_sum[MT];
 #pragma unroll
-        for (int j = 0; j < J; ++j) {
-          const int c = cc + (j << p.cc_log2);
-          if (c < p.chunks_per_row) {
-            const uint4 q = *reinterpret_cast<const uint4 *>(sb + static_cast<size_t>(r) * p.w.row_bytes +
-                                                             static_cast<size_t>(c) * kChunkBytes);
-            const int block = (c * kW) >> p.block_shift;
-            const float scale = ss[r * p.w.n_blocks + block];
-            int zp = default_zp;
-            if (has_zp) {
-              if constexpr (BITS == 8) {
-                zp = sz[r * p.w.zp_row_bytes + block];
-              } else {
-                const int byte = sz[r * p.w.zp_row_bytes + (block >> 1)];
-                zp = (block & 1) ? (byte >> 4) : (byte & 0x0f);
-              }
+        for (int mi = 0; mi < MT; ++mi) {
+          const unsigned char *arow = act_base + mi * act_m_bytes;
+#pragma unroll
+          for (int u = 0; u < Traits::kUnits; ++u) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(arow + ActUnitOffset(c * Traits::kUnits + u));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(ap[mi][2 * u]) : "r"(v.x), "r"(v.y));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(ap[mi][2 * u + 1]) : "r"(v.z), "r"(v.w));
+          }
+          a_sum[mi] = reinterpret_cast<const float *>(arow + act_row_bytes)[c];
+        }
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          const int row = row_of[r];
+          const uint4 q = *reinterpret_cast<const uint4 *>(sb + static_cast<size_t>(row) * p.w.row_bytes +
+                                                           static_cast<size_t>(c_read) * kChunkBytes);
+          const float scale = ss[row * p.w.n_blocks + block];
+          int zp = default_zp;
+          if (has_zp) {
+            if constexpr (BITS == 8) {
+              zp = sz[row * p.w.zp_row_bytes + block];
+            } else {
+              const int byte = sz[row * p.w.zp_row_bytes + (block >> 1)];
+              zp = (byte >> ((block & 1) * 4)) & 0x0f;
             }
-            const float zpf = static_cast<float>(zp);
+          }
+          const float neg_zp = -static_cast<float>(zp);
 #pragma unroll
-            for (int mi = 0; mi < MT; ++mi) {
-              const float raw = ChunkDot<BITS>(q, ap[mi][j]);
-              acc[i * MT + mi] = fmaf(scale, fmaf(-zpf, a_sum[mi][j], raw), acc[i * MT + mi]);
-            }
+          for (int mi = 0; mi < MT; ++mi) {
+            const float raw = ChunkDot<BITS>(q, ap[mi], magic, neg_magic2);
+            acc[r * MT + mi] = fmaf(scale, fmaf(neg_zp, a_sum[mi], raw), acc[r * MT + mi]);
           }
         }
       }
+#endif
     }
-    // stage no longer needed by this warp
+    // this warp is done with the stage
     __syncwarp();
     if (lane == 0) {
       ptx::MbarArrive(&empty_bar[s]);
     }
-
-    // reduce over the chunk columns of the row group
     const float mine = WarpMultiReduce<kV>(acc, lane);
-    const int value_index = (lane * kV) >> 5; // = i * MT + mi
-    const bool writer_lane = (lane & (32 / kV - 1)) == 0;
-    const std::int64_t row0 = row_begin + static_cast<std::int64_t>(t) * p.tile_rows;
-    if (warps_per_group == 1) {
-      if (writer_lane) {
-        const int i = value_index / MT;
-        const int mi = value_index % MT;
-        const int r = rg * kRowsPerThread + i;
-        const int m = m_base + mi;
-        if (r < rows && m < p.m_total) {
-          const std::int64_t col = row0 + r;
-          const float bias = p.w.bias != nullptr ? p.w.bias[col] : 0.0f;
-          p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] = mine + bias;
-        }
-      }
-    } else {
-      float *buf = red + static_cast<size_t>(t & 1) * p.row_groups * kV * warps_per_group +
-                   static_cast<size_t>(rg) * kV * warps_per_group;
-      if (writer_lane) {
-        buf[value_index * warps_per_group + warp_in_group] = mine;
-      }
-      // named barrier over the threads of this row group only (ids 1..8; 0 is __syncthreads)
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(1 << p.cc_log2) : "memory");
-      if (cc < kV) {
-        float total = 0.0f;
-        for (int wg = 0; wg < warps_per_group; ++wg) {
-          total += buf[cc * warps_per_group + wg];
-        }
-        const int i = cc / MT;
-        const int mi = cc % MT;
-        const int r = rg * kRowsPerThread + i;
-        const int m = m_base + mi;
-        if (r < rows && m < p.m_total) {
-          const std::int64_t col = row0 + r;
-          const float bias = p.w.bias != nullptr ? p.w.bias[col] : 0.0f;
-          p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] = total + bias;
-        }
-      }
+    if (out_valid) {
+      p.out.y[static_cast<std::int64_t>(out_m) * p.out.ld + p.out.col_offset + row0 + out_r] = mine + bias;
     }
   }
 }
@@ -451,15 +479,16 @@ int Log2Exact(int v) {
   return l;
 }
 
-template <int BITS, int MT, int J>
+template <int BITS, int MT, int RPW>
 cudaError_t LaunchStreamInstance(const StreamParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
-  auto kernel = nbits_gemv_stream_kernel<BITS, MT, J>;
-  cudaError_t err =
+  auto kernel = nbits_gemv_stream_kernel<BITS, MT, RPW>;
+  // per device and cheap: set on every launch rather than caching across devices
+  const cudaError_t attr =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (err != cudaSuccess) {
-    return err;
+  if (attr != cudaSuccess) {
+    return attr;
   }
-  kernel<<<grid, kConsumerThreads + kProducerThreads, smem, stream>>>(p);
+  kernel<<<grid, kThreads, smem, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -476,66 +505,75 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
   if (w.bits == 4 && w.block_size < 32) {
     return nullptr; // a 16-byte chunk must lie inside one quantization block
   }
-  const int chunks_per_row = w.row_bytes / kChunkBytes;
-  if (chunks_per_row > 2 * kConsumerThreads) {
-    return nullptr;
-  }
+  const int mt = m == 1 ? 1 : 2;
   StreamParams p{};
   p.w = w;
   p.a = a;
   p.m_total = static_cast<int>(m);
   p.out = out;
   p.status = status_word;
-  p.chunks_per_row = chunks_per_row;
-  int cc = 32;
-  while (cc < chunks_per_row && cc < kConsumerThreads) {
-    cc <<= 1;
-  }
-  p.cc_log2 = Log2Exact(cc);
-  p.row_groups = kConsumerThreads / cc;
-  p.tile_rows = p.row_groups * kRowsPerThread;
-  const int j = (chunks_per_row + cc - 1) / cc;
+  p.magic = kMagicBits;
+  p.chunks_per_row = w.row_bytes / kChunkBytes;
+  p.chunk_iters = (p.chunks_per_row + 31) / 32;
   p.block_shift = Log2Exact(w.block_size);
-  p.stage_b_bytes = p.tile_rows * w.row_bytes;
-  p.stage_scale_bytes = (p.tile_rows * w.n_blocks * 4 + 15) & ~15;
-  p.stage_zp_bytes = w.zp != nullptr ? ((p.tile_rows * w.zp_row_bytes + 15) & ~15) : 0;
-  p.stage_bytes = (p.stage_b_bytes + p.stage_scale_bytes + p.stage_zp_bytes + 127) & ~127;
-  const int warps_per_group = cc / 32;
-  const size_t tail_bytes = 2 * kMaxStages * sizeof(std::uint64_t) +
-                            static_cast<size_t>(2) * p.row_groups * kRowsPerThread * 2 * warps_per_group * sizeof(float);
-  const size_t budget = 200 * 1024;
-  int stages = static_cast<int>((budget - tail_bytes) / static_cast<size_t>(p.stage_bytes));
-  if (stages > kMaxStages) {
-    stages = kMaxStages;
+  const int units_per_chunk = w.bits == 4 ? 8 : 4;
+  const int chunk_slots = p.chunk_iters * 32;
+  p.a_bytes = mt * (chunk_slots * units_per_chunk * 16 + chunk_slots * 4);
+  p.a_bytes = (p.a_bytes + 127) & ~127;
+  const size_t barrier_bytes = 2 * kMaxStages * sizeof(std::uint64_t);
+  const size_t budget = 226 * 1024 - barrier_bytes - static_cast<size_t>(p.a_bytes);
+  if (static_cast<size_t>(p.a_bytes) + barrier_bytes + 32 * 1024 > 226 * 1024) {
+    return nullptr; // K too large to keep the activations in shared memory
   }
-  if (stages < 2) {
+  int rpw = 4;
+  for (;; rpw >>= 1) {
+    p.rows_per_warp = rpw;
+    p.tile_rows = kConsumerWarps * rpw;
+    p.stage_b_bytes = p.tile_rows * w.row_bytes;
+    p.stage_scale_bytes = (p.tile_rows * w.n_blocks * 4 + 15) & ~15;
+    p.stage_zp_bytes = w.zp != nullptr ? ((p.tile_rows * w.zp_row_bytes + 15) & ~15) : 0;
+    p.stage_bytes = (p.stage_b_bytes + p.stage_scale_bytes + p.stage_zp_bytes + 127) & ~127;
+    p.stages = static_cast<int>(budget / static_cast<size_t>(p.stage_bytes));
+    if (p.stages > kMaxStages) {
+      p.stages = kMaxStages;
+    }
+    if (p.stages >= 2 || rpw == 1) {
+      break;
+    }
+  }
+  if (p.stages < 2) {
     return nullptr;
   }
-  p.stages = stages;
-  const size_t smem = static_cast<size_t>(stages) * p.stage_bytes + tail_bytes;
+  const size_t smem = static_cast<size_t>(p.stages) * p.stage_bytes + p.a_bytes + barrier_bytes;
 
   int ctas = sm_count > 0 ? sm_count : 148;
-  const std::int64_t max_ctas = (w.n + p.tile_rows - 1) / p.tile_rows;
-  if (ctas > max_ctas) {
-    ctas = static_cast<int>(max_ctas);
+  // hand out rows in multiples of rows_per_warp so that warps stay fully used
+  const std::int64_t groups = (w.n + rpw - 1) / rpw;
+  if (ctas > groups) {
+    ctas = static_cast<int>(groups);
   }
-  p.rows_per_cta = static_cast<int>((w.n + ctas - 1) / ctas);
+  p.rows_per_cta = static_cast<int>((groups + ctas - 1) / ctas) * rpw;
 
-  const int mt = (m == 1 || j == 2) ? 1 : 2; // two chunk columns x two rows of A would spill
   dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>((m + mt - 1) / mt), 1);
   cudaError_t err = cudaErrorInvalidValue;
   const char *name = nullptr;
-#define MNB_STREAM_CASE(B_, M_, J_)                                                              \
-  if (w.bits == B_ && mt == M_ && j == J_) {                                                     \
-    err = LaunchStreamInstance<B_, M_, J_>(p, grid, smem, stream);                               \
-    name = "nbits_gemv_stream_kernel<" #B_ "," #M_ "," #J_ ">";                                  \
+#define MNB_STREAM_CASE(B_, M_, R_)                                                              \
+  if (w.bits == B_ && mt == M_ && rpw == R_) {                                                   \
+    err = LaunchStreamInstance<B_, M_, R_>(p, grid, smem, stream);                               \
+    name = "nbits_gemv_stream_kernel<" #B_ "," #M_ "," #R_ ">";                                  \
   }
-  MNB_STREAM_CASE(4, 1, 1)
-  MNB_STREAM_CASE(4, 2, 1)
+  MNB_STREAM_CASE(4, 1, 4)
   MNB_STREAM_CASE(4, 1, 2)
-  MNB_STREAM_CASE(8, 1, 1)
-  MNB_STREAM_CASE(8, 2, 1)
+  MNB_STREAM_CASE(4, 1, 1)
+  MNB_STREAM_CASE(4, 2, 4)
+  MNB_STREAM_CASE(4, 2, 2)
+  MNB_STREAM_CASE(4, 2, 1)
+  MNB_STREAM_CASE(8, 1, 4)
   MNB_STREAM_CASE(8, 1, 2)
+  MNB_STREAM_CASE(8, 1, 1)
+  MNB_STREAM_CASE(8, 2, 4)
+  MNB_STREAM_CASE(8, 2, 2)
+  MNB_STREAM_CASE(8, 2, 1)
 #undef MNB_STREAM_CASE
   if (err != cudaSuccess) {
     return nullptr;

@@ -64,7 +64,7 @@ def test_dequant_integers_bit_exact(cuda_device, bits, bs, k, n, zp):
 def test_config1_single_node(cuda_device):
     case = syn.config1()
     y, kernel = run_device(case)
-    assert kernel.startswith("nbits_gemv_stream_kernel<4,1,1>"), kernel
+    assert kernel.startswith("nbits_gemv_stream_kernel<4,1,"), kernel
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, None, None, case.n, case.k, 4, 32)) <= TOL_FP32
 
