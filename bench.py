@@ -240,6 +240,8 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling runs)")
     parser.add_argument("--no-graph", action="store_true", help="plain launches instead of a CUDA graph")
+    parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma"],
+                        help="kernel family for the decode workload (auto = library dispatch)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -285,13 +287,17 @@ def main() -> None:
         per_launch_bytes = weights[0].algorithmic_bytes(m)
         assert copies * per_launch_bytes > L2_BYTES
 
+        decode_path = {"auto": _capi.PATH_AUTO, "gemv": _capi.PATH_GEMV, "mma": _capi.PATH_GEMV_MMA}[args.decode_path]
+
         def step():
             for w, y in zip(weights, ys):
-                w.matmul_device(a, y)
+                w.matmul_device(a, y, path=decode_path)
 
         step()
         torch.cuda.synchronize()
         kernel_name = _capi.last_kernel()
+        if any(w.poll_status() != 0 for w in weights):
+            raise SystemExit(f"bench: {kernel_name} reported a device-side timeout; not timing a broken kernel")
         replay, graphed = (step, False) if args.no_graph else capture_graph(torch, step)
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
@@ -340,7 +346,7 @@ def main() -> None:
 
                 def sweep_step():
                     for w, y in zip(weights, ys_s):
-                        w.matmul_device(a_s, y)
+                        w.matmul_device(a_s, y, path=decode_path)
 
                 sweep_step()
                 torch.cuda.synchronize()

@@ -64,6 +64,7 @@ struct mnb_weights {
   bool owns = false;
   void *owned[4] = {nullptr, nullptr, nullptr, nullptr};
   int *status_dev = nullptr;
+  void *meta_dev = nullptr; // prepared scales / zero points for the MMA decode kernel
   // scratch, grown on demand (guarded by `mutex`)
   std::mutex mutex;
   void *scratch_a = nullptr; // bf16 activations (prefill) or int8 activations (accuracy_level 4)
@@ -137,6 +138,27 @@ int SetupCommon(mnb_weights *h) {
   if (err != cudaSuccess) {
     return FailCuda("cudaStreamCreate", err);
   }
+  return MNB_OK;
+}
+
+// Builds the task-major scales / zero-point array once per node (constant-weight policy).
+int PrepareMeta(mnb_weights *h) {
+  const mnb::MetaGeometry geo = mnb::MetaGeometryOf(h->view);
+  if (geo.bytes == 0) {
+    return MNB_OK; // geometry not taken by the MMA decode kernel
+  }
+  cudaError_t err = cudaMalloc(&h->meta_dev, geo.bytes);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMalloc(meta)", err);
+  }
+  if (!mnb::LaunchPrepareMeta(h->view, static_cast<unsigned char *>(h->meta_dev), h->stream)) {
+    return FailCuda("prepare meta", cudaGetLastError());
+  }
+  err = cudaStreamSynchronize(h->stream);
+  if (err != cudaSuccess) {
+    return FailCuda("prepare meta", err);
+  }
+  h->view.meta = static_cast<const unsigned char *>(h->meta_dev);
   return MNB_OK;
 }
 
@@ -324,6 +346,11 @@ static int CreateImpl(int device, const uint8_t *b, const float *scales, const u
     h->view.scales = scales;
     h->view.zp = zero_points;
     h->view.bias = bias;
+    rc = PrepareMeta(h);
+    if (rc != MNB_OK) {
+      mnb_weights_destroy(h);
+      return rc;
+    }
     *out = h;
     return MNB_OK;
   }
@@ -352,6 +379,11 @@ static int CreateImpl(int device, const uint8_t *b, const float *scales, const u
   h->view.scales = static_cast<const float *>(h->owned[1]);
   h->view.zp = static_cast<const std::uint8_t *>(h->owned[2]);
   h->view.bias = static_cast<const float *>(h->owned[3]);
+  rc = PrepareMeta(h);
+  if (rc != MNB_OK) {
+    mnb_weights_destroy(h);
+    return rc;
+  }
   *out = h;
   return MNB_OK;
 }
@@ -384,7 +416,7 @@ int mnb_weights_destroy(mnb_weights *h) {
       }
     }
   }
-  for (void *ptr : {static_cast<void *>(h->status_dev), h->scratch_a, h->scratch_s,
+  for (void *ptr : {static_cast<void *>(h->status_dev), h->meta_dev, h->scratch_a, h->scratch_s,
                     static_cast<void *>(h->a_dev), static_cast<void *>(h->y_dev)}) {
     if (ptr != nullptr) {
       cudaFree(ptr);

@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstddef>
 #include <cstdint>
 
 namespace mnb {
@@ -17,6 +18,7 @@ struct WeightView {
   const float *scales;
   const std::uint8_t *zp;
   const float *bias;
+  const unsigned char *meta; // prepared task-major scales / zero points (see MetaGeometryOf), or null
   std::int64_t n;
   std::int64_t k;
   int bits;
@@ -74,6 +76,19 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
                              int *status_word, cudaStream_t stream, int sm_count);
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                               cudaStream_t stream);
+// Prepared side array used by the MMA decode kernel: per (8-row half tile, task slice) one
+// record {float scale[8][bpt]; uint8 zp[8][bpt] (only with zero points)}. bytes == 0 means
+// the geometry is outside what that kernel takes.
+struct MetaGeometry {
+  int bpt;             // quantization blocks per task
+  int slices;          // tasks per row tile
+  int rec_bytes;
+  int rec_scale_bytes;
+  int half_tiles;
+  std::size_t bytes;
+};
+MetaGeometry MetaGeometryOf(const WeightView &w);
+bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t stream);
 const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                           int *status_word, cudaStream_t stream, int sm_count);
 

@@ -24,12 +24,11 @@
 
 #include "nbits_common.cuh"
 #include "nbits_ptx.cuh"
+#include "nbits_tma.cuh"
 
-#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include <cstdint>
-#include <mutex>
 
 namespace mnb {
 namespace {
@@ -109,10 +108,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                               const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
   using Smem = GemmSmem<BT>;
   constexpr int kStages = Smem::kStages;
-  extern __shared__ unsigned char smem_unaligned[];
-  // 1024-byte alignment is required by the 128-byte swizzle atoms
-  unsigned char *smem = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<std::uintptr_t>(smem_unaligned) + 1023) & ~static_cast<std::uintptr_t>(1023));
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms; the pointer stays in the
+  // shared address space (no integer round trip) so that accesses compile to LDS/STS
+  unsigned char *smem = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
   unsigned char *stage0 = smem;
   std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(smem + kStages * Smem::kStage);
   std::uint64_t *full_tma = bars;               // [kStages] TMA landed
@@ -303,43 +302,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---- host side -----------------------------------------------------------------------------
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn GetEncodeTiled() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) ==
-            cudaSuccess &&
-        result == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-  });
-  return fn;
-}
-
-bool EncodeMap2D(CUtensorMap *map, CUtensorMapDataType type, int elem_bytes, const void *base,
-                 std::uint64_t inner, std::uint64_t outer, std::uint64_t row_stride_bytes,
-                 std::uint32_t box_inner, std::uint32_t box_outer, CUtensorMapSwizzle swizzle) {
-  EncodeTiledFn encode = GetEncodeTiled();
-  if (encode == nullptr) {
-    return false;
-  }
-  (void)elem_bytes;
-  const cuuint64_t dims[2] = {inner, outer};
-  const cuuint64_t strides[1] = {row_stride_bytes};
-  const cuuint32_t box[2] = {box_inner, box_outer};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  return encode(map, type, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 int Log2Of(int v) {
   int l = 0;

@@ -1,12 +1,593 @@
-// Decode on warp-level tensor-core MMA with an exact 3-way bf16 split of the activations.
-// Not built yet: the launcher reports "unsupported" so callers get MNB_ERR_UNSUPPORTED.
+// Decode path of MatMulNBits on warp-level tensor-core MMA with fp32-grade accuracy.
+//
+// Why tensor cores for a GEMV: on CUDA cores every 4-bit code costs one integer extraction
+// plus two floating-point operations per activation row, and the integer pipe (half rate)
+// becomes the limit before HBM does. Here a code costs 5/8 integer operation and half an
+// fp16x2 operation, and the multiply-accumulate is free: the weights are the MMA "A" operand
+// (16 rows x 16 k per step) and the activations the "B" operand.
+//
+// Exactness. (q - zp) is an integer of magnitude < 256: exact in fp16. Each activation row is
+// scaled by a power of two so that its largest magnitude is in [2^14, 2^15) and split into
+// two fp16 pieces a = h1 + h2 (22 significant bits; what is dropped is below 2^-22 |a| or
+// 2^-39 max|a|), which occupy two MMA columns. fp16 x fp16 products are exact in the fp32
+// accumulator; accumulators are restarted per quantization block and the block sums are
+// combined in ordinary fp32 arithmetic: acc += scale * (D[piece 0] + D[piece 1]). The result
+// differs from a sequential fp32 evaluation by less than the 1e-5 bar of the CUDA-core path.
+//
+// Columns of the 16x8 MMA tile = (token, block-inside-supergroup, piece). A "supergroup" is
+// 128 consecutive k (each of the four lanes of a quad loads 16 bytes = 32 codes of a row).
+// For block_size 32 / 64 the four lanes' codes lie in different quantization blocks; the
+// activation fragment of a lane is zero except in the column of its own block, so every
+// column accumulates exactly one block and the per-block scale can be applied afterwards.
+//
+// Data movement: persistent CTA per SM; a producer warp fills a ring of task slots with 1-D
+// bulk (TMA) copies - 16 weight rows x 16 quantization blocks per task plus that task's
+// scales / zero points from a prepared, task-major side array - completed on mbarriers.
+// Eight consumer warps own whole 16-row tiles (no cross-warp reduction). All waits bounded.
+//
+// Conventions: packed-INT4 nibble order of
+// onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:60-93; "stream B once, split N"
+// partition of onnx_light_cpu/impl/math/gemm_kernel.cc:1219-1258.
+
 #include "nbits_common.cuh"
+#include "nbits_ptx.cuh"
+#include "nbits_tma.cuh"
+
+#include <cuda_fp16.h>
+
+#include <cstdint>
+#include <cstdlib>
 
 namespace mnb {
+namespace {
 
-const char *LaunchGemvMma(const WeightView &, const float *, std::int64_t, OutputView, int *,
-                          cudaStream_t, int) {
-  return nullptr;
+constexpr int kPairs = 8;                 // 16-row tiles in flight per CTA
+constexpr int kWarps = 2 * kPairs;        // consumer warps: two per tile, alternating k slices
+constexpr int kConsumerThreads = kWarps * 32;
+constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kMaxSlots = 32;
+constexpr int kMaxTokens = 4;             // most activation rows handled per CTA pass
+
+struct MmaParams {
+  WeightView w;
+  const float *a;
+  int m_total;
+  OutputView out;
+  int *status;
+  int half_tiles;       // ceil(n / 8)
+  int bpt;              // quantization blocks per task
+  int slices;           // tasks per row tile = ceil(n_blocks / bpt)
+  int slice_b_bytes;    // packed bytes of one row inside a task
+  int sg_per_task;      // 128-k supergroups per task
+  int sg_per_block;     // supergroups per quantization block (block_size >= 128), else 1
+  int rec_bytes;        // bytes of one prepared meta record (bpt blocks x 8 rows)
+  int rec_scale_bytes;  // scale part of a record
+  int slot_bytes;
+  int num_slots;
+  int act_row_bytes;    // bytes between activation piece rows in shared memory
+  int k_pad;            // activation positions per piece row (all tasks, zero beyond K)
+  int tokens_per_pass;  // activation rows per grid.y pass (8 columns / blocks-per-supergroup / 2)
+  std::uint32_t magic;  // 0x64006400, passed at run time so that it stays in a register
+};
+
+__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t mask, std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ std::uint32_t Hsub2(std::uint32_t a, std::uint32_t b) {
+  std::uint32_t d;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ std::uint32_t Hfma2(std::uint32_t a, std::uint32_t b, std::uint32_t c) {
+  std::uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ void MmaF16(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                       std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Eight codes of `w` minus the zero point, as four fp16 pairs (code j, code j+4), j = 0..3.
+// `offs` = (1024 + zp) x2, `offs16` = -(64 + zp) x2, `sixteenth` = (1/16) x2.
+__device__ __forceinline__ void Dequant8(std::uint32_t w, std::uint32_t magic, std::uint32_t offs,
+                                         std::uint32_t offs16, std::uint32_t sixteenth,
+                                         std::uint32_t (&p)[4]) {
+  const std::uint32_t w8 = w >> 8;
+  p[0] = Hsub2(AndOr(w, 0x000f000fu, magic), offs);
+  p[1] = Hfma2(AndOr(w, 0x00f000f0u, magic), sixteenth, offs16);
+  p[2] = Hsub2(AndOr(w8, 0x000f000fu, magic), offs);
+  p[3] = Hfma2(AndOr(w8, 0x00f000f0u, magic), sixteenth, offs16);
+}
+
+// Position (in fp16 elements) of activation k inside a piece row: supergroup-major, then the
+// word index i = (k % 32) / 8, the quad lane t = (k % 128) / 32, then the eight k of a word in
+// the order 0,4,1,5,2,6,3,7 (the order the pair extraction produces).
+__device__ __forceinline__ int ActPosition(int k) {
+  const int sg = k >> 7;
+  const int rem = k & 127;
+  const int t = rem >> 5;
+  const int i = (rem & 31) >> 3;
+  const int j = rem & 7;
+  const int pos = j < 4 ? 2 * j : 2 * (j - 4) + 1;
+  return (sg << 7) + (i << 5) + (t << 3) + pos;
+}
+
+// NB_SG_LOG2: log2 of quantization blocks per 128-k supergroup (block 128+: 0, 64: 1, 32: 2).
+// BIG_BLOCK: a block spans several supergroups (block_size >= 256).
+template <int NB_SG_LOG2, bool BIG_BLOCK>
+__global__ void __launch_bounds__(kThreads, 1)
+    nbits_gemv_mma_kernel(const __grid_constant__ CUtensorMap map_b, const MmaParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  // keep the pointer in the shared address space (no integer round trip) while aligning it
+  unsigned char *smem_raw = smem_dyn + ((128u - (ptx::SmemAddr(smem_dyn) & 127u)) & 127u);
+  // layout: [slots][activation piece rows: 2 per token][per-token 2^-e][amax scratch]
+  //         [pair exchange: 2 x kPairs x 32 lanes x 2][barriers]
+  unsigned char *slots = smem_raw;
+  unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
+  float *inv_scale = reinterpret_cast<float *>(act + 2 * p.tokens_per_pass * p.act_row_bytes);
+  float *scratch = inv_scale + kMaxTokens;          // [kWarps]
+  float2 *pair_buf = reinterpret_cast<float2 *>(scratch + kWarps); // [2][kPairs][32]
+  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + 2 * kPairs * 32);
+  std::uint64_t *empty_bar = full_bar + kMaxSlots;
+  // task index currently assigned to each slot. A slot is consumed by different warps in
+  // successive rounds, and an mbarrier phase parity only tells two neighbouring phases apart,
+  // so a consumer first waits until the producer has assigned ITS task to the slot (which
+  // happens after the previous round was released) and only then waits on the parity.
+  volatile int *slot_task = reinterpret_cast<volatile int *>(empty_bar + kMaxSlots);
+
+  constexpr int kNbSg = 1 << NB_SG_LOG2;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int m_base = blockIdx.y * p.tokens_per_pass;
+  int tokens = p.m_total - m_base;
+  if (tokens > p.tokens_per_pass) {
+    tokens = p.tokens_per_pass;
+  }
+
+  // this CTA's half tiles (8 rows each), split as evenly as the grid allows
+  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * p.half_tiles / gridDim.x);
+  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * p.half_tiles / gridDim.x);
+  const int n_tiles = (h_end - h_begin + 1) >> 1;
+  const std::int64_t row_limit =
+      static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.num_slots; ++s) {
+      ptx::MbarInit(&full_bar[s], 1);
+      ptx::MbarInit(&empty_bar[s], 1);
+      slot_task[s] = -1;
+    }
+    ptx::FenceMbarInit();
+  }
+  __syncthreads();
+
+  if (warp == kWarps) {
+    // ------------------------------ producer ------------------------------
+    // One lane issues, per task, one 2-D tiled TMA load of the weight tile (16 rows x the
+    // slice; rows past the matrix end are zero-filled) and one bulk copy of the task's
+    // scale / zero-point records (two consecutive half tiles of the same slice).
+    if (lane == 0) {
+      ptx::PrefetchTensorMap(&map_b);
+      int task = 0;
+      bool ok = true;
+      const std::uint32_t box_bytes = 16u * static_cast<std::uint32_t>(p.slice_b_bytes);
+      for (int wave0 = 0; wave0 < n_tiles && ok; wave0 += kPairs) {
+        const int wave_tiles = n_tiles - wave0 < kPairs ? n_tiles - wave0 : kPairs;
+        for (int s = 0; s < p.slices && ok; ++s) {
+          for (int wt = 0; wt < wave_tiles; ++wt, ++task) {
+            const int slot = task % p.num_slots;
+            const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
+            if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+              atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+              ok = false;
+              break;
+            }
+            const int h0 = h_begin + 2 * (wave0 + wt);
+            const int valid_halves = h0 + 1 < p.half_tiles ? 2 : 1;
+            unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+            const std::uint32_t meta_bytes = static_cast<std::uint32_t>(valid_halves) * p.rec_bytes;
+            slot_task[slot] = task;
+            ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
+            ptx::TmaLoad2D(dst, &map_b, s * (p.slice_b_bytes / 4), h0 * 8, &full_bar[slot]);
+            ptx::BulkLoad(dst + box_bytes,
+                          p.w.meta + (static_cast<std::int64_t>(s) * p.half_tiles + h0) * p.rec_bytes, meta_bytes,
+                          &full_bar[slot]);
+          }
+        }
+      }
+      // stay until every copy issued has been consumed (bounded), so none lands after exit
+      const int first = task - p.num_slots < 0 ? 0 : task - p.num_slots;
+      for (int i = first; i < task && ok; ++i) {
+        if (!ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
+          break;
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  // Activation staging: per token a power-of-two scale, two fp16 pieces, permuted order.
+  for (int mi = 0; mi < p.tokens_per_pass; ++mi) {
+    const bool live = mi < tokens;
+    const float *src = p.a + static_cast<std::int64_t>(m_base + mi) * p.w.k;
+    float amax = 0.0f;
+    if (live) {
+      for (int k = tid; k < p.w.k; k += kConsumerThreads) {
+        amax = fmaxf(amax, fabsf(__ldg(src + k)));
+      }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+    }
+    if (lane == 0) {
+      scratch[warp] = amax;
+    }
+    asm volatile("bar.sync 9, %0;" ::"n"(kConsumerThreads) : "memory");
+    amax = scratch[0];
+#pragma unroll
+    for (int i = 1; i < kWarps; ++i) {
+      amax = fmaxf(amax, scratch[i]);
+    }
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+      e = 14 - ilogbf(amax);
+      e = e > 100 ? 100 : (e < -100 ? -100 : e);
+    }
+    const float up = scalbnf(1.0f, e);
+    if (tid == 0) {
+      inv_scale[mi] = scalbnf(1.0f, -e);
+    }
+    __half *row_hi = reinterpret_cast<__half *>(act + (2 * mi) * p.act_row_bytes);
+    __half *row_lo = reinterpret_cast<__half *>(act + (2 * mi + 1) * p.act_row_bytes);
+    for (int k = tid; k < p.k_pad; k += kConsumerThreads) {
+      float v = 0.0f;
+      if (live && k < p.w.k) {
+        v = __ldg(src + k) * up;
+      }
+      const __half h1 = __float2half_rn(v);
+      const __half h2 = __float2half_rn(v - __half2float(h1));
+      const int pos = ActPosition(k);
+      row_hi[pos] = h1;
+      row_lo[pos] = h2;
+    }
+    asm volatile("bar.sync 9, %0;" ::"n"(kConsumerThreads) : "memory");
+  }
+
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int pair = warp >> 1;   // which tile of a wave this warp works on
+  const int parity = warp & 1;  // which k slices of that tile
+  // role of this lane's column (g) in the activation fragment
+  const int pc_b = g >> 1;
+  const int piece_b = g & 1;
+  const int m_b = pc_b >> NB_SG_LOG2;
+  const int blk_b = pc_b & (kNbSg - 1);
+  // block-in-supergroup of this lane's own codes: lane t holds k = 32t .. 32t+31
+  const int tb = NB_SG_LOG2 == 2 ? t : (NB_SG_LOG2 == 1 ? t >> 1 : 0);
+  const bool b_active = m_b < tokens && blk_b == tb;
+  const unsigned char *act_lane = act + (2 * (b_active ? m_b : 0) + piece_b) * p.act_row_bytes + t * 16;
+  // role of this lane's accumulator columns (2t, 2t+1)
+  const int m_d = t >> NB_SG_LOG2;
+  const int blk_d = t & (kNbSg - 1);
+
+  const std::uint32_t magic = p.magic;
+  const std::uint32_t sixteenth = 0x2c002c00u;  // fp16 1/16 twice
+  const std::uint32_t plus960 = 0x63806380u;    // fp16 960 twice
+  const bool has_zp = p.w.zp != nullptr;
+  const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
+  const int box_bytes = 16 * p.slice_b_bytes;
+
+  int tile_count = 0;
+  bool dead = false; // a bounded wait gave up: skip the math but keep the pair barrier protocol
+  for (int tile = pair; tile < n_tiles; tile += kPairs, ++tile_count) {
+    const int wave0 = tile - pair;
+    const int wave_tiles = n_tiles - wave0 < kPairs ? n_tiles - wave0 : kPairs;
+    const int h0 = h_begin + 2 * tile;
+    const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
+    float acc0 = 0.0f, acc1 = 0.0f; // rows g and g + 8, accumulator column pair t
+    float da[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float db[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+
+    for (int s = parity; s < p.slices && !dead; s += 2) {
+      const int task = wave0 * p.slices + s * wave_tiles + pair;
+      const int slot = task % p.num_slots;
+      const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
+      bool assigned = false;
+      for (std::uint32_t spin = 0; spin < ptx::kSpinLimit; ++spin) {
+        if (slot_task[slot] == task) {
+          assigned = true;
+          break;
+        }
+        __nanosleep(32);
+      }
+      if (!assigned || !ptx::MbarWait(&full_bar[slot], round & 1u)) {
+        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        dead = true;
+        break;
+      }
+      const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
+      const unsigned char *row_lo = sb + g * p.slice_b_bytes + t * 16;
+      const unsigned char *row_hi = row_lo + 8 * p.slice_b_bytes;
+      const unsigned char *meta0 = sb + box_bytes;       // rows 0..7: [block][row]
+      const unsigned char *meta1 = meta0 + p.rec_bytes;  // rows 8..15
+      const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * 256;
+
+#pragma unroll 2
+      for (int sg = 0; sg < p.sg_per_task; ++sg) {
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + sg * 64);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + sg * 64);
+        // block (inside the task) of this lane's codes, and of its accumulator columns
+        const int blk_codes = BIG_BLOCK ? sg / p.sg_per_block : (sg << NB_SG_LOG2) + tb;
+        const int blk_acc = BIG_BLOCK ? blk_codes : (sg << NB_SG_LOG2) + blk_d;
+        std::uint32_t offs0 = default_offs, offs1 = default_offs;
+        if (has_zp) {
+          const std::uint32_t z0 = meta0[p.rec_scale_bytes + blk_codes * 8 + g];
+          const std::uint32_t z1 = meta1[p.rec_scale_bytes + blk_codes * 8 + g];
+          offs0 = __byte_perm(z0, 0x64646464u, 0x4040); // (1024 + zp) twice
+          offs1 = __byte_perm(z1, 0x64646464u, 0x4040);
+        }
+        const std::uint32_t offs0_16 = Hsub2(plus960, offs0); // -(64 + zp)
+        const std::uint32_t offs1_16 = Hsub2(plus960, offs1);
+        uint4 bf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          bf[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (b_active) {
+            bf[i] = *reinterpret_cast<const uint4 *>(act_task + sg * 256 + i * 64);
+          }
+        }
+        const std::uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
+        const std::uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          std::uint32_t pa[4], pb[4];
+          Dequant8(w0[i], magic, offs0, offs0_16, sixteenth, pa);
+          Dequant8(w1[i], magic, offs1, offs1_16, sixteenth, pb);
+          // two accumulator sets halve the dependent chain of MMAs
+          MmaF16(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
+          MmaF16(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
+        }
+        const bool block_done = BIG_BLOCK ? ((sg + 1) % p.sg_per_block) == 0 : true;
+        if (block_done) {
+          const float s0 = reinterpret_cast<const float *>(meta0)[blk_acc * 8 + g];
+          const float s1 = reinterpret_cast<const float *>(meta1)[blk_acc * 8 + g];
+          acc0 = fmaf(s0, (da[0] + da[1]) + (db[0] + db[1]), acc0);
+          acc1 = fmaf(s1, (da[2] + da[3]) + (db[2] + db[3]), acc1);
+          da[0] = da[1] = da[2] = da[3] = 0.0f;
+          db[0] = db[1] = db[2] = db[3] = 0.0f;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        ptx::MbarArrive(&empty_bar[slot]);
+      }
+    }
+    // blocks of one supergroup sit in neighbouring lanes of the quad: add them up
+    if (NB_SG_LOG2 >= 1) {
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 1);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 1);
+    }
+    if (NB_SG_LOG2 >= 2) {
+      acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
+      acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
+    }
+    // the odd warp of the pair hands its half of K to the even warp
+    float2 *exchange = pair_buf + ((tile_count & 1) * kPairs + pair) * 32 + lane;
+    if (parity == 1) {
+      *exchange = make_float2(acc0, acc1);
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    if (parity == 0) {
+      const float2 other = *exchange;
+      acc0 += other.x;
+      acc1 += other.y;
+      if (blk_d == 0 && m_d < tokens) {
+        const float undo = inv_scale[m_d];
+        const std::int64_t m = m_base + m_d;
+        const std::int64_t r_lo = row0 + g;
+        const std::int64_t r_hi = row0 + g + 8;
+        if (r_lo < row_limit) {
+          const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_lo) : 0.0f;
+          p.out.y[m * p.out.ld + p.out.col_offset + r_lo] = fmaf(acc0, undo, bias);
+        }
+        if (r_hi < row_limit) {
+          const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_hi) : 0.0f;
+          p.out.y[m * p.out.ld + p.out.col_offset + r_hi] = fmaf(acc1, undo, bias);
+        }
+      }
+    }
+  }
+}
+
+// ---- prepared side array -----------------------------------------------------------------
+// meta[(slice * half_tiles + half_tile)] = { float scale[bpt][8 rows] ; uint8 zp[bpt][8 rows] }
+// (the zero-point part only when the node has zero points). Rows beyond N and blocks beyond
+// n_blocks get scale 0.
+__global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightView w, int bpt, int half_tiles,
+                                                                 int rec_bytes, int rec_scale_bytes,
+                                                                 unsigned char *meta, std::int64_t records) {
+  const std::int64_t per_record = 8 * bpt;
+  const std::int64_t total = records * per_record;
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
+    const std::int64_t record = i / per_record;
+    const int within = static_cast<int>(i - record * per_record);
+    const int r = within / bpt;
+    const int b = within - r * bpt;
+    const int slice = static_cast<int>(record / half_tiles);
+    const std::int64_t half_tile = record - static_cast<std::int64_t>(slice) * half_tiles;
+    const std::int64_t row = half_tile * 8 + r;
+    const int block = slice * bpt + b;
+    float scale = 0.0f;
+    int zp = 0;
+    if (row < w.n && block < w.n_blocks) {
+      scale = w.scales[row * w.n_blocks + block];
+      zp = ZeroPointOf(w, row, block);
+    }
+    unsigned char *rec = meta + record * rec_bytes;
+    reinterpret_cast<float *>(rec)[b * 8 + r] = scale;
+    if (w.zp != nullptr) {
+      rec[rec_scale_bytes + b * 8 + r] = static_cast<unsigned char>(zp);
+    }
+  }
+}
+
+int Log2Of(int v) {
+  int l = 0;
+  while ((1 << l) < v) {
+    ++l;
+  }
+  return l;
+}
+
+} // namespace
+
+MetaGeometry MetaGeometryOf(const WeightView &w) {
+  MetaGeometry geo{};
+  if (w.bits != 4 || w.block_size < 32 || w.block_size > 1024 || (w.row_bytes % 16) != 0 ||
+      GetEncodeTiled() == nullptr) {
+    return geo; // unsupported: bytes == 0
+  }
+  int bpt = 2048 / w.block_size;
+  if (bpt > 16) {
+    bpt = 16;
+  }
+  const char *override_bpt = std::getenv("MNB_GEMV_BLOCKS_PER_TASK");
+  if (override_bpt != nullptr) {
+    const int v = std::atoi(override_bpt);
+    if (v >= 2 && v <= 16 && (v & (v - 1)) == 0 && v * w.block_size >= 128 && v * w.block_size <= 2048) {
+      bpt = v;
+    }
+  }
+  geo.bpt = bpt;
+  geo.slices = (w.n_blocks + bpt - 1) / bpt;
+  geo.rec_scale_bytes = 8 * bpt * 4;
+  geo.rec_bytes = geo.rec_scale_bytes + (w.zp != nullptr ? 8 * bpt : 0);
+  geo.half_tiles = static_cast<int>((w.n + 7) / 8);
+  geo.bytes = static_cast<std::size_t>(geo.half_tiles) * geo.slices * geo.rec_bytes;
+  return geo;
+}
+
+bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t stream) {
+  const MetaGeometry geo = MetaGeometryOf(w);
+  if (geo.bytes == 0 || meta == nullptr) {
+    return false;
+  }
+  const std::int64_t records = static_cast<std::int64_t>(geo.half_tiles) * geo.slices;
+  std::int64_t blocks = (records * 8 * geo.bpt + 255) / 256;
+  if (blocks > 148 * 8) {
+    blocks = 148 * 8;
+  }
+  nbits_prepare_meta_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      w, geo.bpt, geo.half_tiles, geo.rec_bytes, geo.rec_scale_bytes, meta, records);
+  if (cudaGetLastError() != cudaSuccess) {
+    return false;
+  }
+  CountLaunch();
+  return true;
+}
+
+const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                          int *status_word, cudaStream_t stream, int sm_count) {
+  const MetaGeometry geo = MetaGeometryOf(w);
+  if (geo.bytes == 0 || w.meta == nullptr || m < 1 || (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0) {
+    return nullptr;
+  }
+  MmaParams p{};
+  p.w = w;
+  p.a = a;
+  p.m_total = static_cast<int>(m);
+  p.out = out;
+  p.status = status_word;
+  p.magic = 0x64006400u;
+  p.half_tiles = geo.half_tiles;
+  p.bpt = geo.bpt;
+  p.slices = geo.slices;
+  p.rec_bytes = geo.rec_bytes;
+  p.rec_scale_bytes = geo.rec_scale_bytes;
+  p.slice_b_bytes = geo.bpt * w.block_size / 2;
+  p.sg_per_task = geo.bpt * w.block_size / 128;
+  int nb_sg_log2 = 0;
+  if (w.block_size >= 128) {
+    p.sg_per_block = w.block_size / 128;
+  } else {
+    p.sg_per_block = 1;
+    nb_sg_log2 = Log2Of(128 / w.block_size);
+  }
+  // tokens per pass: columns = tokens * blocks-per-supergroup * 2 pieces <= 8
+  int tokens_per_pass = kMaxTokens >> nb_sg_log2;
+  if (m > 16 || tokens_per_pass < 1) {
+    return nullptr;
+  }
+  if (tokens_per_pass > m) {
+    tokens_per_pass = static_cast<int>(m);
+  }
+  p.tokens_per_pass = tokens_per_pass;
+  p.k_pad = p.slices * p.sg_per_task * 128;
+  if (p.k_pad < w.k) {
+    return nullptr;
+  }
+  p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
+  p.slot_bytes = (16 * p.slice_b_bytes + 2 * p.rec_bytes + 127) & ~127;
+  const size_t fixed = static_cast<size_t>(2 * tokens_per_pass) * p.act_row_bytes +
+                       (kMaxTokens + kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
+                       2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
+  const size_t limit = 225 * 1024;
+  if (fixed + 2 * static_cast<size_t>(p.slot_bytes) > limit) {
+    return nullptr;
+  }
+  int slots = static_cast<int>((limit - fixed) / p.slot_bytes);
+  if (slots > kMaxSlots) {
+    slots = kMaxSlots;
+  }
+  p.num_slots = slots;
+  const size_t smem = static_cast<size_t>(slots) * p.slot_bytes + fixed + 128; // + alignment slack
+
+  int ctas = sm_count > 0 ? sm_count : 148;
+  const int tiles = (geo.half_tiles + 1) / 2;
+  if (ctas > tiles) {
+    ctas = tiles;
+  }
+  CUtensorMap map_b;
+  if (!EncodeMap2D(&map_b, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, w.b, static_cast<std::uint64_t>(w.row_bytes / 4),
+                   static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.row_bytes),
+                   static_cast<std::uint32_t>(p.slice_b_bytes / 4), 16, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    return nullptr;
+  }
+  dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>((m + tokens_per_pass - 1) / tokens_per_pass), 1);
+  cudaError_t err = cudaErrorInvalidValue;
+#define MNB_MMA_CASE(LOG2_, BIG_)                                                                \
+  if (nb_sg_log2 == LOG2_ && (p.sg_per_block > 1) == BIG_) {                                     \
+    auto kernel = nbits_gemv_mma_kernel<LOG2_, BIG_>;                                            \
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                               static_cast<int>(smem));                                          \
+    if (err == cudaSuccess) {                                                                    \
+      kernel<<<grid, kThreads, smem, stream>>>(map_b, p);                                        \
+      err = cudaGetLastError();                                                                  \
+    }                                                                                            \
+  }
+  MNB_MMA_CASE(0, false)
+  MNB_MMA_CASE(0, true)
+  MNB_MMA_CASE(1, false)
+  MNB_MMA_CASE(2, false)
+#undef MNB_MMA_CASE
+  if (err != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_gemv_mma_kernel";
 }
 
 } // namespace mnb

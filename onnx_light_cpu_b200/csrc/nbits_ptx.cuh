@@ -10,7 +10,7 @@
 namespace mnb {
 namespace ptx {
 
-constexpr std::uint32_t kSpinLimit = 1u << 21; // polls; each failed poll backs off ~64 ns
+constexpr std::uint32_t kSpinLimit = 1u << 18; // polls; each failed poll backs off ~64 ns (tens of ms in all)
 
 __device__ __forceinline__ std::uint32_t SmemAddr(const void *ptr) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(ptr));

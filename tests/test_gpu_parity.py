@@ -102,6 +102,50 @@ def test_decode_edge_cases(cuda_device, m, k, n, bits, bs, zp, bias):
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32, kernel
 
 
+MMA_CASES = [
+    # m, k, n, block, zp, bias
+    (1, 4096, 4096, 32, False, False),     # cfg1 geometry
+    (1, 4096, 1024, 128, True, True),      # cfg2 geometry, reduced N
+    (4, 4096, 1000, 128, True, True),      # four tokens in one pass, N not a multiple of 8
+    (16, 4096, 200, 128, True, False),     # four passes
+    (2, 4096, 333, 64, True, True),        # two blocks per supergroup
+    (3, 2048, 77, 64, False, True),        # two passes of two tokens
+    (1, 14336, 96, 32, True, False),       # wide K, small blocks
+    (2, 4096, 40, 32, True, True),         # one token per pass
+    (1, 4096, 130, 256, True, True),       # block spans two supergroups
+    (4, 8192, 64, 1024, False, False),
+    (1, 4000, 50, 32, True, True),         # K not a multiple of 128: partial last supergroup
+    (1, 4096 + 64, 24, 128, True, False),  # partial last block
+    (1, 4096, 7, 128, True, True),         # fewer rows than one half tile
+    (1, 4096, 14336, 128, True, True),     # cfg2 at full size: many tiles per CTA, slot ring wraps
+    (2, 4096, 16032, 32, True, False),     # one lm-head shard: long ring, two passes
+]
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", MMA_CASES)
+def test_decode_mma_path(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("mma", m, k, n, 4, bs, seed=m * 11 + k + n + bs, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_MMA)
+    assert kernel == "nbits_gemv_mma_kernel"
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+
+
+def test_decode_mma_path_wide_dynamic_range(cuda_device):
+    """Activations spanning many orders of magnitude, large and tiny rows: the per-row power-of-two
+    scaling keeps the two-piece fp16 split accurate."""
+    case = syn.make_case("mma_range", 4, 4096, 256, 4, 128, seed=99, bias=True)
+    rng = np.random.default_rng(1)
+    case.a[0] *= 1e4
+    case.a[1] *= 1e-6
+    case.a[2] *= np.exp(rng.uniform(-8, 8, size=case.k)).astype(np.float32)
+    case.a[3] = 0.0
+    y, _ = run_device(case, path=_capi.PATH_GEMV_MMA)
+    ref = oracle_f64(case)
+    for row in range(3):
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    assert np.array_equal(y[3], case.bias)
+
+
 def test_generic_kernel_matches_stream_kernel(cuda_device):
     """Two independent CUDA implementations of the decode path agree."""
     import torch
