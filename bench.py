@@ -42,10 +42,9 @@ PREFILL = dict(m=2048, k=4096, n=4096, bits=4, block_size=64)
 LMHEAD = dict(k=4096, n=128256, bits=4, block_size=32)
 L2_BYTES = 126 * 1024 * 1024
 
-# DRAM bytes per launch of nbits_gemv_stream_kernel<4,1,1> on the decode workload, from the ncu
-# capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until
-# a capture exists.
-NCU_DECODE_TRAFFIC_BYTES = None
+# DRAM bytes per launch of nbits_gemv_mma_kernel on the decode workload, from the ncu capture
+# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
+NCU_DECODE_TRAFFIC_BYTES = 31_775_488  # profiles/decode_mma_cfg2.md
 
 
 def measured_peaks() -> tuple[dict, str]:

@@ -206,7 +206,14 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
   const char *name = nullptr;
   switch (chosen) {
   case MNB_PATH_GEMV: {
-    if (m <= 16) {
+    // decode default: the tensor-core kernel with the exact two-piece split, as long as the
+    // tokens fit in at most four passes over the weights (4 / 2 / 1 tokens per pass for
+    // block_size >= 128 / 64 / 32)
+    const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
+    if (m <= 16 && path == MNB_PATH_AUTO && m <= 4 * per_pass) {
+      name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
+    if (name == nullptr && m <= 16) {
       name = mnb::LaunchGemvStream(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
     if (name == nullptr) {

@@ -41,6 +41,20 @@
 namespace mnb {
 namespace {
 
+#ifdef MNB_TIMELINE
+// Debug builds only: per-CTA event times (globaltimer ns) for offline inspection.
+__device__ unsigned long long g_timeline[148 * 64];
+__device__ __forceinline__ unsigned long long NowNs() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define MNB_MARK(slot_) \
+  do { if (blockIdx.y == 0 && (slot_) < 64) g_timeline[blockIdx.x * 64 + (slot_)] = NowNs(); } while (0)
+#else
+#define MNB_MARK(slot_) do { } while (0)
+#endif
+
 constexpr int kPairs = 8;                 // 16-row tiles in flight per CTA
 constexpr int kWarps = 2 * kPairs;        // consumer warps: two per tile, alternating k slices
 constexpr int kConsumerThreads = kWarps * 32;
@@ -133,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   //         [pair exchange: 2 x kPairs x 32 lanes x 2][barriers]
   unsigned char *slots = smem_raw;
   unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
-  float *inv_scale = reinterpret_cast<float *>(act + 2 * p.tokens_per_pass * p.act_row_bytes);
+  float *inv_scale = reinterpret_cast<float *>(act + (2 * p.tokens_per_pass + 1) * p.act_row_bytes);
   float *scratch = inv_scale + kMaxTokens;          // [kWarps]
   float2 *pair_buf = reinterpret_cast<float2 *>(scratch + kWarps); // [2][kPairs][32]
   std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + 2 * kPairs * 32);
@@ -162,20 +176,25 @@ __global__ void __launch_bounds__(kThreads, 1)
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
   if (tid == 0) {
-    for (int s = 0; s < p.num_slots; ++s) {
-      ptx::MbarInit(&full_bar[s], 1);
-      ptx::MbarInit(&empty_bar[s], 1);
-      slot_task[s] = -1;
-    }
-    ptx::FenceMbarInit();
+    MNB_MARK(0);
   }
-  __syncthreads();
 
   if (warp == kWarps) {
     // ------------------------------ producer ------------------------------
     // One lane issues, per task, one 2-D tiled TMA load of the weight tile (16 rows x the
     // slice; rows past the matrix end are zero-filled) and one bulk copy of the task's
     // scale / zero-point records (two consecutive half tiles of the same slice).
+    if (lane == 0) {
+      for (int s = 0; s < p.num_slots; ++s) {
+        ptx::MbarInit(&full_bar[s], 1);
+        ptx::MbarInit(&empty_bar[s], 1);
+        slot_task[s] = -1;
+      }
+      ptx::FenceMbarInit();
+    }
+    __syncwarp();
+    // the consumers join this barrier after staging the activations; the producer does not wait
+    asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_b);
       int task = 0;
@@ -197,6 +216,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
             const std::uint32_t meta_bytes = static_cast<std::uint32_t>(valid_halves) * p.rec_bytes;
             slot_task[slot] = task;
+            MNB_MARK(32 + task);
             ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
             ptx::TmaLoad2D(dst, &map_b, s * (p.slice_b_bytes / 4), h0 * 8, &full_bar[slot]);
             ptx::BulkLoad(dst + box_bytes,
@@ -218,11 +238,49 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // ------------------------------ consumers ------------------------------
   // Activation staging: per token a power-of-two scale, two fp16 pieces, permuted order.
+  // A thread owns whole 8-k words (one 16-byte store per piece); up to four words per thread
+  // stay in registers between the max reduction and the split, so A is read once.
+  const int words_total = p.k_pad >> 3;
+  unsigned char *zero_row = act + 2 * p.tokens_per_pass * p.act_row_bytes;
+  for (int i = tid; i < (p.act_row_bytes >> 4); i += kConsumerThreads) {
+    reinterpret_cast<uint4 *>(zero_row)[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
   for (int mi = 0; mi < p.tokens_per_pass; ++mi) {
     const bool live = mi < tokens;
     const float *src = p.a + static_cast<std::int64_t>(m_base + mi) * p.w.k;
+    const bool in_registers = words_total <= 4 * kConsumerThreads;
+    const bool vector_ok = (reinterpret_cast<std::uintptr_t>(src) & 15u) == 0;
+    float v[4][8];
     float amax = 0.0f;
-    if (live) {
+    if (in_registers) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k0 = (tid + j * kConsumerThreads) << 3;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[j][e] = 0.0f;
+        }
+        if (live && k0 < p.w.k) {
+          if (vector_ok && k0 + 8 <= p.w.k) {
+            const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + k0));
+            const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + k0 + 4));
+            v[j][0] = lo.x, v[j][1] = lo.y, v[j][2] = lo.z, v[j][3] = lo.w;
+            v[j][4] = hi.x, v[j][5] = hi.y, v[j][6] = hi.z, v[j][7] = hi.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              if (k0 + e < p.w.k) {
+                v[j][e] = __ldg(src + k0 + e);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          amax = fmaxf(amax, fabsf(v[j][e]));
+        }
+      }
+    } else if (live) {
       for (int k = tid; k < p.w.k; k += kConsumerThreads) {
         amax = fmaxf(amax, fabsf(__ldg(src + k)));
       }
@@ -240,29 +298,64 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 1; i < kWarps; ++i) {
       amax = fmaxf(amax, scratch[i]);
     }
-    int e = 0;
+    int e2 = 0;
     if (amax > 0.0f && amax < 3.0e38f) {
-      e = 14 - ilogbf(amax);
-      e = e > 100 ? 100 : (e < -100 ? -100 : e);
+      e2 = 14 - ilogbf(amax);
+      e2 = e2 > 100 ? 100 : (e2 < -100 ? -100 : e2);
     }
-    const float up = scalbnf(1.0f, e);
+    const float up = scalbnf(1.0f, e2);
     if (tid == 0) {
-      inv_scale[mi] = scalbnf(1.0f, -e);
+      inv_scale[mi] = scalbnf(1.0f, -e2);
     }
-    __half *row_hi = reinterpret_cast<__half *>(act + (2 * mi) * p.act_row_bytes);
-    __half *row_lo = reinterpret_cast<__half *>(act + (2 * mi + 1) * p.act_row_bytes);
-    for (int k = tid; k < p.k_pad; k += kConsumerThreads) {
-      float v = 0.0f;
-      if (live && k < p.w.k) {
-        v = __ldg(src + k) * up;
+    unsigned char *row_hi = act + (2 * mi) * p.act_row_bytes;
+    unsigned char *row_lo = act + (2 * mi + 1) * p.act_row_bytes;
+    // splits eight scaled activations into two fp16 pieces and stores both 16-byte words
+    auto store_word = [&](int k0, const float (&x)[8]) {
+      std::uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { // stored order inside a word: k = 0,4,1,5,2,6,3,7
+        const __half a_hi = __float2half_rn(x[q]);
+        const __half b_hi = __float2half_rn(x[q + 4]);
+        const __half a_lo = __float2half_rn(x[q] - __half2float(a_hi));
+        const __half b_lo = __float2half_rn(x[q + 4] - __half2float(b_hi));
+        hi[q] = static_cast<std::uint32_t>(__half_as_ushort(a_hi)) |
+                (static_cast<std::uint32_t>(__half_as_ushort(b_hi)) << 16);
+        lo[q] = static_cast<std::uint32_t>(__half_as_ushort(a_lo)) |
+                (static_cast<std::uint32_t>(__half_as_ushort(b_lo)) << 16);
       }
-      const __half h1 = __float2half_rn(v);
-      const __half h2 = __float2half_rn(v - __half2float(h1));
-      const int pos = ActPosition(k);
-      row_hi[pos] = h1;
-      row_lo[pos] = h2;
+      const int byte = ActPosition(k0) * 2;
+      *reinterpret_cast<uint4 *>(row_hi + byte) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4 *>(row_lo + byte) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    };
+    if (in_registers) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int word = tid + j * kConsumerThreads;
+        if (word < words_total) {
+          float x[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            x[e] = v[j][e] * up;
+          }
+          store_word(word << 3, x);
+        }
+      }
+    } else {
+      for (int word = tid; word < words_total; word += kConsumerThreads) {
+        const int k0 = word << 3;
+        float x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          x[e] = (live && k0 + e < p.w.k) ? __ldg(src + k0 + e) * up : 0.0f;
+        }
+        store_word(k0, x);
+      }
     }
-    asm volatile("bar.sync 9, %0;" ::"n"(kConsumerThreads) : "memory");
+  }
+  // activations staged and (through the producer's arrival) barriers initialised
+  asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
+  if (tid == 0) {
+    MNB_MARK(1);
   }
 
   const int g = lane >> 2;
@@ -277,7 +370,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // block-in-supergroup of this lane's own codes: lane t holds k = 32t .. 32t+31
   const int tb = NB_SG_LOG2 == 2 ? t : (NB_SG_LOG2 == 1 ? t >> 1 : 0);
   const bool b_active = m_b < tokens && blk_b == tb;
-  const unsigned char *act_lane = act + (2 * (b_active ? m_b : 0) + piece_b) * p.act_row_bytes + t * 16;
+  // lanes whose column takes no part read a row of zeros, so the loads need no predicate
+  const unsigned char *act_lane =
+      (b_active ? act + (2 * m_b + piece_b) * p.act_row_bytes : zero_row) + t * 16;
   // role of this lane's accumulator columns (2t, 2t+1)
   const int m_d = t >> NB_SG_LOG2;
   const int blk_d = t & (kNbSg - 1);
@@ -288,6 +383,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const bool has_zp = p.w.zp != nullptr;
   const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
   const int box_bytes = 16 * p.slice_b_bytes;
+  // per-lane offsets inside a meta record: scales [block][8 rows], zero points [block][8 rows]
+  const int scale_lane = ((BIG_BLOCK ? 0 : blk_d) * 8 + g) * 4;
+  const int zp_lane = p.rec_scale_bytes + (BIG_BLOCK ? 0 : tb) * 8 + g;
+  constexpr int kMetaStride = BIG_BLOCK ? 0 : kNbSg * 8; // record entries per supergroup
 
   int tile_count = 0;
   bool dead = false; // a bounded wait gave up: skip the math but keep the pair barrier protocol
@@ -304,74 +403,77 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int task = wave0 * p.slices + s * wave_tiles + pair;
       const int slot = task % p.num_slots;
       const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
-      bool assigned = false;
-      for (std::uint32_t spin = 0; spin < ptx::kSpinLimit; ++spin) {
-        if (slot_task[slot] == task) {
-          assigned = true;
-          break;
+      // first use of a slot: its barrier is still in phase 0, no tag needed
+      bool assigned = round == 0;
+      for (std::uint32_t spin = 0; !assigned && spin < ptx::kSpinLimit; ++spin) {
+        assigned = slot_task[slot] == task;
+        if (!assigned) {
+          __nanosleep(256);
         }
-        __nanosleep(32);
       }
       if (!assigned || !ptx::MbarWait(&full_bar[slot], round & 1u)) {
         atomicExch(p.status, kDeviceTimeoutFullBarrier);
         dead = true;
         break;
       }
+      if (lane == 0) {
+        MNB_MARK(2 + task);
+      }
       const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
       const unsigned char *row_lo = sb + g * p.slice_b_bytes + t * 16;
       const unsigned char *row_hi = row_lo + 8 * p.slice_b_bytes;
-      const unsigned char *meta0 = sb + box_bytes;       // rows 0..7: [block][row]
+      const unsigned char *meta0 = sb + box_bytes;       // rows 0..7
       const unsigned char *meta1 = meta0 + p.rec_bytes;  // rows 8..15
       const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * 256;
 
-#pragma unroll 2
-      for (int sg = 0; sg < p.sg_per_task; ++sg) {
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + sg * 64);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + sg * 64);
-        // block (inside the task) of this lane's codes, and of its accumulator columns
-        const int blk_codes = BIG_BLOCK ? sg / p.sg_per_block : (sg << NB_SG_LOG2) + tb;
-        const int blk_acc = BIG_BLOCK ? blk_codes : (sg << NB_SG_LOG2) + blk_d;
-        std::uint32_t offs0 = default_offs, offs1 = default_offs;
-        if (has_zp) {
-          const std::uint32_t z0 = meta0[p.rec_scale_bytes + blk_codes * 8 + g];
-          const std::uint32_t z1 = meta1[p.rec_scale_bytes + blk_codes * 8 + g];
-          offs0 = __byte_perm(z0, 0x64646464u, 0x4040); // (1024 + zp) twice
-          offs1 = __byte_perm(z1, 0x64646464u, 0x4040);
-        }
-        const std::uint32_t offs0_16 = Hsub2(plus960, offs0); // -(64 + zp)
-        const std::uint32_t offs1_16 = Hsub2(plus960, offs1);
-        uint4 bf[4];
+      for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += 4) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          bf[i] = make_uint4(0u, 0u, 0u, 0u);
-          if (b_active) {
-            bf[i] = *reinterpret_cast<const uint4 *>(act_task + sg * 256 + i * 64);
+        for (int u = 0; u < 4; ++u) {
+          const int sg = sg0 + u;
+          const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + sg0 * 64 + u * 64);
+          const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + sg0 * 64 + u * 64);
+          // entry (inside the record) of the block of this lane's codes / accumulator columns
+          const int entry = BIG_BLOCK ? (sg / p.sg_per_block) * 8 : sg0 * kMetaStride + u * kMetaStride;
+          std::uint32_t offs0 = default_offs, offs1 = default_offs;
+          if (has_zp) {
+            const std::uint32_t z0 = meta0[zp_lane + entry];
+            const std::uint32_t z1 = meta1[zp_lane + entry];
+            offs0 = __byte_perm(z0, 0x64646464u, 0x4040); // (1024 + zp) twice
+            offs1 = __byte_perm(z1, 0x64646464u, 0x4040);
           }
-        }
-        const std::uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
-        const std::uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+          const std::uint32_t offs0_16 = Hsub2(plus960, offs0); // -(64 + zp)
+          const std::uint32_t offs1_16 = Hsub2(plus960, offs1);
+          uint4 bf[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          std::uint32_t pa[4], pb[4];
-          Dequant8(w0[i], magic, offs0, offs0_16, sixteenth, pa);
-          Dequant8(w1[i], magic, offs1, offs1_16, sixteenth, pb);
-          // two accumulator sets halve the dependent chain of MMAs
-          MmaF16(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
-          MmaF16(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
-        }
-        const bool block_done = BIG_BLOCK ? ((sg + 1) % p.sg_per_block) == 0 : true;
-        if (block_done) {
-          const float s0 = reinterpret_cast<const float *>(meta0)[blk_acc * 8 + g];
-          const float s1 = reinterpret_cast<const float *>(meta1)[blk_acc * 8 + g];
-          acc0 = fmaf(s0, (da[0] + da[1]) + (db[0] + db[1]), acc0);
-          acc1 = fmaf(s1, (da[2] + da[3]) + (db[2] + db[3]), acc1);
-          da[0] = da[1] = da[2] = da[3] = 0.0f;
-          db[0] = db[1] = db[2] = db[3] = 0.0f;
+          for (int i = 0; i < 4; ++i) {
+            bf[i] = *reinterpret_cast<const uint4 *>(act_task + sg0 * 256 + u * 256 + i * 64);
+          }
+          const std::uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
+          const std::uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            std::uint32_t pa[4], pb[4];
+            Dequant8(w0[i], magic, offs0, offs0_16, sixteenth, pa);
+            Dequant8(w1[i], magic, offs1, offs1_16, sixteenth, pb);
+            // two accumulator sets halve the dependent chain of MMAs
+            MmaF16(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
+            MmaF16(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
+          }
+          const bool block_done = BIG_BLOCK ? ((sg + 1) % p.sg_per_block) == 0 : true;
+          if (block_done) {
+            const float s0 = *reinterpret_cast<const float *>(meta0 + scale_lane + entry * 4);
+            const float s1 = *reinterpret_cast<const float *>(meta1 + scale_lane + entry * 4);
+            acc0 = fmaf(s0, (da[0] + da[1]) + (db[0] + db[1]), acc0);
+            acc1 = fmaf(s1, (da[2] + da[3]) + (db[2] + db[3]), acc1);
+            da[0] = da[1] = da[2] = da[3] = 0.0f;
+            db[0] = db[1] = db[2] = db[3] = 0.0f;
+          }
         }
       }
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
+        MNB_MARK(17 + task);
       }
     }
     // blocks of one supergroup sit in neighbouring lanes of the quad: add them up
@@ -453,6 +555,12 @@ int Log2Of(int v) {
 }
 
 } // namespace
+
+#ifdef MNB_TIMELINE
+extern "C" int mnb_debug_copy_timeline(unsigned long long *host, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline, sizeof(unsigned long long) * count));
+}
+#endif
 
 MetaGeometry MetaGeometryOf(const WeightView &w) {
   MetaGeometry geo{};
@@ -536,12 +644,12 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   }
   p.tokens_per_pass = tokens_per_pass;
   p.k_pad = p.slices * p.sg_per_task * 128;
-  if (p.k_pad < w.k) {
+  if (p.k_pad < w.k || (p.sg_per_task % 4) != 0) {
     return nullptr;
   }
   p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
   p.slot_bytes = (16 * p.slice_b_bytes + 2 * p.rec_bytes + 127) & ~127;
-  const size_t fixed = static_cast<size_t>(2 * tokens_per_pass) * p.act_row_bytes +
+  const size_t fixed = static_cast<size_t>(2 * tokens_per_pass + 1) * p.act_row_bytes +
                        (kMaxTokens + kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
                        2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
   const size_t limit = 225 * 1024;

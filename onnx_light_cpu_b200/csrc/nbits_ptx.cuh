@@ -58,8 +58,8 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t *bar, std::uint32_t parit
     if (MbarTryWait(bar, parity)) {
       return true;
     }
-    if (spin > 64) {
-      __nanosleep(64);
+    if (spin > 8) {
+      __nanosleep(128); // try_wait already suspends for a while; keep pollers off the issue ports
     }
   }
   return false;

@@ -64,17 +64,24 @@ def test_dequant_integers_bit_exact(cuda_device, bits, bs, k, n, zp):
 def test_config1_single_node(cuda_device):
     case = syn.config1()
     y, kernel = run_device(case)
-    assert kernel.startswith("nbits_gemv_stream_kernel<4,1,"), kernel
+    assert kernel == "nbits_gemv_mma_kernel", kernel
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, None, None, case.n, case.k, 4, 32)) <= TOL_FP32
+    y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
+    assert kernel2.startswith("nbits_gemv_stream_kernel<4,1,"), kernel2
+    assert rel_err(y2, oracle_f64(case)) <= TOL_FP32
 
 
 @pytest.mark.parametrize("m", [1, 4, 16])
 def test_config2_decode_sweep(cuda_device, m):
     case = syn.config2(m)
     y, kernel = run_device(case)
-    assert kernel.startswith("nbits_gemv_stream_kernel"), kernel
-    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    assert kernel == "nbits_gemv_mma_kernel", kernel
+    ref = oracle_f64(case)
+    assert rel_err(y, ref) <= TOL_FP32
+    y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
+    assert kernel2.startswith("nbits_gemv_stream_kernel"), kernel2
+    assert rel_err(y2, ref) <= TOL_FP32
 
 
 DECODE_EDGES = [
@@ -95,10 +102,11 @@ DECODE_EDGES = [
 ]
 
 
+@pytest.mark.parametrize("path", [_capi.PATH_AUTO, _capi.PATH_GEMV])
 @pytest.mark.parametrize("m,k,n,bits,bs,zp,bias", DECODE_EDGES)
-def test_decode_edge_cases(cuda_device, m, k, n, bits, bs, zp, bias):
+def test_decode_edge_cases(cuda_device, m, k, n, bits, bs, zp, bias, path):
     case = syn.make_case("edge", m, k, n, bits, bs, seed=m * 7 + k + n + bits, zero_points=zp, bias=bias)
-    y, kernel = run_device(case)
+    y, kernel = run_device(case, path=path)
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32, kernel
 
 
@@ -281,7 +289,7 @@ def test_registered_operator_end_to_end(cuda_device):
     y = session.run(case.a)
     assert y.shape == (4, 1024)
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
-    assert session.last_device_kernel.startswith("nbits_gemv_stream_kernel")
+    assert session.last_device_kernel == "nbits_gemv_mma_kernel"
     y3 = session.run(case.a.reshape(2, 2, case.k))          # leading dims are kept
     assert y3.shape == (2, 2, 1024) and np.array_equal(y3.reshape(4, 1024), y)
     assert pkg.used_kernel_names() == ["onnx_light_cuda::MatMulNBits"] * 2
