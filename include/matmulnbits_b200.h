@@ -120,6 +120,29 @@ int mnb_quantize_a_device(const float *a_dev, int64_t m, int64_t k, int block_si
 int mnb_int8_block_dots_device(mnb_weights *weights, const int8_t *aq_dev, int64_t m,
                                int32_t *dots_dev, void *stream);
 
+/* accuracy_level-4 product Y = MatMulNBits(A) that allocates nothing. It has no counterpart in
+ * the reference. It is meant for callers that are not allowed to reach cudaMalloc while they
+ * run: a serving loop whose steady state must stay free of the device-wide synchronisation and
+ * the possible out-of-memory failure of an allocation, or a host that owns all device memory
+ * itself and gives a plug-in none. mnb_matmul_device(accuracy_level = 4) grows cudaMalloc'ed
+ * scratch for the quantized activations; this entry point keeps them in an array that is part
+ * of the library image instead (about 0.3 MB on every GPU that loads the library, held until
+ * the process exits).
+ *   - limits: 1 <= m <= MNB_STATIC_MAX_TOKENS and ceil(K/block_size)*block_size <=
+ *     MNB_STATIC_MAX_PADDED_K; anything larger is refused with MNB_ERR_INVALID_ARGUMENT;
+ *   - a_dev [m, K] and y_dev [m, N] are device pointers, the work is queued on `stream`;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress with that device current); make that first call outside any
+ *     stream capture;
+ *   - all calls share the one array. It keeps the previous call's bytes; every byte a call
+ *     reads it first rewrites itself, so nothing needs clearing, but two calls whose kernels
+ *     overlap on the GPU (different streams, different handles) would race on it: keep calls
+ *     to this entry point ordered on the device. */
+#define MNB_STATIC_MAX_TOKENS 16
+#define MNB_STATIC_MAX_PADDED_K 16384
+int mnb_matmul_int8_static(mnb_weights *weights, const float *a_dev, int64_t m, float *y_dev,
+                           void *stream);
+
 /* Number of kernels this library has launched in the calling process (for benchmarks). */
 int64_t mnb_launch_count(void);
 

@@ -590,6 +590,89 @@ int mnb_int8_block_dots_device(mnb_weights *h, const int8_t *aq_dev, int64_t m, 
   return MNB_OK;
 }
 
+// ---- accuracy_level 4 without any allocation ------------------------------------------------
+// The quantized activations and their block scales live in a fixed array inside the library
+// image instead of cudaMalloc'ed scratch. Every GPU that loads the library carries the array
+// until the process exits.
+namespace {
+constexpr std::int64_t kStaticMaxTokens = MNB_STATIC_MAX_TOKENS;
+constexpr std::int64_t kStaticMaxPaddedK = MNB_STATIC_MAX_PADDED_K;
+constexpr std::size_t kStaticAqBytes = static_cast<std::size_t>(kStaticMaxTokens) * kStaticMaxPaddedK;
+constexpr std::size_t kStaticScaleBytes =
+    static_cast<std::size_t>(kStaticMaxTokens) * (kStaticMaxPaddedK / 16) * sizeof(float);
+constexpr int kStaticMaxDevices = 64;
+} // namespace
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticAqBytes + kStaticScaleBytes];
+
+namespace {
+std::mutex g_static_mutex;
+unsigned char *g_static_address[kStaticMaxDevices] = {};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
+// address is looked up once per device, with that device current, and handed to the kernels.
+int StaticScratchFor(int device, unsigned char **out) {
+  if (device < 0 || device >= kStaticMaxDevices) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_int8_static: device index out of range.");
+  }
+  std::lock_guard<std::mutex> guard(g_static_mutex);
+  if (g_static_address[device] == nullptr) {
+    unsigned char *ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      return FailCuda("cudaGetSymbolAddress(static scratch)", err);
+    }
+    g_static_address[device] = ptr;
+  }
+  *out = g_static_address[device];
+  return MNB_OK;
+}
+} // namespace
+
+int mnb_matmul_int8_static(mnb_weights *h, const float *a_dev, int64_t m, float *y_dev, void *stream) {
+  if (h == nullptr || a_dev == nullptr || y_dev == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_int8_static: null argument.");
+  }
+  const WeightView &w = h->view;
+  const std::int64_t padded_k = static_cast<std::int64_t>(w.n_blocks) * w.block_size;
+  if (m < 1 || m > kStaticMaxTokens || padded_k > kStaticMaxPaddedK) {
+    char text[200];
+    std::snprintf(text, sizeof(text),
+                  "mnb_matmul_int8_static: M=%lld, padded K=%lld exceed the built-in scratch "
+                  "(M <= %lld, ceil(K/block_size)*block_size <= %lld); use mnb_matmul_device.",
+                  static_cast<long long>(m), static_cast<long long>(padded_k),
+                  static_cast<long long>(kStaticMaxTokens), static_cast<long long>(kStaticMaxPaddedK));
+    return Fail(MNB_ERR_INVALID_ARGUMENT, text);
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  unsigned char *scratch = nullptr;
+  const int rc = StaticScratchFor(h->device, &scratch);
+  if (rc != MNB_OK) {
+    return rc;
+  }
+  // Every byte of the two regions that the matmul reads is rewritten by the quantization
+  // kernel of the same call (padding columns included), so nothing has to be cleared.
+  std::int8_t *aq = reinterpret_cast<std::int8_t *>(scratch);
+  float *a_scales = reinterpret_cast<float *>(scratch + kStaticAqBytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char *name = mnb::LaunchQuantizeAPadded(a_dev, m, w.k, w.block_size, aq, a_scales, s);
+  if (name != nullptr) {
+    OutputView out{y_dev, w.n, 0};
+    name = mnb::LaunchInt8Matmul(w, aq, a_scales, m, out, s, h->sm_count);
+  }
+  if (name == nullptr) {
+    return Fail(MNB_ERR_UNSUPPORTED,
+                "mnb_matmul_int8_static: needs 16-byte aligned weight rows and block_size >= 32 for "
+                "4-bit weights.");
+  }
+  mnb::t_last_kernel = name;
+  return MNB_OK;
+}
+
 int64_t mnb_launch_count(void) { return mnb::g_launches.load(std::memory_order_relaxed); }
 
 const char *mnb_last_kernel(void) { return mnb::t_last_kernel; }

@@ -129,6 +129,16 @@ class MatMulNBitsWeights:
             self._handle, a.data_ptr(), m, accuracy_level, path, y.data_ptr(),
             self.n if ld_y is None else ld_y, col_offset, raw))
 
+    def matmul_int8_static(self, a, y, stream=None) -> None:
+        """accuracy_level-4 product through the entry point that allocates nothing (its
+        activation scratch is a fixed array inside the library; limits in the C header).
+        ``a`` [m, K] and ``y`` [m, N] are torch CUDA fp32 tensors."""
+        import torch
+
+        m = a.numel() // self.k
+        raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
+        _capi.check(self._lib.mnb_matmul_int8_static(self._handle, a.data_ptr(), m, y.data_ptr(), raw))
+
     def poll_status(self) -> int:
         status = ctypes.c_int(0)
         _capi.check(self._lib.mnb_weights_poll_status(self._handle, ctypes.byref(status)))
