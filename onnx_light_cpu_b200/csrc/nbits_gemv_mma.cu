@@ -110,6 +110,15 @@ __device__ __forceinline__ void MmaF16(float (&d)[4], std::uint32_t a0, std::uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Same with a zero accumulator input: starts a fresh sum without clearing registers first.
+__device__ __forceinline__ void MmaF16Zero(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                           std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 // Eight codes of `w` minus the zero point, as four fp16 pairs (code j, code j+4), j = 0..3.
 // `offs` = (1024 + zp) x2, `offs16` = -(64 + zp) x2, `sixteenth` = (1/16) x2.
 __device__ __forceinline__ void Dequant8(std::uint32_t w, std::uint32_t magic, std::uint32_t offs,
@@ -137,7 +146,7 @@ __device__ __forceinline__ int ActPosition(int k) {
 
 // NB_SG_LOG2: log2 of quantization blocks per 128-k supergroup (block 128+: 0, 64: 1, 32: 2).
 // BIG_BLOCK: a block spans several supergroups (block_size >= 256).
-template <int NB_SG_LOG2, bool BIG_BLOCK>
+template <int NB_SG_LOG2, bool BIG_BLOCK, bool HAS_ZP>
 __global__ void __launch_bounds__(kThreads, 1)
     nbits_gemv_mma_kernel(const __grid_constant__ CUtensorMap map_b, const MmaParams p) {
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -178,6 +187,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tid == 0) {
     MNB_MARK(0);
   }
+  // the next kernel in the stream may start filling SMs as they free up
+  ptx::GridDependencyLaunch();
 
   if (warp == kWarps) {
     // ------------------------------ producer ------------------------------
@@ -240,6 +251,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Activation staging: per token a power-of-two scale, two fp16 pieces, permuted order.
   // A thread owns whole 8-k words (one 16-byte store per piece); up to four words per thread
   // stay in registers between the max reduction and the split, so A is read once.
+  // A (and Y) may be produced / still read by the previous kernel in the stream: from here on
+  // the consumers depend on it. The producer warp above only touches the constant weights.
+  ptx::GridDependencyWait();
   const int words_total = p.k_pad >> 3;
   unsigned char *zero_row = act + 2 * p.tokens_per_pass * p.act_row_bytes;
   for (int i = tid; i < (p.act_row_bytes >> 4); i += kConsumerThreads) {
@@ -380,13 +394,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t magic = p.magic;
   const std::uint32_t sixteenth = 0x2c002c00u;  // fp16 1/16 twice
   const std::uint32_t plus960 = 0x63806380u;    // fp16 960 twice
-  const bool has_zp = p.w.zp != nullptr;
   const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
   const int box_bytes = 16 * p.slice_b_bytes;
-  // per-lane offsets inside a meta record: scales [block][8 rows], zero points [block][8 rows]
-  const int scale_lane = ((BIG_BLOCK ? 0 : blk_d) * 8 + g) * 4;
-  const int zp_lane = p.rec_scale_bytes + (BIG_BLOCK ? 0 : tb) * 8 + g;
-  constexpr int kMetaStride = BIG_BLOCK ? 0 : kNbSg * 8; // record entries per supergroup
+  // meta record: float scale[8 rows][bpt + 4] (padded rows keep lanes on different banks),
+  // then uint8 zp[8 rows][bpt]
+  const int scale_row_bytes = (p.bpt + 4) * 4;
+  constexpr int kNb = kNbSg; // quantization blocks per supergroup (1 when a block spans several)
 
   int tile_count = 0;
   bool dead = false; // a bounded wait gave up: skip the math but keep the pair barrier protocol
@@ -396,8 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int h0 = h_begin + 2 * tile;
     const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
     float acc0 = 0.0f, acc1 = 0.0f; // rows g and g + 8, accumulator column pair t
-    float da[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float db[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float da[4], db[4];
 
     for (int s = parity; s < p.slices && !dead; s += 2) {
       const int task = wave0 * p.slices + s * wave_tiles + pair;
@@ -424,51 +436,84 @@ __global__ void __launch_bounds__(kThreads, 1)
       const unsigned char *row_hi = row_lo + 8 * p.slice_b_bytes;
       const unsigned char *meta0 = sb + box_bytes;       // rows 0..7
       const unsigned char *meta1 = meta0 + p.rec_bytes;  // rows 8..15
+      const float *sc0 = reinterpret_cast<const float *>(meta0 + g * scale_row_bytes);
+      const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes);
+      const unsigned char *zr0 = meta0 + p.rec_scale_bytes + g * p.bpt;
+      const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt;
       const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * 256;
 
       for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += 4) {
+        // scales / zero points of the four supergroups of this round
+        float s0v[4], s1v[4];
+        std::uint32_t z0v[4], z1v[4];
+        if constexpr (!BIG_BLOCK && NB_SG_LOG2 == 0) {
+          // one block per supergroup: four consecutive blocks, one vector load each
+          const float4 a4 = *reinterpret_cast<const float4 *>(sc0 + sg0);
+          const float4 b4 = *reinterpret_cast<const float4 *>(sc1 + sg0);
+          s0v[0] = a4.x, s0v[1] = a4.y, s0v[2] = a4.z, s0v[3] = a4.w;
+          s1v[0] = b4.x, s1v[1] = b4.y, s1v[2] = b4.z, s1v[3] = b4.w;
+          if constexpr (HAS_ZP) {
+            const std::uint32_t za = *reinterpret_cast<const std::uint32_t *>(zr0 + sg0);
+            const std::uint32_t zb = *reinterpret_cast<const std::uint32_t *>(zr1 + sg0);
+            z0v[0] = __byte_perm(za, 0x64646464u, 0x4040), z1v[0] = __byte_perm(zb, 0x64646464u, 0x4040);
+            z0v[1] = __byte_perm(za, 0x64646464u, 0x4141), z1v[1] = __byte_perm(zb, 0x64646464u, 0x4141);
+            z0v[2] = __byte_perm(za, 0x64646464u, 0x4242), z1v[2] = __byte_perm(zb, 0x64646464u, 0x4242);
+            z0v[3] = __byte_perm(za, 0x64646464u, 0x4343), z1v[3] = __byte_perm(zb, 0x64646464u, 0x4343);
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int sg = sg0 + u;
+            const int blk_codes = BIG_BLOCK ? sg / p.sg_per_block : sg * kNb + tb;
+            const int blk_acc = BIG_BLOCK ? blk_codes : sg * kNb + blk_d;
+            s0v[u] = sc0[blk_acc];
+            s1v[u] = sc1[blk_acc];
+            if constexpr (HAS_ZP) {
+              z0v[u] = __byte_perm(static_cast<std::uint32_t>(zr0[blk_codes]), 0x64646464u, 0x4040);
+              z1v[u] = __byte_perm(static_cast<std::uint32_t>(zr1[blk_codes]), 0x64646464u, 0x4040);
+            }
+          }
+        }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int sg = sg0 + u;
-          const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + sg0 * 64 + u * 64);
-          const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + sg0 * 64 + u * 64);
-          // entry (inside the record) of the block of this lane's codes / accumulator columns
-          const int entry = BIG_BLOCK ? (sg / p.sg_per_block) * 8 : sg0 * kMetaStride + u * kMetaStride;
-          std::uint32_t offs0 = default_offs, offs1 = default_offs;
-          if (has_zp) {
-            const std::uint32_t z0 = meta0[zp_lane + entry];
-            const std::uint32_t z1 = meta1[zp_lane + entry];
-            offs0 = __byte_perm(z0, 0x64646464u, 0x4040); // (1024 + zp) twice
-            offs1 = __byte_perm(z1, 0x64646464u, 0x4040);
-          }
+          const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + u * 64);
+          const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + u * 64);
+          const std::uint32_t offs0 = HAS_ZP ? z0v[u] : default_offs; // (1024 + zp) twice
+          const std::uint32_t offs1 = HAS_ZP ? z1v[u] : default_offs;
           const std::uint32_t offs0_16 = Hsub2(plus960, offs0); // -(64 + zp)
           const std::uint32_t offs1_16 = Hsub2(plus960, offs1);
           uint4 bf[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            bf[i] = *reinterpret_cast<const uint4 *>(act_task + sg0 * 256 + u * 256 + i * 64);
+            bf[i] = *reinterpret_cast<const uint4 *>(act_task + u * 256 + i * 64);
           }
           const std::uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
           const std::uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
+          // a block that spans several supergroups keeps accumulating; otherwise start afresh
+          const bool fresh = BIG_BLOCK ? ((sg0 + u) % p.sg_per_block) == 0 : true;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             std::uint32_t pa[4], pb[4];
             Dequant8(w0[i], magic, offs0, offs0_16, sixteenth, pa);
             Dequant8(w1[i], magic, offs1, offs1_16, sixteenth, pb);
             // two accumulator sets halve the dependent chain of MMAs
-            MmaF16(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
-            MmaF16(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
+            if (i == 0 && fresh) {
+              MmaF16Zero(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
+              MmaF16Zero(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
+            } else {
+              MmaF16(da, pa[0], pb[0], pa[1], pb[1], bf[i].x, bf[i].y);
+              MmaF16(db, pa[2], pb[2], pa[3], pb[3], bf[i].z, bf[i].w);
+            }
           }
-          const bool block_done = BIG_BLOCK ? ((sg + 1) % p.sg_per_block) == 0 : true;
+          const bool block_done = BIG_BLOCK ? ((sg0 + u + 1) % p.sg_per_block) == 0 : true;
           if (block_done) {
-            const float s0 = *reinterpret_cast<const float *>(meta0 + scale_lane + entry * 4);
-            const float s1 = *reinterpret_cast<const float *>(meta1 + scale_lane + entry * 4);
-            acc0 = fmaf(s0, (da[0] + da[1]) + (db[0] + db[1]), acc0);
-            acc1 = fmaf(s1, (da[2] + da[3]) + (db[2] + db[3]), acc1);
-            da[0] = da[1] = da[2] = da[3] = 0.0f;
-            db[0] = db[1] = db[2] = db[3] = 0.0f;
+            acc0 = fmaf(s0v[u], (da[0] + da[1]) + (db[0] + db[1]), acc0);
+            acc1 = fmaf(s1v[u], (da[2] + da[3]) + (db[2] + db[3]), acc1);
           }
         }
+        row_lo += 256;
+        row_hi += 256;
+        act_task += 1024;
       }
       __syncwarp();
       if (lane == 0) {
@@ -514,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---- prepared side array -----------------------------------------------------------------
-// meta[(slice * half_tiles + half_tile)] = { float scale[bpt][8 rows] ; uint8 zp[bpt][8 rows] }
+// meta[(slice * half_tiles + half_tile)] = { float scale[8 rows][bpt + 4] ; uint8 zp[8 rows][bpt] }
 // (the zero-point part only when the node has zero points). Rows beyond N and blocks beyond
 // n_blocks get scale 0.
 __global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightView w, int bpt, int half_tiles,
@@ -539,9 +584,9 @@ __global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightVie
       zp = ZeroPointOf(w, row, block);
     }
     unsigned char *rec = meta + record * rec_bytes;
-    reinterpret_cast<float *>(rec)[b * 8 + r] = scale;
+    reinterpret_cast<float *>(rec)[r * (bpt + 4) + b] = scale;
     if (w.zp != nullptr) {
-      rec[rec_scale_bytes + b * 8 + r] = static_cast<unsigned char>(zp);
+      rec[rec_scale_bytes + r * bpt + b] = static_cast<unsigned char>(zp);
     }
   }
 }
@@ -552,6 +597,16 @@ int Log2Of(int v) {
     ++l;
   }
   return l;
+}
+
+// Programmatic dependent launch is off unless MNB_DEPENDENT_LAUNCH=1: on the decode benchmark
+// (back-to-back launches in a CUDA graph) it measured 7 % slower than plain serialization.
+bool UseDependentLaunch() {
+  static const bool enabled = [] {
+    const char *value = std::getenv("MNB_DEPENDENT_LAUNCH");
+    return value != nullptr && value[0] == '1';
+  }();
+  return enabled;
 }
 
 } // namespace
@@ -581,7 +636,7 @@ MetaGeometry MetaGeometryOf(const WeightView &w) {
   }
   geo.bpt = bpt;
   geo.slices = (w.n_blocks + bpt - 1) / bpt;
-  geo.rec_scale_bytes = 8 * bpt * 4;
+  geo.rec_scale_bytes = 8 * (bpt + 4) * 4;
   geo.rec_bytes = geo.rec_scale_bytes + (w.zp != nullptr ? 8 * bpt : 0);
   geo.half_tiles = static_cast<int>((w.n + 7) / 8);
   geo.bytes = static_cast<std::size_t>(geo.half_tiles) * geo.slices * geo.rec_bytes;
@@ -676,20 +731,33 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   }
   dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>((m + tokens_per_pass - 1) / tokens_per_pass), 1);
   cudaError_t err = cudaErrorInvalidValue;
-#define MNB_MMA_CASE(LOG2_, BIG_)                                                                \
-  if (nb_sg_log2 == LOG2_ && (p.sg_per_block > 1) == BIG_) {                                     \
-    auto kernel = nbits_gemv_mma_kernel<LOG2_, BIG_>;                                            \
+#define MNB_MMA_CASE(LOG2_, BIG_, ZP_)                                                           \
+  if (nb_sg_log2 == LOG2_ && (p.sg_per_block > 1) == BIG_ && (w.zp != nullptr) == ZP_) {         \
+    auto kernel = nbits_gemv_mma_kernel<LOG2_, BIG_, ZP_>;                                       \
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
                                static_cast<int>(smem));                                          \
     if (err == cudaSuccess) {                                                                    \
-      kernel<<<grid, kThreads, smem, stream>>>(map_b, p);                                        \
-      err = cudaGetLastError();                                                                  \
+      cudaLaunchConfig_t config = {};                                                            \
+      config.gridDim = grid;                                                                     \
+      config.blockDim = dim3(kThreads, 1, 1);                                                    \
+      config.dynamicSmemBytes = smem;                                                            \
+      config.stream = stream;                                                                    \
+      cudaLaunchAttribute attribute[1];                                                          \
+      attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
+      attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
+      config.attrs = attribute;                                                                  \
+      config.numAttrs = UseDependentLaunch() ? 1 : 0;                                            \
+      err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
     }                                                                                            \
   }
-  MNB_MMA_CASE(0, false)
-  MNB_MMA_CASE(0, true)
-  MNB_MMA_CASE(1, false)
-  MNB_MMA_CASE(2, false)
+  MNB_MMA_CASE(0, false, true)
+  MNB_MMA_CASE(0, false, false)
+  MNB_MMA_CASE(0, true, true)
+  MNB_MMA_CASE(0, true, false)
+  MNB_MMA_CASE(1, false, true)
+  MNB_MMA_CASE(1, false, false)
+  MNB_MMA_CASE(2, false, true)
+  MNB_MMA_CASE(2, false, false)
 #undef MNB_MMA_CASE
   if (err != cudaSuccess) {
     return nullptr;

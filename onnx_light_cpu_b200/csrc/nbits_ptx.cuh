@@ -89,6 +89,20 @@ __device__ __forceinline__ void PrefetchTensorMap(const void *tensor_map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still draining. GridDependencyLaunch() lets the NEXT
+// kernel's CTAs be scheduled as soon as SM resources free up; GridDependencyWait() blocks until
+// the PREVIOUS kernel has completed and its writes are visible. Only memory the previous
+// kernel cannot have written (the constant weights) may be touched before the wait.
+__device__ __forceinline__ void GridDependencyLaunch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void GridDependencyWait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------------------------
 
 // Whole-warp instruction. Writes the TMEM base address of `columns` columns to *smem_result.
