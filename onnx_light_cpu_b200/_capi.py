@@ -26,6 +26,7 @@ PATH_GEMV = 1
 PATH_TCGEN05 = 2
 PATH_INT8 = 3
 PATH_GEMV_MMA = 4
+PATH_TCGEN05_WIDE = 5
 
 # every symbol include/matmulnbits_b200.h declares
 EXPORTED_SYMBOLS = (

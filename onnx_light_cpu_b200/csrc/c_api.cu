@@ -228,7 +228,8 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     }
     break;
   }
-  case MNB_PATH_TCGEN05: {
+  case MNB_PATH_TCGEN05:
+  case MNB_PATH_TCGEN05_WIDE: {
     if (!mnb::GemmTcgen05Supports(w, m)) {
       return Fail(MNB_ERR_UNSUPPORTED,
                   "MatMulNBits: the tcgen05 path needs bits=4, block_size>=32, K%64==0.");
@@ -238,7 +239,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       return rc;
     }
     name = mnb::LaunchGemmTcgen05(w, a_dev, m, static_cast<std::uint16_t *>(h->scratch_a), out,
-                                  h->status_dev, stream, h->sm_count);
+                                  h->status_dev, stream, h->sm_count, chosen == MNB_PATH_TCGEN05_WIDE);
     break;
   }
   case MNB_PATH_INT8: {

@@ -95,7 +95,7 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
 // Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
                               std::uint16_t *a_bf16, OutputView out, int *status_word,
-                              cudaStream_t stream, int sm_count);
+                              cudaStream_t stream, int sm_count, bool force_wide = false);
 std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k);
 bool GemmTcgen05Supports(const WeightView &w, std::int64_t m);
 

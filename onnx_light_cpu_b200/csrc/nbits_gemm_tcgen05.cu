@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 namespace mnb {
 namespace {
@@ -70,6 +71,7 @@ struct GemmParams {
   int k_steps;
   int *status;
   int block_shift;
+  std::uint32_t magic; // 0x43004300, passed at run time so that it stays in a register
 };
 
 template <int BT> struct GemmSmem {
@@ -82,24 +84,44 @@ template <int BT> struct GemmSmem {
   static constexpr int kTotal = kStages * kStage + kBarrierBytes + 1024; // + alignment slack
 };
 
-// Dequantizes 8 nibbles of `w` (one 16-byte output chunk in permuted k order).
-__device__ __forceinline__ uint4 DequantWord(std::uint32_t w, __nv_bfloat162 offset,
-                                             __nv_bfloat162 scale) {
+// d = (a & mask) | c in one LOP3 (truth table 0xEA); `c` is kept in a register by the caller.
+__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t mask, std::uint32_t c) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
+  return d;
+}
+
+// ((x - offset) * scale) on bf16 pairs: the subtraction is exact (small integers), the product
+// is rounded once.
+__device__ __forceinline__ std::uint32_t SubMulBf16x2(std::uint32_t x, std::uint32_t offset, std::uint32_t scale) {
+  std::uint32_t d;
+  asm("{\n\t"
+      ".reg .b32 t;\n\t"
+      "sub.rn.bf16x2 t, %1, %2;\n\t"
+      "mul.rn.bf16x2 %0, t, %3;\n\t"
+      "}"
+      : "=r"(d)
+      : "r"(x), "r"(offset), "r"(scale));
+  return d;
+}
+
+// Dequantizes the 8 nibbles of `w` into one 16-byte chunk of bf16 in the k order 0,4,1,5,2,6,3,7.
+// `magic` = 0x43004300 (128.0 twice), `offset` = (128 + zp) twice, `scale` = block scale twice.
+__device__ __forceinline__ uint4 DequantWord(std::uint32_t w, std::uint32_t magic, std::uint32_t offset,
+                                             std::uint32_t scale) {
   uint4 out;
-  std::uint32_t v[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const std::uint32_t bits = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u; // 128 + q, exact
-    __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162 *>(&bits);
-    x = __hsub2(x, offset);  // q - zp, exact
-    x = __hmul2(x, scale);   // one bf16 rounding
-    v[j] = *reinterpret_cast<std::uint32_t *>(&x);
-  }
-  out.x = v[0];
-  out.y = v[1];
-  out.z = v[2];
-  out.w = v[3];
+  out.x = SubMulBf16x2(AndOr(w, 0x000f000fu, magic), offset, scale);
+  out.y = SubMulBf16x2(AndOr(w >> 4, 0x000f000fu, magic), offset, scale);
+  out.z = SubMulBf16x2(AndOr(w >> 8, 0x000f000fu, magic), offset, scale);
+  out.w = SubMulBf16x2(AndOr(w >> 12, 0x000f000fu, magic), offset, scale);
   return out;
+}
+
+// bf16 pair (v, v) from a float, round to nearest even.
+__device__ __forceinline__ std::uint32_t Bf16Pair(float v) {
+  std::uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(d) : "f"(v));
+  return d;
 }
 
 template <int BT>
@@ -203,57 +225,65 @@ __global__ void __launch_bounds__(kThreads, 1)
     const std::int64_t grow = static_cast<std::int64_t>(n0) + row;
     const bool row_valid = grow < p.w.n;
     const std::int64_t safe_row = row_valid ? grow : 0;
-    const int default_zp = 8;
+    // per-thread views of this row's scales and packed zero points
+    const float *scale_row = p.w.scales + safe_row * p.w.n_blocks;
+    const std::uint8_t *zp_row = p.w.zp != nullptr ? p.w.zp + safe_row * p.w.zp_row_bytes : nullptr;
+    const int last_block = p.w.n_blocks - 1;
+    const std::uint32_t magic = p.magic;
+    // fixed shared-memory offsets of this thread inside a stage
+    const int packed_offset = Smem::kStageA + Smem::kStageW + row * 32 + half * 16;
+    int store_offset[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = half * 4 + i; // 16-byte chunk index inside the 128-byte row
+      store_offset[i] = Smem::kStageA + row * 128 + ((c ^ (row & 7)) << 4);
+    }
 
-    auto load_meta = [&](int ks, float &scale, int &zp) {
+    auto load_meta = [&](int ks, std::uint32_t &scale2, std::uint32_t &offset2) {
       int block = (ks * kTileK + half * 32) >> p.block_shift;
-      if (block >= p.w.n_blocks) {
-        block = p.w.n_blocks - 1;
+      block = block > last_block ? last_block : block;
+      const float scale = row_valid ? __ldg(scale_row + block) : 0.0f;
+      int zp = 8;
+      if (zp_row != nullptr) {
+        const int byte = __ldg(zp_row + (block >> 1));
+        zp = (byte >> ((block & 1) * 4)) & 0x0f;
       }
-      scale = row_valid ? __ldg(p.w.scales + safe_row * p.w.n_blocks + block) : 0.0f;
-      zp = default_zp;
-      if (p.w.zp != nullptr) {
-        const int byte = __ldg(p.w.zp + safe_row * p.w.zp_row_bytes + (block >> 1));
-        zp = (block & 1) ? (byte >> 4) : (byte & 0x0f);
-      }
+      scale2 = Bf16Pair(scale);
+      offset2 = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
     };
 
-    float scale_next;
-    int zp_next;
-    load_meta(0, scale_next, zp_next);
+    std::uint32_t scale_next, offset_next;
+    load_meta(0, scale_next, offset_next);
     bool ok = true;
+    int s = 0;
+    std::uint32_t phase = 0;
     for (int ks = 0; ks < p.k_steps; ++ks) {
-      const int s = ks % kStages;
-      const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
-      const float scale = scale_next;
-      const int zp = zp_next;
+      const std::uint32_t scale2 = scale_next;
+      const std::uint32_t offset2 = offset_next;
       if (ks + 1 < p.k_steps) {
-        load_meta(ks + 1, scale_next, zp_next);
+        load_meta(ks + 1, scale_next, offset_next);
       }
-      if (!ptx::MbarWait(&full_tma[s], round & 1u)) {
+      if (!ptx::MbarWait(&full_tma[s], phase)) {
         atomicExch(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
         break;
       }
-      unsigned char *sa = stage0 + s * Smem::kStage;
-      unsigned char *sw = sa + Smem::kStageA;
-      const unsigned char *sp = sw + Smem::kStageW;
-      const uint4 q = *reinterpret_cast<const uint4 *>(sp + row * 32 + half * 16);
-      const __nv_bfloat162 offset = __float2bfloat162_rn(static_cast<float>(128 + zp));
-      const __nv_bfloat162 scale2 = __float2bfloat162_rn(scale);
-      const std::uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 chunk = DequantWord(words[i], offset, scale2);
-        const int c = half * 4 + i; // 16-byte chunk index inside the 128-byte row
-        *reinterpret_cast<uint4 *>(sw + row * 128 + ((c ^ (row & 7)) << 4)) = chunk;
-      }
+      unsigned char *stage = stage0 + s * Smem::kStage;
+      const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset);
+      *reinterpret_cast<uint4 *>(stage + store_offset[0]) = DequantWord(q.x, magic, offset2, scale2);
+      *reinterpret_cast<uint4 *>(stage + store_offset[1]) = DequantWord(q.y, magic, offset2, scale2);
+      *reinterpret_cast<uint4 *>(stage + store_offset[2]) = DequantWord(q.z, magic, offset2, scale2);
+      *reinterpret_cast<uint4 *>(stage + store_offset[3]) = DequantWord(q.w, magic, offset2, scale2);
       // make the generic-proxy stores visible to the tensor core (async proxy), then signal
       ptx::FenceProxyAsyncShared();
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&full_deq[s]);
+      }
+      if (++s == kStages) {
+        s = 0;
+        phase ^= 1u;
       }
     }
 
@@ -301,6 +331,250 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Wide variant for large M: one CTA owns 256 weight rows x 256 tokens (two 128-lane accumulators,
+// all 512 TMEM columns). Per 64-k step it brings in 32 KB of activations and 8 KB of packed
+// weights for twice the MMA work of the 128-row kernel, which halves the L2 traffic per flop
+// and lets four stages in flight cover the TMA latency. The dequantized tile is transient, so
+// it lives in its own two buffers instead of the TMA ring.
+constexpr int kWideRows = 256;
+constexpr int kWideTokens = 256;
+constexpr int kWideStages = 4;
+constexpr int kWideStageA = kWideTokens * 128;   // 32 KB
+constexpr int kWideStageP = kWideRows * 32;      // 8 KB
+constexpr int kWideBufW = kWideRows * 128;       // 32 KB, two 16 KB sub-tiles
+constexpr int kWideSmem = kWideStages * (kWideStageA + kWideStageP) + 2 * kWideBufW + 256 + 1024;
+
+__global__ void __launch_bounds__(kThreads, 1)
+    nbits_gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a,
+                                   const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  unsigned char *smem = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
+  unsigned char *ring_a = smem;                                     // [stages][32 KB]
+  unsigned char *buf_w = ring_a + kWideStages * kWideStageA;        // [2][32 KB]
+  unsigned char *ring_p = buf_w + 2 * kWideBufW;                    // [stages][8 KB]
+  std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(ring_p + kWideStages * kWideStageP);
+  std::uint64_t *full_tma = bars;                    // [stages] activations + packed weights landed
+  std::uint64_t *empty = bars + kWideStages;         // [stages] MMAs that read the stage retired
+  std::uint64_t *w_full = bars + 2 * kWideStages;    // [2] weights dequantized into the buffer
+  std::uint64_t *w_empty = w_full + 2;               // [2] MMAs that read the buffer retired
+  std::uint64_t *accum_full = w_empty + 2;
+  std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(accum_full + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int n0 = blockIdx.x * kWideRows;
+  const int m0 = blockIdx.y * kWideTokens;
+
+  if (tid == 0) {
+    for (int s = 0; s < kWideStages; ++s) {
+      ptx::MbarInit(&full_tma[s], 1);
+      ptx::MbarInit(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::MbarInit(&w_full[b], kDequantWarps);
+      ptx::MbarInit(&w_empty[b], 1);
+    }
+    ptx::MbarInit(accum_full, 1);
+    *abort_flag = 0;
+    ptx::FenceMbarInit();
+  }
+  if (warp == 0) {
+    ptx::TmemAlloc(tmem_slot, 512);
+    ptx::TmemRelinquish();
+  }
+  ptx::TcFenceBefore();
+  __syncthreads();
+  ptx::TcFenceAfter();
+  const std::uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      ptx::PrefetchTensorMap(&map_a);
+      ptx::PrefetchTensorMap(&map_p);
+      int s = 0;
+      std::uint32_t phase = 0;
+      for (int ks = 0; ks < p.k_steps; ++ks) {
+        if (!ptx::MbarWait(&empty[s], phase ^ 1u)) {
+          atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::MbarArriveExpectTx(&full_tma[s], kWideStageA + kWideStageP);
+        ptx::TmaLoad2D(ring_a + s * kWideStageA, &map_a, ks * kTileK, m0, &full_tma[s]);
+        ptx::TmaLoad2D(ring_p + s * kWideStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
+        if (++s == kWideStages) {
+          s = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr std::uint32_t idesc = ptx::UmmaIdescBf16(128, kWideTokens);
+      bool ok = true;
+      int s = 0;
+      for (int ks = 0; ks < p.k_steps; ++ks) {
+        const int b = ks & 1;
+        // the buffer's dequantizers waited for the stage's TMA, so the activations are in too
+        if (!ptx::MbarWait(&w_full[b], static_cast<std::uint32_t>(ks >> 1) & 1u)) {
+          atomicExch(p.status, kDeviceTimeoutMmaBarrier);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        ptx::TcFenceAfter();
+        const std::uint32_t sa = ptx::SmemAddr(ring_a + s * kWideStageA);
+        const std::uint32_t sw = ptx::SmemAddr(buf_w + b * kWideBufW);
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+#pragma unroll
+          for (int kk = 0; kk < kTileK / 16; ++kk) {
+            const std::uint64_t desc_w = ptx::UmmaDescKMajorSw128(sw + sub * (kWideBufW / 2) + kk * 32);
+            const std::uint64_t desc_a = ptx::UmmaDescKMajorSw128(sa + kk * 32);
+            ptx::UmmaBf16(tmem_base + sub * kWideTokens, desc_w, desc_a, idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+        }
+        ptx::UmmaCommit(&empty[s]);
+        ptx::UmmaCommit(&w_empty[b]);
+        if (++s == kWideStages) {
+          s = 0;
+        }
+      }
+      if (ok) {
+        ptx::UmmaCommit(accum_full);
+      }
+    }
+  } else {
+    // ------------------------------- dequantizers -------------------------------
+    const int dq = tid - 64;          // 0..255
+    const int row = dq >> 1;          // weight row inside each 128-row sub-tile
+    const int half = dq & 1;          // which 32 of the 64 k of the stage
+    const std::uint32_t magic = p.magic;
+    const int last_block = p.w.n_blocks - 1;
+    const float *scale_row[2];
+    const std::uint8_t *zp_row[2];
+    bool row_valid[2];
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+      const std::int64_t grow = static_cast<std::int64_t>(n0) + sub * 128 + row;
+      row_valid[sub] = grow < p.w.n;
+      const std::int64_t safe_row = row_valid[sub] ? grow : 0;
+      scale_row[sub] = p.w.scales + safe_row * p.w.n_blocks;
+      zp_row[sub] = p.w.zp != nullptr ? p.w.zp + safe_row * p.w.zp_row_bytes : nullptr;
+    }
+    const int packed_offset = row * 32 + half * 16;
+    int store_offset[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = half * 4 + i; // 16-byte chunk index inside the 128-byte row
+      store_offset[i] = row * 128 + ((c ^ (row & 7)) << 4);
+    }
+
+    auto load_meta = [&](int ks, std::uint32_t (&scale2)[2], std::uint32_t (&offset2)[2]) {
+      int block = (ks * kTileK + half * 32) >> p.block_shift;
+      block = block > last_block ? last_block : block;
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+        const float scale = row_valid[sub] ? __ldg(scale_row[sub] + block) : 0.0f;
+        int zp = 8;
+        if (zp_row[sub] != nullptr) {
+          const int byte = __ldg(zp_row[sub] + (block >> 1));
+          zp = (byte >> ((block & 1) * 4)) & 0x0f;
+        }
+        scale2[sub] = Bf16Pair(scale);
+        offset2[sub] = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
+      }
+    };
+
+    std::uint32_t scale_next[2], offset_next[2];
+    load_meta(0, scale_next, offset_next);
+    bool ok = true;
+    int s = 0;
+    std::uint32_t phase = 0;
+    for (int ks = 0; ks < p.k_steps; ++ks) {
+      const int b = ks & 1;
+      const std::uint32_t scale2[2] = {scale_next[0], scale_next[1]};
+      const std::uint32_t offset2[2] = {offset_next[0], offset_next[1]};
+      if (ks + 1 < p.k_steps) {
+        load_meta(ks + 1, scale_next, offset_next);
+      }
+      // packed weights of this stage landed, and the buffer's previous reader has retired
+      if (!ptx::MbarWait(&full_tma[s], phase) ||
+          !ptx::MbarWait(&w_empty[b], (static_cast<std::uint32_t>(ks >> 1) & 1u) ^ 1u)) {
+        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      const unsigned char *packed = ring_p + s * kWideStageP + packed_offset;
+      unsigned char *dst = buf_w + b * kWideBufW;
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(packed + sub * 128 * 32);
+        unsigned char *tile = dst + sub * (kWideBufW / 2);
+        *reinterpret_cast<uint4 *>(tile + store_offset[0]) = DequantWord(q.x, magic, offset2[sub], scale2[sub]);
+        *reinterpret_cast<uint4 *>(tile + store_offset[1]) = DequantWord(q.y, magic, offset2[sub], scale2[sub]);
+        *reinterpret_cast<uint4 *>(tile + store_offset[2]) = DequantWord(q.z, magic, offset2[sub], scale2[sub]);
+        *reinterpret_cast<uint4 *>(tile + store_offset[3]) = DequantWord(q.w, magic, offset2[sub], scale2[sub]);
+      }
+      ptx::FenceProxyAsyncShared();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::MbarArrive(&w_full[b]);
+      }
+      if (++s == kWideStages) {
+        s = 0;
+        phase ^= 1u;
+      }
+    }
+
+    // ------------------------------- epilogue -------------------------------
+    if (ok) {
+      if (!ptx::MbarWait(accum_full, 0)) {
+        atomicExch(p.status, kDeviceTimeoutEpilogueBarrier);
+        *abort_flag = 1;
+        ok = false;
+      }
+    }
+    if (ok && *abort_flag == 0) {
+      ptx::TcFenceAfter();
+      const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+      const int sub = (warp - 2) >> 2;         // warps 2..5 read sub-tile 0, warps 6..9 sub-tile 1
+      const int n_local = sub * 128 + quarter * 32 + lane;
+      const std::int64_t col = static_cast<std::int64_t>(n0) + n_local;
+      const float bias = (p.w.bias != nullptr && col < p.w.n) ? __ldg(p.w.bias + col) : 0.0f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kWideTokens; c0 += 32) {
+        std::uint32_t v[32];
+        ptx::TmemLoad32x32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + sub * kWideTokens + c0, v);
+        ptx::TmemLoadWait();
+        if (col < p.w.n) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = m0 + c0 + j;
+            if (m < p.m_total) {
+              p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] =
+                  __uint_as_float(v[j]) + bias;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::TcFenceBefore();
+  __syncthreads();
+  if (warp == 0) {
+    ptx::TcFenceAfter();
+    ptx::TmemDealloc(tmem_base, 512);
+  }
+}
+
 // ---- host side -----------------------------------------------------------------------------
 
 int Log2Of(int v) {
@@ -334,6 +608,7 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
   p.k_steps = static_cast<int>(w.k / kTileK);
   p.status = status_word;
   p.block_shift = Log2Of(w.block_size);
+  p.magic = 0x43004300u;
   auto kernel = nbits_gemm_tcgen05_kernel<BT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) !=
       cudaSuccess) {
@@ -350,6 +625,50 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
                    : (BT == 128 ? "nbits_gemm_tcgen05_kernel<128>" : "nbits_gemm_tcgen05_kernel<64>");
 }
 
+// MNB_GEMM_NARROW=1 keeps the 128-row tiles for every size (A/B measurements).
+bool ForceNarrowTiles() {
+  static const bool value = [] {
+    const char *env = std::getenv("MNB_GEMM_NARROW");
+    return env != nullptr && env[0] == '1';
+  }();
+  return value;
+}
+
+const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
+                       int *status_word, cudaStream_t stream) {
+  CUtensorMap map_a, map_p;
+  if (!EncodeMap2D(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16, static_cast<std::uint64_t>(w.k),
+                   static_cast<std::uint64_t>(m), static_cast<std::uint64_t>(w.k) * 2, kTileK, kWideTokens,
+                   CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return nullptr;
+  }
+  if (!EncodeMap2D(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.b, static_cast<std::uint64_t>(w.row_bytes),
+                   static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.row_bytes), kTileK / 2,
+                   kWideRows, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    return nullptr;
+  }
+  GemmParams p{};
+  p.w = w;
+  p.out = out;
+  p.m_total = static_cast<int>(m);
+  p.k_steps = static_cast<int>(w.k / kTileK);
+  p.status = status_word;
+  p.block_shift = Log2Of(w.block_size);
+  p.magic = 0x43004300u;
+  if (cudaFuncSetAttribute(nbits_gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kWideSmem) != cudaSuccess) {
+    return nullptr;
+  }
+  dim3 grid(static_cast<unsigned>((w.n + kWideRows - 1) / kWideRows),
+            static_cast<unsigned>((m + kWideTokens - 1) / kWideTokens), 1);
+  nbits_gemm_tcgen05_wide_kernel<<<grid, kThreads, kWideSmem, stream>>>(map_a, map_p, p);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_gemm_tcgen05_wide_kernel";
+}
+
 } // namespace
 
 std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k) {
@@ -364,7 +683,7 @@ bool GemmTcgen05Supports(const WeightView &w, std::int64_t m) {
 
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
                               std::uint16_t *a_bf16, OutputView out, int *status_word,
-                              cudaStream_t stream, int sm_count) {
+                              cudaStream_t stream, int sm_count, bool force_wide) {
   if (!GemmTcgen05Supports(w, m) || (reinterpret_cast<std::uintptr_t>(a) & 15u) != 0) {
     return nullptr;
   }
@@ -382,7 +701,12 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   CountLaunch();
   const std::int64_t n_tiles = (w.n + kTileN - 1) / kTileN;
   const int sms = sm_count > 0 ? sm_count : 148;
-  // pick the widest token tile that still gives every SM a tile
+  // large problems: 256 x 256 tiles (half the operand traffic per flop)
+  const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
+  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8 && !ForceNarrowTiles())) {
+    return LaunchWide(w, m, a_bf16, out, status_word, stream);
+  }
+  // otherwise the widest token tile that still gives every SM a tile
   if (m > 128 && n_tiles * ((m + 255) / 256) >= sms) {
     return LaunchTile<256>(w, m, a_bf16, out, status_word, stream);
   }

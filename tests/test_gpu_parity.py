@@ -221,6 +221,21 @@ def test_prefill_tcgen05(cuda_device, m, k, n, bs, zp, bias):
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
 
 
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (512, 4096, 512, 64, True, False),
+    (300, 1024, 700, 32, True, True),      # ragged in both directions, two row tiles
+    (257, 512, 130, 128, False, True),     # one token over a tile boundary
+    (64, 256, 256, 64, True, False),
+])
+def test_prefill_tcgen05_wide_tiles(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("prefill_wide", m, k, n, 4, bs, seed=m + k + n + 1, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_TCGEN05_WIDE)
+    assert kernel == "nbits_gemm_tcgen05_wide_kernel", kernel
+    ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
+    assert rel_err(y, ref_bf16) <= TOL_BF16
+    assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+
+
 def test_prefill_auto_dispatch_and_full_size_property(cuda_device):
     """cfg3 at full size M=2048: a checksum identity instead of a full CPU product. With A = ones
     the result is the per-column sum of the (bf16-rounded) dequantized weights."""
@@ -229,7 +244,7 @@ def test_prefill_auto_dispatch_and_full_size_property(cuda_device):
     case = syn.config3(2048)
     case.a = np.ones_like(case.a)
     y, kernel = run_device(case)
-    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    assert kernel.startswith("nbits_gemm_tcgen05"), kernel
     ints = o.dequant_int(case.b, case.zero_points, case.n, case.k, 4, 64).astype(np.float64)
     scales = np.repeat(case.scales.reshape(case.n, -1).astype(np.float64), 64, axis=1)
     col_sums = (ints * scales).sum(axis=1)
