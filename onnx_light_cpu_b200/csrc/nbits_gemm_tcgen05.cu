@@ -84,37 +84,33 @@ template <int BT> struct GemmSmem {
   static constexpr int kTotal = kStages * kStage + kBarrierBytes + 1024; // + alignment slack
 };
 
-// d = (a & mask) | c in one LOP3 (truth table 0xEA); `c` is kept in a register by the caller.
-__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t mask, std::uint32_t c) {
-  std::uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
-  return d;
-}
-
-// ((x - offset) * scale) on bf16 pairs: the subtraction is exact (small integers), the product
-// is rounded once.
-__device__ __forceinline__ std::uint32_t SubMulBf16x2(std::uint32_t x, std::uint32_t offset, std::uint32_t scale) {
-  std::uint32_t d;
-  asm("{\n\t"
-      ".reg .b32 t;\n\t"
-      "sub.rn.bf16x2 t, %1, %2;\n\t"
-      "mul.rn.bf16x2 %0, t, %3;\n\t"
-      "}"
-      : "=r"(d)
-      : "r"(x), "r"(offset), "r"(scale));
-  return d;
-}
-
-// Dequantizes the 8 nibbles of `w` into one 16-byte chunk of bf16 in the k order 0,4,1,5,2,6,3,7.
-// `magic` = 0x43004300 (128.0 twice), `offset` = (128 + zp) twice, `scale` = block scale twice.
-__device__ __forceinline__ uint4 DequantWord(std::uint32_t w, std::uint32_t magic, std::uint32_t offset,
-                                             std::uint32_t scale) {
-  uint4 out;
-  out.x = SubMulBf16x2(AndOr(w, 0x000f000fu, magic), offset, scale);
-  out.y = SubMulBf16x2(AndOr(w >> 4, 0x000f000fu, magic), offset, scale);
-  out.z = SubMulBf16x2(AndOr(w >> 8, 0x000f000fu, magic), offset, scale);
-  out.w = SubMulBf16x2(AndOr(w >> 12, 0x000f000fu, magic), offset, scale);
-  return out;
+// Dequantizes the 8 nibbles of `w` into one 16-byte chunk of bf16 in the k order 0,4,1,5,2,6,3,7
+// and stores it at shared address `dst`. One asm block so that the four results are born in the
+// register quad the vector store needs. `magic` = 0x43004300 (128.0 twice), `offset` =
+// (128 + zp) twice, `scale` = block scale twice.
+__device__ __forceinline__ void DequantStore(std::uint32_t dst, std::uint32_t w, std::uint32_t magic,
+                                             std::uint32_t offset, std::uint32_t scale) {
+  asm volatile("{\n\t"
+               ".reg .b32 x0, x1, x2, x3, s1, s2, s3;\n\t"
+               "shr.u32 s1, %1, 4;\n\t"
+               "shr.u32 s2, %1, 8;\n\t"
+               "shr.u32 s3, %1, 12;\n\t"
+               "lop3.b32 x0, %1, 0x000f000f, %2, 0xEA;\n\t"
+               "lop3.b32 x1, s1, 0x000f000f, %2, 0xEA;\n\t"
+               "lop3.b32 x2, s2, 0x000f000f, %2, 0xEA;\n\t"
+               "lop3.b32 x3, s3, 0x000f000f, %2, 0xEA;\n\t"
+               "sub.rn.bf16x2 x0, x0, %3;\n\t"
+               "sub.rn.bf16x2 x1, x1, %3;\n\t"
+               "sub.rn.bf16x2 x2, x2, %3;\n\t"
+               "sub.rn.bf16x2 x3, x3, %3;\n\t"
+               "mul.rn.bf16x2 x0, x0, %4;\n\t"
+               "mul.rn.bf16x2 x1, x1, %4;\n\t"
+               "mul.rn.bf16x2 x2, x2, %4;\n\t"
+               "mul.rn.bf16x2 x3, x3, %4;\n\t"
+               "st.shared.v4.b32 [%0], {x0, x1, x2, x3};\n\t"
+               "}" ::"r"(dst),
+               "r"(w), "r"(magic), "r"(offset), "r"(scale)
+               : "memory");
 }
 
 // bf16 pair (v, v) from a float, round to nearest even.
@@ -271,10 +267,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       unsigned char *stage = stage0 + s * Smem::kStage;
       const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset);
-      *reinterpret_cast<uint4 *>(stage + store_offset[0]) = DequantWord(q.x, magic, offset2, scale2);
-      *reinterpret_cast<uint4 *>(stage + store_offset[1]) = DequantWord(q.y, magic, offset2, scale2);
-      *reinterpret_cast<uint4 *>(stage + store_offset[2]) = DequantWord(q.z, magic, offset2, scale2);
-      *reinterpret_cast<uint4 *>(stage + store_offset[3]) = DequantWord(q.w, magic, offset2, scale2);
+      const std::uint32_t base = ptx::SmemAddr(stage);
+      DequantStore(base + store_offset[0], q.x, magic, offset2, scale2);
+      DequantStore(base + store_offset[1], q.y, magic, offset2, scale2);
+      DequantStore(base + store_offset[2], q.z, magic, offset2, scale2);
+      DequantStore(base + store_offset[3], q.w, magic, offset2, scale2);
       // make the generic-proxy stores visible to the tensor core (async proxy), then signal
       ptx::FenceProxyAsyncShared();
       __syncwarp();
@@ -337,13 +334,28 @@ __global__ void __launch_bounds__(kThreads, 1)
 // weights for twice the MMA work of the 128-row kernel, which halves the L2 traffic per flop
 // and lets four stages in flight cover the TMA latency. The dequantized tile is transient, so
 // it lives in its own two buffers instead of the TMA ring.
+#ifdef MNB_TIMELINE
+// Debug builds only: event times (globaltimer ns) of CTA 0 for offline inspection.
+__device__ unsigned long long g_gemm_timeline[4 * 80];
+__device__ __forceinline__ unsigned long long GemmNowNs() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define MNB_GEMM_MARK(row_, ks_) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && (ks_) < 80) g_gemm_timeline[(row_) * 80 + (ks_)] = GemmNowNs(); } while (0)
+#else
+#define MNB_GEMM_MARK(row_, ks_) do { } while (0)
+#endif
+
 constexpr int kWideRows = 256;
 constexpr int kWideTokens = 256;
-constexpr int kWideStages = 4;
+constexpr int kWideStages = 3;
+constexpr int kWideBuffers = 3; // dequantized-weight buffers: the dequantizers run up to two steps ahead
 constexpr int kWideStageA = kWideTokens * 128;   // 32 KB
 constexpr int kWideStageP = kWideRows * 32;      // 8 KB
 constexpr int kWideBufW = kWideRows * 128;       // 32 KB, two 16 KB sub-tiles
-constexpr int kWideSmem = kWideStages * (kWideStageA + kWideStageP) + 2 * kWideBufW + 256 + 1024;
+constexpr int kWideSmem = kWideStages * (kWideStageA + kWideStageP) + kWideBuffers * kWideBufW + 256 + 1024;
 
 __global__ void __launch_bounds__(kThreads, 1)
     nbits_gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -351,14 +363,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
   unsigned char *ring_a = smem;                                     // [stages][32 KB]
-  unsigned char *buf_w = ring_a + kWideStages * kWideStageA;        // [2][32 KB]
-  unsigned char *ring_p = buf_w + 2 * kWideBufW;                    // [stages][8 KB]
+  unsigned char *buf_w = ring_a + kWideStages * kWideStageA;        // [buffers][32 KB]
+  unsigned char *ring_p = buf_w + kWideBuffers * kWideBufW;                    // [stages][8 KB]
   std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(ring_p + kWideStages * kWideStageP);
   std::uint64_t *full_tma = bars;                    // [stages] activations + packed weights landed
   std::uint64_t *empty = bars + kWideStages;         // [stages] MMAs that read the stage retired
-  std::uint64_t *w_full = bars + 2 * kWideStages;    // [2] weights dequantized into the buffer
-  std::uint64_t *w_empty = w_full + 2;               // [2] MMAs that read the buffer retired
-  std::uint64_t *accum_full = w_empty + 2;
+  std::uint64_t *w_full = bars + 2 * kWideStages;    // [buffers] weights dequantized into the buffer
+  std::uint64_t *w_empty = w_full + kWideBuffers;    // [buffers] MMAs that read the buffer retired
+  std::uint64_t *accum_full = w_empty + kWideBuffers;
   std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(accum_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -373,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::MbarInit(&full_tma[s], 1);
       ptx::MbarInit(&empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kWideBuffers; ++b) {
       ptx::MbarInit(&w_full[b], kDequantWarps);
       ptx::MbarInit(&w_empty[b], 1);
     }
@@ -398,11 +410,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       int s = 0;
       std::uint32_t phase = 0;
       for (int ks = 0; ks < p.k_steps; ++ks) {
-        if (!ptx::MbarWait(&empty[s], phase ^ 1u)) {
+        if (!ptx::MbarWaitHot(&empty[s], phase ^ 1u)) {
           atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
           *abort_flag = 1;
           break;
         }
+        MNB_GEMM_MARK(0, ks);
         ptx::MbarArriveExpectTx(&full_tma[s], kWideStageA + kWideStageP);
         ptx::TmaLoad2D(ring_a + s * kWideStageA, &map_a, ks * kTileK, m0, &full_tma[s]);
         ptx::TmaLoad2D(ring_p + s * kWideStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
@@ -418,16 +431,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr std::uint32_t idesc = ptx::UmmaIdescBf16(128, kWideTokens);
       bool ok = true;
       int s = 0;
+      int b = 0;
+      std::uint32_t b_phase = 0;
       for (int ks = 0; ks < p.k_steps; ++ks) {
-        const int b = ks & 1;
         // the buffer's dequantizers waited for the stage's TMA, so the activations are in too
-        if (!ptx::MbarWait(&w_full[b], static_cast<std::uint32_t>(ks >> 1) & 1u)) {
+        if (!ptx::MbarWaitHot(&w_full[b], b_phase)) {
           atomicExch(p.status, kDeviceTimeoutMmaBarrier);
           *abort_flag = 1;
           ok = false;
           break;
         }
         ptx::TcFenceAfter();
+        MNB_GEMM_MARK(3, ks);
         const std::uint32_t sa = ptx::SmemAddr(ring_a + s * kWideStageA);
         const std::uint32_t sw = ptx::SmemAddr(buf_w + b * kWideBufW);
 #pragma unroll
@@ -443,6 +458,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::UmmaCommit(&w_empty[b]);
         if (++s == kWideStages) {
           s = 0;
+        }
+        if (++b == kWideBuffers) {
+          b = 0;
+          b_phase ^= 1u;
         }
       }
       if (ok) {
@@ -496,40 +515,50 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = true;
     int s = 0;
     std::uint32_t phase = 0;
+    int b = 0;
+    std::uint32_t b_phase = 0;
     for (int ks = 0; ks < p.k_steps; ++ks) {
-      const int b = ks & 1;
       const std::uint32_t scale2[2] = {scale_next[0], scale_next[1]};
       const std::uint32_t offset2[2] = {offset_next[0], offset_next[1]};
       if (ks + 1 < p.k_steps) {
         load_meta(ks + 1, scale_next, offset_next);
       }
       // packed weights of this stage landed, and the buffer's previous reader has retired
-      if (!ptx::MbarWait(&full_tma[s], phase) ||
-          !ptx::MbarWait(&w_empty[b], (static_cast<std::uint32_t>(ks >> 1) & 1u) ^ 1u)) {
+      if (!ptx::MbarWaitHot(&full_tma[s], phase) || !ptx::MbarWaitHot(&w_empty[b], b_phase ^ 1u)) {
         atomicExch(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
         break;
+      }
+      if (tid == 64) {
+        MNB_GEMM_MARK(1, ks);
       }
       const unsigned char *packed = ring_p + s * kWideStageP + packed_offset;
       unsigned char *dst = buf_w + b * kWideBufW;
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         const uint4 q = *reinterpret_cast<const uint4 *>(packed + sub * 128 * 32);
-        unsigned char *tile = dst + sub * (kWideBufW / 2);
-        *reinterpret_cast<uint4 *>(tile + store_offset[0]) = DequantWord(q.x, magic, offset2[sub], scale2[sub]);
-        *reinterpret_cast<uint4 *>(tile + store_offset[1]) = DequantWord(q.y, magic, offset2[sub], scale2[sub]);
-        *reinterpret_cast<uint4 *>(tile + store_offset[2]) = DequantWord(q.z, magic, offset2[sub], scale2[sub]);
-        *reinterpret_cast<uint4 *>(tile + store_offset[3]) = DequantWord(q.w, magic, offset2[sub], scale2[sub]);
+        const std::uint32_t tile = ptx::SmemAddr(dst + sub * (kWideBufW / 2));
+        DequantStore(tile + store_offset[0], q.x, magic, offset2[sub], scale2[sub]);
+        DequantStore(tile + store_offset[1], q.y, magic, offset2[sub], scale2[sub]);
+        DequantStore(tile + store_offset[2], q.z, magic, offset2[sub], scale2[sub]);
+        DequantStore(tile + store_offset[3], q.w, magic, offset2[sub], scale2[sub]);
       }
       ptx::FenceProxyAsyncShared();
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&w_full[b]);
       }
+      if (tid == 64) {
+        MNB_GEMM_MARK(2, ks);
+      }
       if (++s == kWideStages) {
         s = 0;
         phase ^= 1u;
+      }
+      if (++b == kWideBuffers) {
+        b = 0;
+        b_phase ^= 1u;
       }
     }
 
@@ -670,6 +699,12 @@ const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t 
 }
 
 } // namespace
+
+#ifdef MNB_TIMELINE
+extern "C" int mnb_debug_copy_gemm_timeline(unsigned long long *host, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_gemm_timeline, sizeof(unsigned long long) * count));
+}
+#endif
 
 std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k) {
   return static_cast<std::size_t>(m) * static_cast<std::size_t>(k) * 2;

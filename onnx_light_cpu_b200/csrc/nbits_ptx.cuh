@@ -65,6 +65,20 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t *bar, std::uint32_t parit
   return false;
 }
 
+// Same bound, for waits on the critical path of a pipeline (a hand-off that is normally a few
+// hundred nanoseconds away): keeps polling without backing off for longer before it sleeps.
+__device__ __forceinline__ bool MbarWaitHot(std::uint64_t *bar, std::uint32_t parity) {
+  for (std::uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (MbarTryWait(bar, parity)) {
+      return true;
+    }
+    if (spin > 2048) {
+      __nanosleep(128);
+    }
+  }
+  return false;
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
 // Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
 __device__ __forceinline__ void BulkLoad(void *smem_dst, const void *gmem_src, std::uint32_t bytes,
