@@ -216,6 +216,11 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     if (name == nullptr && m <= 16) {
       name = mnb::LaunchGemvStream(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO) {
+      // shapes the CUDA-core kernel cannot stage (very long K with several tokens): many passes of
+      // the tensor-core kernel still beat the generic one by a wide margin
+      name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
     if (name == nullptr) {
       name = mnb::LaunchGemvGeneric(w, a_dev, m, out, stream);
     }

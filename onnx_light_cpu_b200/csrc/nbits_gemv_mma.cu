@@ -61,6 +61,10 @@ constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kThreads = (kWarps + 1) * 32;
 constexpr int kMaxSlots = 32;
 constexpr int kMaxTokens = 4;             // most activation rows handled per CTA pass
+#ifndef MNB_MMA_UNROLL
+#define MNB_MMA_UNROLL 4
+#endif
+constexpr int kUnroll = MNB_MMA_UNROLL;   // supergroups per loop round (1, 2 or 4)
 
 struct MmaParams {
   WeightView w;
@@ -209,30 +213,35 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_b);
       int task = 0;
+      int slot = 0;              // task % num_slots, kept incrementally
+      std::uint32_t round = 0;   // task / num_slots
       bool ok = true;
       const std::uint32_t box_bytes = 16u * static_cast<std::uint32_t>(p.slice_b_bytes);
+      const int x_step = p.slice_b_bytes / 4;
+      const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
       for (int wave0 = 0; wave0 < n_tiles && ok; wave0 += kPairs) {
         const int wave_tiles = n_tiles - wave0 < kPairs ? n_tiles - wave0 : kPairs;
-        for (int s = 0; s < p.slices && ok; ++s) {
-          for (int wt = 0; wt < wave_tiles; ++wt, ++task) {
-            const int slot = task % p.num_slots;
-            const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
-            if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+        const unsigned char *meta_slice = p.w.meta + static_cast<std::int64_t>(h_begin + 2 * wave0) * p.rec_bytes;
+        for (int s = 0; s < p.slices && ok; ++s, meta_slice += meta_slice_stride) {
+          int h0 = h_begin + 2 * wave0;
+          const unsigned char *meta_src = meta_slice;
+          for (int wt = 0; wt < wave_tiles; ++wt, ++task, h0 += 2, meta_src += 2 * p.rec_bytes) {
+            if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
               atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
               ok = false;
               break;
             }
-            const int h0 = h_begin + 2 * (wave0 + wt);
-            const int valid_halves = h0 + 1 < p.half_tiles ? 2 : 1;
+            const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
             unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
-            const std::uint32_t meta_bytes = static_cast<std::uint32_t>(valid_halves) * p.rec_bytes;
             slot_task[slot] = task;
             MNB_MARK(32 + task);
             ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
-            ptx::TmaLoad2D(dst, &map_b, s * (p.slice_b_bytes / 4), h0 * 8, &full_bar[slot]);
-            ptx::BulkLoad(dst + box_bytes,
-                          p.w.meta + (static_cast<std::int64_t>(s) * p.half_tiles + h0) * p.rec_bytes, meta_bytes,
-                          &full_bar[slot]);
+            ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
+            ptx::BulkLoad(dst + box_bytes, meta_src, meta_bytes, &full_bar[slot]);
+            if (++slot == p.num_slots) {
+              slot = 0;
+              ++round;
+            }
           }
         }
       }
@@ -442,11 +451,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt;
       const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * 256;
 
-      for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += 4) {
-        // scales / zero points of the four supergroups of this round
-        float s0v[4], s1v[4];
-        std::uint32_t z0v[4], z1v[4];
-        if constexpr (!BIG_BLOCK && NB_SG_LOG2 == 0) {
+      for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += kUnroll) {
+        // scales / zero points of the supergroups of this round
+        float s0v[kUnroll], s1v[kUnroll];
+        std::uint32_t z0v[kUnroll], z1v[kUnroll];
+        if constexpr (!BIG_BLOCK && NB_SG_LOG2 == 0 && kUnroll == 4) {
           // one block per supergroup: four consecutive blocks, one vector load each
           const float4 a4 = *reinterpret_cast<const float4 *>(sc0 + sg0);
           const float4 b4 = *reinterpret_cast<const float4 *>(sc1 + sg0);
@@ -462,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         } else {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < kUnroll; ++u) {
             const int sg = sg0 + u;
             const int blk_codes = BIG_BLOCK ? sg / p.sg_per_block : sg * kNb + tb;
             const int blk_acc = BIG_BLOCK ? blk_codes : sg * kNb + blk_d;
@@ -475,7 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kUnroll; ++u) {
           const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + u * 64);
           const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + u * 64);
           const std::uint32_t offs0 = HAS_ZP ? z0v[u] : default_offs; // (1024 + zp) twice
@@ -511,9 +520,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             acc1 = fmaf(s1v[u], (da[2] + da[3]) + (db[2] + db[3]), acc1);
           }
         }
-        row_lo += 256;
-        row_hi += 256;
-        act_task += 1024;
+        row_lo += 64 * kUnroll;
+        row_hi += 64 * kUnroll;
+        act_task += 256 * kUnroll;
       }
       __syncwarp();
       if (lane == 0) {
@@ -623,14 +632,12 @@ MetaGeometry MetaGeometryOf(const WeightView &w) {
       GetEncodeTiled() == nullptr) {
     return geo; // unsupported: bytes == 0
   }
+  // a task covers 2048 k of 16 rows (16 KB of packed weights): 64 / 32 / 16 / 8 ... blocks
   int bpt = 2048 / w.block_size;
-  if (bpt > 16) {
-    bpt = 16;
-  }
   const char *override_bpt = std::getenv("MNB_GEMV_BLOCKS_PER_TASK");
   if (override_bpt != nullptr) {
     const int v = std::atoi(override_bpt);
-    if (v >= 2 && v <= 16 && (v & (v - 1)) == 0 && v * w.block_size >= 128 && v * w.block_size <= 2048) {
+    if (v >= 2 && v <= 64 && (v & (v - 1)) == 0 && v * w.block_size >= 512 && v * w.block_size <= 2048) {
       bpt = v;
     }
   }
