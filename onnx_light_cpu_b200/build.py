@@ -23,6 +23,7 @@ CUDA_SOURCES = [
     "csrc/nbits_gemv.cu",
     "csrc/nbits_gemv_mma.cu",
     "csrc/nbits_int8.cu",
+    "csrc/nbits_int8_mma.cu",
     "csrc/nbits_gemm_tcgen05.cu",
 ]
 CUDA_HEADERS = ["csrc/nbits_common.cuh", "csrc/nbits_ptx.cuh", "../include/matmulnbits_b200.h"]

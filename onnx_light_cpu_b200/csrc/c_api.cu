@@ -196,7 +196,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
   int chosen = path;
   if (chosen == MNB_PATH_AUTO) {
     if (accuracy_level == 4) {
-      chosen = MNB_PATH_INT8;
+      chosen = MNB_PATH_INT8_MMA; // falls through to the dp4a kernel when the shape does not fit
     } else if (m <= 16) {
       chosen = MNB_PATH_GEMV;
     } else {
@@ -247,6 +247,26 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
                                   h->status_dev, stream, h->sm_count, chosen == MNB_PATH_TCGEN05_WIDE);
     break;
   }
+  case MNB_PATH_INT8_MMA: {
+    const std::size_t need = mnb::Int8MmaScratchBytes(w, m);
+    if (need != 0) {
+      const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchInt8Mma(w, a_dev, m, static_cast<unsigned char *>(h->scratch_a), out, h->status_dev,
+                                stream, h->sm_count);
+    }
+    if (name != nullptr) {
+      break;
+    }
+    if (path == MNB_PATH_INT8_MMA) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the integer-MMA path needs bits=4, 32 <= block_size <= 1024 and packed "
+                  "rows that are a multiple of 128 bytes.");
+    }
+  }
+    [[fallthrough]];
   case MNB_PATH_INT8: {
     const std::size_t aq_bytes = static_cast<std::size_t>(m) * w.n_blocks * w.block_size;
     int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, aq_bytes);

@@ -109,6 +109,12 @@ const char *LaunchInt8BlockDots(const WeightView &w, const std::int8_t *aq, std:
 const char *LaunchInt8Matmul(const WeightView &w, const std::int8_t *aq, const float *a_scales,
                              std::int64_t m, OutputView out, cudaStream_t stream, int sm_count);
 
+// accuracy_level 4 on integer MMA: quantizes `a` into `scratch` (Int8MmaScratchBytes, 0 when the
+// shape is outside what the kernel takes) and multiplies.
+std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m);
+const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                          OutputView out, int *status_word, cudaStream_t stream, int sm_count);
+
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 
 void CountLaunch(int launches = 1);

@@ -1,0 +1,630 @@
+// accuracy_level = 4 path of MatMulNBits on integer tensor-core MMA (mma.sync m16n8k32, u8 x s8).
+//
+// Definition of the level (owned by this project, see nbits_int8.cu): activations are quantized
+// per (token, quantization block) to int8, the block dot products sum aq * (q - zp) are exact
+// int32 and are combined in fp32 as  Y += (sa * scale) * float(dot).
+//
+// Mapping. The 4-bit codes are the MMA "A" operand as unsigned bytes: a lane loads one 32-bit
+// word (eight codes of one weight row), `w & 0x0f0f0f0f` and `(w >> 4) & 0x0f0f0f0f` are two
+// A registers. That places codes 0,2,4,6 of the word in k slots 4t..4t+3 and codes 1,3,5,7 in
+// slots 16+4t..16+4t+3 of the 32-wide step; the activations are stored in that order by the
+// quantization kernel, so no shuffle is needed. The zero point is taken out afterwards with
+// the per-block activation sums: sum aq*(q - zp) = D - zp * sum aq. One MMA step covers 32
+// consecutive k, so a quantization block (32, 64, 128, ...) is a whole number of steps and the
+// int32 accumulator restarts at each block.
+//
+// Data movement. Persistent CTA per SM, a producer lane fills a ring of 16 KB tasks (16 weight
+// rows x 2048 k) with one 3-D tiled TMA load each - box {128 bytes, 16 rows, 8 segments} with
+// the 128-byte swizzle, so that the eight lanes that read the same 16-byte column of eight
+// different rows hit eight different banks - plus one bulk copy of the task's scales and zero
+// points from the prepared side array shared with the fp32 decode kernel. The quantized
+// activations of a pass (8 or 16 tokens), their scales and sums arrive with one bulk copy.
+// Sixteen consumer warps share every task (one 128-k group each) and their sums are added
+// through shared memory once per row tile. Every wait on data is bounded.
+//
+// Conventions: packed-INT4 nibble order of
+// onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:60-93; u8 x s8 -> s32 dot and
+// zero-point correction through sums as in the same file, :48-56 and :208-223.
+
+#include "nbits_common.cuh"
+#include "nbits_ptx.cuh"
+#include "nbits_tma.cuh"
+
+#include <cstdint>
+
+namespace mnb {
+namespace {
+
+constexpr int kWarps = 16;                   // consumer warps = 128-k groups of a task
+constexpr int kConsumerThreads = kWarps * 32;
+constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kMaxSlots = 16;
+constexpr int kTaskK = 2048;                 // k per task
+constexpr int kTaskBytes = 16 * kTaskK / 2;  // packed weights of a task: 16 rows
+constexpr int kSegments = kTaskK / 256;      // 128-byte segments per row inside a task
+
+struct ImmaParams {
+  WeightView w;
+  const unsigned char *act; // [passes][pass_bytes]: quantized activations, then scales and sums
+  int m_total;
+  OutputView out;
+  int *status;
+  int half_tiles;
+  int bpt;             // quantization blocks per task
+  int slices;          // tasks per row tile
+  int rec_bytes;
+  int rec_scale_bytes;
+  int slot_bytes;
+  int num_slots;
+  int tp;              // tokens per pass (8 or 16)
+  int act_row_bytes;   // bytes between token rows of the quantized activations
+  int table_offset;    // byte offset of the scale / sum table inside a pass
+  int pass_bytes;
+  int groups_per_block; // 128-k groups per quantization block (block_size >= 256), else 1
+};
+static_assert(kTaskK == kWarps * 128, "one 128-k group of a task per consumer warp");
+
+__device__ __forceinline__ void MmaU8S8(int (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                        std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void MmaU8S8Zero(int (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                            std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ void TmaLoad3D(void *smem_dst, const void *tensor_map, int x, int y, int z,
+                                          std::uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(ptx::SmemAddr(smem_dst)),
+               "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(ptx::SmemAddr(bar))
+               : "memory");
+}
+
+// Byte position of activation k inside a token row: 128-k group major, then the quad lane
+// t = (k / 8) % 4 that consumes it, the step s = (k / 32) % 4, then even k before odd k.
+__host__ __device__ inline int ActBytePosition(int k) {
+  const int j = k & 7;
+  const int t = (k >> 3) & 3;
+  const int s = (k >> 5) & 3;
+  return ((k >> 7) << 7) + (t << 5) + (s << 3) + ((j & 1) ? 4 + (j >> 1) : (j >> 1));
+}
+
+// Quantizes one pass layout: one warp per (token slot, table entry) over passes * tp slots and
+// the task-padded entry count. An entry covers min(block_size, 128) consecutive k: a whole
+// quantization block, or a 128-k part of a larger one (same scale, its own sum). Slots beyond
+// M, entries beyond the last block and k beyond K become zeros.
+__global__ void __launch_bounds__(256)
+    nbits_quantize_a_imma_kernel(const float *a, int m_total, std::int64_t k, int block_size, int entry_k,
+                                 int entries_pad, int tp, int act_row_bytes, int table_offset, int pass_bytes,
+                                 int passes, unsigned char *act) {
+  // the multiply kernel behind this one may start (barrier set-up, first weight tiles) right away
+  ptx::GridDependencyLaunch();
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::int64_t item = static_cast<std::int64_t>(blockIdx.x) * 8 + warp;
+  if (item >= static_cast<std::int64_t>(passes) * tp * entries_pad) {
+    return;
+  }
+  const int slot = static_cast<int>(item / entries_pad);
+  const int entry = static_cast<int>(item - static_cast<std::int64_t>(slot) * entries_pad);
+  const int pass = slot / tp;
+  const int token = slot - pass * tp;
+  const int row = slot; // passes are consecutive groups of tp tokens
+  const std::int64_t e0 = static_cast<std::int64_t>(entry) * entry_k;
+  const std::int64_t k0 = e0 / block_size * block_size; // start of the enclosing quantization block
+  const bool live = row < m_total;
+  const float *src = a + static_cast<std::int64_t>(row) * k;
+  float amax = 0.0f;
+  if (live) {
+    for (int e = lane; e < block_size; e += 32) {
+      if (k0 + e < k) {
+        amax = fmaxf(amax, fabsf(src[k0 + e]));
+      }
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  }
+  const float sa = __fdiv_rn(amax, 127.0f);
+  unsigned char *base = act + static_cast<std::int64_t>(pass) * pass_bytes;
+  std::int8_t *dst = reinterpret_cast<std::int8_t *>(base) + static_cast<std::int64_t>(token) * act_row_bytes;
+  int sum = 0;
+  for (int e = lane; e < entry_k; e += 32) {
+    const std::int64_t kk = e0 + e;
+    int q = 0;
+    if (live && kk < k && sa > 0.0f) {
+      const float r = rintf(__fdiv_rn(src[kk], sa));
+      q = static_cast<int>(fminf(127.0f, fmaxf(-127.0f, r)));
+    }
+    sum += q;
+    dst[ActBytePosition(static_cast<int>(kk))] = static_cast<std::int8_t>(q);
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+  }
+  if (lane == 0) {
+    unsigned char *cell = base + table_offset + static_cast<std::int64_t>(entry) * tp * 8;
+    reinterpret_cast<float *>(cell)[token] = sa;
+    reinterpret_cast<int *>(cell + tp * 4)[token] = sum;
+  }
+}
+
+// NT: 8-token column tiles per pass (tp = 8 * NT). SPB: 32-k steps per table entry: 1 / 2 for
+// block_size 32 / 64, 4 for block_size >= 128.
+//
+// All sixteen consumer warps work on the same task: warp w takes the 128-k group w of its 2048
+// k. The ring therefore only has to cover the memory latency, every warp is busy whatever the
+// number of row tiles of the CTA, and the pipeline starts with the first task that lands. The
+// price is a sum over the sixteen warps per row tile, done through shared memory by NT warps
+// (rotating with the tile index) while the others go on with the next tile.
+template <int NT, int SPB, bool HAS_ZP>
+__global__ void __launch_bounds__(kThreads, 1)
+    nbits_int8_mma_kernel(const __grid_constant__ CUtensorMap map_b, const ImmaParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  unsigned char *smem_raw = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
+  // layout: [slots][activations of the pass + table][partial sums: 2 x 16 warps][barriers]
+  unsigned char *slots = smem_raw;
+  unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
+  float4 *partial = reinterpret_cast<float4 *>(act + p.pass_bytes); // [2][kWarps][NT][32]
+  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(partial + 2 * kWarps * NT * 32);
+  std::uint64_t *empty_bar = full_bar + kMaxSlots;
+  std::uint64_t *act_bar = empty_bar + kMaxSlots;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int m_base = blockIdx.y * p.tp;
+
+  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * p.half_tiles / gridDim.x);
+  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * p.half_tiles / gridDim.x);
+  const int n_tiles = (h_end - h_begin + 1) >> 1;
+  const std::int64_t row_limit =
+      static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
+
+  if (warp == kWarps) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      for (int s = 0; s < p.num_slots; ++s) {
+        ptx::MbarInit(&full_bar[s], 1);
+        ptx::MbarInit(&empty_bar[s], kWarps);
+      }
+      ptx::MbarInit(act_bar, 1);
+      ptx::FenceMbarInit();
+    }
+    __syncwarp();
+    asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
+    if (lane == 0) {
+      ptx::PrefetchTensorMap(&map_b);
+      int task = 0;
+      int slot = 0;
+      std::uint32_t round = 0;
+      bool ok = true;
+      bool act_issued = false;
+      const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
+      // The quantized activations come from the kernel launched just before this one, which may
+      // still be running (programmatic dependent launch): the weights do not depend on it, so a
+      // first ring of weight tiles is requested before waiting for that kernel.
+      auto issue_activations = [&]() {
+        ptx::GridDependencyWait();
+        ptx::MbarArriveExpectTx(act_bar, static_cast<std::uint32_t>(p.pass_bytes));
+        ptx::BulkLoad(act, p.act + static_cast<std::int64_t>(blockIdx.y) * p.pass_bytes,
+                      static_cast<std::uint32_t>(p.pass_bytes), act_bar);
+        act_issued = true;
+      };
+      for (int tile = 0; tile < n_tiles && ok; ++tile) {
+        const int h0 = h_begin + 2 * tile;
+        const unsigned char *meta_src = p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes;
+        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+        for (int s = 0; s < p.slices; ++s, ++task, meta_src += meta_slice_stride) {
+          if (round != 0) {
+            if (!act_issued) {
+              issue_activations();
+            }
+            if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+              atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+              ok = false;
+              break;
+            }
+          }
+          unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+          ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
+          TmaLoad3D(dst, &map_b, 0, h0 * 8, s * kSegments, &full_bar[slot]);
+          ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
+          if (++slot == p.num_slots) {
+            slot = 0;
+            ++round;
+          }
+        }
+      }
+      if (!act_issued) {
+        issue_activations();
+      }
+      // stay until every copy issued has been consumed (bounded), so none lands after exit
+      const int first = task - p.num_slots < 0 ? 0 : task - p.num_slots;
+      for (int i = first; i < task && ok; ++i) {
+        if (!ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
+          break;
+        }
+      }
+      ptx::MbarWait(act_bar, 0);
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory"); // barriers initialised
+  bool dead = false; // a bounded wait gave up: skip the math, keep the barrier protocol
+  if (!ptx::MbarWait(act_bar, 0)) {
+    atomicExch(p.status, kDeviceTimeoutFullBarrier);
+    dead = true;
+  }
+
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const std::uint32_t nib = 0x0f0f0f0fu;
+  // this warp's 128-k group inside every task: segment warp / 2, chunks 4 * (warp % 2) + step.
+  // Byte offset of the lane's word for each step (rows g; rows g + 8 are 1024 bytes further):
+  int word_off[4];
+#pragma unroll
+  for (int st = 0; st < 4; ++st) {
+    const int c = (warp & 1) * 4 + st;
+    word_off[st] = (warp >> 1) * 2048 + g * 128 + ((c ^ g) << 4) + 4 * t;
+  }
+  constexpr int kEntriesPerGroup = 4 / SPB;
+  const int scale_row_bytes = (p.bpt + 4) * 4;
+  // scale / zero-point index of this warp's first block inside a task record row
+  const int meta_index = p.groups_per_block > 1 ? warp / p.groups_per_block : warp * kEntriesPerGroup;
+  const int entry_bytes = p.tp * 8;
+  const int entries_per_task = 16 * kEntriesPerGroup;
+  const unsigned char *table = act + p.table_offset + 8 * t + warp * kEntriesPerGroup * entry_bytes;
+  const unsigned char *act_lane = act + g * p.act_row_bytes + t * 32 + warp * 128;
+
+  int task = 0;
+  int slot = 0;
+  std::uint32_t round = 0;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int h0 = h_begin + 2 * tile;
+    const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
+    float acc[NT][4];
+    int d[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[nt][i] = 0.0f;
+        d[nt][i] = 0;
+      }
+    }
+
+    for (int s = 0; s < p.slices; ++s, ++task) {
+      if (!dead && !ptx::MbarWait(&full_bar[slot], round & 1u)) {
+        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        dead = true;
+      }
+      if (!dead) {
+        const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
+        std::uint32_t w_lo[4], w_hi[4];
+#pragma unroll
+        for (int st = 0; st < 4; ++st) {
+          w_lo[st] = *reinterpret_cast<const std::uint32_t *>(sb + word_off[st]);
+          w_hi[st] = *reinterpret_cast<const std::uint32_t *>(sb + word_off[st] + 1024);
+        }
+        const unsigned char *meta0 = sb + kTaskBytes;
+        const unsigned char *meta1 = meta0 + p.rec_bytes;
+        const float *sc0 = reinterpret_cast<const float *>(meta0 + g * scale_row_bytes) + meta_index;
+        const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes) + meta_index;
+        float ws_lo[kEntriesPerGroup], ws_hi[kEntriesPerGroup];
+        int zp_lo[kEntriesPerGroup], zp_hi[kEntriesPerGroup];
+        if constexpr (SPB == 1) {
+          const float4 a4 = *reinterpret_cast<const float4 *>(sc0);
+          const float4 b4 = *reinterpret_cast<const float4 *>(sc1);
+          ws_lo[0] = a4.x, ws_lo[1] = a4.y, ws_lo[2] = a4.z, ws_lo[3] = a4.w;
+          ws_hi[0] = b4.x, ws_hi[1] = b4.y, ws_hi[2] = b4.z, ws_hi[3] = b4.w;
+        } else if constexpr (SPB == 2) {
+          const float2 a2 = *reinterpret_cast<const float2 *>(sc0);
+          const float2 b2 = *reinterpret_cast<const float2 *>(sc1);
+          ws_lo[0] = a2.x, ws_lo[1] = a2.y, ws_hi[0] = b2.x, ws_hi[1] = b2.y;
+        } else {
+          ws_lo[0] = sc0[0], ws_hi[0] = sc1[0];
+        }
+        if constexpr (HAS_ZP) {
+          const unsigned char *zr0 = meta0 + p.rec_scale_bytes + g * p.bpt + meta_index;
+          const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt + meta_index;
+          if constexpr (SPB == 1) {
+            const std::uint32_t za = *reinterpret_cast<const std::uint32_t *>(zr0);
+            const std::uint32_t zb = *reinterpret_cast<const std::uint32_t *>(zr1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              zp_lo[i] = static_cast<int>((za >> (8 * i)) & 0xffu);
+              zp_hi[i] = static_cast<int>((zb >> (8 * i)) & 0xffu);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < kEntriesPerGroup; ++i) {
+              zp_lo[i] = zr0[i];
+              zp_hi[i] = zr1[i];
+            }
+          }
+        }
+        // activations of the four steps: 32 bytes per lane and column tile
+        uint4 bq[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const unsigned char *src = act_lane + static_cast<size_t>(s) * kTaskK + nt * 8 * p.act_row_bytes;
+          bq[nt][0] = *reinterpret_cast<const uint4 *>(src);
+          bq[nt][1] = *reinterpret_cast<const uint4 *>(src + 16);
+        }
+        // the weights are in registers: hand the slot back before the arithmetic
+        __syncwarp();
+        if (lane == 0) {
+          ptx::MbarArrive(&empty_bar[slot]);
+        }
+        const unsigned char *cell = table + static_cast<size_t>(s) * entries_per_task * entry_bytes;
+#pragma unroll
+        for (int st = 0; st < 4; ++st) {
+          const std::uint32_t a0 = w_lo[st] & nib;
+          const std::uint32_t a1 = w_hi[st] & nib;
+          const std::uint32_t a2 = (w_lo[st] >> 4) & nib;
+          const std::uint32_t a3 = (w_hi[st] >> 4) & nib;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 &q = bq[nt][st >> 1];
+            const std::uint32_t b0 = (st & 1) ? q.z : q.x;
+            const std::uint32_t b1 = (st & 1) ? q.w : q.y;
+            if ((st % SPB) == 0) {
+              MmaU8S8Zero(d[nt], a0, a1, a2, a3, b0, b1);
+            } else {
+              MmaU8S8(d[nt], a0, a1, a2, a3, b0, b1);
+            }
+          }
+          if (((st + 1) % SPB) == 0) {
+            // a table entry is complete: D - zp * sum(aq), scaled, into the fp32 sums
+            const int idx = st / SPB;
+            const int zl = HAS_ZP ? zp_lo[idx] : 8;
+            const int zh = HAS_ZP ? zp_hi[idx] : 8;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const float2 sa = *reinterpret_cast<const float2 *>(cell + idx * entry_bytes + nt * 32);
+              const int2 sum = *reinterpret_cast<const int2 *>(cell + idx * entry_bytes + p.tp * 4 + nt * 32);
+              const int e0 = d[nt][0] - zl * sum.x;
+              const int e1 = d[nt][1] - zl * sum.y;
+              const int e2 = d[nt][2] - zh * sum.x;
+              const int e3 = d[nt][3] - zh * sum.y;
+              acc[nt][0] = fmaf(sa.x * ws_lo[idx], static_cast<float>(e0), acc[nt][0]);
+              acc[nt][1] = fmaf(sa.y * ws_lo[idx], static_cast<float>(e1), acc[nt][1]);
+              acc[nt][2] = fmaf(sa.x * ws_hi[idx], static_cast<float>(e2), acc[nt][2]);
+              acc[nt][3] = fmaf(sa.y * ws_hi[idx], static_cast<float>(e3), acc[nt][3]);
+            }
+          }
+        }
+      }
+      if (++slot == p.num_slots) {
+        slot = 0;
+        ++round;
+      }
+    }
+
+    // ---- sum over the sixteen warps -----------------------------------------------------------
+    // Buffer b = tile % 2. Named barriers 2 + b ("partials of this tile written") and 4 + b
+    // ("buffer read, may be overwritten"), 512 participants each: the NT reducing warps of a
+    // tile wait on the first and arrive on the second, everybody else the other way round.
+    const int b = tile & 1;
+    const int reducer0 = (tile * NT) & (kWarps - 1);
+    const bool reduces = ((warp - reducer0) & (kWarps - 1)) < NT;
+    if (tile >= 2) {
+      const int previous0 = ((tile - 2) * NT) & (kWarps - 1);
+      const bool reduced_previous = ((warp - previous0) & (kWarps - 1)) < NT;
+      if (!reduced_previous) {
+        asm volatile("bar.sync %0, %1;" ::"r"(4 + b), "n"(kConsumerThreads) : "memory");
+      }
+    }
+    float4 *mine = partial + ((b * kWarps + warp) * NT) * 32 + lane;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      mine[nt * 32] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+    }
+    if (!reduces) {
+      asm volatile("bar.arrive %0, %1;" ::"r"(2 + b), "n"(kConsumerThreads) : "memory");
+    } else {
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + b), "n"(kConsumerThreads) : "memory");
+      const int nt = (warp - reducer0) & (kWarps - 1);
+      const float4 *column = partial + (b * kWarps * NT + nt) * 32 + lane;
+      float4 total = column[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) {
+        const float4 v = column[w * NT * 32];
+        total.x += v.x, total.y += v.y, total.z += v.z, total.w += v.w;
+      }
+      if (tile + 2 < n_tiles) {
+        asm volatile("bar.arrive %0, %1;" ::"r"(4 + b), "n"(kConsumerThreads) : "memory");
+      }
+      const std::int64_t r_lo = row0 + g;
+      const std::int64_t r_hi = row0 + g + 8;
+      const float bias_lo = (p.w.bias != nullptr && r_lo < row_limit) ? __ldg(p.w.bias + r_lo) : 0.0f;
+      const float bias_hi = (p.w.bias != nullptr && r_hi < row_limit) ? __ldg(p.w.bias + r_hi) : 0.0f;
+      const std::int64_t m0 = m_base + nt * 8 + 2 * t;
+      float *y0 = p.out.y + m0 * p.out.ld + p.out.col_offset;
+      float *y1 = y0 + p.out.ld;
+      if (m0 < p.m_total) {
+        if (r_lo < row_limit) {
+          y0[r_lo] = total.x + bias_lo;
+        }
+        if (r_hi < row_limit) {
+          y0[r_hi] = total.z + bias_hi;
+        }
+      }
+      if (m0 + 1 < p.m_total) {
+        if (r_lo < row_limit) {
+          y1[r_lo] = total.y + bias_lo;
+        }
+        if (r_hi < row_limit) {
+          y1[r_hi] = total.w + bias_hi;
+        }
+      }
+    }
+  }
+}
+
+bool EncodeWeightsMap3D(CUtensorMap *map, const WeightView &w) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr) {
+    return false;
+  }
+  // a packed row seen as [segments][32 words]; dimension order: word, row, segment
+  const cuuint64_t dims[3] = {32, static_cast<cuuint64_t>(w.n), static_cast<cuuint64_t>(w.row_bytes / 128)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(w.row_bytes), 128};
+  const cuuint32_t box[3] = {32, 16, kSegments};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<std::uint8_t *>(w.b), dims, strides, box,
+                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct ImmaGeometry {
+  bool ok;
+  int tp;
+  int passes;
+  int act_row_bytes;
+  int table_offset;
+  int pass_bytes;
+  int entry_k;      // k covered by one scale / sum table entry: min(block_size, 128)
+  int entries_pad;  // table entries of a token, padded to whole tasks
+  int slot_bytes;
+  int num_slots;
+  std::size_t smem;
+};
+
+ImmaGeometry ImmaGeometryOf(const WeightView &w, std::int64_t m) {
+  ImmaGeometry geo{};
+  const MetaGeometry meta = MetaGeometryOf(w);
+  if (meta.bytes == 0 || meta.bpt * w.block_size != kTaskK || (w.row_bytes % 128) != 0 || m < 1 ||
+      (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0) {
+    return geo;
+  }
+  const int k_pad = meta.slices * kTaskK;
+  geo.entry_k = w.block_size < 128 ? w.block_size : 128;
+  geo.entries_pad = k_pad / geo.entry_k;
+  geo.slot_bytes = (kTaskBytes + 2 * meta.rec_bytes + 1023) & ~1023;
+  const std::size_t limit = 225 * 1024;
+  for (int tp = m > 8 ? 16 : 8; tp >= 8; tp -= 8) {
+    geo.tp = tp;
+    geo.act_row_bytes = k_pad + 16; // 16: rows of a column tile land on different banks
+    geo.table_offset = tp * geo.act_row_bytes;
+    geo.pass_bytes = geo.table_offset + geo.entries_pad * tp * 8;
+    const std::size_t fixed = static_cast<std::size_t>(geo.pass_bytes) +
+                              2 * kWarps * (tp / 8) * 32 * sizeof(float4) +
+                              (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64;
+    if (geo.pass_bytes < (1 << 20) && fixed + 2 * static_cast<std::size_t>(geo.slot_bytes) + 1024 <= limit) {
+      int slots = static_cast<int>((limit - fixed - 1024) / geo.slot_bytes);
+      geo.num_slots = slots > kMaxSlots ? kMaxSlots : slots;
+      geo.smem = static_cast<std::size_t>(geo.num_slots) * geo.slot_bytes + fixed + 1024;
+      geo.passes = static_cast<int>((m + tp - 1) / tp);
+      geo.ok = true;
+      return geo;
+    }
+  }
+  return geo;
+}
+
+} // namespace
+
+std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m) {
+  const ImmaGeometry geo = ImmaGeometryOf(w, m);
+  return geo.ok ? static_cast<std::size_t>(geo.passes) * geo.pass_bytes : 0;
+}
+
+// Quantizes `a` into `scratch` (Int8MmaScratchBytes) and runs the integer-MMA kernel.
+const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                          OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+  const ImmaGeometry geo = ImmaGeometryOf(w, m);
+  if (!geo.ok || w.meta == nullptr || scratch == nullptr) {
+    return nullptr;
+  }
+  const MetaGeometry meta = MetaGeometryOf(w);
+  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
+  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+      geo.table_offset, geo.pass_bytes, geo.passes, scratch);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+
+  ImmaParams p{};
+  p.w = w;
+  p.act = scratch;
+  p.m_total = static_cast<int>(m);
+  p.out = out;
+  p.status = status_word;
+  p.half_tiles = meta.half_tiles;
+  p.bpt = meta.bpt;
+  p.slices = meta.slices;
+  p.rec_bytes = meta.rec_bytes;
+  p.rec_scale_bytes = meta.rec_scale_bytes;
+  p.slot_bytes = geo.slot_bytes;
+  p.num_slots = geo.num_slots;
+  p.tp = geo.tp;
+  p.act_row_bytes = geo.act_row_bytes;
+  p.table_offset = geo.table_offset;
+  p.pass_bytes = geo.pass_bytes;
+  p.groups_per_block = w.block_size >= 256 ? w.block_size / 128 : 1;
+  const int spb = geo.entry_k / 32;
+
+  CUtensorMap map_b;
+  if (!EncodeWeightsMap3D(&map_b, w)) {
+    return nullptr;
+  }
+  int ctas = sm_count > 0 ? sm_count : 148;
+  const int tiles = (meta.half_tiles + 1) / 2;
+  if (ctas > tiles) {
+    ctas = tiles;
+  }
+  dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(geo.passes), 1);
+  cudaError_t err = cudaErrorInvalidValue;
+#define MNB_IMMA_CASE(NT_, SPB_, ZP_)                                                            \
+  if (geo.tp == 8 * NT_ && spb == SPB_ && (w.zp != nullptr) == ZP_) {                            \
+    auto kernel = nbits_int8_mma_kernel<NT_, SPB_, ZP_>;                                         \
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                               static_cast<int>(geo.smem));                                      \
+    if (err == cudaSuccess) {                                                                    \
+      cudaLaunchConfig_t config = {};                                                            \
+      config.gridDim = grid;                                                                     \
+      config.blockDim = dim3(kThreads, 1, 1);                                                    \
+      config.dynamicSmemBytes = geo.smem;                                                        \
+      config.stream = stream;                                                                    \
+      cudaLaunchAttribute attribute[1];                                                          \
+      attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
+      attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
+      config.attrs = attribute;                                                                  \
+      config.numAttrs = 1;                                                                       \
+      err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
+    }                                                                                            \
+  }
+#define MNB_IMMA_CASES(SPB_)                                                                     \
+  MNB_IMMA_CASE(1, SPB_, true)                                                                   \
+  MNB_IMMA_CASE(1, SPB_, false)                                                                  \
+  MNB_IMMA_CASE(2, SPB_, true)                                                                   \
+  MNB_IMMA_CASE(2, SPB_, false)
+  MNB_IMMA_CASES(1)
+  MNB_IMMA_CASES(2)
+  MNB_IMMA_CASES(4)
+#undef MNB_IMMA_CASES
+#undef MNB_IMMA_CASE
+  if (err != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_int8_mma_kernel";
+}
+
+} // namespace mnb

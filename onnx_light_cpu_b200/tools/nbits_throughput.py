@@ -30,6 +30,9 @@ SHAPES = (
     ("cfg4_gate_m16", 16, 4096, 14336, 4, 32, False, False, 0),
     ("cfg4_gate_m16_level4", 16, 4096, 14336, 4, 32, False, False, 4),
     ("cfg4_down_m16", 16, 14336, 4096, 4, 32, False, False, 0),
+    ("cfg4_down_m16_level4", 16, 14336, 4096, 4, 32, False, False, 4),
+    ("cfg2_decode_m1_level4", 1, 4096, 14336, 4, 128, True, True, 4),
+    ("cfg2_decode_m16_level4", 16, 4096, 14336, 4, 128, True, True, 4),
     ("cfg5_shard8_m1", 1, 4096, 16032, 4, 32, True, False, 0),
     ("cfg5_shard8_m1_8bit", 1, 4096, 16032, 8, 32, True, False, 0),
 )

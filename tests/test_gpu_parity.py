@@ -287,11 +287,50 @@ def test_int8_block_dots_bit_exact(cuda_device, bits, bs, k, n):
                                               (9, 1024, 50, 8, 32, True), (16, 4064, 31, 4, 32, True)])
 def test_int8_path_outputs(cuda_device, m, k, n, bits, bs, zp):
     case = syn.make_case("lvl4", m, k, n, bits, bs, seed=m + n, zero_points=zp, bias=True)
-    y, kernel = run_device(case, accuracy_level=4)
+    y, kernel = run_device(case, accuracy_level=4, path=_capi.PATH_INT8)
     assert kernel.startswith("nbits_int8_matmul_kernel"), kernel
     ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, bits, bs)
     assert rel_err(y, ref) <= TOL_FP32   # same integers, fp32 scaling in a different order
     assert rel_err(y, oracle_f64(case)) <= 2e-2   # int8 activations vs exact
+
+
+# integer tensor-core kernel: every block size class, with and without zero points, one and two
+# column tiles of tokens, several passes, ragged N, a last task that is only partly filled, a K
+# that ends inside a block, and a K long enough to need the 8-token layout
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (16, 4096, 128, 32, False, True), (16, 4096, 100, 32, True, True), (1, 4096, 77, 128, True, False),
+    (8, 2048, 48, 64, True, True), (5, 2304, 33, 64, False, False), (16, 4096, 64, 256, True, True),
+    (3, 4096, 24, 1024, False, True), (20, 6144, 40, 128, True, True), (37, 2048, 16, 32, True, False),
+    (16, 14336, 40, 32, False, True), (9, 2000, 21, 128, True, True), (16, 4096, 2400, 32, False, False),
+    (4, 1056, 16, 32, True, True),
+])
+def test_int8_mma_path_outputs(cuda_device, m, k, n, bs, zp, bias):
+    if (((k + bs - 1) // bs) * bs // 2) % 128 != 0:
+        # packed rows must be whole 128-byte segments; other shapes go to the dp4a kernel
+        case = syn.make_case("imma_fallback", m, k, n, 4, bs, seed=m + n + bs, zero_points=zp, bias=bias)
+        y, kernel = run_device(case, accuracy_level=4)
+        assert kernel.startswith("nbits_int8_matmul_kernel"), kernel
+    else:
+        case = syn.make_case("imma", m, k, n, 4, bs, seed=m + n + bs, zero_points=zp, bias=bias)
+        y, kernel = run_device(case, accuracy_level=4)
+        assert kernel == "nbits_int8_mma_kernel", kernel
+        y2, kernel2 = run_device(case, accuracy_level=4, path=_capi.PATH_INT8_MMA)
+        assert kernel2 == kernel and np.array_equal(y, y2)   # deterministic
+    ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
+    assert rel_err(y, ref) <= TOL_FP32
+    assert rel_err(y, oracle_f64(case)) <= 2e-2
+
+
+def test_int8_mma_path_rejects_unsupported_shapes(cuda_device):
+    import torch
+
+    case = syn.make_case("imma_reject", 2, 96, 8, 4, 32, seed=5)   # 48-byte rows
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=96, N=8, bits=4, block_size=32)
+    with pytest.raises(_capi.MatMulNBitsError) as info:
+        weights.matmul_device(torch.from_numpy(case.a).cuda(), torch.zeros((2, 8), device="cuda"),
+                              accuracy_level=4, path=_capi.PATH_INT8_MMA)
+    assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
+    weights.close()
 
 
 # ---- through the registered operator (host tensors) -----------------------------------------------
