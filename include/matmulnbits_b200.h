@@ -43,7 +43,8 @@ typedef enum mnb_path {
   MNB_PATH_INT8 = 3,    /* accuracy_level 4: per-block int8 A, int32 block dots */
   MNB_PATH_GEMV_MMA = 4, /* decode on warp-level MMA, exact two-piece fp16 split of A */
   MNB_PATH_TCGEN05_WIDE = 5, /* prefill, 256 x 256 tiles for any M (AUTO picks them for large M) */
-  MNB_PATH_INT8_MMA = 6  /* accuracy_level 4 on integer tensor-core MMA (AUTO picks it when the shape fits) */
+  MNB_PATH_INT8_MMA = 6, /* accuracy_level 4 on integer tensor-core MMA (AUTO picks it when the shape fits) */
+  MNB_PATH_GEMV_MMA_MULTI = 7 /* decode on warp-level MMA, several column tiles of tokens per pass */
 } mnb_path;
 
 /* Device-resident, immutable weights of one MatMulNBits node. Plays the role the reference

@@ -28,6 +28,7 @@ PATH_INT8 = 3
 PATH_GEMV_MMA = 4
 PATH_TCGEN05_WIDE = 5
 PATH_INT8_MMA = 6
+PATH_GEMV_MMA_MULTI = 7
 
 # every symbol include/matmulnbits_b200.h declares
 EXPORTED_SYMBOLS = (

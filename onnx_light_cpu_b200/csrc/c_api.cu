@@ -206,12 +206,17 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
   const char *name = nullptr;
   switch (chosen) {
   case MNB_PATH_GEMV: {
-    // decode default: the tensor-core kernel with the exact two-piece split, as long as the
-    // tokens fit in at most four passes over the weights (4 / 2 / 1 tokens per pass for
-    // block_size >= 128 / 64 / 32)
+    // decode default: the tensor-core kernels with the exact two-piece split. One column tile
+    // holds 4 / 2 / 1 tokens for block_size >= 128 / 64 / 32; more tokens go to the kernel that
+    // shares a pass over the weights between several column tiles.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m <= 16 && path == MNB_PATH_AUTO && m <= 4 * per_pass) {
-      name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    if (m <= 16 && path == MNB_PATH_AUTO) {
+      if (m > per_pass) {
+        name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+      }
+      if (name == nullptr && m <= 4 * per_pass) {
+        name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+      }
     }
     if (name == nullptr && m <= 16) {
       name = mnb::LaunchGemvStream(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
@@ -230,6 +235,15 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     if (name == nullptr) {
       return Fail(MNB_ERR_UNSUPPORTED, "MatMulNBits: shape not supported by the MMA decode kernel.");
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_MMA_MULTI: {
+    name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the multi-tile MMA decode kernel needs more tokens than one column tile "
+                  "holds (4 / 2 / 1 for block_size >= 128 / 64 / 32), M <= 16 and a supported shape.");
     }
     break;
   }

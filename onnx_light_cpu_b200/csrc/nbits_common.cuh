@@ -91,6 +91,10 @@ MetaGeometry MetaGeometryOf(const WeightView &w);
 bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t stream);
 const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                           int *status_word, cudaStream_t stream, int sm_count);
+// Same arithmetic with two or four column tiles of tokens per pass over the weights; nullptr
+// when one column tile is enough for `m` or the shape is outside what the kernel takes.
+const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                               int *status_word, cudaStream_t stream, int sm_count);
 
 // Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,

@@ -31,6 +31,7 @@
 
 #include "nbits_common.cuh"
 #include "nbits_ptx.cuh"
+#include "nbits_mma_common.cuh"
 #include "nbits_tma.cuh"
 
 #include <cuda_fp16.h>
@@ -40,6 +41,8 @@
 
 namespace mnb {
 namespace {
+
+using namespace mma_decode;
 
 #ifdef MNB_TIMELINE
 // Debug builds only: per-CTA event times (globaltimer ns) for offline inspection.
@@ -88,66 +91,6 @@ struct MmaParams {
   std::uint32_t magic;  // 0x64006400, passed at run time so that it stays in a register
 };
 
-__device__ __forceinline__ std::uint32_t AndOr(std::uint32_t a, std::uint32_t mask, std::uint32_t c) {
-  std::uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(c));
-  return d;
-}
-
-__device__ __forceinline__ std::uint32_t Hsub2(std::uint32_t a, std::uint32_t b) {
-  std::uint32_t d;
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-__device__ __forceinline__ std::uint32_t Hfma2(std::uint32_t a, std::uint32_t b, std::uint32_t c) {
-  std::uint32_t d;
-  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-
-__device__ __forceinline__ void MmaF16(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
-                                       std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Same with a zero accumulator input: starts a fresh sum without clearing registers first.
-__device__ __forceinline__ void MmaF16Zero(float (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
-                                           std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
-               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
-}
-
-// Eight codes of `w` minus the zero point, as four fp16 pairs (code j, code j+4), j = 0..3.
-// `offs` = (1024 + zp) x2, `offs16` = -(64 + zp) x2, `sixteenth` = (1/16) x2.
-__device__ __forceinline__ void Dequant8(std::uint32_t w, std::uint32_t magic, std::uint32_t offs,
-                                         std::uint32_t offs16, std::uint32_t sixteenth,
-                                         std::uint32_t (&p)[4]) {
-  const std::uint32_t w8 = w >> 8;
-  p[0] = Hsub2(AndOr(w, 0x000f000fu, magic), offs);
-  p[1] = Hfma2(AndOr(w, 0x00f000f0u, magic), sixteenth, offs16);
-  p[2] = Hsub2(AndOr(w8, 0x000f000fu, magic), offs);
-  p[3] = Hfma2(AndOr(w8, 0x00f000f0u, magic), sixteenth, offs16);
-}
-
-// Position (in fp16 elements) of activation k inside a piece row: supergroup-major, then the
-// word index i = (k % 32) / 8, the quad lane t = (k % 128) / 32, then the eight k of a word in
-// the order 0,4,1,5,2,6,3,7 (the order the pair extraction produces).
-__device__ __forceinline__ int ActPosition(int k) {
-  const int sg = k >> 7;
-  const int rem = k & 127;
-  const int t = rem >> 5;
-  const int i = (rem & 31) >> 3;
-  const int j = rem & 7;
-  const int pos = j < 4 ? 2 * j : 2 * (j - 4) + 1;
-  return (sg << 7) + (i << 5) + (t << 3) + pos;
-}
-
 // NB_SG_LOG2: log2 of quantization blocks per 128-k supergroup (block 128+: 0, 64: 1, 32: 2).
 // BIG_BLOCK: a block spans several supergroups (block_size >= 256).
 template <int NB_SG_LOG2, bool BIG_BLOCK, bool HAS_ZP>
@@ -161,8 +104,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   unsigned char *slots = smem_raw;
   unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
   float *inv_scale = reinterpret_cast<float *>(act + (2 * p.tokens_per_pass + 1) * p.act_row_bytes);
-  float *scratch = inv_scale + kMaxTokens;          // [kWarps]
-  float2 *pair_buf = reinterpret_cast<float2 *>(scratch + kWarps); // [2][kPairs][32]
+  float *scratch = inv_scale + kMaxTokens;          // [2][kWarps], alternating with the token index
+  float2 *pair_buf = reinterpret_cast<float2 *>(scratch + 2 * kWarps); // [2][kPairs][32]
   std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + 2 * kPairs * 32);
   std::uint64_t *empty_bar = full_bar + kMaxSlots;
   // task index currently assigned to each slot. A slot is consumed by different warps in
@@ -312,14 +255,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int offset = 16; offset > 0; offset >>= 1) {
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
     }
+    // two scratch rows: a warp that is one token ahead writes the other row, and it cannot be
+    // two ahead because of the barrier in between
+    float *row_max = scratch + (mi & 1) * kWarps;
     if (lane == 0) {
-      scratch[warp] = amax;
+      row_max[warp] = amax;
     }
     asm volatile("bar.sync 9, %0;" ::"n"(kConsumerThreads) : "memory");
-    amax = scratch[0];
+    amax = row_max[0];
 #pragma unroll
     for (int i = 1; i < kWarps; ++i) {
-      amax = fmaxf(amax, scratch[i]);
+      amax = fmaxf(amax, row_max[i]);
     }
     int e2 = 0;
     if (amax > 0.0f && amax < 3.0e38f) {
@@ -600,14 +546,6 @@ __global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightVie
   }
 }
 
-int Log2Of(int v) {
-  int l = 0;
-  while ((1 << l) < v) {
-    ++l;
-  }
-  return l;
-}
-
 // Programmatic dependent launch is off unless MNB_DEPENDENT_LAUNCH=1: on the decode benchmark
 // (back-to-back launches in a CUDA graph) it measured 7 % slower than plain serialization.
 bool UseDependentLaunch() {
@@ -712,7 +650,7 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
   p.slot_bytes = (16 * p.slice_b_bytes + 2 * p.rec_bytes + 127) & ~127;
   const size_t fixed = static_cast<size_t>(2 * tokens_per_pass + 1) * p.act_row_bytes +
-                       (kMaxTokens + kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
+                       (kMaxTokens + 2 * kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
                        2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
   const size_t limit = 225 * 1024;
   if (fixed + 2 * static_cast<size_t>(p.slot_bytes) > limit) {

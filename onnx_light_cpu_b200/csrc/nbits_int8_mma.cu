@@ -37,7 +37,10 @@ namespace {
 
 constexpr int kWarps = 16;                   // consumer warps = 128-k groups of a task
 constexpr int kConsumerThreads = kWarps * 32;
-constexpr int kThreads = (kWarps + 1) * 32;
+// one issuing thread cannot keep enough tile loads in flight for the full memory bandwidth
+// (measured 4.4 TB/s against 6.7 TB/s with four): four producer warps issue tasks round-robin
+constexpr int kProducers = 4;
+constexpr int kThreads = (kWarps + kProducers) * 32;
 constexpr int kMaxSlots = 16;
 constexpr int kTaskK = 2048;                 // k per task
 constexpr int kTaskBytes = 16 * kTaskK / 2;  // packed weights of a task: 16 rows
@@ -56,6 +59,7 @@ struct ImmaParams {
   int rec_scale_bytes;
   int slot_bytes;
   int num_slots;
+  int producers;       // producer warps in use: min(kProducers, num_slots), see the producer loop
   int tp;              // tokens per pass (8 or 16)
   int act_row_bytes;   // bytes between token rows of the quantized activations
   int table_offset;    // byte offset of the scale / sum table inside a pass
@@ -191,9 +195,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::int64_t row_limit =
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
-  if (warp == kWarps) {
-    // ------------------------------ producer ------------------------------
-    if (lane == 0) {
+  if (warp >= kWarps) {
+    // ------------------------------ producers ------------------------------
+    // Producer j issues tasks j, j + kProducers, ...; producer 0 also fetches the activations.
+    const int producer = warp - kWarps;
+    if (producer == 0 && lane == 0) {
       for (int s = 0; s < p.num_slots; ++s) {
         ptx::MbarInit(&full_bar[s], 1);
         ptx::MbarInit(&empty_bar[s], kWarps);
@@ -201,16 +207,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::MbarInit(act_bar, 1);
       ptx::FenceMbarInit();
     }
-    __syncwarp();
+    asm volatile("bar.sync 11, %0;" ::"n"(kProducers * 32) : "memory"); // barriers initialised
     asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_b);
-      int task = 0;
-      int slot = 0;
-      std::uint32_t round = 0;
-      bool ok = true;
-      bool act_issued = false;
+      const int total = n_tiles * p.slices;
       const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
+      bool ok = true;
+      bool act_issued = producer != 0;
       // The quantized activations come from the kernel launched just before this one, which may
       // still be running (programmatic dependent launch): the weights do not depend on it, so a
       // first ring of weight tiles is requested before waiting for that kernel.
@@ -221,42 +225,53 @@ __global__ void __launch_bounds__(kThreads, 1)
                       static_cast<std::uint32_t>(p.pass_bytes), act_bar);
         act_issued = true;
       };
-      for (int tile = 0; tile < n_tiles && ok; ++tile) {
-        const int h0 = h_begin + 2 * tile;
-        const unsigned char *meta_src = p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes;
-        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
-        for (int s = 0; s < p.slices; ++s, ++task, meta_src += meta_slice_stride) {
-          if (round != 0) {
-            if (!act_issued) {
-              issue_activations();
-            }
-            if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
-              atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
-              ok = false;
-              break;
-            }
+      int tile = 0;
+      int s = producer;
+      // A producer that has passed the wait for task T - producers knows that task
+      // T - producers - num_slots is consumed. The parity wait for task T is only unambiguous
+      // when task T - 2 * num_slots is consumed too, which follows when producers <= num_slots;
+      // the host sets p.producers accordingly and the remaining producer warps stay idle.
+      for (int task = producer; producer < p.producers && task < total && ok;
+           task += p.producers, s += p.producers) {
+        while (s >= p.slices) {
+          s -= p.slices;
+          ++tile;
+        }
+        const int slot = task % p.num_slots;
+        const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
+        if (round != 0) {
+          if (!act_issued) {
+            issue_activations();
           }
-          unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
-          ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
-          TmaLoad3D(dst, &map_b, 0, h0 * 8, s * kSegments, &full_bar[slot]);
-          ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
-          if (++slot == p.num_slots) {
-            slot = 0;
-            ++round;
+          if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+            atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+            ok = false;
+            break;
           }
         }
+        const int h0 = h_begin + 2 * tile;
+        const unsigned char *meta_src =
+            p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes + s * meta_slice_stride;
+        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+        unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+        ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
+        TmaLoad3D(dst, &map_b, 0, h0 * 8, s * kSegments, &full_bar[slot]);
+        ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
       }
       if (!act_issued) {
         issue_activations();
       }
-      // stay until every copy issued has been consumed (bounded), so none lands after exit
-      const int first = task - p.num_slots < 0 ? 0 : task - p.num_slots;
-      for (int i = first; i < task && ok; ++i) {
-        if (!ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
+      // stay until every copy this lane issued has been consumed (bounded), so none lands after exit
+      const int first = total - p.num_slots < 0 ? 0 : total - p.num_slots;
+      for (int i = first; i < total && ok; ++i) {
+        if (producer < p.producers && (i % p.producers) == producer &&
+            !ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
           break;
         }
       }
-      ptx::MbarWait(act_bar, 0);
+      if (producer == 0) {
+        ptx::MbarWait(act_bar, 0);
+      }
     }
     return;
   }
@@ -573,6 +588,7 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   p.rec_scale_bytes = meta.rec_scale_bytes;
   p.slot_bytes = geo.slot_bytes;
   p.num_slots = geo.num_slots;
+  p.producers = geo.num_slots < kProducers ? geo.num_slots : kProducers;
   p.tp = geo.tp;
   p.act_row_bytes = geo.act_row_bytes;
   p.table_offset = geo.table_offset;

@@ -76,7 +76,7 @@ def test_config1_single_node(cuda_device):
 def test_config2_decode_sweep(cuda_device, m):
     case = syn.config2(m)
     y, kernel = run_device(case)
-    assert kernel == "nbits_gemv_mma_kernel", kernel
+    assert kernel == ("nbits_gemv_mma_kernel" if m <= 4 else "nbits_gemv_mma_multi_kernel"), kernel
     ref = oracle_f64(case)
     assert rel_err(y, ref) <= TOL_FP32
     y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
@@ -129,6 +129,19 @@ MMA_CASES = [
     (2, 4096, 16032, 32, True, False),     # one lm-head shard: long ring, two passes
 ]
 
+# shapes with more tokens than one column tile holds: (m, k, n, block, zp, bias)
+MMA_MULTI_CASES = [
+    (2, 4096, 16032, 32, True, False),     # one lm-head shard: long ring, two column tiles
+    (8, 4096, 200, 128, True, True),       # two column tiles of four tokens, one pass
+    (16, 2048, 100, 128, False, True),     # four column tiles, one pass
+    (13, 4096, 120, 128, True, False),     # two passes of two column tiles, last one ragged
+    (4, 4096, 64, 32, False, True),        # four column tiles of one token
+    (16, 4096, 40, 32, True, True),        # four passes of four tokens
+    (5, 4096, 77, 64, True, True),         # three of four column tiles of two tokens in use
+    (8, 4096, 48, 512, False, False),      # block spans four supergroups, two column tiles
+    (7, 4096, 14336, 128, True, True),     # full size with seven tokens
+]
+
 
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", MMA_CASES)
 def test_decode_mma_path(cuda_device, m, k, n, bs, zp, bias):
@@ -136,6 +149,30 @@ def test_decode_mma_path(cuda_device, m, k, n, bs, zp, bias):
     y, kernel = run_device(case, path=_capi.PATH_GEMV_MMA)
     assert kernel == "nbits_gemv_mma_kernel"
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", MMA_MULTI_CASES)
+def test_decode_mma_multi_tile_path(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("mma_multi", m, k, n, 4, bs, seed=m * 11 + k + n + bs, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_MMA_MULTI)
+    assert kernel == "nbits_gemv_mma_multi_kernel"
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    y_auto, kernel_auto = run_device(case)   # AUTO picks the same kernel for these shapes
+    assert kernel_auto == kernel and np.array_equal(y, y_auto)
+    y_single, _ = run_device(case, path=_capi.PATH_GEMV_MMA)   # one column tile per pass
+    assert rel_err(y, y_single) <= TOL_FP32
+
+
+def test_decode_mma_multi_tile_path_rejects_single_tile_shapes(cuda_device):
+    import torch
+
+    case = syn.make_case("mma_multi_reject", 3, 4096, 64, 4, 128, seed=8)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=128)
+    with pytest.raises(_capi.MatMulNBitsError) as info:
+        weights.matmul_device(torch.from_numpy(case.a).cuda(), torch.zeros((3, 64), device="cuda"),
+                              path=_capi.PATH_GEMV_MMA_MULTI)
+    assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
+    weights.close()
 
 
 def test_decode_mma_path_wide_dynamic_range(cuda_device):
