@@ -89,14 +89,29 @@ class ClockSampler:
         self._stop.set()
         self._thread.join(timeout=10)
 
+    def hold(self, step, torch, seconds: float = 1.0) -> None:
+        """Keeps replaying `step` for about `seconds` with the sampler running: the timed region of
+        the decode workload lasts tens of milliseconds, less than one nvidia-smi query, so the
+        clocks are also sampled over a longer window of the very same launches."""
+        self.window_seconds = seconds
+        deadline = time.perf_counter() + seconds
+        while time.perf_counter() < deadline:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
+
     def summary(self) -> dict:
         mhz = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
         max_mhz = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [name for i, name in enumerate(names)
                    if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(max_mhz) if max_mhz else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        out = {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(max_mhz) if max_mhz else None,
+               "reasons": reasons, "samples": len(self.samples)}
+        if getattr(self, "window_seconds", None):
+            out["window"] = (f"timed region, then {self.window_seconds:.1f} s of the same step "
+                             "(one nvidia-smi query takes longer than the timed region)")
+        return out
 
 
 def cpu_port_baseline(seconds: float = 3.0) -> dict:
@@ -301,6 +316,7 @@ def main() -> None:
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
             seconds = time_steps(torch, dist, replay, args.steps, args.warmup, world)
+            clocks.hold(replay, torch)
         # graph replays do not pass through the launcher: count the kernels inside the graph
         gpu_launches = args.steps * copies if graphed else _capi.launch_count() - launches_before
         value = per_launch_bytes * copies * args.steps / seconds / 1e9
@@ -339,7 +355,7 @@ def main() -> None:
         if not args.skip_extras:
             # ---- decode sweep M = 4, 16 ----
             sweep = {}
-            for m_sweep in (4, 16):
+            for m_sweep in (4, 8, 16):
                 a_s = torch.randn(m_sweep, cfg["k"], device="cuda").half().float()
                 ys_s = [torch.empty(m_sweep, cfg["n"], device="cuda") for _ in range(copies)]
 
@@ -357,6 +373,34 @@ def main() -> None:
                 sweep[f"m{m_sweep}"] = {"gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "kernel": name}
             extras["decode_sweep"] = sweep
             del weights, ys
+            torch.cuda.empty_cache()
+
+            # ---- accuracy_level 4 (int8 activations, integer MMA), cfg4 gate/up geometry, M = 16 ----
+            icfg = {"k": 4096, "n": 14336, "bits": 4, "block_size": 32}
+            icopies = 5
+            iw = device_weights(torch, pkg, icfg, icopies, seed=1401, zp=False, bias=False)
+            a_i8 = torch.randn(16, icfg["k"], device="cuda")
+            ys_i8 = [torch.empty(16, icfg["n"], device="cuda") for _ in range(icopies)]
+
+            def int8_step():
+                for w, y in zip(iw, ys_i8):
+                    w.matmul_device(a_i8, y, accuracy_level=4)
+
+            int8_step()
+            torch.cuda.synchronize()
+            iname = _capi.last_kernel()
+            istatus = max(w.poll_status() for w in iw)
+            rep, _ = capture_graph(torch, int8_step)
+            isteps = max(5, args.steps // 4)
+            sec = time_steps(torch, dist, rep, isteps, 3, 1)
+            ibytes = iw[0].algorithmic_bytes(16)
+            igbs = ibytes * icopies * isteps / sec / 1e9
+            extras["int8"] = {
+                "workload": "cfg4 gate/up projection M=16 K=4096 N=14336 bits=4 block=32, accuracy_level=4",
+                "gbs": igbs, "frac_of_hbm_peak": igbs / peaks["hbm_gbs"], "us_per_call": sec / (icopies * isteps) * 1e6,
+                "kernel": iname, "device_status": istatus,
+                "includes": "activation quantization kernel + integer-MMA kernel (dependent launch)"}
+            del iw, ys_i8
             torch.cuda.empty_cache()
 
             # ---- prefill M = 2048 (bf16 tcgen05 path) ----
@@ -415,7 +459,9 @@ def main() -> None:
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
             seconds = time_steps(torch, dist, step, args.steps, args.warmup, world)
-        gpu_launches = (_capi.launch_count() - launches_before) * world
+            launches_timed = _capi.launch_count() - launches_before
+            clocks.hold(step, torch)
+        gpu_launches = launches_timed * world
         value = full_bytes * copies * args.steps / seconds / 1e9
         workload = "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + NCCL all-gather"
         config = {"workload": workload, "weight_copies": copies, "shard_columns": shard_cfg["n"],

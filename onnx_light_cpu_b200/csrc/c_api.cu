@@ -23,6 +23,10 @@ thread_local const char *t_last_kernel = "";
 
 void CountLaunch(int launches) { g_launches.fetch_add(launches, std::memory_order_relaxed); }
 
+thread_local bool t_dependent_launch_hint = false;
+void SetDependentLaunchHint(bool allowed) { t_dependent_launch_hint = allowed; }
+bool DependentLaunchHint() { return t_dependent_launch_hint; }
+
 // out[n*K + k] = q - zp, one thread per element.
 __global__ void __launch_bounds__(256)
     nbits_dequant_int_kernel(const WeightView w, std::int32_t *out) {
@@ -63,7 +67,10 @@ struct mnb_weights {
   int sm_count = 148;
   bool owns = false;
   void *owned[4] = {nullptr, nullptr, nullptr, nullptr};
+  // status word of the bounded device-side waits: page-locked host memory (`status_host`) and its
+  // device alias (`status_dev`), so reading it after a synchronize needs no copy
   int *status_dev = nullptr;
+  int *status_host = nullptr;
   void *meta_dev = nullptr; // prepared scales / zero points for the MMA decode kernel
   // scratch, grown on demand (guarded by `mutex`)
   std::mutex mutex;
@@ -126,13 +133,14 @@ int SetupCommon(mnb_weights *h) {
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, h->device) == cudaSuccess && sms > 0) {
     h->sm_count = sms;
   }
-  err = cudaMalloc(&h->status_dev, sizeof(int));
+  err = cudaHostAlloc(reinterpret_cast<void **>(&h->status_host), sizeof(int), cudaHostAllocMapped);
   if (err != cudaSuccess) {
-    return FailCuda("cudaMalloc(status)", err);
+    return FailCuda("cudaHostAlloc(status)", err);
   }
-  err = cudaMemset(h->status_dev, 0, sizeof(int));
+  *h->status_host = 0;
+  err = cudaHostGetDevicePointer(reinterpret_cast<void **>(&h->status_dev), h->status_host, 0);
   if (err != cudaSuccess) {
-    return FailCuda("cudaMemset(status)", err);
+    return FailCuda("cudaHostGetDevicePointer(status)", err);
   }
   err = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
   if (err != cudaSuccess) {
@@ -177,6 +185,23 @@ int Grow(void **ptr, std::size_t *have, std::size_t need) {
   }
   *have = need;
   return MNB_OK;
+}
+
+// Copies a small page-locked host buffer into device memory with a kernel: a kernel behind a
+// kernel starts sooner than a kernel behind a copy-engine transfer, and the bytes of a decode
+// step (M x K floats) cross the host link in a microsecond or two.
+__global__ void __launch_bounds__(256) nbits_fetch_kernel(const uint4 *src, uint4 *dst, int count16,
+                                                          const float *src_tail, float *dst_tail, int tail) {
+  // a kernel launched behind this one with programmatic serialization may start at once; it
+  // waits for this grid before it touches `dst`
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count16) {
+    dst[i] = src[i];
+  }
+  if (i < tail) {
+    dst_tail[i] = src_tail[i];
+  }
 }
 
 // Core dispatch. The caller holds h->mutex and has made h->device current.
@@ -463,11 +488,14 @@ int mnb_weights_destroy(mnb_weights *h) {
       }
     }
   }
-  for (void *ptr : {static_cast<void *>(h->status_dev), h->meta_dev, h->scratch_a, h->scratch_s,
+  for (void *ptr : {h->meta_dev, h->scratch_a, h->scratch_s,
                     static_cast<void *>(h->a_dev), static_cast<void *>(h->y_dev)}) {
     if (ptr != nullptr) {
       cudaFree(ptr);
     }
+  }
+  if (h->status_host != nullptr) {
+    cudaFreeHost(h->status_host);
   }
   delete h;
   return MNB_OK;
@@ -527,34 +555,72 @@ int mnb_matmul_host(mnb_weights *h, const float *a_host, int64_t m, int accuracy
   if (rc != MNB_OK) {
     return rc;
   }
-  rc = Grow(reinterpret_cast<void **>(&h->y_dev), &h->y_dev_bytes, y_bytes);
-  if (rc != MNB_OK) {
-    return rc;
+  constexpr std::size_t kDirectLimit = 1u << 20;
+  cudaPointerAttributes attributes{};
+  const float *a_alias = nullptr;
+  if (a_bytes <= kDirectLimit && (reinterpret_cast<std::uintptr_t>(a_host) & 15u) == 0 &&
+      cudaPointerGetAttributes(&attributes, a_host) == cudaSuccess && attributes.type == cudaMemoryTypeHost &&
+      attributes.devicePointer != nullptr) {
+    a_alias = static_cast<const float *>(attributes.devicePointer);
+  } else {
+    cudaGetLastError(); // an unregistered pointer reports an error on some drivers: not a failure here
   }
-  err = cudaMemcpyAsync(h->a_dev, a_host, a_bytes, cudaMemcpyHostToDevice, h->stream);
+  if (a_alias != nullptr) {
+    const int count16 = static_cast<int>(a_bytes / 16);
+    const int tail = static_cast<int>((a_bytes - static_cast<std::size_t>(count16) * 16) / sizeof(float));
+    const int threads = count16 > tail ? count16 : tail;
+    nbits_fetch_kernel<<<(threads + 255) / 256, 256, 0, h->stream>>>(
+        reinterpret_cast<const uint4 *>(a_alias), reinterpret_cast<uint4 *>(h->a_dev), count16,
+        a_alias + static_cast<std::size_t>(count16) * 4, h->a_dev + static_cast<std::size_t>(count16) * 4, tail);
+    err = cudaGetLastError();
+    if (err == cudaSuccess) {
+      mnb::CountLaunch();
+    }
+  } else {
+    err = cudaMemcpyAsync(h->a_dev, a_host, a_bytes, cudaMemcpyHostToDevice, h->stream);
+  }
   if (err != cudaSuccess) {
     return FailCuda("copy A to device", err);
   }
-  OutputView out{h->y_dev, h->view.n, 0};
+  // Y: when the caller's buffer is page-locked (cudaHostAlloc / cudaHostRegister) and small (a
+  // decode-sized result), the kernels store straight into it through its device alias, which
+  // saves a copy launch per call; any other buffer gets a device staging buffer and a
+  // device-to-host copy, which keeps the SMs from waiting on the host link for large results.
+  float *y_alias = nullptr;
+  if (y_bytes > kDirectLimit) {
+    // staged below
+  } else if (cudaPointerGetAttributes(&attributes, y_host) == cudaSuccess &&
+             attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
+    y_alias = static_cast<float *>(attributes.devicePointer);
+  } else {
+    cudaGetLastError(); // an unregistered pointer reports an error on some drivers: not a failure here
+  }
+  if (y_alias == nullptr) {
+    rc = Grow(reinterpret_cast<void **>(&h->y_dev), &h->y_dev_bytes, y_bytes);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+  }
+  OutputView out{y_alias != nullptr ? y_alias : h->y_dev, h->view.n, 0};
+  mnb::SetDependentLaunchHint(a_alias != nullptr);
   rc = Dispatch(h, h->a_dev, m, accuracy_level, path, out, h->stream);
+  mnb::SetDependentLaunchHint(false);
   if (rc != MNB_OK) {
     return rc;
   }
-  err = cudaMemcpyAsync(y_host, h->y_dev, y_bytes, cudaMemcpyDeviceToHost, h->stream);
-  if (err != cudaSuccess) {
-    return FailCuda("copy Y to host", err);
+  if (y_alias == nullptr) {
+    err = cudaMemcpyAsync(y_host, h->y_dev, y_bytes, cudaMemcpyDeviceToHost, h->stream);
+    if (err != cudaSuccess) {
+      return FailCuda("copy Y to host", err);
+    }
   }
-  int status = 0;
-  err = cudaMemcpyAsync(&status, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost, h->stream);
-  if (err == cudaSuccess) {
-    err = cudaStreamSynchronize(h->stream);
-  }
+  err = cudaStreamSynchronize(h->stream);
   if (err != cudaSuccess) {
     return FailCuda("MatMulNBits execution", err);
   }
+  const int status = *static_cast<volatile int *>(h->status_host);
   if (status != 0) {
-    cudaMemsetAsync(h->status_dev, 0, sizeof(int), h->stream);
-    cudaStreamSynchronize(h->stream);
+    *h->status_host = 0;
     char text[96];
     std::snprintf(text, sizeof(text), "matmulnbits_b200: device-side wait timed out (status %d).", status);
     return Fail(MNB_ERR_DEVICE_TIMEOUT, text);
@@ -571,14 +637,12 @@ int mnb_weights_poll_status(mnb_weights *h, int *status) {
   if (err == cudaSuccess) {
     err = cudaDeviceSynchronize();
   }
-  if (err == cudaSuccess) {
-    err = cudaMemcpy(status, h->status_dev, sizeof(int), cudaMemcpyDeviceToHost);
-  }
   if (err != cudaSuccess) {
     return FailCuda("status read", err);
   }
+  *status = *static_cast<volatile int *>(h->status_host);
   if (*status != 0) {
-    cudaMemset(h->status_dev, 0, sizeof(int));
+    *h->status_host = 0;
   }
   return MNB_OK;
 }

@@ -45,6 +45,15 @@ enum DeviceStatus : int {
   kDeviceTimeoutEpilogueBarrier = 4,
 };
 
+// The status word lives in page-locked host memory mapped into the device address space, so
+// that the host can read it after a synchronize without a copy. A plain store is enough: any
+// non-zero code means "a bounded wait gave up", and which of several reporters wins is
+// irrelevant.
+__device__ __forceinline__ void ReportStatus(int *word, int code) {
+  *reinterpret_cast<volatile int *>(word) = code;
+  __threadfence_system();
+}
+
 __host__ __device__ inline int ZeroPointOf(const WeightView &w, std::int64_t row, int block) {
   if (w.zp == nullptr) {
     return 1 << (w.bits - 1);
@@ -122,5 +131,12 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 
 void CountLaunch(int launches = 1);
+
+// Set by the host-buffer entry point around its dispatch: the kernel launched just before
+// (the small copy of A out of page-locked host memory) has triggered its dependents, so the
+// decode kernels may be launched with programmatic stream serialization and begin streaming
+// weights while that copy is still in flight. They wait for it before they read A.
+void SetDependentLaunchHint(bool allowed);
+bool DependentLaunchHint();
 
 } // namespace mnb

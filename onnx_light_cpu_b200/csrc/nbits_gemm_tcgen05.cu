@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int s = ks % kStages;
         const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
         if (!ptx::MbarWait(&empty[s], (round & 1u) ^ 1u)) {
-          atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+          ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
           *abort_flag = 1;
           break;
         }
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int s = ks % kStages;
         const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
         if (!ptx::MbarWait(&full_deq[s], round & 1u)) {
-          atomicExch(p.status, kDeviceTimeoutMmaBarrier);
+          ReportStatus(p.status, kDeviceTimeoutMmaBarrier);
           *abort_flag = 1;
           ok = false;
           break;
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         load_meta(ks + 1, scale_next, offset_next);
       }
       if (!ptx::MbarWait(&full_tma[s], phase)) {
-        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
         break;
@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------- epilogue -------------------------------
     if (ok) {
       if (!ptx::MbarWait(accum_full, 0)) {
-        atomicExch(p.status, kDeviceTimeoutEpilogueBarrier);
+        ReportStatus(p.status, kDeviceTimeoutEpilogueBarrier);
         *abort_flag = 1;
         ok = false;
       }
@@ -411,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       std::uint32_t phase = 0;
       for (int ks = 0; ks < p.k_steps; ++ks) {
         if (!ptx::MbarWaitHot(&empty[s], phase ^ 1u)) {
-          atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+          ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
           *abort_flag = 1;
           break;
         }
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int ks = 0; ks < p.k_steps; ++ks) {
         // the buffer's dequantizers waited for the stage's TMA, so the activations are in too
         if (!ptx::MbarWaitHot(&w_full[b], b_phase)) {
-          atomicExch(p.status, kDeviceTimeoutMmaBarrier);
+          ReportStatus(p.status, kDeviceTimeoutMmaBarrier);
           *abort_flag = 1;
           ok = false;
           break;
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       // packed weights of this stage landed, and the buffer's previous reader has retired
       if (!ptx::MbarWaitHot(&full_tma[s], phase) || !ptx::MbarWaitHot(&w_empty[b], b_phase ^ 1u)) {
-        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
         break;
@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ------------------------------- epilogue -------------------------------
     if (ok) {
       if (!ptx::MbarWait(accum_full, 0)) {
-        atomicExch(p.status, kDeviceTimeoutEpilogueBarrier);
+        ReportStatus(p.status, kDeviceTimeoutEpilogueBarrier);
         *abort_flag = 1;
         ok = false;
       }

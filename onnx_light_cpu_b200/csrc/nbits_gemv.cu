@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) nbits_gemv_stream_kernel(const St
       const std::uint32_t round = static_cast<std::uint32_t>(t / p.stages);
       if (!ptx::MbarWait(&empty_bar[s], (round & 1u) ^ 1u)) {
         if (lane == 0) {
-          atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+          ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
         }
         break;
       }
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1) nbits_gemv_stream_kernel(const St
     }
 
     if (!ptx::MbarWait(&full_bar[s], round & 1u)) {
-      atomicExch(p.status, kDeviceTimeoutFullBarrier);
+      ReportStatus(p.status, kDeviceTimeoutFullBarrier);
       return;
     }
     const unsigned char *sb = stage_base + static_cast<size_t>(s) * p.stage_bytes;

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const unsigned char *meta_src = meta_slice;
           for (int wt = 0; wt < wave_tiles; ++wt, ++task, h0 += 2, meta_src += 2 * p.rec_bytes) {
             if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
-              atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+              ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
               ok = false;
               break;
             }
@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (!assigned || !ptx::MbarWait(&full_bar[slot], round & 1u)) {
-        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         dead = true;
         break;
       }
@@ -691,7 +691,7 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
       attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
-      config.numAttrs = UseDependentLaunch() ? 1 : 0;                                            \
+      config.numAttrs = (UseDependentLaunch() || DependentLaunchHint()) ? 1 : 0;                                            \
       err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
     }                                                                                            \
   }

@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int slot = task % p.num_slots;
         const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
         if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
-          atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+          ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
           ok = false;
           break;
         }
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     for (int s = 0; s < p.slices; ++s, ++task) {
       if (!dead && !ptx::MbarWait(&full_bar[slot], round & 1u)) {
-        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         dead = true;
       }
       if (!dead) {
@@ -590,7 +590,7 @@ const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t
       attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
-      config.numAttrs = 0;                                            \
+      config.numAttrs = DependentLaunchHint() ? 1 : 0;                                            \
       err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
     }                                                                                            \
   }

@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             issue_activations();
           }
           if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
-            atomicExch(p.status, kDeviceTimeoutEmptyBarrier);
+            ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
             ok = false;
             break;
           }
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory"); // barriers initialised
   bool dead = false; // a bounded wait gave up: skip the math, keep the barrier protocol
   if (!ptx::MbarWait(act_bar, 0)) {
-    atomicExch(p.status, kDeviceTimeoutFullBarrier);
+    ReportStatus(p.status, kDeviceTimeoutFullBarrier);
     dead = true;
   }
 
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     for (int s = 0; s < p.slices; ++s, ++task) {
       if (!dead && !ptx::MbarWait(&full_bar[slot], round & 1u)) {
-        atomicExch(p.status, kDeviceTimeoutFullBarrier);
+        ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         dead = true;
       }
       if (!dead) {

@@ -394,6 +394,33 @@ def test_registered_operator_end_to_end(cuda_device):
     assert rel_err(s4.run(case.a), ref4) <= TOL_FP32
 
 
+def test_host_call_pinned_and_pageable_buffers(cuda_device):
+    """The host-buffer entry point stores into page-locked result buffers directly and stages any other
+    buffer through device memory: both give the device result, call after call."""
+    import torch
+
+    case = syn.config2(3, n=1000)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n,
+                                     bits=4, block_size=128)
+    ref = oracle_f64(case)
+    a_pinned = torch.from_numpy(case.a).pin_memory()
+    y_pinned = torch.full((3, case.n), float("nan")).pin_memory()
+    y_pageable = np.full((3, case.n), np.nan, dtype=np.float32)
+    for _ in range(2):
+        weights.matmul_host_ptr(a_pinned.data_ptr(), 3, y_pinned.data_ptr())
+        assert rel_err(y_pinned.numpy(), ref) <= TOL_FP32
+        weights.matmul_host_ptr(case.a.ctypes.data, 3, y_pageable.ctypes.data)
+        assert np.array_equal(y_pageable, y_pinned.numpy())
+        y_pinned.fill_(float("nan"))
+        y_pageable.fill(np.nan)
+    # a window of a larger pinned buffer, not 16-byte aligned
+    wide = torch.full((3 * case.n + 5,), float("nan")).pin_memory()
+    weights.matmul_host_ptr(a_pinned.data_ptr(), 3, wide.data_ptr() + 4 * 3)
+    assert rel_err(wide.numpy()[3:3 + 3 * case.n].reshape(3, case.n), ref) <= TOL_FP32
+    assert np.isnan(wide.numpy()[:3]).all() and np.isnan(wide.numpy()[3 + 3 * case.n:]).all()
+    weights.close()
+
+
 def test_llama_layer_shapes_both_accuracy_levels(cuda_device):
     """cfg4 geometry (seven projections, M=16, block 32, no zero points) at reduced N."""
     for level in (0, 4):
