@@ -456,16 +456,19 @@ def main() -> None:
         step()
         torch.cuda.synchronize()
         kernel_name = _capi.last_kernel()
+        # plain launches: capturing the kernel + NCCL all-gather pair in a CUDA graph did not
+        # complete on this stack (the capture never returned), so the pair is launched per step
+        replay, graphed = step, False
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
-            seconds = time_steps(torch, dist, step, args.steps, args.warmup, world)
-            launches_timed = _capi.launch_count() - launches_before
-            clocks.hold(step, torch)
+            seconds = time_steps(torch, dist, replay, args.steps, args.warmup, world)
+            launches_timed = args.steps * copies if graphed else _capi.launch_count() - launches_before
+            clocks.hold(replay, torch)
         gpu_launches = launches_timed * world
         value = full_bytes * copies * args.steps / seconds / 1e9
         workload = "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + NCCL all-gather"
         config = {"workload": workload, "weight_copies": copies, "shard_columns": shard_cfg["n"],
-                  "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name,
+                  "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name, "cuda_graph": graphed,
                   "l2_defeat": f"{copies} weight copies per rank"}
         shard_bytes = weights[0].algorithmic_bytes(m)
         roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
