@@ -102,6 +102,37 @@ int mnb_matmul_device_strided(mnb_weights *weights, const float *a_dev, int64_t 
                               int accuracy_level, int path, float *y_dev, int64_t ld_y,
                               int64_t col_offset, void *stream);
 
+/* Column gather without a collective ----------------------------------------------------------
+ * For a node sharded by output column over the GPUs of one box, each rank can store its columns
+ * straight into every rank's gathered result through peer-mapped memory instead of running an
+ * all-gather afterwards. No counterpart in the reference (a CPU library has no such step); the
+ * closest notion is the N split of onnx_light_cpu/impl/math/gemm_kernel.cc:1219-1258, whose
+ * threads write disjoint column ranges of one shared Y.
+ *
+ * mnb_peer_buffer_create allocates `bytes` of device memory (zero filled) that other processes
+ * of the box can map, and writes its inter-process handle (MNB_IPC_HANDLE_BYTES bytes, to be
+ * sent to the peers by any host channel). mnb_peer_buffer_open maps a peer's buffer into this
+ * process and enables peer access; _close unmaps it; _destroy frees an own buffer. */
+#define MNB_IPC_HANDLE_BYTES 64
+#define MNB_MAX_GATHER_RANKS 8
+int mnb_peer_buffer_create(int device, size_t bytes, void **dev_ptr, unsigned char *handle_out);
+int mnb_peer_buffer_open(int device, const unsigned char *handle, void **peer_ptr);
+int mnb_peer_buffer_close(int device, void *peer_ptr);
+int mnb_peer_buffer_destroy(int device, void *dev_ptr);
+
+/* Decode product (M <= 16, accuracy_level 0, 4-bit shapes the tensor-core decode kernels take)
+ * whose [m, N] result is stored at the same window (ld_y, col_offset) of `ranks` buffers:
+ * y_ranks[r] is rank r's gathered result as mapped in this process (y_ranks[rank] is the local
+ * one). Afterwards a one-warp kernel sets flags_ranks[r][rank] = epoch on every rank and waits,
+ * bounded, until the local flags_ranks[rank][0..ranks) all carry `epoch`: when the stream
+ * reaches that point every rank's columns of this step are in the local buffer. `epoch` must
+ * grow by one per step on all ranks; each flags array holds at least `ranks` ints, zero at
+ * start. Every rank must make the same sequence of calls. A wait that gives up sets the status
+ * word (mnb_weights_poll_status). */
+int mnb_matmul_device_gather(mnb_weights *weights, const float *a_dev, int64_t m,
+                             float *const *y_ranks, int *const *flags_ranks, int ranks, int rank,
+                             int64_t ld_y, int64_t col_offset, int epoch, void *stream);
+
 /* Waits for the device and reads the status word that kernels with bounded waits write when
  * they give up (0 = fine, see MNB_ERR_DEVICE_TIMEOUT). Clears it after reading. The
  * host-buffer call checks it itself; callers of the asynchronous entry points use this. */

@@ -29,6 +29,8 @@ PATH_GEMV_MMA = 4
 PATH_TCGEN05_WIDE = 5
 PATH_INT8_MMA = 6
 PATH_GEMV_MMA_MULTI = 7
+IPC_HANDLE_BYTES = 64
+MAX_GATHER_RANKS = 8
 
 # every symbol include/matmulnbits_b200.h declares
 EXPORTED_SYMBOLS = (
@@ -42,6 +44,11 @@ EXPORTED_SYMBOLS = (
     "mnb_matmul_host",
     "mnb_matmul_device",
     "mnb_matmul_device_strided",
+    "mnb_peer_buffer_create",
+    "mnb_peer_buffer_open",
+    "mnb_peer_buffer_close",
+    "mnb_peer_buffer_destroy",
+    "mnb_matmul_device_gather",
     "mnb_weights_poll_status",
     "mnb_dequant_int_device",
     "mnb_quantize_a_device",
@@ -91,6 +98,11 @@ def load() -> ctypes.CDLL:
     lib.mnb_matmul_host.argtypes = [vp, vp, i64, i32, i32, vp]
     lib.mnb_matmul_device.argtypes = [vp, vp, i64, i32, i32, vp, vp]
     lib.mnb_matmul_device_strided.argtypes = [vp, vp, i64, i32, i32, vp, i64, i64, vp]
+    lib.mnb_peer_buffer_create.argtypes = [i32, c.c_size_t, c.POINTER(vp), vp]
+    lib.mnb_peer_buffer_open.argtypes = [i32, vp, c.POINTER(vp)]
+    lib.mnb_peer_buffer_close.argtypes = [i32, vp]
+    lib.mnb_peer_buffer_destroy.argtypes = [i32, vp]
+    lib.mnb_matmul_device_gather.argtypes = [vp, vp, i64, c.POINTER(vp), c.POINTER(vp), i32, i32, i64, i64, i32, vp]
     lib.mnb_weights_poll_status.argtypes = [vp, c.POINTER(i32)]
     lib.mnb_dequant_int_device.argtypes = [vp, vp, vp]
     lib.mnb_quantize_a_device.argtypes = [vp, i64, i64, i32, vp, vp, vp]

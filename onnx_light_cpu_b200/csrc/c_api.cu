@@ -204,6 +204,36 @@ __global__ void __launch_bounds__(256) nbits_fetch_kernel(const uint4 *src, uint
   }
 }
 
+// One warp: lane r tells rank r that this rank's columns of step `epoch` are stored, then waits
+// until rank r's flag in the local array carries the epoch. The stores of the kernels before
+// this one in the stream have completed when it starts; the system-scope fences order the flag
+// against them for the peers and the peers' data against the flag for this GPU.
+struct PeerFlags {
+  int *ranks[MNB_MAX_GATHER_RANKS];
+};
+
+__global__ void __launch_bounds__(32) nbits_publish_wait_kernel(PeerFlags flags, int ranks, int rank, int epoch,
+                                                                int *status) {
+  const int lane = threadIdx.x;
+  if (lane < ranks) {
+    __threadfence_system();
+    *reinterpret_cast<volatile int *>(flags.ranks[lane] + rank) = epoch;
+    volatile int *mine = flags.ranks[rank] + lane;
+    bool arrived = false;
+    for (std::uint32_t spin = 0; spin < (1u << 22); ++spin) { // about a second in all
+      if (*mine - epoch >= 0) {
+        arrived = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!arrived) {
+      mnb::ReportStatus(status, mnb::kDeviceTimeoutPeerFlag);
+    }
+    __threadfence_system();
+  }
+}
+
 // Core dispatch. The caller holds h->mutex and has made h->device current.
 int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_level, int path,
              OutputView out, cudaStream_t stream) {
@@ -520,6 +550,166 @@ int mnb_matmul_device_strided(mnb_weights *h, const float *a_dev, int64_t m, int
   }
   OutputView out{y_dev, ld_y, col_offset};
   return Dispatch(h, a_dev, m, accuracy_level, path, out, static_cast<cudaStream_t>(stream));
+}
+
+int mnb_peer_buffer_create(int device, size_t bytes, void **dev_ptr, unsigned char *handle_out) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == MNB_IPC_HANDLE_BYTES, "handle size");
+  if (dev_ptr == nullptr || handle_out == nullptr || bytes == 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_peer_buffer_create: null argument or zero size.");
+  }
+  cudaError_t err = cudaSetDevice(device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  void *ptr = nullptr;
+  err = cudaMalloc(&ptr, bytes);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMalloc(peer buffer)", err);
+  }
+  err = cudaMemset(ptr, 0, bytes);
+  cudaIpcMemHandle_t handle;
+  if (err == cudaSuccess) {
+    err = cudaIpcGetMemHandle(&handle, ptr);
+  }
+  if (err != cudaSuccess) {
+    cudaFree(ptr);
+    return FailCuda("cudaIpcGetMemHandle", err);
+  }
+  std::memcpy(handle_out, &handle, sizeof(handle));
+  *dev_ptr = ptr;
+  return MNB_OK;
+}
+
+int mnb_peer_buffer_open(int device, const unsigned char *handle_bytes, void **peer_ptr) {
+  if (handle_bytes == nullptr || peer_ptr == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_peer_buffer_open: null argument.");
+  }
+  cudaError_t err = cudaSetDevice(device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  cudaIpcMemHandle_t handle;
+  std::memcpy(&handle, handle_bytes, sizeof(handle));
+  err = cudaIpcOpenMemHandle(peer_ptr, handle, cudaIpcMemLazyEnablePeerAccess);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaIpcOpenMemHandle", err);
+  }
+  // Copies into the mapping work as soon as it exists, loads and stores from kernels only once
+  // peer access to the owning device is enabled for this context: do it here, explicitly.
+  cudaPointerAttributes attributes{};
+  err = cudaPointerGetAttributes(&attributes, *peer_ptr);
+  if (err == cudaSuccess && attributes.device >= 0 && attributes.device != device) {
+    int can = 0;
+    err = cudaDeviceCanAccessPeer(&can, device, attributes.device);
+    if (err == cudaSuccess && can == 0) {
+      cudaIpcCloseMemHandle(*peer_ptr);
+      *peer_ptr = nullptr;
+      return Fail(MNB_ERR_UNSUPPORTED, "mnb_peer_buffer_open: the two GPUs cannot address each other's memory.");
+    }
+    if (err == cudaSuccess) {
+      err = cudaDeviceEnablePeerAccess(attributes.device, 0);
+      if (err == cudaErrorPeerAccessAlreadyEnabled) {
+        err = cudaSuccess;
+      }
+    }
+  }
+  cudaGetLastError(); // drop the benign "already enabled"
+  if (err != cudaSuccess) {
+    cudaIpcCloseMemHandle(*peer_ptr);
+    *peer_ptr = nullptr;
+    return FailCuda("enabling peer access", err);
+  }
+  return MNB_OK;
+}
+
+int mnb_peer_buffer_close(int device, void *peer_ptr) {
+  if (peer_ptr == nullptr) {
+    return MNB_OK;
+  }
+  cudaSetDevice(device);
+  const cudaError_t err = cudaIpcCloseMemHandle(peer_ptr);
+  return err == cudaSuccess ? MNB_OK : FailCuda("cudaIpcCloseMemHandle", err);
+}
+
+int mnb_peer_buffer_destroy(int device, void *dev_ptr) {
+  if (dev_ptr == nullptr) {
+    return MNB_OK;
+  }
+  cudaSetDevice(device);
+  const cudaError_t err = cudaFree(dev_ptr);
+  return err == cudaSuccess ? MNB_OK : FailCuda("cudaFree(peer buffer)", err);
+}
+
+int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, float *const *y_ranks,
+                             int *const *flags_ranks, int ranks, int rank, int64_t ld_y, int64_t col_offset,
+                             int epoch, void *stream_ptr) {
+  if (h == nullptr || a_dev == nullptr || y_ranks == nullptr || flags_ranks == nullptr) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: null argument.");
+  }
+  if (ranks < 1 || ranks > MNB_MAX_GATHER_RANKS || rank < 0 || rank >= ranks) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: 1 <= ranks <= 8 and 0 <= rank < ranks.");
+  }
+  if (m < 1 || m > 16) {
+    return Fail(MNB_ERR_UNSUPPORTED, "mnb_matmul_device_gather: decode sizes only (1 <= M <= 16).");
+  }
+  if (ld_y < h->view.n || col_offset < 0 || col_offset + h->view.n > ld_y) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: output window does not fit its row.");
+  }
+  for (int r = 0; r < ranks; ++r) {
+    if (y_ranks[r] == nullptr || flags_ranks[r] == nullptr) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: null buffer in the rank tables.");
+    }
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  // A and the local result must live on the GPU that holds the weights: a handle created on
+  // another device (the default device of a second rank, say) would otherwise read them through
+  // an address that GPU cannot reach.
+  for (const void *ptr : {static_cast<const void *>(a_dev), static_cast<const void *>(y_ranks[rank])}) {
+    cudaPointerAttributes attributes{};
+    if (cudaPointerGetAttributes(&attributes, ptr) != cudaSuccess || attributes.type != cudaMemoryTypeDevice ||
+        attributes.device != h->device) {
+      cudaGetLastError();
+      return Fail(MNB_ERR_INVALID_ARGUMENT,
+                  "mnb_matmul_device_gather: A and the local result buffer must be device memory of the GPU "
+                  "the weights were created on.");
+    }
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  OutputView out{y_ranks[rank], ld_y, col_offset};
+  PeerFlags flags{};
+  for (int r = 0; r < ranks; ++r) {
+    flags.ranks[r] = flags_ranks[r];
+    if (r != rank) {
+      out.peers[out.n_peers++] = y_ranks[r];
+    }
+  }
+  const WeightView &w = h->view;
+  const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
+  const char *name = nullptr;
+  if (m > per_pass) {
+    name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+  }
+  if (name == nullptr) {
+    name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+  }
+  if (name == nullptr) {
+    return Fail(MNB_ERR_UNSUPPORTED,
+                "mnb_matmul_device_gather: only shapes of the tensor-core decode kernels (bits=4, "
+                "32 <= block_size <= 1024, 16-byte aligned rows) store to peers.");
+  }
+  cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
+  nbits_publish_wait_kernel<<<1, 32, 0, stream>>>(flags, ranks, rank, epoch, h->status_dev);
+  const cudaError_t launch_err = cudaGetLastError();
+  if (launch_err != cudaSuccess) {
+    return FailCuda("launch of the publish kernel", launch_err);
+  }
+  mnb::CountLaunch();
+  mnb::t_last_kernel = name;
+  return MNB_OK;
 }
 
 int mnb_matmul_device(mnb_weights *h, const float *a_dev, int64_t m, int accuracy_level, int path,

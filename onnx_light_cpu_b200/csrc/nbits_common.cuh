@@ -30,11 +30,25 @@ struct WeightView {
 };
 
 // Where a kernel writes its [m, n] result inside a possibly wider row-major matrix.
+constexpr int kMaxPeers = 7;
 struct OutputView {
   float *y;
   std::int64_t ld;         // leading dimension in elements
   std::int64_t col_offset; // first column written
+  // Column-sharded gather without a collective: the same window of `n_peers` other GPUs' result
+  // buffers (peer-mapped device memory, same ld / col_offset), written with plain stores next to
+  // the local one. Only the tensor-core decode kernels honour it; the dispatcher refuses the
+  // others when n_peers > 0.
+  float *peers[kMaxPeers];
+  int n_peers;
 };
+
+__device__ __forceinline__ void StoreOutput(const OutputView &out, std::int64_t index, float value) {
+  out.y[index] = value;
+  for (int r = 0; r < out.n_peers; ++r) {
+    out.peers[r][index] = value;
+  }
+}
 
 // Error word written by kernels whose bounded waits gave up (0 = fine).
 enum DeviceStatus : int {
@@ -43,6 +57,7 @@ enum DeviceStatus : int {
   kDeviceTimeoutEmptyBarrier = 2,
   kDeviceTimeoutMmaBarrier = 3,
   kDeviceTimeoutEpilogueBarrier = 4,
+  kDeviceTimeoutPeerFlag = 5,
 };
 
 // The status word lives in page-locked host memory mapped into the device address space, so

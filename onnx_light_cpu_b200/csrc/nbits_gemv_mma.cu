@@ -502,11 +502,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         const std::int64_t r_hi = row0 + g + 8;
         if (r_lo < row_limit) {
           const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_lo) : 0.0f;
-          p.out.y[m * p.out.ld + p.out.col_offset + r_lo] = fmaf(acc0, undo, bias);
+          StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_lo, fmaf(acc0, undo, bias));
         }
         if (r_hi < row_limit) {
           const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_hi) : 0.0f;
-          p.out.y[m * p.out.ld + p.out.col_offset + r_hi] = fmaf(acc1, undo, bias);
+          StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_hi, fmaf(acc1, undo, bias));
         }
       }
     }

@@ -2,8 +2,11 @@
 
 Every output column n needs only row n of B / scales / zero_points / bias and all of A, so the
 weight rows are split into ``world`` contiguous ranges, A is replicated, each rank computes
-``Y[:, lo:hi]`` and the shards are all-gathered. The gathered layout is ``[world, M, N/world]``;
-:func:`assemble` turns it into the row-major ``[M, N]`` the operator defines.
+``Y[:, lo:hi]`` and the shards are gathered: either by an all-gather behind the kernel
+(:class:`ShardedMatMulNBits`) or by the kernel itself, which stores its columns into every rank's
+result through peer-mapped memory (:class:`PeerGather`). The gathered layout is
+``[world, M, N/world]``; :func:`assemble` turns it into the row-major ``[M, N]`` the operator
+defines.
 """
 
 from __future__ import annotations
@@ -61,3 +64,92 @@ class ShardedMatMulNBits:
     def run(self, a, y_shard, y_gathered, accuracy_level=0):
         self.weights.matmul_device(a, y_shard, accuracy_level=accuracy_level)
         return gather_shards(y_shard, self.dist, y_gathered)
+
+
+class _DeviceArray:
+    """Minimal ``__cuda_array_interface__`` carrier so that torch can view library-owned memory."""
+
+    def __init__(self, ptr: int, shape: tuple, typestr: str):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class PeerGather:
+    """Gathered decode results without a collective.
+
+    Every rank owns one buffer that the other ranks map (CUDA inter-process handles exchanged over
+    the process group, any backend): ``slots`` gathered results ``[world, m_max, n_shard]`` fp32 and
+    one flag array per slot. :meth:`run` launches the decode kernel, which stores this rank's
+    columns into all ``world`` buffers, and a one-warp kernel that raises this rank's flag on every
+    rank and waits for everybody's flag locally. When the stream reaches the end of :meth:`run`
+    the slot's local result is complete. Use at least two slots and alternate them, so that a fast
+    rank writing step i+1 never touches what a slow rank still reads of step i.
+    """
+
+    def __init__(self, dist, device_index: int, m_max: int, n_shard: int, slots: int = 2):
+        import ctypes
+
+        import torch
+
+        from onnx_light_cpu_b200 import _capi
+
+        self._capi, self._ctypes, self._torch = _capi, ctypes, torch
+        self.lib = _capi.load()
+        self.dist, self.device = dist, device_index
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        if self.world > _capi.MAX_GATHER_RANKS:
+            raise ValueError(f"at most {_capi.MAX_GATHER_RANKS} ranks")
+        self.m_max, self.n_shard, self.slots = m_max, n_shard, slots
+        self.slot_floats = self.world * m_max * n_shard
+        self.flags_offset = (slots * self.slot_floats * 4 + 255) // 256 * 256
+        self.bytes = self.flags_offset + slots * 256
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * _capi.IPC_HANDLE_BYTES)()
+        _capi.check(self.lib.mnb_peer_buffer_create(device_index, self.bytes, ctypes.byref(own), handle))
+        self.own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle))
+        self.bases = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.own)
+                continue
+            ptr = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * _capi.IPC_HANDLE_BYTES).from_buffer_copy(raw)
+            _capi.check(self.lib.mnb_peer_buffer_open(device_index, buf, ctypes.byref(ptr)))
+            self.bases.append(ptr.value)
+        self.epochs = [0] * slots
+        self._views = [torch.as_tensor(_DeviceArray(self.own + s * self.slot_floats * 4,
+                                                    (self.world, m_max, n_shard), "<f4"),
+                                       device=torch.device("cuda", device_index)) for s in range(slots)]
+        dist.barrier()
+
+    def result(self, slot: int):
+        """Local gathered result of ``slot`` as a torch tensor ``[world, m_max, n_shard]`` (a view)."""
+        return self._views[slot]
+
+    def run(self, weights, a, slot: int, stream=None) -> None:
+        """``weights``: this rank's :class:`MatMulNBitsWeights` shard; ``a`` [m, K] on this GPU."""
+        c, torch = self._ctypes, self._torch
+        m = a.numel() // weights.k
+        if m > self.m_max or weights.n != self.n_shard:
+            raise ValueError("shape does not match the gather buffers")
+        self.epochs[slot] += 1
+        window = (slot * self.world + self.rank) * self.m_max * self.n_shard * 4
+        y_ranks = (c.c_void_p * self.world)(*[base + window for base in self.bases])
+        flags = (c.c_void_p * self.world)(*[base + self.flags_offset + slot * 256 for base in self.bases])
+        raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
+        self._capi.check(self.lib.mnb_matmul_device_gather(
+            weights._handle, a.data_ptr(), m, y_ranks, flags, self.world, self.rank, self.n_shard, 0,
+            self.epochs[slot], raw))
+
+    def close(self) -> None:
+        if self.own is None:
+            return
+        self._torch.cuda.synchronize()
+        self.dist.barrier()   # nobody unmaps or frees while a peer may still store
+        for r, base in enumerate(self.bases):
+            if r != self.rank:
+                self.lib.mnb_peer_buffer_close(self.device, base)
+        self.dist.barrier()
+        self.lib.mnb_peer_buffer_destroy(self.device, self.own)
+        self.own = None

@@ -1,0 +1,81 @@
+"""Column-sharded decode whose kernel stores its columns into every rank's gathered result through
+peer-mapped memory (no collective). Needs two GPUs on one box; runs as two child processes, one per
+GPU, that exchange the buffer handles over a gloo process group."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-5
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import onnx_light_cpu_b200 as pkg
+    from onnx_light_cpu_b200.tools import sharded
+    from onnx_light_cpu_b200.tools import synthetic as syn
+    from oracle import nbits_oracle as o
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        for bs, n, ms in ((128, 2048, (1, 3, 8, 1)), (32, 640, (1, 2, 1))):
+            k = 4096
+            case = syn.make_case("peer", max(ms), k, n, 4, bs, seed=77 + bs, zero_points=True, bias=True)
+            lo, hi = sharded.shard_bounds(n, world, rank)
+            nb = k // bs
+            weights = pkg.MatMulNBitsWeights(case.b[lo:hi], case.scales.reshape(n, nb)[lo:hi].reshape(-1),
+                                             case.zero_points[lo:hi], case.bias[lo:hi], K=k, N=hi - lo, bits=4,
+                                             block_size=bs, device=rank)
+            gather = sharded.PeerGather(dist, rank, m_max=max(ms), n_shard=hi - lo, slots=2)
+            for step, m in enumerate(ms):
+                a_host = (case.a[:m] * (1.0 + step)).astype(np.float32)
+                a = torch.from_numpy(a_host).cuda()
+                slot = step % 2
+                gather.run(weights, a, slot)
+                torch.cuda.synchronize()
+                assert weights.poll_status() == 0
+                got = sharded.assemble(gather.result(slot)[:, :m, :]).cpu().numpy()
+                ref = o.matmul_f64(a_host, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
+                err = float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+                assert err <= TOL_FP32, (rank, bs, step, m, err)
+                dist.barrier()   # the host check of this step is over on every rank
+            gather.close()
+            weights.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_entry_point_single_rank():
+    """World size 1: the entry point, the flag kernel and the buffer views without any peer."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(1, _free_port()), nprocs=1, join=True)
+
+
+def test_peer_store_gather_two_gpus():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on one box")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
