@@ -254,6 +254,9 @@ def main() -> None:
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling runs)")
     parser.add_argument("--no-graph", action="store_true", help="plain launches instead of a CUDA graph")
+    parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                        help="multi-GPU: kernels store into every rank's result through peer-mapped memory "
+                             "(default) or an NCCL all-gather follows each kernel")
     parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma"],
                         help="kernel family for the decode workload (auto = library dispatch)")
     args = parser.parse_args()
@@ -444,21 +447,41 @@ def main() -> None:
         m = 1
         a = torch.randn(m, cfg["k"], device="cuda")
         dist.broadcast(a, src=0)
-        y_shard = [torch.empty(m, shard_cfg["n"], device="cuda") for _ in range(copies)]
-        y_full = [torch.empty(world, m, shard_cfg["n"], device="cuda") for _ in range(copies)]
         full_bytes = _capi.algorithmic_bytes(m, cfg["n"], cfg["k"], cfg["bits"], cfg["block_size"], True, False)
+        from onnx_light_cpu_b200.tools import sharded
 
-        def step():
-            for w, ys_, yf in zip(weights, y_shard, y_full):
-                w.matmul_device(a, ys_)
-                dist.all_gather_into_tensor(yf, ys_)
+        if args.gather == "peer":
+            # one kernel per node: it stores this rank's columns into all ranks' gathered results
+            # and a one-warp kernel behind it exchanges "done" flags (no collective on the data path)
+            gather = sharded.PeerGather(dist, local_rank, m_max=m, n_shard=shard_cfg["n"], slots=copies)
+            y_full = [gather.result(i) for i in range(copies)]
+
+            def step():
+                for i, w in enumerate(weights):
+                    gather.run(w, a, i)
+        else:
+            gather = None
+            y_shard = [torch.empty(m, shard_cfg["n"], device="cuda") for _ in range(copies)]
+            y_full = [torch.empty(world, m, shard_cfg["n"], device="cuda") for _ in range(copies)]
+
+            def step():
+                for w, ys_, yf in zip(weights, y_shard, y_full):
+                    w.matmul_device(a, ys_)
+                    dist.all_gather_into_tensor(yf, ys_)
 
         step()
         torch.cuda.synchronize()
         kernel_name = _capi.last_kernel()
-        # plain launches: capturing the kernel + NCCL all-gather pair in a CUDA graph did not
-        # complete on this stack (the capture never returned), so the pair is launched per step
-        replay, graphed = step, False
+        # The peer-store step is kernels only and replays from a CUDA graph. With NCCL the pair is
+        # launched per step: capturing kernel + all-gather did not complete on this stack.
+        if gather is not None and not args.no_graph:
+            replay, graphed = capture_graph(torch, step)
+            ok = torch.tensor([1 if graphed else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                raise SystemExit("bench: CUDA graph capture of the peer-store step failed on some rank")
+        else:
+            replay, graphed = step, False
         launches_before = _capi.launch_count()
         with ClockSampler(local_rank) as clocks:
             seconds = time_steps(torch, dist, replay, args.steps, args.warmup, world)
@@ -466,14 +489,16 @@ def main() -> None:
             clocks.hold(replay, torch)
         gpu_launches = launches_timed * world
         value = full_bytes * copies * args.steps / seconds / 1e9
-        workload = "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + NCCL all-gather"
+        how = "peer-store gather inside the kernel" if gather is not None else "NCCL all-gather"
+        workload = f"cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + {how}"
         config = {"workload": workload, "weight_copies": copies, "shard_columns": shard_cfg["n"],
                   "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name, "cuda_graph": graphed,
+                  "gather": args.gather,
                   "l2_defeat": f"{copies} weight copies per rank"}
         shard_bytes = weights[0].algorithmic_bytes(m)
         roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": value / world / peaks["hbm_gbs"], "traffic": None,
-                    "peak_kind": f"of {peak_kind} (copy bandwidth), per GPU, all-gather time included",
+                    "peak_kind": f"of {peak_kind} (copy bandwidth), per GPU, gather time included",
                     "algorithmic_bytes_per_launch": shard_bytes}
         scaling = "strong"
         # end to end: A from pinned host memory, gathered Y back to pinned host memory
@@ -482,11 +507,14 @@ def main() -> None:
         host_steps = max(3, min(args.steps, 50))
 
         def host_step():
-            for w, ys_, yf in zip(weights, y_shard, y_full):
+            for i, w in enumerate(weights):
                 a.copy_(a_host, non_blocking=True)
-                w.matmul_device(a, ys_)
-                dist.all_gather_into_tensor(yf, ys_)
-                y_host.copy_(yf, non_blocking=True)
+                if gather is not None:
+                    gather.run(w, a, i)
+                else:
+                    w.matmul_device(a, y_shard[i])
+                    dist.all_gather_into_tensor(y_full[i], y_shard[i])
+                y_host.copy_(y_full[i], non_blocking=True)
                 torch.cuda.synchronize()
 
         host_step()

@@ -126,8 +126,10 @@ int mnb_peer_buffer_destroy(int device, void *dev_ptr);
  * one). Afterwards a one-warp kernel sets flags_ranks[r][rank] = epoch on every rank and waits,
  * bounded, until the local flags_ranks[rank][0..ranks) all carry `epoch`: when the stream
  * reaches that point every rank's columns of this step are in the local buffer. `epoch` must
- * grow by one per step on all ranks; each flags array holds at least `ranks` ints, zero at
- * start. Every rank must make the same sequence of calls. A wait that gives up sets the status
+ * grow by one per step on all ranks, or be 0 on all ranks and all steps: then the step number is
+ * kept on the device in flags_ranks[rank][MNB_MAX_GATHER_RANKS] and incremented by the call
+ * itself, which is what a captured and replayed CUDA graph needs. Each flags array holds at
+ * least MNB_MAX_GATHER_RANKS + 1 ints, zero at start. Every rank must make the same sequence of calls. A wait that gives up sets the status
  * word (mnb_weights_poll_status). */
 int mnb_matmul_device_gather(mnb_weights *weights, const float *a_dev, int64_t m,
                              float *const *y_ranks, int *const *flags_ranks, int ranks, int rank,

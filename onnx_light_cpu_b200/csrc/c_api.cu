@@ -215,6 +215,16 @@ struct PeerFlags {
 __global__ void __launch_bounds__(32) nbits_publish_wait_kernel(PeerFlags flags, int ranks, int rank, int epoch,
                                                                 int *status) {
   const int lane = threadIdx.x;
+  if (epoch == 0) {
+    // self-counting mode (what a replayed CUDA graph needs): the step number lives next to the
+    // local flags and grows by one per call, in lockstep on all ranks
+    int *counter = flags.ranks[rank] + MNB_MAX_GATHER_RANKS;
+    epoch = *reinterpret_cast<volatile int *>(counter) + 1;
+    __syncwarp();
+    if (lane == 0) {
+      *reinterpret_cast<volatile int *>(counter) = epoch;
+    }
+  }
   if (lane < ranks) {
     __threadfence_system();
     *reinterpret_cast<volatile int *>(flags.ranks[lane] + rank) = epoch;

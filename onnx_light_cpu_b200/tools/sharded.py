@@ -117,7 +117,6 @@ class PeerGather:
             buf = (ctypes.c_ubyte * _capi.IPC_HANDLE_BYTES).from_buffer_copy(raw)
             _capi.check(self.lib.mnb_peer_buffer_open(device_index, buf, ctypes.byref(ptr)))
             self.bases.append(ptr.value)
-        self.epochs = [0] * slots
         self._views = [torch.as_tensor(_DeviceArray(self.own + s * self.slot_floats * 4,
                                                     (self.world, m_max, n_shard), "<f4"),
                                        device=torch.device("cuda", device_index)) for s in range(slots)]
@@ -128,19 +127,18 @@ class PeerGather:
         return self._views[slot]
 
     def run(self, weights, a, slot: int, stream=None) -> None:
-        """``weights``: this rank's :class:`MatMulNBitsWeights` shard; ``a`` [m, K] on this GPU."""
+        """``weights``: this rank's :class:`MatMulNBitsWeights` shard; ``a`` [m, K] on this GPU.
+        The step number is kept on the device, so the call can be captured in a CUDA graph."""
         c, torch = self._ctypes, self._torch
         m = a.numel() // weights.k
         if m > self.m_max or weights.n != self.n_shard:
             raise ValueError("shape does not match the gather buffers")
-        self.epochs[slot] += 1
         window = (slot * self.world + self.rank) * self.m_max * self.n_shard * 4
         y_ranks = (c.c_void_p * self.world)(*[base + window for base in self.bases])
         flags = (c.c_void_p * self.world)(*[base + self.flags_offset + slot * 256 for base in self.bases])
         raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
         self._capi.check(self.lib.mnb_matmul_device_gather(
-            weights._handle, a.data_ptr(), m, y_ranks, flags, self.world, self.rank, self.n_shard, 0,
-            self.epochs[slot], raw))
+            weights._handle, a.data_ptr(), m, y_ranks, flags, self.world, self.rank, self.n_shard, 0, 0, raw))
 
     def close(self) -> None:
         if self.own is None:
