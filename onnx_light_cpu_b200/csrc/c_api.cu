@@ -8,6 +8,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -22,6 +23,15 @@ thread_local const char *t_last_kernel = "";
 } // namespace
 
 void CountLaunch(int launches) { g_launches.fetch_add(launches, std::memory_order_relaxed); }
+
+int WantedProducers(int kernel_default) {
+  static const int wanted = [] {
+    const char *value = std::getenv("MNB_GEMV_PRODUCERS");
+    const int v = value != nullptr ? std::atoi(value) : 0;
+    return (v == 1 || v == 2 || v == 4) ? v : 0;
+  }();
+  return wanted != 0 ? wanted : kernel_default;
+}
 
 thread_local bool t_dependent_launch_hint = false;
 void SetDependentLaunchHint(bool allowed) { t_dependent_launch_hint = allowed; }

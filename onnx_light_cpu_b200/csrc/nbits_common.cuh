@@ -145,6 +145,12 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
 
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 
+// Producer lanes per CTA that issue the tile loads of the ring-fed kernels: env
+// MNB_GEMV_PRODUCERS (1, 2 or 4) or the kernel's own default. Measured: the pair kernel is
+// fastest with one paced issuer (cfg2 M=1: 12.9 / 13.3 / 14.6 us with 1 / 2 / 4), the kernels whose
+// warps share every task with four (level 4, cfg2 M=16: 16.5 vs 18.0 us).
+int WantedProducers(int kernel_default);
+
 void CountLaunch(int launches = 1);
 
 // Set by the host-buffer entry point around its dispatch: the kernel launched just before

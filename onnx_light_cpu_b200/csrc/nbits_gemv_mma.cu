@@ -61,13 +61,17 @@ __device__ __forceinline__ unsigned long long NowNs() {
 constexpr int kPairs = 8;                 // 16-row tiles in flight per CTA
 constexpr int kWarps = 2 * kPairs;        // consumer warps: two per tile, alternating k slices
 constexpr int kConsumerThreads = kWarps * 32;
-constexpr int kThreads = (kWarps + 1) * 32;
+// Up to four producer warps can share the tasks (one issuing thread sustains 4.4 TB/s on long
+// streams, four 6.7 TB/s); at decode sizes a single paced issuer is faster, see WantedProducers().
+constexpr int kProducers = 4;
+constexpr int kThreads = (kWarps + kProducers) * 32;
 constexpr int kMaxSlots = 32;
 constexpr int kMaxTokens = 4;             // most activation rows handled per CTA pass
 #ifndef MNB_MMA_UNROLL
 #define MNB_MMA_UNROLL 4
 #endif
 constexpr int kUnroll = MNB_MMA_UNROLL;   // supergroups per loop round (1, 2 or 4)
+constexpr int kZeroBytes = 256 * kUnroll + 64; // what an inactive lane reads in one loop round
 
 struct MmaParams {
   WeightView w;
@@ -85,6 +89,7 @@ struct MmaParams {
   int rec_scale_bytes;  // scale part of a record
   int slot_bytes;
   int num_slots;
+  int producers;        // producer warps in use (num_slots is a multiple of it)
   int act_row_bytes;    // bytes between activation piece rows in shared memory
   int k_pad;            // activation positions per piece row (all tasks, zero beyond K)
   int tokens_per_pass;  // activation rows per grid.y pass (8 columns / blocks-per-supergroup / 2)
@@ -103,7 +108,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   //         [pair exchange: 2 x kPairs x 32 lanes x 2][barriers]
   unsigned char *slots = smem_raw;
   unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
-  float *inv_scale = reinterpret_cast<float *>(act + (2 * p.tokens_per_pass + 1) * p.act_row_bytes);
+  float *inv_scale = reinterpret_cast<float *>(act + 2 * p.tokens_per_pass * p.act_row_bytes + kZeroBytes);
   float *scratch = inv_scale + kMaxTokens;          // [2][kWarps], alternating with the token index
   float2 *pair_buf = reinterpret_cast<float2 *>(scratch + 2 * kWarps); // [2][kPairs][32]
   std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + 2 * kPairs * 32);
@@ -137,12 +142,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
 
-  if (warp == kWarps) {
-    // ------------------------------ producer ------------------------------
-    // One lane issues, per task, one 2-D tiled TMA load of the weight tile (16 rows x the
-    // slice; rows past the matrix end are zero-filled) and one bulk copy of the task's
-    // scale / zero-point records (two consecutive half tiles of the same slice).
-    if (lane == 0) {
+  if (warp >= kWarps) {
+    // ------------------------------ producers ------------------------------
+    // One lane per producer warp issues, per task, one 2-D tiled TMA load of the weight tile (16
+    // rows x the slice; rows past the matrix end are zero-filled) and one bulk copy of the
+    // task's scale / zero-point records (two consecutive half tiles of the same slice).
+    // Producer j takes the tasks with index % producers == j. num_slots is a multiple of the
+    // number of producers, so all rounds of a slot belong to the same producer and its parity
+    // waits on that slot follow each other in order.
+    const int producer = warp - kWarps;
+    if (producer == 0 && lane == 0) {
       for (int s = 0; s < p.num_slots; ++s) {
         ptx::MbarInit(&full_bar[s], 1);
         ptx::MbarInit(&empty_bar[s], 1);
@@ -150,14 +159,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ptx::FenceMbarInit();
     }
-    __syncwarp();
-    // the consumers join this barrier after staging the activations; the producer does not wait
+    // barriers initialised: the producers go on at once; the consumers join barrier 10 after
+    // staging the activations, the producers only arrive there
+    asm volatile("bar.sync 11, %0;" ::"n"(kProducers * 32) : "memory");
     asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
-    if (lane == 0) {
+    if (lane == 0 && producer < p.producers) {
       ptx::PrefetchTensorMap(&map_b);
       int task = 0;
       int slot = 0;              // task % num_slots, kept incrementally
       std::uint32_t round = 0;   // task / num_slots
+      int turn = 0;              // task % producers
       bool ok = true;
       const std::uint32_t box_bytes = 16u * static_cast<std::uint32_t>(p.slice_b_bytes);
       const int x_step = p.slice_b_bytes / 4;
@@ -169,18 +180,23 @@ __global__ void __launch_bounds__(kThreads, 1)
           int h0 = h_begin + 2 * wave0;
           const unsigned char *meta_src = meta_slice;
           for (int wt = 0; wt < wave_tiles; ++wt, ++task, h0 += 2, meta_src += 2 * p.rec_bytes) {
-            if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
-              ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
-              ok = false;
-              break;
+            if (turn == producer) {
+              if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+                ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
+                ok = false;
+                break;
+              }
+              const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+              unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+              slot_task[slot] = task;
+              MNB_MARK(32 + task);
+              ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
+              ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
+              ptx::BulkLoad(dst + box_bytes, meta_src, meta_bytes, &full_bar[slot]);
             }
-            const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
-            unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
-            slot_task[slot] = task;
-            MNB_MARK(32 + task);
-            ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
-            ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
-            ptx::BulkLoad(dst + box_bytes, meta_src, meta_bytes, &full_bar[slot]);
+            if (++turn == p.producers) {
+              turn = 0;
+            }
             if (++slot == p.num_slots) {
               slot = 0;
               ++round;
@@ -188,10 +204,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      // stay until every copy issued has been consumed (bounded), so none lands after exit
+      // stay until every copy this lane issued has been consumed (bounded), so none lands after exit
       const int first = task - p.num_slots < 0 ? 0 : task - p.num_slots;
       for (int i = first; i < task && ok; ++i) {
-        if (!ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
+        if ((i % p.producers) == producer &&
+            !ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
           break;
         }
       }
@@ -207,8 +224,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   // the consumers depend on it. The producer warp above only touches the constant weights.
   ptx::GridDependencyWait();
   const int words_total = p.k_pad >> 3;
+  // lanes whose MMA column takes no part read zeros: a small region that they re-read every
+  // round (their pointer does not advance), not a whole row
   unsigned char *zero_row = act + 2 * p.tokens_per_pass * p.act_row_bytes;
-  for (int i = tid; i < (p.act_row_bytes >> 4); i += kConsumerThreads) {
+  for (int i = tid; i < (kZeroBytes >> 4); i += kConsumerThreads) {
     reinterpret_cast<uint4 *>(zero_row)[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   for (int mi = 0; mi < p.tokens_per_pass; ++mi) {
@@ -342,6 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // lanes whose column takes no part read a row of zeros, so the loads need no predicate
   const unsigned char *act_lane =
       (b_active ? act + (2 * m_b + piece_b) * p.act_row_bytes : zero_row) + t * 16;
+  const int lane_step = b_active ? 256 : 0; // bytes per supergroup in this lane's activation row
   // role of this lane's accumulator columns (2t, 2t+1)
   const int m_d = t >> NB_SG_LOG2;
   const int blk_d = t & (kNbSg - 1);
@@ -395,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes);
       const unsigned char *zr0 = meta0 + p.rec_scale_bytes + g * p.bpt;
       const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt;
-      const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * 256;
+      const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * lane_step;
 
       for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += kUnroll) {
         // scales / zero points of the supergroups of this round
@@ -468,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         row_lo += 64 * kUnroll;
         row_hi += 64 * kUnroll;
-        act_task += 256 * kUnroll;
+        act_task += lane_step * kUnroll;
       }
       __syncwarp();
       if (lane == 0) {
@@ -649,7 +669,7 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   }
   p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
   p.slot_bytes = (16 * p.slice_b_bytes + 2 * p.rec_bytes + 127) & ~127;
-  const size_t fixed = static_cast<size_t>(2 * tokens_per_pass + 1) * p.act_row_bytes +
+  const size_t fixed = static_cast<size_t>(2 * tokens_per_pass) * p.act_row_bytes + kZeroBytes +
                        (kMaxTokens + 2 * kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
                        2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
   const size_t limit = 225 * 1024;
@@ -659,6 +679,14 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   int slots = static_cast<int>((limit - fixed) / p.slot_bytes);
   if (slots > kMaxSlots) {
     slots = kMaxSlots;
+  }
+  // four producers need a ring that is a multiple of four deep (see the producer loop)
+  const int wanted_producers = WantedProducers(1);
+  if (wanted_producers > 1 && slots >= wanted_producers) {
+    slots -= slots % wanted_producers;
+    p.producers = wanted_producers;
+  } else {
+    p.producers = 1;
   }
   p.num_slots = slots;
   const size_t smem = static_cast<size_t>(slots) * p.slot_bytes + fixed + 128; // + alignment slack

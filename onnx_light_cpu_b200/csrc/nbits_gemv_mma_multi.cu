@@ -558,7 +558,7 @@ const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t
     slots = kMaxSlots;
   }
   p.num_slots = slots;
-  p.producers = slots < kProducers ? slots : kProducers;
+  p.producers = slots < WantedProducers(kProducers) ? slots : WantedProducers(kProducers);
   const size_t smem = static_cast<size_t>(slots) * p.slot_bytes + fixed + 128; // + alignment slack
 
   int ctas = sm_count > 0 ? sm_count : 148;

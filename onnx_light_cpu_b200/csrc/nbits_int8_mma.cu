@@ -588,7 +588,7 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   p.rec_scale_bytes = meta.rec_scale_bytes;
   p.slot_bytes = geo.slot_bytes;
   p.num_slots = geo.num_slots;
-  p.producers = geo.num_slots < kProducers ? geo.num_slots : kProducers;
+  p.producers = geo.num_slots < WantedProducers(kProducers) ? geo.num_slots : WantedProducers(kProducers);
   p.tp = geo.tp;
   p.act_row_bytes = geo.act_row_bytes;
   p.table_offset = geo.table_offset;
