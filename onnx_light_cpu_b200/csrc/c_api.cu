@@ -94,6 +94,9 @@ struct mnb_weights {
   std::size_t a_dev_bytes = 0;
   std::size_t y_dev_bytes = 0;
   cudaStream_t stream = nullptr;
+  // last (A, Y) pair of the device-pointer entry points whose location has been checked
+  const void *checked_a = nullptr;
+  const void *checked_y = nullptr;
 };
 
 namespace {
@@ -567,6 +570,32 @@ int mnb_matmul_device_strided(mnb_weights *h, const float *a_dev, int64_t m, int
   const cudaError_t err = cudaSetDevice(h->device);
   if (err != cudaSuccess) {
     return FailCuda("cudaSetDevice", err);
+  }
+  // Device memory of another GPU would be read through an address this GPU cannot reach (a
+  // fault, not an error code): check where A and Y live, once per pointer pair.
+  if (m > 0 && (a_dev != h->checked_a || y_dev != h->checked_y)) {
+    for (const void *ptr : {static_cast<const void *>(a_dev), static_cast<const void *>(y_dev)}) {
+      cudaPointerAttributes attributes{};
+      const cudaError_t query = cudaPointerGetAttributes(&attributes, ptr);
+      if (query != cudaSuccess) {
+        cudaGetLastError();
+        continue; // not known to the runtime: leave the decision to the launch
+      }
+      if (attributes.type == cudaMemoryTypeDevice && attributes.device != h->device) {
+        char text[160];
+        std::snprintf(text, sizeof(text),
+                      "MatMulNBits: A and Y must be memory of GPU %d, where the weights are (got memory of GPU %d).",
+                      h->device, attributes.device);
+        return Fail(MNB_ERR_INVALID_ARGUMENT, text);
+      }
+      if (attributes.type == cudaMemoryTypeUnregistered) {
+        return Fail(MNB_ERR_INVALID_ARGUMENT,
+                    "MatMulNBits: the device-pointer entry points take device memory; use mnb_matmul_host for "
+                    "host buffers.");
+      }
+    }
+    h->checked_a = a_dev;
+    h->checked_y = y_dev;
   }
   OutputView out{y_dev, ld_y, col_offset};
   return Dispatch(h, a_dev, m, accuracy_level, path, out, static_cast<cudaStream_t>(stream));

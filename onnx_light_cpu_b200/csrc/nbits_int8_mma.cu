@@ -9,7 +9,9 @@
 // A registers. That places codes 0,2,4,6 of the word in k slots 4t..4t+3 and codes 1,3,5,7 in
 // slots 16+4t..16+4t+3 of the 32-wide step; the activations are stored in that order by the
 // quantization kernel, so no shuffle is needed. The zero point is taken out afterwards with
-// the per-block activation sums: sum aq*(q - zp) = D - zp * sum aq. One MMA step covers 32
+// the per-block activation sums: sum aq*(q - zp) = D - zp * sum aq. A node without zero points
+// (zp = 8 everywhere) skips that: its codes enter as the signed bytes 16 * (q - 8), which cost
+// the same three operations per word, and the factor 16 is folded into the activation scale. One MMA step covers 32
 // consecutive k, so a quantization block (32, 64, 128, ...) is a whole number of steps and the
 // int32 accumulator restarts at each block.
 //
@@ -84,6 +86,31 @@ __device__ __forceinline__ void MmaU8S8Zero(int (&d)[4], std::uint32_t a0, std::
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// Signed A operand: used when the node has no zero points, with codes stored as 16 * (q - 8).
+__device__ __forceinline__ void MmaS8S8(int (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                        std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void MmaS8S8Zero(int (&d)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                            std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// (x & 0xf0f0f0f0) ^ 0x80808080: a code in the high nibble of each byte, minus 8, times 16, as a
+// signed byte (the nibble pattern q ^ 8 is q - 8 in 4-bit two's complement).
+__device__ __forceinline__ std::uint32_t SignedHighNibbles(std::uint32_t x) {
+  std::uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(x), "r"(0xf0f0f0f0u), "r"(0x80808080u));
+  return d;
+}
+
 __device__ __forceinline__ void TmaLoad3D(void *smem_dst, const void *tensor_map, int x, int y, int z,
                                           std::uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -108,7 +135,7 @@ __host__ __device__ inline int ActBytePosition(int k) {
 __global__ void __launch_bounds__(256)
     nbits_quantize_a_imma_kernel(const float *a, int m_total, std::int64_t k, int block_size, int entry_k,
                                  int entries_pad, int tp, int act_row_bytes, int table_offset, int pass_bytes,
-                                 int passes, unsigned char *act) {
+                                 int passes, float table_scale, unsigned char *act) {
   // the multiply kernel behind this one may start (barrier set-up, first weight tiles) right away
   ptx::GridDependencyLaunch();
   const int warp = threadIdx.x >> 5;
@@ -158,7 +185,9 @@ __global__ void __launch_bounds__(256)
   }
   if (lane == 0) {
     unsigned char *cell = base + table_offset + static_cast<std::int64_t>(entry) * tp * 8;
-    reinterpret_cast<float *>(cell)[token] = sa;
+    // table_scale is 1, or 1/16 for nodes without zero points, whose codes enter the MMA as
+    // 16 * (q - 8): an exact power-of-two factor either way
+    reinterpret_cast<float *>(cell)[token] = sa * table_scale;
     reinterpret_cast<int *>(cell + tp * 4)[token] = sum;
   }
 }
@@ -387,34 +416,45 @@ __global__ void __launch_bounds__(kThreads, 1)
         const unsigned char *cell = table + static_cast<size_t>(s) * entries_per_task * entry_bytes;
 #pragma unroll
         for (int st = 0; st < 4; ++st) {
-          const std::uint32_t a0 = w_lo[st] & nib;
-          const std::uint32_t a1 = w_hi[st] & nib;
-          const std::uint32_t a2 = (w_lo[st] >> 4) & nib;
-          const std::uint32_t a3 = (w_hi[st] >> 4) & nib;
+          // with zero points: unsigned codes, zero point taken out afterwards through the sums;
+          // without: 16 * (q - 8) as signed bytes, nothing to take out (same three operations)
+          const std::uint32_t a0 = HAS_ZP ? (w_lo[st] & nib) : SignedHighNibbles(w_lo[st] << 4);
+          const std::uint32_t a1 = HAS_ZP ? (w_hi[st] & nib) : SignedHighNibbles(w_hi[st] << 4);
+          const std::uint32_t a2 = HAS_ZP ? ((w_lo[st] >> 4) & nib) : SignedHighNibbles(w_lo[st]);
+          const std::uint32_t a3 = HAS_ZP ? ((w_hi[st] >> 4) & nib) : SignedHighNibbles(w_hi[st]);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint4 &q = bq[nt][st >> 1];
             const std::uint32_t b0 = (st & 1) ? q.z : q.x;
             const std::uint32_t b1 = (st & 1) ? q.w : q.y;
-            if ((st % SPB) == 0) {
-              MmaU8S8Zero(d[nt], a0, a1, a2, a3, b0, b1);
+            if constexpr (HAS_ZP) {
+              if ((st % SPB) == 0) {
+                MmaU8S8Zero(d[nt], a0, a1, a2, a3, b0, b1);
+              } else {
+                MmaU8S8(d[nt], a0, a1, a2, a3, b0, b1);
+              }
             } else {
-              MmaU8S8(d[nt], a0, a1, a2, a3, b0, b1);
+              if ((st % SPB) == 0) {
+                MmaS8S8Zero(d[nt], a0, a1, a2, a3, b0, b1);
+              } else {
+                MmaS8S8(d[nt], a0, a1, a2, a3, b0, b1);
+              }
             }
           }
           if (((st + 1) % SPB) == 0) {
             // a table entry is complete: D - zp * sum(aq), scaled, into the fp32 sums
             const int idx = st / SPB;
-            const int zl = HAS_ZP ? zp_lo[idx] : 8;
-            const int zh = HAS_ZP ? zp_hi[idx] : 8;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               const float2 sa = *reinterpret_cast<const float2 *>(cell + idx * entry_bytes + nt * 32);
-              const int2 sum = *reinterpret_cast<const int2 *>(cell + idx * entry_bytes + p.tp * 4 + nt * 32);
-              const int e0 = d[nt][0] - zl * sum.x;
-              const int e1 = d[nt][1] - zl * sum.y;
-              const int e2 = d[nt][2] - zh * sum.x;
-              const int e3 = d[nt][3] - zh * sum.y;
+              int e0 = d[nt][0], e1 = d[nt][1], e2 = d[nt][2], e3 = d[nt][3];
+              if constexpr (HAS_ZP) {
+                const int2 sum = *reinterpret_cast<const int2 *>(cell + idx * entry_bytes + p.tp * 4 + nt * 32);
+                e0 -= zp_lo[idx] * sum.x;
+                e1 -= zp_lo[idx] * sum.y;
+                e2 -= zp_hi[idx] * sum.x;
+                e3 -= zp_hi[idx] * sum.y;
+              }
               acc[nt][0] = fmaf(sa.x * ws_lo[idx], static_cast<float>(e0), acc[nt][0]);
               acc[nt][1] = fmaf(sa.y * ws_lo[idx], static_cast<float>(e1), acc[nt][1]);
               acc[nt][2] = fmaf(sa.x * ws_hi[idx], static_cast<float>(e2), acc[nt][2]);
@@ -569,7 +609,7 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
   nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
       a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
-      geo.table_offset, geo.pass_bytes, geo.passes, scratch);
+      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
   if (cudaGetLastError() != cudaSuccess) {
     return nullptr;
   }

@@ -421,6 +421,18 @@ def test_host_call_pinned_and_pageable_buffers(cuda_device):
     weights.close()
 
 
+def test_device_entry_point_refuses_host_pointers(cuda_device):
+    import torch
+
+    case = syn.make_case("host_ptr", 1, 4096, 64, 4, 128, seed=3)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=128)
+    y = torch.zeros((1, 64), device="cuda")
+    with pytest.raises(_capi.MatMulNBitsError, match="take device memory") as info:
+        _capi.check(weights._lib.mnb_matmul_device(weights._handle, case.a.ctypes.data, 1, 0, 0, y.data_ptr(), None))
+    assert info.value.status == _capi.MNB_ERR_INVALID_ARGUMENT
+    weights.close()
+
+
 def test_llama_layer_shapes_both_accuracy_levels(cuda_device):
     """cfg4 geometry (seven projections, M=16, block 32, no zero points) at reduced N."""
     for level in (0, 4):

@@ -79,3 +79,23 @@ def test_peer_store_gather_two_gpus():
     import torch.multiprocessing as mp
 
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_device_entry_point_refuses_memory_of_another_gpu():
+    """Weights on GPU 0, activations on GPU 1: an error code, not a fault."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on one box")
+    import onnx_light_cpu_b200 as pkg
+    from onnx_light_cpu_b200 import _capi
+    from onnx_light_cpu_b200.tools import synthetic as syn
+
+    case = syn.make_case("wrong_gpu", 1, 4096, 64, 4, 128, seed=3)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=128, device=0)
+    a = torch.from_numpy(case.a).to("cuda:1")
+    y = torch.zeros((1, 64), device="cuda:1")
+    with pytest.raises(_capi.MatMulNBitsError, match="must be memory of GPU 0") as info:
+        weights.matmul_device(a, y)
+    assert info.value.status == _capi.MNB_ERR_INVALID_ARGUMENT
+    weights.close()
