@@ -27,7 +27,8 @@ CUDA_SOURCES = [
     "csrc/nbits_int8_mma.cu",
     "csrc/nbits_gemm_tcgen05.cu",
 ]
-CUDA_HEADERS = ["csrc/nbits_common.cuh", "csrc/nbits_ptx.cuh", "../include/matmulnbits_b200.h"]
+CUDA_HEADERS = ["csrc/nbits_common.cuh", "csrc/nbits_ptx.cuh", "csrc/nbits_tma.cuh", "csrc/nbits_mma_common.cuh",
+                "../include/matmulnbits_b200.h"]
 HOST_SOURCES = [
     "kernels/kernel_registration.cc",
     "kernels/kernel_usage.cc",

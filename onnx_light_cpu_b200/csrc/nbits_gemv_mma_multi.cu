@@ -186,122 +186,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   // A (and Y) may be produced / still read by the previous kernel in the stream: from here on
   // the consumers depend on it. The producer warp above only touches the constant weights.
   ptx::GridDependencyWait();
-  const int words_total = p.k_pad >> 3;
   unsigned char *zero_row = act + 2 * p.token_rows * p.act_row_bytes;
   for (int i = tid; i < (p.act_row_bytes >> 4); i += kConsumerThreads) {
     reinterpret_cast<uint4 *>(zero_row)[i] = make_uint4(0u, 0u, 0u, 0u);
   }
-  // rows of tokens beyond the last one are never read (their lanes point at the zero row)
-  for (int mi = 0; mi < tokens; ++mi) {
-    const bool live = true;
-    const float *src = p.a + static_cast<std::int64_t>(m_base + mi) * p.w.k;
-    const bool in_registers = words_total <= 4 * kConsumerThreads;
-    const bool vector_ok = (reinterpret_cast<std::uintptr_t>(src) & 15u) == 0;
-    float v[4][8];
-    float amax = 0.0f;
-    if (in_registers) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k0 = (tid + j * kConsumerThreads) << 3;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          v[j][e] = 0.0f;
-        }
-        if (live && k0 < p.w.k) {
-          if (vector_ok && k0 + 8 <= p.w.k) {
-            const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + k0));
-            const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + k0 + 4));
-            v[j][0] = lo.x, v[j][1] = lo.y, v[j][2] = lo.z, v[j][3] = lo.w;
-            v[j][4] = hi.x, v[j][5] = hi.y, v[j][6] = hi.z, v[j][7] = hi.w;
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              if (k0 + e < p.w.k) {
-                v[j][e] = __ldg(src + k0 + e);
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          amax = fmaxf(amax, fabsf(v[j][e]));
-        }
-      }
-    } else if (live) {
-      for (int k = tid; k < p.w.k; k += kConsumerThreads) {
-        amax = fmaxf(amax, fabsf(__ldg(src + k)));
-      }
-    }
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
-    }
-    // two scratch rows: a warp that is one token ahead writes the other row, and it cannot be
-    // two ahead because of the barrier in between
-    float *row_max = scratch + (mi & 1) * kWarps;
-    if (lane == 0) {
-      row_max[warp] = amax;
-    }
-    asm volatile("bar.sync 9, %0;" ::"n"(kConsumerThreads) : "memory");
-    amax = row_max[0];
-#pragma unroll
-    for (int i = 1; i < kWarps; ++i) {
-      amax = fmaxf(amax, row_max[i]);
-    }
-    int e2 = 0;
-    if (amax > 0.0f && amax < 3.0e38f) {
-      e2 = 14 - ilogbf(amax);
-      e2 = e2 > 100 ? 100 : (e2 < -100 ? -100 : e2);
-    }
-    const float up = scalbnf(1.0f, e2);
-    if (tid == 0) {
-      inv_scale[mi] = scalbnf(1.0f, -e2);
-    }
-    unsigned char *row_hi = act + (2 * mi) * p.act_row_bytes;
-    unsigned char *row_lo = act + (2 * mi + 1) * p.act_row_bytes;
-    // splits eight scaled activations into two fp16 pieces and stores both 16-byte words
-    auto store_word = [&](int k0, const float (&x)[8]) {
-      std::uint32_t hi[4], lo[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) { // stored order inside a word: k = 0,4,1,5,2,6,3,7
-        const __half a_hi = __float2half_rn(x[q]);
-        const __half b_hi = __float2half_rn(x[q + 4]);
-        const __half a_lo = __float2half_rn(x[q] - __half2float(a_hi));
-        const __half b_lo = __float2half_rn(x[q + 4] - __half2float(b_hi));
-        hi[q] = static_cast<std::uint32_t>(__half_as_ushort(a_hi)) |
-                (static_cast<std::uint32_t>(__half_as_ushort(b_hi)) << 16);
-        lo[q] = static_cast<std::uint32_t>(__half_as_ushort(a_lo)) |
-                (static_cast<std::uint32_t>(__half_as_ushort(b_lo)) << 16);
-      }
-      const int byte = ActPosition(k0) * 2;
-      *reinterpret_cast<uint4 *>(row_hi + byte) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4 *>(row_lo + byte) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    };
-    if (in_registers) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int word = tid + j * kConsumerThreads;
-        if (word < words_total) {
-          float x[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            x[e] = v[j][e] * up;
-          }
-          store_word(word << 3, x);
-        }
-      }
-    } else {
-      for (int word = tid; word < words_total; word += kConsumerThreads) {
-        const int k0 = word << 3;
-        float x[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          x[e] = (live && k0 + e < p.w.k) ? __ldg(src + k0 + e) * up : 0.0f;
-        }
-        store_word(k0, x);
-      }
-    }
-  }
+  // all rows at once, one group of warps per row (rows beyond `tokens` are never read: their
+  // lanes point at the zero region)
+  StageActivations<kWarps>(p.a + static_cast<std::int64_t>(m_base) * p.w.k, tokens, static_cast<int>(p.w.k), p.k_pad,
+                           act, p.act_row_bytes, inv_scale, scratch, tid);
   // activations staged and (through the producer's arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
   if (tid == 0) {
