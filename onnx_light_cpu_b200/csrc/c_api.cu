@@ -82,6 +82,7 @@ struct mnb_weights {
   int *status_dev = nullptr;
   int *status_host = nullptr;
   void *meta_dev = nullptr; // prepared scales / zero points for the MMA decode kernel
+  unsigned *arrivals_dev = nullptr; // finished-CTA counter of the fused gather (zero between launches)
   // scratch, grown on demand (guarded by `mutex`)
   std::mutex mutex;
   void *scratch_a = nullptr; // bf16 activations (prefill) or int8 activations (accuracy_level 4)
@@ -155,6 +156,13 @@ int SetupCommon(mnb_weights *h) {
   if (err != cudaSuccess) {
     return FailCuda("cudaHostGetDevicePointer(status)", err);
   }
+  err = cudaMalloc(&h->arrivals_dev, sizeof(unsigned));
+  if (err == cudaSuccess) {
+    err = cudaMemset(h->arrivals_dev, 0, sizeof(unsigned));
+  }
+  if (err != cudaSuccess) {
+    return FailCuda("cudaMalloc(arrival counter)", err);
+  }
   err = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
   if (err != cudaSuccess) {
     return FailCuda("cudaStreamCreate", err);
@@ -217,44 +225,10 @@ __global__ void __launch_bounds__(256) nbits_fetch_kernel(const uint4 *src, uint
   }
 }
 
-// One warp: lane r tells rank r that this rank's columns of step `epoch` are stored, then waits
-// until rank r's flag in the local array carries the epoch. The stores of the kernels before
-// this one in the stream have completed when it starts; the system-scope fences order the flag
-// against them for the peers and the peers' data against the flag for this GPU.
-struct PeerFlags {
-  int *ranks[MNB_MAX_GATHER_RANKS];
-};
-
-__global__ void __launch_bounds__(32) nbits_publish_wait_kernel(PeerFlags flags, int ranks, int rank, int epoch,
-                                                                int *status) {
-  const int lane = threadIdx.x;
-  if (epoch == 0) {
-    // self-counting mode (what a replayed CUDA graph needs): the step number lives next to the
-    // local flags and grows by one per call, in lockstep on all ranks
-    int *counter = flags.ranks[rank] + MNB_MAX_GATHER_RANKS;
-    epoch = *reinterpret_cast<volatile int *>(counter) + 1;
-    __syncwarp();
-    if (lane == 0) {
-      *reinterpret_cast<volatile int *>(counter) = epoch;
-    }
-  }
-  if (lane < ranks) {
-    __threadfence_system();
-    *reinterpret_cast<volatile int *>(flags.ranks[lane] + rank) = epoch;
-    volatile int *mine = flags.ranks[rank] + lane;
-    bool arrived = false;
-    for (std::uint32_t spin = 0; spin < (1u << 22); ++spin) { // about a second in all
-      if (*mine - epoch >= 0) {
-        arrived = true;
-        break;
-      }
-      __nanosleep(200);
-    }
-    if (!arrived) {
-      mnb::ReportStatus(status, mnb::kDeviceTimeoutPeerFlag);
-    }
-    __threadfence_system();
-  }
+// Stand-alone form of the flag exchange, launched behind kernels that do not run it themselves.
+// The stores of the kernels before it in the stream have completed when it starts.
+__global__ void __launch_bounds__(32) nbits_publish_wait_kernel(mnb::GatherTail tail, int *status) {
+  mnb::PublishAndWait(tail, threadIdx.x, status);
 }
 
 // Core dispatch. The caller holds h->mutex and has made h->device current.
@@ -541,7 +515,7 @@ int mnb_weights_destroy(mnb_weights *h) {
       }
     }
   }
-  for (void *ptr : {h->meta_dev, h->scratch_a, h->scratch_s,
+  for (void *ptr : {static_cast<void *>(h->arrivals_dev), h->meta_dev, h->scratch_a, h->scratch_s,
                     static_cast<void *>(h->a_dev), static_cast<void *>(h->y_dev)}) {
     if (ptr != nullptr) {
       cudaFree(ptr);
@@ -729,9 +703,13 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   OutputView out{y_ranks[rank], ld_y, col_offset};
-  PeerFlags flags{};
+  mnb::GatherTail tail{};
+  tail.ranks = ranks;
+  tail.rank = rank;
+  tail.epoch = epoch;
+  tail.arrivals = h->arrivals_dev;
   for (int r = 0; r < ranks; ++r) {
-    flags.ranks[r] = flags_ranks[r];
+    tail.flags[r] = flags_ranks[r];
     if (r != rank) {
       out.peers[out.n_peers++] = y_ranks[r];
     }
@@ -739,8 +717,18 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   const WeightView &w = h->view;
   const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
   const char *name = nullptr;
+  bool fused = false;
   if (m > per_pass) {
     name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+  }
+  static const bool fuse_tail = [] {
+    const char *value = std::getenv("MNB_GATHER_FUSED");
+    return value == nullptr || value[0] != '0';
+  }();
+  if (name == nullptr && m <= per_pass && fuse_tail) {
+    // one pass over the weights: the kernel's last CTA runs the flag exchange itself
+    name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &tail);
+    fused = name != nullptr;
   }
   if (name == nullptr) {
     name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
@@ -750,13 +738,15 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
                 "mnb_matmul_device_gather: only shapes of the tensor-core decode kernels (bits=4, "
                 "32 <= block_size <= 1024, 16-byte aligned rows) store to peers.");
   }
-  cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
-  nbits_publish_wait_kernel<<<1, 32, 0, stream>>>(flags, ranks, rank, epoch, h->status_dev);
-  const cudaError_t launch_err = cudaGetLastError();
-  if (launch_err != cudaSuccess) {
-    return FailCuda("launch of the publish kernel", launch_err);
+  if (!fused) {
+    cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
+    nbits_publish_wait_kernel<<<1, 32, 0, stream>>>(tail, h->status_dev);
+    const cudaError_t launch_err = cudaGetLastError();
+    if (launch_err != cudaSuccess) {
+      return FailCuda("launch of the publish kernel", launch_err);
+    }
+    mnb::CountLaunch();
   }
-  mnb::CountLaunch();
   mnb::t_last_kernel = name;
   return MNB_OK;
 }

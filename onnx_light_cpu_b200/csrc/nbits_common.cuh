@@ -69,6 +69,50 @@ __device__ __forceinline__ void ReportStatus(int *word, int code) {
   __threadfence_system();
 }
 
+// Flag exchange that ends a gathered step (column shards stored into every rank's result
+// through peer memory): one warp tells every rank that this rank's columns of step `epoch` are
+// stored and waits, bounded (about a second), until the local flag of every rank carries the
+// epoch. flags[r] is rank r's flag array as mapped here: kMaxGatherRanks flags, then the step
+// counter used when epoch == 0 (self-counting mode, what a replayed CUDA graph needs: the step
+// number grows by one per call, in lockstep on all ranks).
+constexpr int kMaxGatherRanks = 8;
+struct GatherTail {
+  int *flags[kMaxGatherRanks];
+  int ranks;         // 0 = no gather
+  int rank;
+  int epoch;
+  unsigned *arrivals; // device counter of finished CTAs, zero between launches (fused variant only)
+};
+
+__device__ __forceinline__ void PublishAndWait(const GatherTail &tail, int lane, int *status) {
+  int epoch = tail.epoch;
+  if (epoch == 0) {
+    int *counter = tail.flags[tail.rank] + kMaxGatherRanks;
+    epoch = *reinterpret_cast<volatile int *>(counter) + 1;
+    __syncwarp();
+    if (lane == 0) {
+      *reinterpret_cast<volatile int *>(counter) = epoch;
+    }
+  }
+  if (lane < tail.ranks) {
+    __threadfence_system();
+    *reinterpret_cast<volatile int *>(tail.flags[lane] + tail.rank) = epoch;
+    volatile int *mine = tail.flags[tail.rank] + lane;
+    bool arrived = false;
+    for (std::uint32_t spin = 0; spin < (1u << 22); ++spin) {
+      if (*mine - epoch >= 0) {
+        arrived = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+    if (!arrived) {
+      ReportStatus(status, 5 /* kDeviceTimeoutPeerFlag */);
+    }
+    __threadfence_system();
+  }
+}
+
 __host__ __device__ inline int ZeroPointOf(const WeightView &w, std::int64_t row, int block) {
   if (w.zp == nullptr) {
     return 1 << (w.bits - 1);
@@ -113,8 +157,11 @@ struct MetaGeometry {
 };
 MetaGeometry MetaGeometryOf(const WeightView &w);
 bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t stream);
+// `tail` (optional): the last CTA to finish runs the flag exchange of a gathered step itself, so
+// no second kernel is needed.
 const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                          int *status_word, cudaStream_t stream, int sm_count);
+                          int *status_word, cudaStream_t stream, int sm_count,
+                          const GatherTail *tail = nullptr);
 // Same arithmetic with two or four column tiles of tokens per pass over the weights; nullptr
 // when one column tile is enough for `m` or the shape is outside what the kernel takes.
 const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t m, OutputView out,

@@ -94,6 +94,7 @@ struct MmaParams {
   int k_pad;            // activation positions per piece row (all tasks, zero beyond K)
   int tokens_per_pass;  // activation rows per grid.y pass (8 columns / blocks-per-supergroup / 2)
   std::uint32_t magic;  // 0x64006400, passed at run time so that it stays in a register
+  GatherTail tail;      // flag exchange of a gathered step, run by the last CTA (ranks == 0: none)
 };
 
 // NB_SG_LOG2: log2 of quantization blocks per 128-k supergroup (block 128+: 0, 64: 1, 32: 2).
@@ -424,6 +425,29 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   }
+  // ---- gathered step: the last CTA of the grid exchanges the flags ---------------------------
+  if (p.tail.ranks > 0) {
+    // every consumer thread fences its own stores (local and peer), then the CTA meets
+    __threadfence_system();
+    asm volatile("bar.sync 12, %0;" ::"n"(kConsumerThreads) : "memory");
+    if (warp == 0) {
+      unsigned last = 0;
+      if (lane == 0) {
+        __threadfence_system(); // cumulative: the CTA's fenced stores before its arrival
+        const unsigned total = gridDim.x * gridDim.y;
+        last = atomicAdd(p.tail.arrivals, 1u) == total - 1 ? 1u : 0u;
+        if (last != 0) {
+          *p.tail.arrivals = 0; // everybody has arrived: ready for the next launch
+        }
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last != 0) {
+        __threadfence_system(); // the other CTAs' fenced stores before the flags
+        PublishAndWait(p.tail, lane, p.status);
+      }
+    }
+  }
+
 }
 
 // ---- prepared side array -----------------------------------------------------------------
@@ -521,7 +545,7 @@ bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t st
 }
 
 const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                          int *status_word, cudaStream_t stream, int sm_count) {
+                          int *status_word, cudaStream_t stream, int sm_count, const GatherTail *tail) {
   const MetaGeometry geo = MetaGeometryOf(w);
   if (geo.bytes == 0 || w.meta == nullptr || m < 1 || (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0) {
     return nullptr;
@@ -533,6 +557,9 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   p.out = out;
   p.status = status_word;
   p.magic = 0x64006400u;
+  if (tail != nullptr) {
+    p.tail = *tail;
+  }
   p.half_tiles = geo.half_tiles;
   p.bpt = geo.bpt;
   p.slices = geo.slices;
