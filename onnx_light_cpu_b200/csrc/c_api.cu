@@ -721,8 +721,8 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   if (m > per_pass) {
     name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
   }
-  // off by default: on two GPUs the first measurement had the fused form behind the separate
-  // flag kernel (56 vs 48 us per lm-head node); MNB_GATHER_FUSED=1 turns it on
+  // off by default: on two GPUs the fused form measured slower than the separate flag kernel
+  // (56.7 vs 48.2 us per lm-head node, same box); MNB_GATHER_FUSED=1 turns it on
   static const bool fuse_tail = [] {
     const char *value = std::getenv("MNB_GATHER_FUSED");
     return value != nullptr && value[0] == '1';
