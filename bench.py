@@ -450,17 +450,30 @@ def main() -> None:
         full_bytes = _capi.algorithmic_bytes(m, cfg["n"], cfg["k"], cfg["bits"], cfg["block_size"], True, False)
         from onnx_light_cpu_b200.tools import sharded
 
+        gather = None
         if args.gather == "peer":
             # one kernel per node: it stores this rank's columns into all ranks' gathered results
             # and a one-warp kernel behind it exchanges "done" flags (no collective on the data path)
-            gather = sharded.PeerGather(dist, local_rank, m_max=m, n_shard=shard_cfg["n"], slots=copies)
+            try:
+                gather = sharded.PeerGather(dist, local_rank, m_max=m, n_shard=shard_cfg["n"], slots=copies)
+                gather.run(weights[0], a, 0)   # one step: every rank sees whether the path works here
+                torch.cuda.synchronize()
+                works = 1 if weights[0].poll_status() == 0 else 0
+            except Exception as exc:  # pragma: no cover - depends on the box
+                print(f"bench: peer-store gather unavailable on rank {rank} ({exc}); using NCCL", file=sys.stderr)
+                works = 0
+            flag = torch.tensor([works], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:   # all ranks take the same path
+                gather = None
+                args.gather = "nccl"
+        if gather is not None:
             y_full = [gather.result(i) for i in range(copies)]
 
             def step():
                 for i, w in enumerate(weights):
                     gather.run(w, a, i)
         else:
-            gather = None
             y_shard = [torch.empty(m, shard_cfg["n"], device="cuda") for _ in range(copies)]
             y_full = [torch.empty(world, m, shard_cfg["n"], device="cuda") for _ in range(copies)]
 
