@@ -89,6 +89,10 @@ struct MmaParams {
   int rec_scale_bytes;  // scale part of a record
   int slot_bytes;
   int num_slots;
+  int full_rows;        // 1: a task is 16 whole weight rows (all of K), one contiguous bulk copy, shared
+                        //    by the two warps of a pair; 0: 16 rows x one 2048-k slice through a TMA box
+  int row_stride;       // bytes between weight rows inside a slot
+  int weight_bytes;     // bytes of the weight part of a slot
   int producers;        // producer warps in use (num_slots is a multiple of it)
   int act_row_bytes;    // bytes between activation piece rows in shared memory
   int k_pad;            // activation positions per piece row (all tasks, zero beyond K)
@@ -155,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (producer == 0 && lane == 0) {
       for (int s = 0; s < p.num_slots; ++s) {
         ptx::MbarInit(&full_bar[s], 1);
-        ptx::MbarInit(&empty_bar[s], 1);
+        ptx::MbarInit(&empty_bar[s], p.full_rows != 0 ? 2 : 1); // released by both warps of the pair
         slot_task[s] = -1;
       }
       ptx::FenceMbarInit();
@@ -174,7 +178,43 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint32_t box_bytes = 16u * static_cast<std::uint32_t>(p.slice_b_bytes);
       const int x_step = p.slice_b_bytes / 4;
       const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
-      for (int wave0 = 0; wave0 < n_tiles && ok; wave0 += kPairs) {
+      if (p.full_rows != 0) {
+        // one task per row tile: 16 whole rows are contiguous in memory, so one large bulk copy
+        // brings them (a single issuing thread sustains 6.4 TB/s with 32 KB copies against
+        // 4.4 TB/s with 16 KB boxes), plus the tile's scale / zero-point records of every slice
+        for (; task < n_tiles && ok; ++task) {
+          if (turn == producer) {
+            if (round != 0 && !ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+              ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
+              ok = false;
+              break;
+            }
+            const int h0 = h_begin + 2 * task;
+            const std::int64_t first_row = static_cast<std::int64_t>(h0) * 8;
+            const std::int64_t rows_left = p.w.n - first_row;
+            const std::uint32_t row_bytes_total =
+                static_cast<std::uint32_t>(rows_left < 16 ? rows_left : 16) * static_cast<std::uint32_t>(p.row_stride);
+            const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+            unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+            slot_task[slot] = task;
+            MNB_MARK(32 + task);
+            ptx::MbarArriveExpectTx(&full_bar[slot], row_bytes_total + static_cast<std::uint32_t>(p.slices) * meta_bytes);
+            ptx::BulkLoad(dst, p.w.b + first_row * p.row_stride, row_bytes_total, &full_bar[slot]);
+            const unsigned char *meta_src = p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes;
+            for (int s = 0; s < p.slices; ++s, meta_src += meta_slice_stride) {
+              ptx::BulkLoad(dst + p.weight_bytes + s * 2 * p.rec_bytes, meta_src, meta_bytes, &full_bar[slot]);
+            }
+          }
+          if (++turn == p.producers) {
+            turn = 0;
+          }
+          if (++slot == p.num_slots) {
+            slot = 0;
+            ++round;
+          }
+        }
+      }
+      for (int wave0 = 0; p.full_rows == 0 && wave0 < n_tiles && ok; wave0 += kPairs) {
         const int wave_tiles = n_tiles - wave0 < kPairs ? n_tiles - wave0 : kPairs;
         const unsigned char *meta_slice = p.w.meta + static_cast<std::int64_t>(h_begin + 2 * wave0) * p.rec_bytes;
         for (int s = 0; s < p.slices && ok; ++s, meta_slice += meta_slice_stride) {
@@ -264,7 +304,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t sixteenth = 0x2c002c00u;  // fp16 1/16 twice
   const std::uint32_t plus960 = 0x63806380u;    // fp16 960 twice
   const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
-  const int box_bytes = 16 * p.slice_b_bytes;
   // meta record: float scale[8 rows][bpt + 4] (padded rows keep lanes on different banks),
   // then uint8 zp[8 rows][bpt]
   const int scale_row_bytes = (p.bpt + 4) * 4;
@@ -280,9 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     float acc0 = 0.0f, acc1 = 0.0f; // rows g and g + 8, accumulator column pair t
     float da[4], db[4];
 
-    for (int s = parity; s < p.slices && !dead; s += 2) {
-      const int task = wave0 * p.slices + s * wave_tiles + pair;
-      const int slot = task % p.num_slots;
+    // waits (bounded) until `task` has landed in its slot; false after a time-out
+    auto wait_task = [&](int task, int slot) {
       const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
       // first use of a slot: its barrier is still in phase 0, no tag needed
       bool assigned = round == 0;
@@ -294,16 +332,33 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!assigned || !ptx::MbarWait(&full_bar[slot], round & 1u)) {
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
-        dead = true;
-        break;
+        return false;
       }
       if (lane == 0) {
         MNB_MARK(2 + task);
       }
+      return true;
+    };
+    // whole-row tasks: the tile is one task, which both warps of the pair wait for and release
+    int slot = tile % p.num_slots;
+    if (p.full_rows != 0 && !wait_task(tile, slot)) {
+      dead = true;
+    }
+
+    for (int s = parity; s < p.slices && !dead; s += 2) {
+      const int task = p.full_rows != 0 ? tile : wave0 * p.slices + s * wave_tiles + pair;
+      if (p.full_rows == 0) {
+        slot = task % p.num_slots;
+        if (!wait_task(task, slot)) {
+          dead = true;
+          break;
+        }
+      }
       const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
-      const unsigned char *row_lo = sb + g * p.slice_b_bytes + t * 16;
-      const unsigned char *row_hi = row_lo + 8 * p.slice_b_bytes;
-      const unsigned char *meta0 = sb + box_bytes;       // rows 0..7
+      const unsigned char *row_lo =
+          sb + g * p.row_stride + (p.full_rows != 0 ? s * p.slice_b_bytes : 0) + t * 16;
+      const unsigned char *row_hi = row_lo + 8 * p.row_stride;
+      const unsigned char *meta0 = sb + p.weight_bytes + (p.full_rows != 0 ? s * 2 * p.rec_bytes : 0); // rows 0..7
       const unsigned char *meta1 = meta0 + p.rec_bytes;  // rows 8..15
       const float *sc0 = reinterpret_cast<const float *>(meta0 + g * scale_row_bytes);
       const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes);
@@ -385,9 +440,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         act_task += lane_step * kUnroll;
       }
       __syncwarp();
-      if (lane == 0) {
+      if (lane == 0 && p.full_rows == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
         MNB_MARK(17 + task);
+      }
+    }
+    if (p.full_rows != 0 && !dead) {
+      __syncwarp();
+      if (lane == 0) {
+        ptx::MbarArrive(&empty_bar[slot]);
+        MNB_MARK(17 + tile);
       }
     }
     // blocks of one supergroup sit in neighbouring lanes of the quad: add them up
@@ -588,11 +650,27 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
     return nullptr;
   }
   p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
-  p.slot_bytes = (16 * p.slice_b_bytes + 2 * p.rec_bytes + 127) & ~127;
+  // Whole-row tasks when a row is exactly one or two slices long (K = 2048 or 4096): 16 rows are
+  // then one contiguous copy of 16 or 32 KB. MNB_GEMV_FULL_ROWS=0 keeps the sliced TMA boxes.
+  static const bool allow_full_rows = [] {
+    const char *value = std::getenv("MNB_GEMV_FULL_ROWS");
+    return value == nullptr || value[0] != '0';
+  }();
+  p.full_rows = (allow_full_rows && w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
+                 w.row_bytes >= 1024) ? 1 : 0;
+  if (p.full_rows != 0) {
+    p.row_stride = w.row_bytes;
+    p.weight_bytes = 16 * w.row_bytes;
+    p.slot_bytes = (p.weight_bytes + p.slices * 2 * p.rec_bytes + 127) & ~127;
+  } else {
+    p.row_stride = p.slice_b_bytes;
+    p.weight_bytes = 16 * p.slice_b_bytes;
+    p.slot_bytes = (p.weight_bytes + 2 * p.rec_bytes + 127) & ~127;
+  }
   const size_t fixed = static_cast<size_t>(2 * tokens_per_pass) * p.act_row_bytes + kZeroBytes +
                        (kMaxTokens + 2 * kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
                        2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
-  const size_t limit = 225 * 1024;
+  const size_t limit = 227 * 1024 - 256; // the most a CTA can ask for, less the alignment slack
   if (fixed + 2 * static_cast<size_t>(p.slot_bytes) > limit) {
     return nullptr;
   }
