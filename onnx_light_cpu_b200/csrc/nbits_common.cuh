@@ -145,10 +145,12 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                               cudaStream_t stream);
 // Prepared side array used by the MMA decode kernel: per (8-row half tile, task slice) one
-// record {float scale[8][bpt]; uint8 zp[8][bpt] (only with zero points)}. bytes == 0 means
+// record {float scale[8][scale_row_floats]; uint8 zp[8][bpt] (only with zero points)}. bytes == 0 means
 // the geometry is outside what that kernel takes.
 struct MetaGeometry {
   int bpt;             // quantization blocks per task
+  int scale_row_floats; // floats per row of a record's scale part: bpt, plus 4 of padding when bpt * 4
+                        // bytes is a multiple of 128 (rows would otherwise all start on the same bank)
   int slices;          // tasks per row tile
   int rec_bytes;
   int rec_scale_bytes;

@@ -65,7 +65,7 @@ constexpr int kConsumerThreads = kWarps * 32;
 // streams, four 6.7 TB/s); at decode sizes a single paced issuer is faster, see WantedProducers().
 constexpr int kProducers = 4;
 constexpr int kThreads = (kWarps + kProducers) * 32;
-constexpr int kMaxSlots = 32;
+constexpr int kMaxSlots = 16;
 constexpr int kMaxTokens = 4;             // most activation rows handled per CTA pass
 #ifndef MNB_MMA_UNROLL
 #define MNB_MMA_UNROLL 4
@@ -110,13 +110,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   // keep the pointer in the shared address space (no integer round trip) while aligning it
   unsigned char *smem_raw = smem_dyn + ((128u - (ptx::SmemAddr(smem_dyn) & 127u)) & 127u);
   // layout: [slots][activation piece rows: 2 per token][per-token 2^-e][amax scratch]
-  //         [pair exchange: 2 x kPairs x 32 lanes x 2][barriers]
+  //         [pair exchange: kPairs x 32 lanes x 2][barriers]
   unsigned char *slots = smem_raw;
   unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
   float *inv_scale = reinterpret_cast<float *>(act + 2 * p.tokens_per_pass * p.act_row_bytes + kZeroBytes);
   float *scratch = inv_scale + kMaxTokens;          // [2][kWarps], alternating with the token index
-  float2 *pair_buf = reinterpret_cast<float2 *>(scratch + 2 * kWarps); // [2][kPairs][32]
-  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + 2 * kPairs * 32);
+  float2 *pair_buf = reinterpret_cast<float2 *>(scratch + 2 * kWarps); // [kPairs][32]
+  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(pair_buf + kPairs * 32);
   std::uint64_t *empty_bar = full_bar + kMaxSlots;
   // task index currently assigned to each slot. A slot is consumed by different warps in
   // successive rounds, and an mbarrier phase parity only tells two neighbouring phases apart,
@@ -304,9 +304,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t sixteenth = 0x2c002c00u;  // fp16 1/16 twice
   const std::uint32_t plus960 = 0x63806380u;    // fp16 960 twice
   const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
-  // meta record: float scale[8 rows][bpt + 4] (padded rows keep lanes on different banks),
+  // meta record: float scale[8 rows][row floats] (rows padded where they would share a bank),
   // then uint8 zp[8 rows][bpt]
-  const int scale_row_bytes = (p.bpt + 4) * 4;
+  const int scale_row_bytes = p.rec_scale_bytes / 8;
   constexpr int kNb = kNbSg; // quantization blocks per supergroup (1 when a block spans several)
 
   int tile_count = 0;
@@ -461,14 +461,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       acc0 += __shfl_xor_sync(0xffffffffu, acc0, 2);
       acc1 += __shfl_xor_sync(0xffffffffu, acc1, 2);
     }
-    // the odd warp of the pair hands its half of K to the even warp
-    float2 *exchange = pair_buf + ((tile_count & 1) * kPairs + pair) * 32 + lane;
+    // the odd warp of the pair hands its half of K to the even warp (one buffer per pair: the
+    // second barrier keeps the next tile's value from overwriting one that is still being read)
+    float2 *exchange = pair_buf + pair * 32 + lane;
     if (parity == 1) {
       *exchange = make_float2(acc0, acc1);
     }
     asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    float2 other = make_float2(0.0f, 0.0f);
     if (parity == 0) {
-      const float2 other = *exchange;
+      other = *exchange;
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    if (parity == 0) {
       acc0 += other.x;
       acc1 += other.y;
       if (blk_d == 0 && m_d < tokens) {
@@ -513,10 +518,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---- prepared side array -----------------------------------------------------------------
-// meta[(slice * half_tiles + half_tile)] = { float scale[8 rows][bpt + 4] ; uint8 zp[8 rows][bpt] }
+// meta[(slice * half_tiles + half_tile)] = { float scale[8 rows][scale_row_floats] ; uint8 zp[8 rows][bpt] }
 // (the zero-point part only when the node has zero points). Rows beyond N and blocks beyond
 // n_blocks get scale 0.
-__global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightView w, int bpt, int half_tiles,
+__global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightView w, int bpt, int scale_row_floats,
+                                                                 int half_tiles,
                                                                  int rec_bytes, int rec_scale_bytes,
                                                                  unsigned char *meta, std::int64_t records) {
   const std::int64_t per_record = 8 * bpt;
@@ -538,7 +544,7 @@ __global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightVie
       zp = ZeroPointOf(w, row, block);
     }
     unsigned char *rec = meta + record * rec_bytes;
-    reinterpret_cast<float *>(rec)[r * (bpt + 4) + b] = scale;
+    reinterpret_cast<float *>(rec)[r * scale_row_floats + b] = scale;
     if (w.zp != nullptr) {
       rec[rec_scale_bytes + r * bpt + b] = static_cast<unsigned char>(zp);
     }
@@ -580,7 +586,8 @@ MetaGeometry MetaGeometryOf(const WeightView &w) {
   }
   geo.bpt = bpt;
   geo.slices = (w.n_blocks + bpt - 1) / bpt;
-  geo.rec_scale_bytes = 8 * (bpt + 4) * 4;
+  geo.scale_row_floats = bpt + (((bpt * 4) % 128) == 0 ? 4 : 0);
+  geo.rec_scale_bytes = 8 * geo.scale_row_floats * 4;
   geo.rec_bytes = geo.rec_scale_bytes + (w.zp != nullptr ? 8 * bpt : 0);
   geo.half_tiles = static_cast<int>((w.n + 7) / 8);
   geo.bytes = static_cast<std::size_t>(geo.half_tiles) * geo.slices * geo.rec_bytes;
@@ -598,7 +605,7 @@ bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t st
     blocks = 148 * 8;
   }
   nbits_prepare_meta_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-      w, geo.bpt, geo.half_tiles, geo.rec_bytes, geo.rec_scale_bytes, meta, records);
+      w, geo.bpt, geo.scale_row_floats, geo.half_tiles, geo.rec_bytes, geo.rec_scale_bytes, meta, records);
   if (cudaGetLastError() != cudaSuccess) {
     return false;
   }
@@ -668,9 +675,9 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
     p.slot_bytes = (p.weight_bytes + 2 * p.rec_bytes + 127) & ~127;
   }
   const size_t fixed = static_cast<size_t>(2 * tokens_per_pass) * p.act_row_bytes + kZeroBytes +
-                       (kMaxTokens + 2 * kWarps) * sizeof(float) + 2 * kPairs * 32 * sizeof(float2) +
+                       (kMaxTokens + 2 * kWarps) * sizeof(float) + kPairs * 32 * sizeof(float2) +
                        2 * kMaxSlots * sizeof(std::uint64_t) + kMaxSlots * sizeof(int) + 128;
-  const size_t limit = 227 * 1024 - 256; // the most a CTA can ask for, less the alignment slack
+  const size_t limit = 227 * 1024 - 128; // the most a CTA can ask for, less the alignment slack
   if (fixed + 2 * static_cast<size_t>(p.slot_bytes) > limit) {
     return nullptr;
   }

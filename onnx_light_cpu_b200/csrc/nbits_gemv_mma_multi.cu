@@ -224,9 +224,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t plus960 = 0x63806380u;    // fp16 960 twice
   const std::uint32_t default_offs = 0x64086408u; // fp16 1024 + 8 twice
   const int box_bytes = 16 * p.slice_b_bytes;
-  // meta record: float scale[8 rows][bpt + 4] (padded rows keep lanes on different banks),
+  // meta record: float scale[8 rows][row floats] (rows padded where they would share a bank),
   // then uint8 zp[8 rows][bpt]
-  const int scale_row_bytes = (p.bpt + 4) * 4;
+  const int scale_row_bytes = p.rec_scale_bytes / 8;
   // this warp's supergroup of every task: block index (inside the task) of the lane's codes and
   // of the lane's accumulator columns
   const int blk_codes = NB_SG_LOG2 == 0 ? warp / p.sg_per_block : warp * kNbSg + tb;

@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     word_off[st] = (warp >> 1) * 2048 + g * 128 + ((c ^ g) << 4) + 4 * t;
   }
   constexpr int kEntriesPerGroup = 4 / SPB;
-  const int scale_row_bytes = (p.bpt + 4) * 4;
+  const int scale_row_bytes = p.rec_scale_bytes / 8;
   // scale / zero-point index of this warp's first block inside a task record row
   const int meta_index = p.groups_per_block > 1 ? warp / p.groups_per_block : warp * kEntriesPerGroup;
   const int entry_bytes = p.tp * 8;
