@@ -35,6 +35,8 @@ SHAPES = (
     ("cfg2_decode_m16_level4", 16, 4096, 14336, 4, 128, True, True, 4),
     ("cfg5_shard8_m1", 1, 4096, 16032, 4, 32, True, False, 0),
     ("cfg5_shard8_m1_8bit", 1, 4096, 16032, 8, 32, True, False, 0),
+    ("cfg5_shard8_m8", 8, 4096, 16032, 4, 32, True, False, 0),
+    ("cfg5_shard8_m256", 256, 4096, 16032, 4, 32, True, False, 0),
 )
 
 
