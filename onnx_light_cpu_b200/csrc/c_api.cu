@@ -227,7 +227,11 @@ __global__ void __launch_bounds__(256) nbits_fetch_kernel(const uint4 *src, uint
 
 // Stand-alone form of the flag exchange, launched behind kernels that do not run it themselves.
 // The stores of the kernels before it in the stream have completed when it starts.
+// When it is launched with programmatic stream serialization (the decode kernels trigger their
+// dependents as they start) its one warp is already resident and waits here for the decode grid
+// to complete and its stores to be visible, which saves the launch latency after that grid.
 __global__ void __launch_bounds__(32) nbits_publish_wait_kernel(mnb::GatherTail tail, int *status) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   mnb::PublishAndWait(tail, threadIdx.x, status);
 }
 
@@ -742,8 +746,24 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   }
   if (!fused) {
     cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
-    nbits_publish_wait_kernel<<<1, 32, 0, stream>>>(tail, h->status_dev);
-    const cudaError_t launch_err = cudaGetLastError();
+    static const bool early_launch = [] {
+      const char *value = std::getenv("MNB_GATHER_PDL");
+      return value == nullptr || value[0] != '0';
+    }();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1, 1, 1);
+    config.blockDim = dim3(32, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = early_launch ? 1 : 0;
+    cudaError_t launch_err = cudaLaunchKernelEx(&config, nbits_publish_wait_kernel, tail, h->status_dev);
+    if (launch_err == cudaSuccess) {
+      launch_err = cudaGetLastError();
+    }
     if (launch_err != cudaSuccess) {
       return FailCuda("launch of the publish kernel", launch_err);
     }
