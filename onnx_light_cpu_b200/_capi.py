@@ -29,6 +29,7 @@ PATH_GEMV_MMA = 4
 PATH_TCGEN05_WIDE = 5
 PATH_INT8_MMA = 6
 PATH_GEMV_MMA_MULTI = 7
+PATH_GEMV_IMMA = 8
 IPC_HANDLE_BYTES = 64
 MAX_GATHER_RANKS = 8
 

@@ -235,6 +235,9 @@ __global__ void __launch_bounds__(32) nbits_publish_wait_kernel(mnb::GatherTail 
   mnb::PublishAndWait(tail, threadIdx.x, status);
 }
 
+// AUTO sends at most this many tokens to the integer-digit decode kernel (two tokens per pass).
+constexpr std::int64_t kImmaAutoTokens = 2;
+
 // Core dispatch. The caller holds h->mutex and has made h->device current.
 int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_level, int path,
              OutputView out, cudaStream_t stream) {
@@ -266,7 +269,11 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     // holds 4 / 2 / 1 tokens for block_size >= 128 / 64 / 32; more tokens go to the kernel that
     // shares a pass over the weights between several column tiles.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m <= 16 && path == MNB_PATH_AUTO) {
+    if (m <= kImmaAutoTokens && path == MNB_PATH_AUTO) {
+      // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
+      name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO) {
       if (m > per_pass) {
         name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
       }
@@ -291,6 +298,15 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     if (name == nullptr) {
       return Fail(MNB_ERR_UNSUPPORTED, "MatMulNBits: shape not supported by the MMA decode kernel.");
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_IMMA: {
+    name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the integer-digit decode kernel takes 4-bit weights with block_size 128 ... "
+                  "1024 and M <= 16.");
     }
     break;
   }

@@ -169,6 +169,12 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
 const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                                int *status_word, cudaStream_t stream, int sm_count);
 
+// Decode for one or two tokens per pass on integer MMA: the activations enter as three base-128
+// digits (22 bits of the row maximum), block dots are exact int32. block_size 128 ... 1024.
+bool GemvImmaSupports(const WeightView &w, std::int64_t m);
+const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                           int *status_word, cudaStream_t stream, int sm_count);
+
 // Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
                               std::uint16_t *a_bf16, OutputView out, int *status_word,

@@ -76,7 +76,8 @@ def test_config1_single_node(cuda_device):
 def test_config2_decode_sweep(cuda_device, m):
     case = syn.config2(m)
     y, kernel = run_device(case)
-    assert kernel == ("nbits_gemv_mma_kernel" if m <= 4 else "nbits_gemv_mma_multi_kernel"), kernel
+    expected = {1: "nbits_gemv_imma_kernel", 4: "nbits_gemv_mma_kernel", 16: "nbits_gemv_mma_multi_kernel"}[m]
+    assert kernel == expected, kernel
     ref = oracle_f64(case)
     assert rel_err(y, ref) <= TOL_FP32
     y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
@@ -189,6 +190,72 @@ def test_decode_mma_path_wide_dynamic_range(cuda_device):
     for row in range(3):
         assert rel_err(y[row], ref[row]) <= TOL_FP32, row
     assert np.array_equal(y[3], case.bias)
+
+
+# shapes for the integer-digit decode kernel: (m, k, n, block, zp, bias)
+IMMA_CASES = [
+    (1, 4096, 96, 128, True, True),        # whole-row tasks, two slices
+    (2, 4096, 200, 128, False, True),      # two tokens = six MMA columns; signed codes (no zero points)
+    (1, 2048, 77, 128, True, False),       # whole-row tasks, one slice: the odd warp of a pair idles
+    (3, 4096, 130, 256, True, True),       # two passes, block spans two supergroups
+    (1, 8192, 64, 1024, False, False),     # sliced tasks through the 2-D box, block spans eight supergroups
+    (2, 14336, 48, 128, True, True),       # wide K: seven slices
+    (1, 4096 + 64, 24, 128, True, False),  # partial last block, rows not whole tasks
+    (1, 4000, 50, 128, True, True),        # K not a multiple of 128
+    (1, 4096, 7, 128, True, True),         # fewer rows than one half tile
+    (5, 4096, 40, 512, True, False),       # three passes, last one with a single token
+    (1, 4096, 14336, 128, True, True),     # cfg2 at full size: seven tiles in six slots for some CTAs
+    (2, 4096, 14336, 128, False, True),
+]
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", IMMA_CASES)
+def test_decode_imma_path(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("imma", m, k, n, 4, bs, seed=m * 13 + k + n + bs, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_IMMA)
+    assert kernel == "nbits_gemv_imma_kernel"
+    ref = oracle_f64(case)
+    for row in range(m):   # every token against its own magnitude
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    y_mma, _ = run_device(case, path=_capi.PATH_GEMV_MMA)   # the fp16 two-piece kernel agrees
+    assert rel_err(y, y_mma) <= TOL_FP32
+    if m <= 2:
+        y_auto, kernel_auto = run_device(case)   # AUTO picks it for one or two tokens
+        assert kernel_auto == kernel and np.array_equal(y, y_auto)
+
+
+def test_decode_imma_path_wide_dynamic_range_and_special_rows(cuda_device):
+    """Rows of very different magnitude, a row whose entries span many orders of magnitude, an
+    all-zero row, a denormal-sized row and a row with a NaN: the 22-bit digits follow each row's own
+    maximum; a non-finite row gives NaN outputs and does not disturb the token next to it."""
+    case = syn.make_case("imma_range", 6, 4096, 256, 4, 128, seed=98, bias=False)
+    rng = np.random.default_rng(2)
+    case.a[0] *= 1e4
+    case.a[1] *= 1e-6
+    case.a[2] *= np.exp(rng.uniform(-8, 8, size=case.k)).astype(np.float32)
+    case.a[3] = 0.0
+    case.a[4] *= 1e-30
+    case.a[5, 17] = np.nan
+    y, _ = run_device(case, path=_capi.PATH_GEMV_IMMA)
+    finite = syn.make_case("imma_range", 6, 4096, 256, 4, 128, seed=98, bias=False)
+    finite.a[:5] = case.a[:5]
+    ref = oracle_f64(finite)
+    for row in (0, 1, 2, 4):   # no bias: tiny rows are judged on their own scale
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    assert not y[3].any()
+    assert np.isnan(y[5]).all()
+
+
+def test_decode_imma_path_rejects_small_blocks(cuda_device):
+    import torch
+
+    case = syn.make_case("imma_reject", 1, 4096, 64, 4, 32, seed=8)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=32)
+    with pytest.raises(_capi.MatMulNBitsError) as info:
+        weights.matmul_device(torch.from_numpy(case.a).cuda(), torch.zeros((1, 64), device="cuda"),
+                              path=_capi.PATH_GEMV_IMMA)
+    assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
+    weights.close()
 
 
 def test_generic_kernel_matches_stream_kernel(cuda_device):
