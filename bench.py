@@ -42,9 +42,12 @@ PREFILL = dict(m=2048, k=4096, n=4096, bits=4, block_size=64)
 LMHEAD = dict(k=4096, n=128256, bits=4, block_size=32)
 L2_BYTES = 126 * 1024 * 1024
 
-# DRAM bytes per launch of nbits_gemv_mma_kernel on the decode workload, from the ncu capture
+# DRAM bytes per launch of the decode kernels on the decode workload, from the ncu captures
 # summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-NCU_DECODE_TRAFFIC_BYTES = 32_258_304  # profiles/decode_mma_cfg2.md
+NCU_DECODE_TRAFFIC_BYTES = {
+    "nbits_gemv_imma_kernel": 31_796_480,  # profiles/decode_imma_cfg2.md
+    "nbits_gemv_mma_kernel": 32_258_304,   # profiles/decode_mma_cfg2.md
+}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -257,7 +260,7 @@ def main() -> None:
     parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                         help="multi-GPU: kernels store into every rank's result through peer-mapped memory "
                              "(default) or an NCCL all-gather follows each kernel")
-    parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma"],
+    parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma", "imma"],
                         help="kernel family for the decode workload (auto = library dispatch)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -304,7 +307,8 @@ def main() -> None:
         per_launch_bytes = weights[0].algorithmic_bytes(m)
         assert copies * per_launch_bytes > L2_BYTES
 
-        decode_path = {"auto": _capi.PATH_AUTO, "gemv": _capi.PATH_GEMV, "mma": _capi.PATH_GEMV_MMA}[args.decode_path]
+        decode_path = {"auto": _capi.PATH_AUTO, "gemv": _capi.PATH_GEMV, "mma": _capi.PATH_GEMV_MMA,
+                       "imma": _capi.PATH_GEMV_IMMA}[args.decode_path]
 
         def step():
             for w, y in zip(weights, ys):
@@ -329,7 +333,7 @@ def main() -> None:
                   "l2_defeat": f"{copies} weight copies = {copies * per_launch_bytes / 1e6:.0f} MB > 126 MB L2",
                   "cuda_graph": graphed, "kernel": kernel_name}
         roofline = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": value / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
+                    "frac": value / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES.get(kernel_name),
                     "peak_kind": f"of {peak_kind} (copy bandwidth)", "kernel": kernel_name,
                     "us_per_launch": launch_us, "algorithmic_bytes_per_launch": per_launch_bytes}
         scaling = "weak"
