@@ -45,7 +45,8 @@ typedef enum mnb_path {
   MNB_PATH_TCGEN05_WIDE = 5, /* prefill, 256 x 256 tiles for any M (AUTO picks them for large M) */
   MNB_PATH_INT8_MMA = 6, /* accuracy_level 4 on integer tensor-core MMA (AUTO picks it when the shape fits) */
   MNB_PATH_GEMV_MMA_MULTI = 7, /* decode on warp-level MMA, several column tiles of tokens per pass */
-  MNB_PATH_GEMV_IMMA = 8 /* decode on integer MMA, A as three base-128 digits (block_size >= 128; AUTO picks it for M <= 2) */
+  MNB_PATH_GEMV_IMMA = 8, /* decode on integer MMA, A as three base-128 digits (block_size >= 128; AUTO picks it for M <= 2) */
+  MNB_PATH_GEMV_DIGITS = 9 /* decode, accuracy_level 0: three digit rows per token through the sixteen-row integer-MMA kernel */
 } mnb_path;
 
 /* Device-resident, immutable weights of one MatMulNBits node. Plays the role the reference

@@ -30,6 +30,7 @@ PATH_TCGEN05_WIDE = 5
 PATH_INT8_MMA = 6
 PATH_GEMV_MMA_MULTI = 7
 PATH_GEMV_IMMA = 8
+PATH_GEMV_DIGITS = 9
 IPC_HANDLE_BYTES = 64
 MAX_GATHER_RANKS = 8
 

@@ -273,6 +273,22 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
       name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
+    // Small blocks with many tokens: the fp16 kernels hold one (block 32) or two (block 64) tokens per
+    // column tile, so 16 tokens are four / two passes over the weights; three digit rows per token
+    // through the sixteen-row integer kernel are fewer passes from M = 5 (block 32) / M = 9 (block 64)
+    // on (measured: block 32 M = 16 80.8 -> 49.4 us, M = 5 40.2 -> 22.2 us; block 64 M = 16 63.1 -> 50.7 us).
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && out.n_peers == 0 &&
+        ((w.block_size == 32 && m >= 5) || (w.block_size == 64 && m >= 9))) {
+      const std::size_t need = mnb::DigitsInt8MmaScratchBytes(w, m);
+      if (need != 0) {
+        const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+        if (rc != MNB_OK) {
+          return rc;
+        }
+        name = mnb::LaunchDigitsInt8Mma(w, a_dev, m, static_cast<unsigned char *>(h->scratch_a), out,
+                                        h->status_dev, stream, h->sm_count);
+      }
+    }
     if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO) {
       if (m > per_pass) {
         name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
@@ -307,6 +323,23 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       return Fail(MNB_ERR_UNSUPPORTED,
                   "MatMulNBits: the integer-digit decode kernel takes 4-bit weights with block_size 128 ... "
                   "1024 and M <= 16.");
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_DIGITS: {
+    const std::size_t need = m <= 16 && out.n_peers == 0 ? mnb::DigitsInt8MmaScratchBytes(w, m) : 0;
+    if (need != 0) {
+      const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchDigitsInt8Mma(w, a_dev, m, static_cast<unsigned char *>(h->scratch_a), out, h->status_dev,
+                                      stream, h->sm_count);
+    }
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the digit-row decode path needs bits=4, 32 <= block_size <= 1024, packed rows "
+                  "that are a multiple of 128 bytes and M <= 16.");
     }
     break;
   }

@@ -198,6 +198,13 @@ std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m);
 const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
                           OutputView out, int *status_word, cudaStream_t stream, int sm_count);
 
+// accuracy_level 0 through the sixteen-row integer-MMA kernel: every token enters as three rows of
+// base-128 digits (22 bits of its row maximum), the three partial results are added behind it.
+// `scratch`: DigitsInt8MmaScratchBytes (0 when the shape is outside what the kernel takes).
+std::size_t DigitsInt8MmaScratchBytes(const WeightView &w, std::int64_t m);
+const char *LaunchDigitsInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                                OutputView out, int *status_word, cudaStream_t stream, int sm_count);
+
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 
 // Producer lanes per CTA that issue the tile loads of the ring-fed kernels: env

@@ -598,6 +598,11 @@ std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m) {
   return geo.ok ? static_cast<std::size_t>(geo.passes) * geo.pass_bytes : 0;
 }
 
+namespace {
+const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
+                           OutputView out, int *status_word, cudaStream_t stream, int sm_count);
+} // namespace
+
 // Quantizes `a` into `scratch` (Int8MmaScratchBytes) and runs the integer-MMA kernel.
 const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
                           OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
@@ -605,7 +610,6 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   if (!geo.ok || w.meta == nullptr || scratch == nullptr) {
     return nullptr;
   }
-  const MetaGeometry meta = MetaGeometryOf(w);
   const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
   nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
       a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
@@ -614,7 +618,15 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
     return nullptr;
   }
   CountLaunch();
+  return LaunchMultiply(w, geo, m, scratch, out, status_word, stream, sm_count);
+}
 
+namespace {
+// The integer-MMA kernel over activations that the kernel launched just before has laid out in
+// `scratch` (it is launched with programmatic stream serialization behind that kernel).
+const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
+                           OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+  const MetaGeometry meta = MetaGeometryOf(w);
   ImmaParams p{};
   p.w = w;
   p.act = scratch;
@@ -681,6 +693,182 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   }
   CountLaunch();
   return "nbits_int8_mma_kernel";
+}
+} // namespace
+
+
+// ---- accuracy_level 0 through the same kernel: activations as three base-128 digits ----------
+//
+// A float row enters the integer MMA exactly enough for the 1e-5 bar of the fp32 decode paths when
+// it is scaled so that its largest magnitude becomes kDigitRange, rounded to a 22-bit integer
+// n = 16384 d0 + 128 d1 + d2 (d1, d2 in [-64, 63], |d0| <= 123) and handed to the kernel as THREE
+// rows of signed bytes with the "activation scales" undo * {16384, 128, 1}: the kernel's per-block
+// int32 dots are exact, its fp32 combination is the usual one, and the three partial rows are added
+// (plus the bias) by a small kernel behind it. M tokens cost 3 M rows: 16 tokens take three passes
+// of sixteen rows. Worth it where the fp16 kernels need one pass per token (block_size 32) or two.
+namespace {
+
+constexpr float kDigitRange = 2.0e6f;
+
+// up[row] = factor applied to A (after `lift`, an exact power of two for rows of tiny magnitude),
+// undo[row] = factor that takes the integer result back (NaN for a row with a non-finite entry).
+// One CTA per row. factors = {up[m], lift[m], undo[m]} as three arrays of m_total floats.
+__global__ void __launch_bounds__(256)
+    nbits_digit_row_factors_kernel(const float *a, int m_total, std::int64_t k, float *factors) {
+  __shared__ float warp_max[8];
+  const int row = blockIdx.x;
+  const float *src = a + static_cast<std::int64_t>(row) * k;
+  float amax = 0.0f;
+  bool bad = false;
+  for (std::int64_t i = threadIdx.x; i < k; i += 256) {
+    const float v = src[i];
+    amax = fmaxf(amax, fabsf(v));
+    bad = bad || (v != v);
+  }
+  if (bad) {
+    amax = __int_as_float(0x7f800000);
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    warp_max[threadIdx.x >> 5] = amax;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) {
+      amax = fmaxf(amax, warp_max[i]);
+    }
+    const bool finite = amax < 3.0e38f;
+    const float lift = amax < 1.0e-18f ? 1.8446744e19f /* 2^64 */ : 1.0f;
+    const float lifted = amax * lift;
+    factors[row] = (finite && lifted > 0.0f) ? kDigitRange / lifted : 0.0f;
+    factors[m_total + row] = lift;
+    factors[2 * m_total + row] = finite ? (lifted / kDigitRange) / lift : __int_as_float(0x7fc00000);
+  }
+}
+
+// Same work split and output layout as nbits_quantize_a_imma_kernel, for the digit rows: row
+// 3 * token + digit of the pass layout holds digit `digit` of token `token`; its table entries carry
+// undo * {16384, 128, 1} * table_scale and the digit sums.
+__global__ void __launch_bounds__(256)
+    nbits_digits_imma_kernel(const float *a, const float *factors, int m_total, std::int64_t k, int entry_k,
+                             int entries_pad, int tp, int act_row_bytes, int table_offset, int pass_bytes,
+                             int passes, float table_scale, unsigned char *act) {
+  ptx::GridDependencyLaunch();
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::int64_t item = static_cast<std::int64_t>(blockIdx.x) * 8 + warp;
+  if (item >= static_cast<std::int64_t>(passes) * tp * entries_pad) {
+    return;
+  }
+  const int slot = static_cast<int>(item / entries_pad);
+  const int entry = static_cast<int>(item - static_cast<std::int64_t>(slot) * entries_pad);
+  const int pass = slot / tp;
+  const int row_in_pass = slot - pass * tp;
+  const int token = slot / 3;
+  const int digit = slot - 3 * token;
+  const bool live = token < m_total;
+  const float *src = a + static_cast<std::int64_t>(token) * k;
+  const float up = live ? factors[token] : 0.0f;
+  const float lift = live ? factors[m_total + token] : 1.0f;
+  const float undo = live ? factors[2 * m_total + token] : 0.0f;
+  unsigned char *base = act + static_cast<std::int64_t>(pass) * pass_bytes;
+  std::int8_t *dst = reinterpret_cast<std::int8_t *>(base) + static_cast<std::int64_t>(row_in_pass) * act_row_bytes;
+  const std::int64_t e0 = static_cast<std::int64_t>(entry) * entry_k;
+  int sum = 0;
+  for (int e = lane; e < entry_k; e += 32) {
+    const std::int64_t kk = e0 + e;
+    int q = 0;
+    if (live && kk < k) {
+      int n = __float2int_rn((src[kk] * lift) * up);
+      const int range = static_cast<int>(kDigitRange);
+      n = n > range ? range : (n < -range ? -range : n);
+      const int low = ((n + 64) & 127) - 64;
+      const int n1 = (n - low) >> 7;
+      const int mid = ((n1 + 64) & 127) - 64;
+      q = digit == 2 ? low : (digit == 1 ? mid : (n1 - mid) >> 7);
+    }
+    sum += q;
+    dst[ActBytePosition(static_cast<int>(kk))] = static_cast<std::int8_t>(q);
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+  }
+  if (lane == 0) {
+    unsigned char *cell = base + table_offset + static_cast<std::int64_t>(entry) * tp * 8;
+    const float weight = digit == 0 ? 16384.0f : (digit == 1 ? 128.0f : 1.0f);
+    reinterpret_cast<float *>(cell)[row_in_pass] = undo * weight * table_scale;
+    reinterpret_cast<int *>(cell + tp * 4)[row_in_pass] = sum;
+  }
+}
+
+// Y[token][n] = P[3 token][n] + P[3 token + 1][n] + P[3 token + 2][n] + bias[n].
+__global__ void __launch_bounds__(256)
+    nbits_digits_combine_kernel(const float *partial, const float *bias, int m_total, std::int64_t n, OutputView out) {
+  const std::int64_t total = static_cast<std::int64_t>(m_total) * n;
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * 256) {
+    const std::int64_t token = i / n;
+    const std::int64_t col = i - token * n;
+    const float *p0 = partial + (3 * token) * n + col;
+    const float sum = (p0[0] + p0[n]) + p0[2 * n];
+    StoreOutput(out, token * out.ld + out.col_offset + col, sum + (bias != nullptr ? bias[col] : 0.0f));
+  }
+}
+
+std::size_t AlignUp(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
+
+} // namespace
+
+std::size_t DigitsInt8MmaScratchBytes(const WeightView &w, std::int64_t m) {
+  const ImmaGeometry geo = ImmaGeometryOf(w, 3 * m);
+  if (!geo.ok) {
+    return 0;
+  }
+  return AlignUp(static_cast<std::size_t>(geo.passes) * geo.pass_bytes) + AlignUp(3 * m * sizeof(float)) +
+         static_cast<std::size_t>(3 * m) * w.n * sizeof(float);
+}
+
+const char *LaunchDigitsInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                                OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+  const ImmaGeometry geo = ImmaGeometryOf(w, 3 * m);
+  if (!geo.ok || w.meta == nullptr || scratch == nullptr || m < 1 || m > 16) {
+    return nullptr;
+  }
+  unsigned char *act = scratch;
+  float *factors = reinterpret_cast<float *>(scratch + AlignUp(static_cast<std::size_t>(geo.passes) * geo.pass_bytes));
+  float *partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(factors) + AlignUp(3 * m * sizeof(float)));
+  nbits_digit_row_factors_kernel<<<static_cast<unsigned>(m), 256, 0, stream>>>(a, static_cast<int>(m), w.k, factors);
+  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
+  nbits_digits_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      a, factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, act);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch(2);
+  WeightView no_bias = w;
+  no_bias.bias = nullptr;
+  OutputView to_partial{};
+  to_partial.y = partial;
+  to_partial.ld = w.n;
+  to_partial.col_offset = 0;
+  if (LaunchMultiply(no_bias, geo, 3 * m, act, to_partial, status_word, stream, sm_count) == nullptr) {
+    return nullptr;
+  }
+  const std::int64_t total = m * w.n;
+  std::int64_t blocks = (total + 255) / 256;
+  blocks = blocks > 148 * 8 ? 148 * 8 : blocks;
+  nbits_digits_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, w.bias, static_cast<int>(m),
+                                                                              w.n, out);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_int8_mma_kernel(digits)";
 }
 
 } // namespace mnb

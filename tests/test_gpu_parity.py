@@ -158,8 +158,12 @@ def test_decode_mma_multi_tile_path(cuda_device, m, k, n, bs, zp, bias):
     y, kernel = run_device(case, path=_capi.PATH_GEMV_MMA_MULTI)
     assert kernel == "nbits_gemv_mma_multi_kernel"
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
-    y_auto, kernel_auto = run_device(case)   # AUTO picks the same kernel for these shapes
-    assert kernel_auto == kernel and np.array_equal(y, y_auto)
+    y_auto, kernel_auto = run_device(case)
+    if (bs == 32 and m >= 5) or (bs == 64 and m >= 9):
+        # AUTO sends many tokens over small blocks through the digit rows of the integer kernel
+        assert kernel_auto == "nbits_int8_mma_kernel(digits)" and rel_err(y, y_auto) <= TOL_FP32
+    else:   # AUTO picks the same kernel for these shapes
+        assert kernel_auto == kernel and np.array_equal(y, y_auto)
     y_single, _ = run_device(case, path=_capi.PATH_GEMV_MMA)   # one column tile per pass
     assert rel_err(y, y_single) <= TOL_FP32
 
@@ -256,6 +260,52 @@ def test_decode_imma_path_rejects_small_blocks(cuda_device):
                               path=_capi.PATH_GEMV_IMMA)
     assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
     weights.close()
+
+
+# shapes for the digit rows through the sixteen-row integer kernel: (m, k, n, block, zp, bias)
+DIGIT_ROW_CASES = [
+    (16, 4096, 128, 32, False, True),      # three passes of sixteen rows, signed codes
+    (5, 4096, 77, 64, True, True),         # fifteen rows: one pass
+    (3, 2048, 200, 128, True, False),      # nine rows: one pass of sixteen, seven of them empty
+    (16, 4096, 300, 128, True, True),
+    (1, 4096, 64, 32, True, False),        # three rows: one pass of eight
+    (7, 8192, 40, 256, False, False),      # block spans two 128-k table entries
+    (11, 14336, 96, 32, True, True),       # wide K: seven slices; 33 rows = three passes, last one ragged
+    (16, 4096, 14336, 32, False, False),   # cfg4 gate / up projection at full size
+]
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", DIGIT_ROW_CASES)
+def test_decode_digit_rows_path(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("digit_rows", m, k, n, 4, bs, seed=m * 17 + k + n + bs, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_DIGITS)
+    assert kernel == "nbits_int8_mma_kernel(digits)"
+    ref = oracle_f64(case)
+    for row in range(m):
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    y_auto, kernel_auto = run_device(case)
+    picked = (bs == 32 and m >= 5) or (bs == 64 and m >= 9)
+    assert (kernel_auto == kernel) == picked
+    assert rel_err(y, y_auto) <= TOL_FP32
+
+
+def test_decode_digit_rows_special_rows(cuda_device):
+    """An all-zero row gives the bias, a row with a NaN gives NaN and leaves its neighbours alone,
+    rows of very different magnitude keep their own relative accuracy."""
+    case = syn.make_case("digit_rows_special", 6, 4096, 128, 4, 32, seed=97, bias=False)
+    case.a[0] *= 1e4
+    case.a[1] *= 1e-6
+    case.a[2] = 0.0
+    case.a[3] *= 1e-30
+    case.a[4, 100] = np.nan
+    y, _ = run_device(case, path=_capi.PATH_GEMV_DIGITS)
+    finite = syn.make_case("digit_rows_special", 6, 4096, 128, 4, 32, seed=97, bias=False)
+    finite.a[:4] = case.a[:4]
+    ref = oracle_f64(finite)
+    for row in (0, 1, 3, 5):
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    assert not y[2].any()
+    assert np.isnan(y[4]).all()
 
 
 def test_generic_kernel_matches_stream_kernel(cuda_device):
