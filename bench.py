@@ -407,6 +407,23 @@ def main() -> None:
                 "gbs": igbs, "frac_of_hbm_peak": igbs / peaks["hbm_gbs"], "us_per_call": sec / (icopies * isteps) * 1e6,
                 "kernel": iname, "device_status": istatus,
                 "includes": "activation quantization kernel + integer-MMA kernel (dependent launch)"}
+            # ---- same projection at accuracy_level 0: digit rows through the integer-MMA kernel ----
+            def level0_step():
+                for w, y in zip(iw, ys_i8):
+                    w.matmul_device(a_i8, y)
+
+            level0_step()
+            torch.cuda.synchronize()
+            lname = _capi.last_kernel()
+            lstatus = max(w.poll_status() for w in iw)
+            rep, _ = capture_graph(torch, level0_step)
+            sec = time_steps(torch, dist, rep, isteps, 3, 1)
+            lgbs = ibytes * icopies * isteps / sec / 1e9
+            extras["level0_m16_block32"] = {
+                "workload": "cfg4 gate/up projection M=16 K=4096 N=14336 bits=4 block=32, accuracy_level=0",
+                "gbs": lgbs, "frac_of_hbm_peak": lgbs / peaks["hbm_gbs"], "us_per_call": sec / (icopies * isteps) * 1e6,
+                "kernel": lname, "device_status": lstatus,
+                "includes": "row factors + digit rows + integer-MMA kernel (three passes of sixteen rows) + combine"}
             del iw, ys_i8
             torch.cuda.empty_cache()
 
