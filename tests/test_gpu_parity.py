@@ -244,7 +244,7 @@ def test_decode_imma_path_wide_dynamic_range_and_special_rows(cuda_device):
     finite = syn.make_case("imma_range", 6, 4096, 256, 4, 128, seed=98, bias=False)
     finite.a[:5] = case.a[:5]
     ref = oracle_f64(finite)
-    for row in (0, 1, 2, 4):   # no bias: tiny rows are judged on their own scale
+    for row in (0, 1, 2, 4):   # no bias: tiny rows are compared on their own scale
         assert rel_err(y[row], ref[row]) <= TOL_FP32, row
     assert not y[3].any()
     assert np.isnan(y[5]).all()
