@@ -41,27 +41,12 @@
 namespace mnb {
 namespace {
 
-#ifdef MNB_TIMELINE
-// Debug builds only: per-CTA event times (globaltimer ns) for offline inspection.
-__device__ unsigned long long g_timeline_imma[148 * 64];
-__device__ __forceinline__ unsigned long long NowNs() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define MNB_MARK(slot_) \
-  do { if (blockIdx.y == 0 && (slot_) < 64) g_timeline_imma[blockIdx.x * 64 + (slot_)] = NowNs(); } while (0)
-#else
-#define MNB_MARK(slot_) do { } while (0)
-#endif
-
 constexpr int kPairs = 8;                 // 16-row tiles in flight per CTA
 constexpr int kWarps = 2 * kPairs;        // consumer warps: two per tile, alternating halves of K
 constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kProducers = 4;             // producer warps present (one issuing lane each; one used by default)
 constexpr int kThreads = (kWarps + kProducers) * 32;
 constexpr int kMaxSlots = 16;
-constexpr int kDefaultWarpsPerTile = 2;   // whole-row tasks; see LaunchGemvImma
 constexpr int kMaxTokens = 2;             // activation rows per CTA pass: 3 digit columns each
 constexpr int kDigits = 3;
 constexpr int kUnroll = 4;                // supergroups per loop round
@@ -88,8 +73,6 @@ struct ImmaParams {
   int row_stride;       // bytes between weight rows inside a slot
   int weight_bytes;     // bytes of the weight part of a slot
   int producers;        // producer warps in use (num_slots is a multiple of it)
-  int warps_per_tile;   // consumer warps that share one row tile, each taking an equal run of
-                        // supergroups: 2, or with whole-row tasks 4 or 8
   int act_row_bytes;    // bytes between digit rows in shared memory (k_pad + 16: bank spread)
   int k_pad;            // activation positions per digit row (all tasks, zero beyond K)
   int tokens_per_pass;  // activation rows per grid.y pass (1 or 2)
@@ -128,31 +111,6 @@ __device__ __forceinline__ void ImmaZero(int (&d)[4], std::uint32_t a0, std::uin
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
   }
-}
-
-// Shared-memory loads by 32-bit shared-space address; OFFSET is an immediate of the instruction.
-template <int OFFSET>
-__device__ __forceinline__ uint4 LdsV4(std::uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr), "n"(OFFSET));
-  return v;
-}
-__device__ __forceinline__ uint2 LdsV2(std::uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ std::uint32_t LdsU32(std::uint32_t addr) {
-  std::uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ std::uint32_t LdsU8(std::uint32_t addr) {
-  std::uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
 }
 
 // The two MMA operands made of one word of eight codes: even codes (low nibbles) and odd codes
@@ -368,9 +326,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::int64_t row_limit =
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
-  if (tid == 0) {
-    MNB_MARK(0);
-  }
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
 
@@ -383,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (producer == 0 && lane == 0) {
       for (int s = 0; s < p.num_slots; ++s) {
         ptx::MbarInit(&full_bar[s], 1);
-        ptx::MbarInit(&empty_bar[s], p.full_rows != 0 ? p.warps_per_tile : 1); // released by every warp of the group
+        ptx::MbarInit(&empty_bar[s], p.full_rows != 0 ? 2 : 1); // released by both warps of the pair
         slot_task[s] = -1;
       }
       ptx::FenceMbarInit();
@@ -419,7 +374,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
             unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
             slot_task[slot] = task;
-            MNB_MARK(32 + task);
             ptx::MbarArriveExpectTx(&full_bar[slot], row_bytes_total + static_cast<std::uint32_t>(p.slices) * meta_bytes);
             ptx::BulkLoad(dst, p.w.b + first_row * p.row_stride, row_bytes_total, &full_bar[slot]);
             const unsigned char *meta_src = p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes;
@@ -489,32 +443,15 @@ __global__ void __launch_bounds__(kThreads, 1)
               p.w.block_size, p.blocks_pad, act, p.act_row_bytes, undo, scratch, sums, HAS_ZP, tid);
   // digits staged and (through the producers' arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
-  if (tid == 0) {
-    MNB_MARK(1);
-  }
 
   const int g = lane >> 2;
   const int t = lane & 3;
-  // A group of `wpt` warps shares a row tile: a pair, or with whole-row tasks four or eight warps
-  // (the sooner a tile is done after its arrival, the sooner its slot is free again and the
-  // shorter the tail behind the last tile).
-  const int wpt = p.warps_per_tile;
-  const int groups = kWarps / wpt;
-  const int pair = warp / wpt;            // which tile of a wave this warp works on
-  const int parity = warp - pair * wpt;   // which part of K of that tile
-  // whole-row tasks: warp `parity` of the group takes `sg_share` consecutive supergroups of the row
-  // (inside one slice: sg_share divides sg_per_task); sliced tasks: the two warps of a pair
-  // alternate whole slices
-  const int sg_share = p.full_rows != 0 ? p.slices * p.sg_per_task / wpt : p.sg_per_task;
-  const int s_first = p.full_rows != 0 ? (parity * sg_share) / p.sg_per_task : parity;
-  const int s_step = p.full_rows != 0 ? p.slices : 2;
-  const int sg_first = p.full_rows != 0 ? (parity * sg_share) % p.sg_per_task : 0;
+  const int pair = warp >> 1;   // which tile of a wave this warp works on
+  const int parity = warp & 1;  // which half of K of that tile
   // this lane's MMA column g as activation operand: digit g % 3 of token g / 3
   const bool b_active = g < kDigits * tokens;
-  const std::uint32_t act_lane_addr = ptx::SmemAddr(b_active ? act + g * p.act_row_bytes + t * 32 : zero_row);
+  const unsigned char *act_lane = b_active ? act + g * p.act_row_bytes + t * 32 : zero_row;
   const int lane_step = b_active ? 128 : 0; // bytes per supergroup in this lane's digit row
-  const std::uint32_t slots_addr = ptx::SmemAddr(slots);
-  const std::uint32_t sums_addr = ptx::SmemAddr(sums);
   // this lane's accumulator columns 2t and 2t + 1: what they add to token 0 and to token 1
   // (digit weights 16384, 128, 1; columns 6 and 7 are unused)
   float to_token0[2], to_token1[2];
@@ -529,24 +466,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int scale_row_bytes = p.rec_scale_bytes / 8;
 
   bool dead = false; // a bounded wait gave up: skip the math but keep the pair barrier protocol
-  for (int tile = pair; tile < n_tiles; tile += groups) {
+  for (int tile = pair; tile < n_tiles; tile += kPairs) {
     const int wave0 = tile - pair;
     const int wave_tiles = n_tiles - wave0 < kPairs ? n_tiles - wave0 : kPairs;
     const int h0 = h_begin + 2 * tile;
     const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
-    // the bias of this lane's two rows is asked for now, so that the latency of the global load
-    // (behind the weight stream in a busy HBM) is not paid after the arithmetic
-    const std::int64_t r_lo = row0 + g;
-    const std::int64_t r_hi = row0 + g + 8;
-    float bias_lo = 0.0f, bias_hi = 0.0f;
-    if (parity == 0 && t < tokens && p.w.bias != nullptr) {
-      if (r_lo < row_limit) {
-        bias_lo = __ldg(p.w.bias + r_lo);
-      }
-      if (r_hi < row_limit) {
-        bias_hi = __ldg(p.w.bias + r_hi);
-      }
-    }
     // per-digit sums of rows g and g + 8, accumulator columns 2t and 2t + 1
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     int d[4] = {0, 0, 0, 0};
@@ -565,9 +489,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         return false;
       }
-      if (lane == 0) {
-        MNB_MARK(2 + task);
-      }
       return true;
     };
     // whole-row tasks: the tile is one task, which both warps of the pair wait for and release
@@ -576,7 +497,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       dead = true;
     }
 
-    for (int s = s_first; s < p.slices && !dead; s += s_step) {
+    for (int s = parity; s < p.slices && !dead; s += 2) {
       const int task = p.full_rows != 0 ? tile : wave0 * p.slices + s * wave_tiles + pair;
       if (p.full_rows == 0) {
         slot = task % p.num_slots;
@@ -585,78 +506,56 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
       }
-      // 32-bit shared-space addresses and loads with immediate offsets: the address arithmetic of
-      // the inner loop is a handful of adds per round
-      const std::uint32_t sb = slots_addr + static_cast<std::uint32_t>(slot) * static_cast<std::uint32_t>(p.slot_bytes);
-      std::uint32_t row_lo =
-          sb + g * p.row_stride + (p.full_rows != 0 ? s * p.slice_b_bytes : 0) + sg_first * 64 + t * 16;
-      std::uint32_t row_hi = row_lo + 8 * p.row_stride;
-      const std::uint32_t meta0 = sb + p.weight_bytes + (p.full_rows != 0 ? s * 2 * p.rec_bytes : 0); // rows 0..7
-      const std::uint32_t meta1 = meta0 + p.rec_bytes;  // rows 8..15
-      // one block per supergroup: the scale / zero-point / digit-sum pointers walk with the
-      // supergroups; larger blocks index them by block number
-      const int walk = BIG_BLOCK ? 0 : sg_first;
-      std::uint32_t sc0 = meta0 + g * scale_row_bytes + 4 * walk;
-      std::uint32_t sc1 = meta1 + g * scale_row_bytes + 4 * walk;
-      std::uint32_t zr0 = meta0 + p.rec_scale_bytes + g * p.bpt + walk;
-      std::uint32_t zr1 = meta1 + p.rec_scale_bytes + g * p.bpt + walk;
-      std::uint32_t act_task =
-          act_lane_addr + static_cast<std::uint32_t>((s * p.sg_per_task + sg_first) * lane_step);
-      std::uint32_t sums_task = sums_addr + static_cast<std::uint32_t>((s * p.bpt * 8 + 2 * t) * 4 + 32 * walk);
+      const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
+      const unsigned char *row_lo =
+          sb + g * p.row_stride + (p.full_rows != 0 ? s * p.slice_b_bytes : 0) + t * 16;
+      const unsigned char *row_hi = row_lo + 8 * p.row_stride;
+      const unsigned char *meta0 = sb + p.weight_bytes + (p.full_rows != 0 ? s * 2 * p.rec_bytes : 0); // rows 0..7
+      const unsigned char *meta1 = meta0 + p.rec_bytes;  // rows 8..15
+      const float *sc0 = reinterpret_cast<const float *>(meta0 + g * scale_row_bytes);
+      const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes);
+      const unsigned char *zr0 = meta0 + p.rec_scale_bytes + g * p.bpt;
+      const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt;
+      const unsigned char *act_task = act_lane + static_cast<size_t>(s) * p.sg_per_task * lane_step;
+      const int *sums_task = sums + s * p.bpt * 8 + 2 * t;
 
-      for (int sg0 = sg_first; sg0 < sg_first + sg_share; sg0 += kUnroll) {
+      for (int sg0 = 0; sg0 < p.sg_per_task; sg0 += kUnroll) {
         // scales / zero points of the blocks this round touches
         float s0v[kUnroll], s1v[kUnroll];
-        std::uint32_t z0v[kUnroll], z1v[kUnroll];
+        int z0v[kUnroll], z1v[kUnroll];
         if constexpr (!BIG_BLOCK) {
           // one block per supergroup: four consecutive blocks, one vector load each
-          const uint4 a4 = LdsV4<0>(sc0);
-          const uint4 b4 = LdsV4<0>(sc1);
-          s0v[0] = __uint_as_float(a4.x), s0v[1] = __uint_as_float(a4.y);
-          s0v[2] = __uint_as_float(a4.z), s0v[3] = __uint_as_float(a4.w);
-          s1v[0] = __uint_as_float(b4.x), s1v[1] = __uint_as_float(b4.y);
-          s1v[2] = __uint_as_float(b4.z), s1v[3] = __uint_as_float(b4.w);
-          sc0 += 16;
-          sc1 += 16;
+          const float4 a4 = *reinterpret_cast<const float4 *>(sc0 + sg0);
+          const float4 b4 = *reinterpret_cast<const float4 *>(sc1 + sg0);
+          s0v[0] = a4.x, s0v[1] = a4.y, s0v[2] = a4.z, s0v[3] = a4.w;
+          s1v[0] = b4.x, s1v[1] = b4.y, s1v[2] = b4.z, s1v[3] = b4.w;
           if constexpr (HAS_ZP) {
-            const std::uint32_t za = LdsU32(zr0);
-            const std::uint32_t zb = LdsU32(zr1);
-            zr0 += 4;
-            zr1 += 4;
+            const std::uint32_t za = *reinterpret_cast<const std::uint32_t *>(zr0 + sg0);
+            const std::uint32_t zb = *reinterpret_cast<const std::uint32_t *>(zr1 + sg0);
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
-              z0v[u] = __byte_perm(za, 0u, 0x4440 + u);
-              z1v[u] = __byte_perm(zb, 0u, 0x4440 + u);
+              z0v[u] = static_cast<int>((za >> (8 * u)) & 0xffu);
+              z1v[u] = static_cast<int>((zb >> (8 * u)) & 0xffu);
             }
           }
         } else {
 #pragma unroll
           for (int u = 0; u < kUnroll; ++u) {
             const int blk = (sg0 + u) / p.sg_per_block;
-            s0v[u] = __uint_as_float(LdsU32(sc0 + 4 * blk));
-            s1v[u] = __uint_as_float(LdsU32(sc1 + 4 * blk));
+            s0v[u] = sc0[blk];
+            s1v[u] = sc1[blk];
             if constexpr (HAS_ZP) {
-              z0v[u] = LdsU8(zr0 + blk);
-              z1v[u] = LdsU8(zr1 + blk);
+              z0v[u] = zr0[blk];
+              z1v[u] = zr1[blk];
             }
           }
         }
-        std::uint32_t act_u = act_task;
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-          uint4 q0, q1;
-          if (u == 0) {
-            q0 = LdsV4<0>(row_lo), q1 = LdsV4<0>(row_hi);
-          } else if (u == 1) {
-            q0 = LdsV4<64>(row_lo), q1 = LdsV4<64>(row_hi);
-          } else if (u == 2) {
-            q0 = LdsV4<128>(row_lo), q1 = LdsV4<128>(row_hi);
-          } else {
-            q0 = LdsV4<192>(row_lo), q1 = LdsV4<192>(row_hi);
-          }
-          const uint4 ba = LdsV4<0>(act_u);
-          const uint4 bb = LdsV4<16>(act_u);
-          act_u += lane_step;
+          const uint4 q0 = *reinterpret_cast<const uint4 *>(row_lo + u * 64);
+          const uint4 q1 = *reinterpret_cast<const uint4 *>(row_hi + u * 64);
+          const uint4 ba = *reinterpret_cast<const uint4 *>(act_task + u * lane_step);
+          const uint4 bb = *reinterpret_cast<const uint4 *>(act_task + u * lane_step + 16);
           const std::uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w};
           const std::uint32_t w1[4] = {q1.x, q1.y, q1.z, q1.w};
           const std::uint32_t bv[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
@@ -677,12 +576,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (block_done) {
             int c0 = d[0], c1 = d[1], c2 = d[2], c3 = d[3];
             if constexpr (HAS_ZP) {
-              const int blk = BIG_BLOCK ? (sg0 + u) / p.sg_per_block : u;
-              const uint2 sum = LdsV2(sums_task + 32 * blk);
-              c0 -= static_cast<int>(z0v[u]) * static_cast<int>(sum.x);
-              c1 -= static_cast<int>(z0v[u]) * static_cast<int>(sum.y);
-              c2 -= static_cast<int>(z1v[u]) * static_cast<int>(sum.x);
-              c3 -= static_cast<int>(z1v[u]) * static_cast<int>(sum.y);
+              const int blk = BIG_BLOCK ? (sg0 + u) / p.sg_per_block : sg0 + u;
+              const int2 sum = *reinterpret_cast<const int2 *>(sums_task + blk * 8);
+              c0 -= z0v[u] * sum.x;
+              c1 -= z0v[u] * sum.y;
+              c2 -= z1v[u] * sum.x;
+              c3 -= z1v[u] * sum.y;
             }
             acc[0] = fmaf(s0v[u], static_cast<float>(c0), acc[0]);
             acc[1] = fmaf(s0v[u], static_cast<float>(c1), acc[1]);
@@ -693,20 +592,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         row_lo += 64 * kUnroll;
         row_hi += 64 * kUnroll;
         act_task += lane_step * kUnroll;
-        if constexpr (!BIG_BLOCK) {
-          sums_task += 32 * kUnroll;
-        }
       }
       __syncwarp();
       if (lane == 0 && p.full_rows == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
       }
     }
-    if (p.full_rows != 0 && wpt == 2 && !dead) {
+    if (p.full_rows != 0 && !dead) {
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
-        MNB_MARK(17 + tile);
       }
     }
     // digits -> tokens: this lane's two columns, then the four lanes of the quad (fixed order)
@@ -721,52 +616,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       hi0 += __shfl_xor_sync(0xffffffffu, hi0, offset);
       hi1 += __shfl_xor_sync(0xffffffffu, hi1, offset);
     }
-    float4 other = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (p.full_rows != 0 && wpt > 2) {
-      // Groups of four or eight warps exchange through the slot itself: a warp's run of supergroups
-      // in rows 0 and 1 of the tile (256 bytes or more per row) is read by that warp alone, so once
-      // the warp is through with it, it holds the warp's 32 x float4 partial sums. One barrier per
-      // tile; warp 0 of the group adds the parts in a fixed order; the slot is released afterwards.
-      unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
-      __syncwarp();
-      if (parity != 0) {
-        unsigned char *mine = sb + (lane >> 4) * p.row_stride + s_first * p.slice_b_bytes + sg_first * 64;
-        reinterpret_cast<float4 *>(mine)[lane & 15] = make_float4(lo0, lo1, hi0, hi1);
-      }
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + pair), "r"(wpt * 32) : "memory");
-      if (parity == 0) {
-        for (int j = 1; j < wpt; ++j) {
-          const int first = j * sg_share;
-          const unsigned char *theirs = sb + (lane >> 4) * p.row_stride +
-                                        (first / p.sg_per_task) * p.slice_b_bytes + (first % p.sg_per_task) * 64;
-          const float4 part = reinterpret_cast<const float4 *>(theirs)[lane & 15];
-          other.x += part.x;
-          other.y += part.y;
-          other.z += part.z;
-          other.w += part.w;
-        }
-      }
-      __syncwarp();
-      if (lane == 0 && !dead) {
-        // the partial sums went through the generic proxy; the next bulk copy into this slot goes
-        // through the async proxy
-        ptx::FenceProxyAsyncShared();
-        ptx::MbarArrive(&empty_bar[slot]);
-        MNB_MARK(17 + tile);
-      }
-    } else {
-      // the odd warp of the pair hands its half of K to the even warp (one buffer per pair: the
-      // second barrier keeps the next tile's value from overwriting one that is still being read)
-      float4 *exchange = pair_buf + pair * 32 + lane;
-      if (parity == 1) {
-        *exchange = make_float4(lo0, lo1, hi0, hi1);
-      }
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
-      if (parity == 0) {
-        other = *exchange;
-      }
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    // the odd warp of the pair hands its half of K to the even warp (one buffer per pair: the
+    // second barrier keeps the next tile's value from overwriting one that is still being read)
+    float4 *exchange = pair_buf + pair * 32 + lane;
+    if (parity == 1) {
+      *exchange = make_float4(lo0, lo1, hi0, hi1);
     }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    float4 other = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (parity == 0) {
+      other = *exchange;
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
     if (parity == 0 && t < tokens) {
       // lane t of the quad stores token t
       const float sum_lo = t == 0 ? lo0 + other.x : lo1 + other.y;
@@ -774,23 +635,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       // signed codes carry a factor 16 (exact power of two)
       const float back = HAS_ZP ? undo[t] : undo[t] * 0.0625f;
       const std::int64_t m = m_base + t;
+      const std::int64_t r_lo = row0 + g;
+      const std::int64_t r_hi = row0 + g + 8;
       if (r_lo < row_limit) {
-        StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_lo, fmaf(sum_lo, back, bias_lo));
+        const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_lo) : 0.0f;
+        StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_lo, fmaf(sum_lo, back, bias));
       }
       if (r_hi < row_limit) {
-        StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_hi, fmaf(sum_hi, back, bias_hi));
+        const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + r_hi) : 0.0f;
+        StoreOutput(p.out, m * p.out.ld + p.out.col_offset + r_hi, fmaf(sum_hi, back, bias));
       }
     }
   }
 }
 
 } // namespace
-
-#ifdef MNB_TIMELINE
-extern "C" int mnb_debug_copy_timeline_imma(unsigned long long *host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline_imma, sizeof(unsigned long long) * count));
-}
-#endif
 
 // The integer decode kernel takes 4-bit weights with block_size 128 ... 1024 whose prepared
 // scale / zero-point records exist (MetaGeometryOf), one or two tokens per pass over the weights.
@@ -836,24 +695,7 @@ const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, 
   }();
   p.full_rows = (allow_full_rows && w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
                  w.row_bytes >= 1024) ? 1 : 0;
-  p.warps_per_tile = 2;
   if (p.full_rows != 0) {
-    // Warps per row tile: a warp's share must be whole loop rounds and whole quantization blocks
-    // inside one slice. MNB_IMMA_WARPS_PER_TILE = 2, 4 or 8 overrides the default.
-    static const int wanted = [] {
-      const char *value = std::getenv("MNB_IMMA_WARPS_PER_TILE");
-      const int v = value != nullptr ? std::atoi(value) : 0;
-      return (v == 2 || v == 4 || v == 8) ? v : kDefaultWarpsPerTile;
-    }();
-    const int row_sgs = p.slices * p.sg_per_task;
-    for (int wpt = wanted; wpt > 2; wpt /= 2) {
-      const int share = row_sgs / wpt;
-      if (row_sgs % wpt == 0 && share >= kUnroll && share % kUnroll == 0 && share % p.sg_per_block == 0 &&
-          p.sg_per_task % share == 0) {
-        p.warps_per_tile = wpt;
-        break;
-      }
-    }
     p.row_stride = w.row_bytes;
     p.weight_bytes = 16 * w.row_bytes;
     p.slot_bytes = (p.weight_bytes + p.slices * 2 * p.rec_bytes + 127) & ~127;
