@@ -819,6 +819,22 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Same, four columns per thread and one token per blockIdx.y: N a multiple of 4 and 16-byte aligned
+// rows of Y, the partial result and the bias.
+__global__ void __launch_bounds__(256)
+    nbits_digits_combine_vec_kernel(const float4 *partial, const float4 *bias, std::int64_t n4, OutputView out) {
+  const std::int64_t token = blockIdx.y;
+  const float4 *p0 = partial + 3 * token * n4;
+  float4 *dst = reinterpret_cast<float4 *>(out.y + token * out.ld + out.col_offset);
+  for (std::int64_t c = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; c < n4;
+       c += static_cast<std::int64_t>(gridDim.x) * 256) {
+    const float4 a = p0[c], b = p0[n4 + c], d = p0[2 * n4 + c];
+    const float4 add = bias != nullptr ? bias[c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    dst[c] = make_float4((a.x + b.x) + d.x + add.x, (a.y + b.y) + d.y + add.y, (a.z + b.z) + d.z + add.z,
+                         (a.w + b.w) + d.w + add.w);
+  }
+}
+
 std::size_t AlignUp(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
 
 } // namespace
@@ -859,11 +875,22 @@ const char *LaunchDigitsInt8Mma(const WeightView &w, const float *a, std::int64_
   if (LaunchMultiply(no_bias, geo, 3 * m, act, to_partial, status_word, stream, sm_count) == nullptr) {
     return nullptr;
   }
-  const std::int64_t total = m * w.n;
-  std::int64_t blocks = (total + 255) / 256;
-  blocks = blocks > 148 * 8 ? 148 * 8 : blocks;
-  nbits_digits_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, w.bias, static_cast<int>(m),
-                                                                              w.n, out);
+  const bool vector_ok = (w.n % 4) == 0 && (out.ld % 4) == 0 && (out.col_offset % 4) == 0 && out.n_peers == 0 &&
+                         (reinterpret_cast<std::uintptr_t>(out.y) & 15u) == 0 &&
+                         (reinterpret_cast<std::uintptr_t>(w.bias) & 15u) == 0;
+  if (vector_ok) {
+    const std::int64_t n4 = w.n / 4;
+    std::int64_t blocks_x = (n4 + 255) / 256;
+    blocks_x = blocks_x > 148 ? 148 : blocks_x;
+    nbits_digits_combine_vec_kernel<<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(m)), 256, 0, stream>>>(
+        reinterpret_cast<const float4 *>(partial), reinterpret_cast<const float4 *>(w.bias), n4, out);
+  } else {
+    const std::int64_t total = m * w.n;
+    std::int64_t blocks = (total + 255) / 256;
+    blocks = blocks > 148 * 8 ? 148 * 8 : blocks;
+    nbits_digits_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, w.bias,
+                                                                                static_cast<int>(m), w.n, out);
+  }
   if (cudaGetLastError() != cudaSuccess) {
     return nullptr;
   }

@@ -108,7 +108,8 @@ def qdq_to_matmulnbits(w_q: np.ndarray, scale: np.ndarray, zero_point: np.ndarra
 
 class QdqMatMulSession:
     """``Y = MatMul(A, DequantizeLinear(w_q, scale, zero_point, axis=0, block_size))`` (+ ``bias``)
-    through the registered MatMulNBits kernel: the operands are converted once, here."""
+    through the registered MatMulNBits kernel (``register_kernels()`` first, as for
+    ``MatMulNBitsSession``): the operands are converted once, here."""
 
     def __init__(self, w_q, scale, zero_point=None, bias=None, *, block_size, bits=4, signed=False,
                  accuracy_level=0):

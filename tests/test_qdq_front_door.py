@@ -4,6 +4,7 @@
 import numpy as np
 import pytest
 
+import onnx_light_cpu_b200 as pkg
 from onnx_light_cpu_b200 import qdq
 from oracle import nbits_oracle as o
 
@@ -82,6 +83,7 @@ def test_pair_runs_on_the_matmulnbits_kernels(cuda_device, m, k, n, bs, signed, 
     rng = np.random.default_rng(5)
     a = rng.normal(size=(m, k)).astype(np.float32)
     bias = rng.normal(0.0, 0.1, size=n).astype(np.float32)
+    pkg.register_kernels()
     session = qdq.QdqMatMulSession(w_q, scale, zp, bias, block_size=bs, signed=signed)
     y = session.run(a)
     ref = a.astype(np.float64) @ _dequantize(w_q, scale, zp, bs) + bias
