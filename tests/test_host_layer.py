@@ -115,3 +115,21 @@ def test_c_abi_argument_errors_without_device():
         assert rc == _capi.MNB_ERR_CUDA and b"no CPU path" in lib.mnb_last_error()
         with pytest.raises(RuntimeError, match="no CUDA device"):
             _session().run(np.zeros((1, 64), np.float32))
+
+
+def test_path_and_status_constants_match_the_header():
+    """The Python constants are the header's enum values (a selector that drifted would silently pick
+    another kernel)."""
+    import re
+    from pathlib import Path
+
+    from onnx_light_cpu_b200 import _capi
+
+    header = (Path(__file__).resolve().parents[1] / "include" / "matmulnbits_b200.h").read_text()
+    paths = dict(re.findall(r"\bMNB_(PATH_[A-Z0-9_]+)\s*=\s*(\d+)", header))
+    assert len(paths) >= 10
+    for name, value in paths.items():
+        assert getattr(_capi, name) == int(value), name
+    for name, value in re.findall(r"\b(MNB_(?:OK|ERR_[A-Z_]+))\s*=\s*(-?\d+)", header):
+        if hasattr(_capi, name):
+            assert getattr(_capi, name) == int(value), name
