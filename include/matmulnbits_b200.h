@@ -46,7 +46,11 @@ typedef enum mnb_path {
   MNB_PATH_INT8_MMA = 6, /* accuracy_level 4 on integer tensor-core MMA (AUTO picks it when the shape fits) */
   MNB_PATH_GEMV_MMA_MULTI = 7, /* decode on warp-level MMA, several column tiles of tokens per pass */
   MNB_PATH_GEMV_IMMA = 8, /* decode on integer MMA, A as three base-128 digits (block_size >= 128; AUTO picks it for M <= 2) */
-  MNB_PATH_GEMV_DIGITS = 9 /* decode, accuracy_level 0: three digit rows per token through the sixteen-row integer-MMA kernel */
+  MNB_PATH_GEMV_DIGITS = 9, /* decode, accuracy_level 0: three digit rows per token through the sixteen-row integer-MMA kernel */
+  MNB_PATH_GEMV_DIRECT = 10, /* decode on integer MMA with the weights streamed from global memory straight into each warp
+                               (no staging ring), M <= 16, block_size 128; AUTO's choice for 2 <= M <= 16 where the shape fits */
+  MNB_PATH_GEMV_RESIDENT = 11 /* decode of one token on integer MMA: a producer warp asks the TMA unit for the CTA's whole
+                                 share of the weights at kernel start; block_size 128; AUTO's first choice for M = 1 */
 } mnb_path;
 
 /* Device-resident, immutable weights of one MatMulNBits node. Plays the role the reference

@@ -31,6 +31,8 @@ PATH_INT8_MMA = 6
 PATH_GEMV_MMA_MULTI = 7
 PATH_GEMV_IMMA = 8
 PATH_GEMV_DIGITS = 9
+PATH_GEMV_DIRECT = 10
+PATH_GEMV_RESIDENT = 11
 IPC_HANDLE_BYTES = 64
 MAX_GATHER_RANKS = 8
 

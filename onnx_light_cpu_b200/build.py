@@ -24,11 +24,13 @@ CUDA_SOURCES = [
     "csrc/nbits_gemv_mma.cu",
     "csrc/nbits_gemv_mma_multi.cu",
     "csrc/nbits_gemv_imma.cu",
+    "csrc/nbits_decode_direct.cu",
+    "csrc/nbits_decode_resident.cu",
     "csrc/nbits_int8.cu",
     "csrc/nbits_int8_mma.cu",
     "csrc/nbits_gemm_tcgen05.cu",
 ]
-CUDA_HEADERS = ["csrc/nbits_common.cuh", "csrc/nbits_ptx.cuh", "csrc/nbits_tma.cuh", "csrc/nbits_mma_common.cuh",
+CUDA_HEADERS = ["csrc/nbits_common.cuh", "csrc/nbits_digits.cuh", "csrc/nbits_ptx.cuh", "csrc/nbits_tma.cuh", "csrc/nbits_mma_common.cuh",
                 "../include/matmulnbits_b200.h"]
 HOST_SOURCES = [
     "kernels/kernel_registration.cc",
@@ -76,14 +78,35 @@ def _run(command: list[str]) -> None:
     result = subprocess.run(command, cwd=PACKAGE_DIR, capture_output=True, text=True)
     if result.returncode != 0:
         raise RuntimeError("build failed: " + " ".join(command) + "\n" + result.stdout + result.stderr)
+    if "-v" in command and result.stderr:
+        print(result.stderr, file=sys.stderr)
 
 
 def build_cuda(force: bool = False, verbose_ptxas: bool = False) -> Path:
-    if force or _stale(CUDA_LIB, CUDA_SOURCES + CUDA_HEADERS):
-        flags = list(NVCC_FLAGS)
-        if verbose_ptxas:
-            flags += ["-Xptxas", "-v"]
-        _run([_nvcc(), *flags, "-o", str(CUDA_LIB), *CUDA_SOURCES])
+    """One object file per source (compiled in parallel, rebuilt only when the source or a header
+    is newer), then one link. Objects live in ``build/`` beside the package sources."""
+    if not (force or verbose_ptxas or _stale(CUDA_LIB, CUDA_SOURCES + CUDA_HEADERS)):
+        return CUDA_LIB
+    headers_stamp = max((PACKAGE_DIR / name).stat().st_mtime for name in CUDA_HEADERS)
+    objects_dir = PACKAGE_DIR / "build"
+    objects_dir.mkdir(exist_ok=True)
+    compile_flags = [flag for flag in NVCC_FLAGS if flag != "-shared"]
+    if verbose_ptxas:
+        compile_flags += ["-Xptxas", "-v"]
+    jobs, objects = [], []
+    for source in CUDA_SOURCES:
+        obj = objects_dir / (Path(source).stem + ".o")
+        objects.append(str(obj))
+        stamp = max((PACKAGE_DIR / source).stat().st_mtime, headers_stamp)
+        if force or verbose_ptxas or not obj.exists() or obj.stat().st_mtime < stamp:
+            jobs.append([_nvcc(), *compile_flags, "-c", "-o", str(obj), source])
+    if jobs:
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+            list(pool.map(_run, jobs))
+    if jobs or not CUDA_LIB.exists():
+        _run([_nvcc(), "-shared", "-o", str(CUDA_LIB), *objects])
     return CUDA_LIB
 
 

@@ -82,6 +82,7 @@ struct mnb_weights {
   int *status_dev = nullptr;
   int *status_host = nullptr;
   void *meta_dev = nullptr; // prepared scales / zero points for the MMA decode kernel
+  void *zp16_dev = nullptr; // prepared zero-point bytes for the direct-stream decode kernel
   unsigned *arrivals_dev = nullptr; // finished-CTA counter of the fused gather (zero between launches)
   // scratch, grown on demand (guarded by `mutex`)
   std::mutex mutex;
@@ -172,6 +173,21 @@ int SetupCommon(mnb_weights *h) {
 
 // Builds the task-major scales / zero-point array once per node (constant-weight policy).
 int PrepareMeta(mnb_weights *h) {
+  if (mnb::DecodeDirectWantsZeroPointBytes(h->view)) {
+    // one byte per block (16 x the zero point): rides the same asynchronous copies as the scales
+    cudaError_t err = cudaMalloc(&h->zp16_dev, static_cast<std::size_t>(h->view.n) * h->view.n_blocks);
+    if (err != cudaSuccess) {
+      return FailCuda("cudaMalloc(zero-point bytes)", err);
+    }
+    if (!mnb::LaunchExpandZeroPoints(h->view, static_cast<unsigned char *>(h->zp16_dev), h->stream)) {
+      return FailCuda("prepare zero-point bytes", cudaGetLastError());
+    }
+    err = cudaStreamSynchronize(h->stream);
+    if (err != cudaSuccess) {
+      return FailCuda("prepare zero-point bytes", err);
+    }
+    h->view.zp16 = static_cast<const unsigned char *>(h->zp16_dev);
+  }
   const mnb::MetaGeometry geo = mnb::MetaGeometryOf(h->view);
   if (geo.bytes == 0) {
     return MNB_OK; // geometry not taken by the MMA decode kernel
@@ -269,7 +285,15 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     // holds 4 / 2 / 1 tokens for block_size >= 128 / 64 / 32; more tokens go to the kernel that
     // shares a pass over the weights between several column tiles.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m <= kImmaAutoTokens && path == MNB_PATH_AUTO) {
+    if (m == 1 && path == MNB_PATH_AUTO) {
+      // one token: the whole share of each SM is asked for at kernel start
+      name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO) {
+      // a few tokens: weights streamed straight into the warps
+      name = mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true);
+    }
+    if (name == nullptr && m <= kImmaAutoTokens && path == MNB_PATH_AUTO) {
       // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
       name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
@@ -323,6 +347,24 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       return Fail(MNB_ERR_UNSUPPORTED,
                   "MatMulNBits: the integer-digit decode kernel takes 4-bit weights with block_size 128 ... "
                   "1024 and M <= 16.");
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_DIRECT: {
+    name = m <= 16 ? mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true) : nullptr;
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the direct-stream decode kernel takes 4-bit weights with block_size 128, a "
+                  "number of blocks per row that is a multiple of 4, 16-byte aligned operands and M <= 16.");
+    }
+    break;
+  }
+  case MNB_PATH_GEMV_RESIDENT: {
+    name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    if (name == nullptr) {
+      return Fail(MNB_ERR_UNSUPPORTED,
+                  "MatMulNBits: the resident decode kernel takes one token, 4-bit weights with block_size 128, K a "
+                  "multiple of 1024 (2048 with zero points) and 16-byte aligned operands.");
     }
     break;
   }
@@ -568,7 +610,7 @@ int mnb_weights_destroy(mnb_weights *h) {
       }
     }
   }
-  for (void *ptr : {static_cast<void *>(h->arrivals_dev), h->meta_dev, h->scratch_a, h->scratch_s,
+  for (void *ptr : {static_cast<void *>(h->arrivals_dev), h->meta_dev, h->zp16_dev, h->scratch_a, h->scratch_s,
                     static_cast<void *>(h->a_dev), static_cast<void *>(h->y_dev)}) {
     if (ptr != nullptr) {
       cudaFree(ptr);

@@ -19,6 +19,7 @@ struct WeightView {
   const std::uint8_t *zp;
   const float *bias;
   const unsigned char *meta; // prepared task-major scales / zero points (see MetaGeometryOf), or null
+  const unsigned char *zp16; // prepared [n, n_blocks] bytes, 16 * zero point (direct decode kernel), or null
   std::int64_t n;
   std::int64_t k;
   int bits;
@@ -174,6 +175,24 @@ const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t
 bool GemvImmaSupports(const WeightView &w, std::int64_t m);
 const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                            int *status_word, cudaStream_t stream, int sm_count);
+
+// Decode for 1 ... 16 tokens on integer MMA with the packed weights streamed from global memory
+// into each warp (cp.async into lane-private slots or plain loads into registers): no staging
+// ring, no producer. 4-bit, block_size 128. `dependent`: launch with programmatic stream
+// serialization (the weight stream starts while the previous kernel of the stream drains; A is
+// read and Y written only after that kernel has completed).
+bool DecodeDirectSupports(const WeightView &w, std::int64_t m);
+// Fills `out` (n * n_blocks bytes) with 16 * zero point per block; the geometry is one the kernel takes.
+bool DecodeDirectWantsZeroPointBytes(const WeightView &w);
+bool LaunchExpandZeroPoints(const WeightView &w, unsigned char *out, cudaStream_t stream);
+const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                               cudaStream_t stream, int sm_count, bool dependent);
+
+// Decode of one token with the CTA's whole share of the packed weights asked for at kernel start
+// (TMA copies issued by a producer warp into shared-memory slots that are normally written once).
+bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
+const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
+                                 cudaStream_t stream, int sm_count);
 
 // Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,

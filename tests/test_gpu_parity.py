@@ -41,6 +41,24 @@ def run_device(case, path=_capi.PATH_AUTO, accuracy_level=0):
     return out, kernel
 
 
+DIRECT = "nbits_decode_direct_kernel"
+RESIDENT = "nbits_decode_resident_kernel"
+
+
+def resident_takes(case):
+    """Shapes AUTO sends to the one-token kernel that asks for all of its weights at kernel start."""
+    blocks = -(-case.k // case.block_size)
+    return (case.bits == 4 and case.block_size == 128 and case.m == 1 and blocks % 8 == 0 and
+            (case.zero_points is None or blocks % 16 == 0))
+
+
+def direct_takes(case):
+    """Shapes AUTO sends to the direct-stream decode kernel: 4-bit, block 128, blocks per row a
+    multiple of four, at most sixteen tokens."""
+    return (case.bits == 4 and case.block_size == 128 and case.m <= 16 and
+            (-(-case.k // case.block_size)) % 4 == 0)
+
+
 def oracle_f64(case):
     return o.matmul_f64(case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits,
                         case.block_size)
@@ -76,8 +94,7 @@ def test_config1_single_node(cuda_device):
 def test_config2_decode_sweep(cuda_device, m):
     case = syn.config2(m)
     y, kernel = run_device(case)
-    expected = {1: "nbits_gemv_imma_kernel", 4: "nbits_gemv_mma_kernel", 16: "nbits_gemv_mma_multi_kernel"}[m]
-    assert kernel == expected, kernel
+    assert kernel == (RESIDENT if m == 1 else DIRECT), kernel
     ref = oracle_f64(case)
     assert rel_err(y, ref) <= TOL_FP32
     y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
@@ -159,7 +176,9 @@ def test_decode_mma_multi_tile_path(cuda_device, m, k, n, bs, zp, bias):
     assert kernel == "nbits_gemv_mma_multi_kernel"
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     y_auto, kernel_auto = run_device(case)
-    if (bs == 32 and m >= 5) or (bs == 64 and m >= 9):
+    if direct_takes(case):
+        assert kernel_auto == DIRECT and rel_err(y, y_auto) <= TOL_FP32
+    elif (bs == 32 and m >= 5) or (bs == 64 and m >= 9):
         # AUTO sends many tokens over small blocks through the digit rows of the integer kernel
         assert kernel_auto == "nbits_int8_mma_kernel(digits)" and rel_err(y, y_auto) <= TOL_FP32
     else:   # AUTO picks the same kernel for these shapes
@@ -224,8 +243,13 @@ def test_decode_imma_path(cuda_device, m, k, n, bs, zp, bias):
     y_mma, _ = run_device(case, path=_capi.PATH_GEMV_MMA)   # the fp16 two-piece kernel agrees
     assert rel_err(y, y_mma) <= TOL_FP32
     if m <= 2:
-        y_auto, kernel_auto = run_device(case)   # AUTO picks it for one or two tokens
-        assert kernel_auto == kernel and np.array_equal(y, y_auto)
+        y_auto, kernel_auto = run_device(case)   # AUTO: the resident / direct-stream kernels where they fit, else this one
+        if resident_takes(case):
+            assert kernel_auto == RESIDENT and rel_err(y, y_auto) <= TOL_FP32
+        elif direct_takes(case):
+            assert kernel_auto == DIRECT and rel_err(y, y_auto) <= TOL_FP32
+        else:
+            assert kernel_auto == kernel and np.array_equal(y, y_auto)
 
 
 def test_decode_imma_path_wide_dynamic_range_and_special_rows(cuda_device):
@@ -262,6 +286,136 @@ def test_decode_imma_path_rejects_small_blocks(cuda_device):
     weights.close()
 
 
+# shapes for the direct-stream decode kernel: (m, k, n, zp, bias)
+DIRECT_CASES = [
+    (1, 4096, 96, True, True),         # one token: eight-row tiles, two segments per step
+    (1, 4096, 77, False, False),       # ragged last tile, default zero point
+    (1, 2048, 40, True, False),        # few tiles: four warps share a tile
+    (1, 1536, 50, True, True),         # twelve blocks per row: the one-token form does not fit, sixteen-row tiles
+    (1, 14336, 48, True, True),        # wide K (down projection)
+    (1, 4000, 50, True, True),         # K not a multiple of the block
+    (1, 4096, 7, True, True),          # fewer rows than a tile
+    (2, 4096, 200, False, True),       # two tokens = one column tile
+    (3, 4096, 130, True, True),        # two column tiles, the second half empty
+    (4, 2048, 333, True, False),
+    (5, 4096, 40, True, False),        # four column tiles, five tokens
+    (8, 4096, 100, True, True),
+    (13, 4096, 120, True, False),      # eight column tiles, ragged
+    (16, 4096, 64, False, True),
+    (16, 14336, 24, True, True),       # wide K with many tokens: several passes
+    (1, 4096, 14336, True, True),      # cfg2 at full size
+    (2, 4096, 14336, False, True),
+    (4, 4096, 14336, True, True),
+    (16, 4096, 14336, True, True),
+]
+
+
+@pytest.mark.parametrize("m,k,n,zp,bias", DIRECT_CASES)
+def test_decode_direct_path(cuda_device, m, k, n, zp, bias):
+    case = syn.make_case("direct", m, k, n, 4, 128, seed=m * 19 + k + n, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_DIRECT)
+    assert kernel == DIRECT
+    ref = oracle_f64(case)
+    for row in range(m):   # every token against its own magnitude
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    y_auto, kernel_auto = run_device(case)
+    if resident_takes(case):
+        assert kernel_auto == RESIDENT and rel_err(y, y_auto) <= TOL_FP32
+    else:
+        assert kernel_auto == DIRECT and np.array_equal(y, y_auto)
+
+
+# shapes for the one-token resident decode kernel: (k, n, zp, bias)
+RESIDENT_CASES = [
+    (4096, 96, True, True),          # one slot per tile, nothing refilled
+    (4096, 77, False, False),        # ragged last tile (rows beyond N filled with zeros), default zero point
+    (2048, 40, True, False),
+    (1024, 50, False, True),         # eight blocks per row
+    (14336, 48, True, True),         # wide K: tasks of eight chunks, two slots per warp, seven parts per tile
+    (4000, 50, True, True),          # K not a multiple of the block
+    (4096, 7, True, True),           # fewer rows than a tile
+    (4096, 14336, True, True),       # cfg2 at full size: one slot is refilled on the SMs with thirteen tiles
+    (4096, 14336, False, False),
+    (4096, 40000, True, False),      # many tiles per SM: every slot refilled several times
+    (8192, 4096, True, True),
+]
+
+
+@pytest.mark.parametrize("k,n,zp,bias", RESIDENT_CASES)
+def test_decode_resident_path(cuda_device, k, n, zp, bias):
+    case = syn.make_case("resident", 1, k, n, 4, 128, seed=k + n, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_RESIDENT)
+    assert kernel == RESIDENT
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    y_auto, kernel_auto = run_device(case)
+    assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    y_direct, _ = run_device(case, path=_capi.PATH_GEMV_DIRECT)   # same digits, same block sums
+    assert rel_err(y, y_direct) <= 1e-6
+
+
+def test_decode_resident_path_special_rows_and_rejections(cuda_device):
+    import torch
+
+    for value, expect_nan in ((np.nan, True), (np.inf, True), (0.0, False)):
+        case = syn.make_case("resident_special", 1, 4096, 64, 4, 128, seed=3, bias=True)
+        if value == 0.0:
+            case.a[:] = 0.0
+        else:
+            case.a[0, 4000] = value
+        y, kernel = run_device(case, path=_capi.PATH_GEMV_RESIDENT)
+        assert kernel == RESIDENT
+        if expect_nan:
+            assert np.isnan(y).all()
+        else:
+            assert np.array_equal(y[0], case.bias)
+    case = syn.make_case("resident_reject", 2, 4096, 64, 4, 128, seed=8)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=128)
+    with pytest.raises(_capi.MatMulNBitsError) as info:   # two tokens
+        weights.matmul_device(torch.from_numpy(case.a).cuda(), torch.zeros((2, 64), device="cuda"),
+                              path=_capi.PATH_GEMV_RESIDENT)
+    assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
+    weights.close()
+
+
+def test_decode_direct_path_special_rows(cuda_device):
+    """Rows of very different magnitude, an all-zero row, a denormal-sized row and a row with a
+    NaN: the 22-bit digits follow each row's own maximum; a non-finite row gives NaN outputs and
+    does not disturb the tokens next to it."""
+    case = syn.make_case("direct_range", 6, 4096, 256, 4, 128, seed=98, bias=False)
+    rng = np.random.default_rng(2)
+    case.a[0] *= 1e4
+    case.a[1] *= 1e-6
+    case.a[2] *= np.exp(rng.uniform(-8, 8, size=case.k)).astype(np.float32)
+    case.a[3] = 0.0
+    case.a[4] *= 1e-30
+    case.a[5, 17] = np.nan
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_DIRECT)
+    assert kernel == DIRECT
+    finite = syn.make_case("direct_range", 6, 4096, 256, 4, 128, seed=98, bias=False)
+    finite.a[:5] = case.a[:5]
+    ref = oracle_f64(finite)
+    for row in (0, 1, 2, 4):   # no bias: tiny rows are compared on their own scale
+        assert rel_err(y[row], ref[row]) <= TOL_FP32, row
+    assert not y[3].any()
+    assert np.isnan(y[5]).all()
+    one = syn.make_case("direct_nan", 1, 4096, 64, 4, 128, seed=3)
+    one.a[0, 4000] = np.inf
+    y1, _ = run_device(one, path=_capi.PATH_GEMV_DIRECT)
+    assert np.isnan(y1).all()
+
+
+def test_decode_direct_path_rejects_other_blocks(cuda_device):
+    import torch
+
+    case = syn.make_case("direct_reject", 1, 4096, 64, 4, 32, seed=8)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=32)
+    with pytest.raises(_capi.MatMulNBitsError) as info:
+        weights.matmul_device(torch.from_numpy(case.a).cuda(), torch.zeros((1, 64), device="cuda"),
+                              path=_capi.PATH_GEMV_DIRECT)
+    assert info.value.status == _capi.MNB_ERR_UNSUPPORTED
+    weights.close()
+
+
 # shapes for the digit rows through the sixteen-row integer kernel: (m, k, n, block, zp, bias)
 DIGIT_ROW_CASES = [
     (16, 4096, 128, 32, False, True),      # three passes of sixteen rows, signed codes
@@ -284,7 +438,7 @@ def test_decode_digit_rows_path(cuda_device, m, k, n, bs, zp, bias):
     for row in range(m):
         assert rel_err(y[row], ref[row]) <= TOL_FP32, row
     y_auto, kernel_auto = run_device(case)
-    picked = (bs == 32 and m >= 5) or (bs == 64 and m >= 9)
+    picked = ((bs == 32 and m >= 5) or (bs == 64 and m >= 9)) and not direct_takes(case)
     assert (kernel_auto == kernel) == picked
     assert rel_err(y, y_auto) <= TOL_FP32
 
@@ -497,7 +651,7 @@ def test_registered_operator_end_to_end(cuda_device):
     y = session.run(case.a)
     assert y.shape == (4, 1024)
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
-    assert session.last_device_kernel == "nbits_gemv_mma_kernel"
+    assert session.last_device_kernel == DIRECT
     y3 = session.run(case.a.reshape(2, 2, case.k))          # leading dims are kept
     assert y3.shape == (2, 2, 1024) and np.array_equal(y3.reshape(4, 1024), y)
     assert pkg.used_kernel_names() == ["onnx_light_cuda::MatMulNBits"] * 2
