@@ -262,7 +262,6 @@ def main() -> None:
                              "(default) or an NCCL all-gather follows each kernel")
     parser.add_argument("--decode-path", default="auto", choices=["auto", "gemv", "mma", "imma", "direct", "resident"],
                         help="kernel family for the decode workload (auto = library dispatch)")
-    parser.add_argument("--weight-copies", type=int, default=8, help=argparse.SUPPRESS)
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -300,12 +299,13 @@ def main() -> None:
 
     if not multi:
         cfg = DECODE
-        copies = args.weight_copies
+        copies = 8
         weights = device_weights(torch, pkg, cfg, copies, seed=1201, zp=True, bias=True)
         m = 1
         a = torch.randn(m, cfg["k"], device="cuda").half().float()
         ys = [torch.empty(m, cfg["n"], device="cuda") for _ in range(copies)]
         per_launch_bytes = weights[0].algorithmic_bytes(m)
+        assert copies * per_launch_bytes > L2_BYTES
 
         decode_path = {"auto": _capi.PATH_AUTO, "gemv": _capi.PATH_GEMV, "mma": _capi.PATH_GEMV_MMA,
                        "imma": _capi.PATH_GEMV_IMMA, "direct": _capi.PATH_GEMV_DIRECT,

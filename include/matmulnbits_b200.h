@@ -48,7 +48,7 @@ typedef enum mnb_path {
   MNB_PATH_GEMV_IMMA = 8, /* decode on integer MMA, A as three base-128 digits (block_size >= 128; AUTO picks it for M <= 2) */
   MNB_PATH_GEMV_DIGITS = 9, /* decode, accuracy_level 0: three digit rows per token through the sixteen-row integer-MMA kernel */
   MNB_PATH_GEMV_DIRECT = 10, /* decode on integer MMA with the weights streamed from global memory straight into each warp
-                               (no staging ring), M <= 16, block_size 128; AUTO's choice for 2 <= M <= 16 where the shape fits */
+                               (no staging ring), M <= 2, block_size 128; AUTO's choice for M = 1 where the resident kernel does not fit */
   MNB_PATH_GEMV_RESIDENT = 11 /* decode of one token on integer MMA: a producer warp asks the TMA unit for the CTA's whole
                                  share of the weights at kernel start; block_size 128; AUTO's first choice for M = 1 */
 } mnb_path;

@@ -289,8 +289,8 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // one token: the whole share of each SM is asked for at kernel start
       name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
-    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO) {
-      // a few tokens: weights streamed straight into the warps
+    if (name == nullptr && m == 1 && path == MNB_PATH_AUTO) {
+      // shapes the resident kernel does not take: every warp streams its own tile
       name = mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true);
     }
     if (name == nullptr && m <= kImmaAutoTokens && path == MNB_PATH_AUTO) {
@@ -351,11 +351,11 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     break;
   }
   case MNB_PATH_GEMV_DIRECT: {
-    name = m <= 16 ? mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true) : nullptr;
+    name = m <= 2 ? mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true) : nullptr;
     if (name == nullptr) {
       return Fail(MNB_ERR_UNSUPPORTED,
                   "MatMulNBits: the direct-stream decode kernel takes 4-bit weights with block_size 128, a "
-                  "number of blocks per row that is a multiple of 4, 16-byte aligned operands and M <= 16.");
+                  "number of blocks per row that is a multiple of 4, 16-byte aligned operands and M <= 2.");
     }
     break;
   }

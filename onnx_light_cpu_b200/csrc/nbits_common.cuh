@@ -176,8 +176,8 @@ bool GemvImmaSupports(const WeightView &w, std::int64_t m);
 const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                            int *status_word, cudaStream_t stream, int sm_count);
 
-// Decode for 1 ... 16 tokens on integer MMA with the packed weights streamed from global memory
-// into each warp (cp.async into lane-private slots or plain loads into registers): no staging
+// Decode for one or two tokens on integer MMA with the packed weights streamed from global memory
+// into each warp (cp.async into lane-private places or plain loads into registers): no staging
 // ring, no producer. 4-bit, block_size 128. `dependent`: launch with programmatic stream
 // serialization (the weight stream starts while the previous kernel of the stream drains; A is
 // read and Y written only after that kernel has completed).

@@ -1,29 +1,18 @@
 // Decode path of MatMulNBits (accuracy_level 0, 1 ... 16 activation rows, 4-bit weights,
-// block_size 128) that streams the packed weights from global memory straight into registers.
+// block_size 128) in which every warp streams its own packed weights from global memory.
 //
-// Why no shared-memory ring: at decode sizes a node is 30 MB and lasts a few microseconds, so what
-// counts is how early the first byte is asked for and how little stands between a byte and its
-// multiply. Every warp owns a row tile (or a contiguous part of its K range), keeps one or two
-// "supersteps" of 128-bit loads in flight in registers (4 KB / 8 KB per warp), and needs no
-// producer, barrier or slot hand-over while it streams. The first loads are issued before the
-// activations are looked at and before the dependency on the previous kernel of the stream is
-// awaited (programmatic dependent launch), so with two resident CTAs per SM the weight stream of
-// node n+1 starts while node n drains.
+// No producer, no shared slots, no hand-over between warps while the weights stream: every warp
+// owns a row tile (or a contiguous part of its K range) and keeps a ring of "supersteps" (four
+// MMA steps, 4 KB per warp) in flight, either in lane-private shared-memory places filled by
+// cp.async (a lane reads back only what it asked for itself) or, when shared memory is full of
+// activation digits, in registers. The first superstep is asked for before the dependency on
+// the previous kernel of the stream is awaited (programmatic dependent launch); the rest of the
+// ring follows BEHIND the request for the activations, because the load pipe serves requests in
+// order and three stages per warp in front of A delayed the digits by two to four microseconds.
+// With two resident CTAs per SM the weight stream of node n+1 starts while node n drains.
 //
-// Arithmetic (exact integer products, fp32-grade result):
-//  * A weight word holds eight codes. `w & 0x0f0f0f0f` are the even codes as bytes, `w & 0xf0f0f0f0`
-//    the odd codes times 16 as bytes: one instruction per MMA operand register, no shift. Even and
-//    odd codes go through separate mma.sync.m16n8k32.s32.u8.s8 accumulators, merged per
-//    quantization block as 16 * even + odd (so every block sum carries a factor 16, undone at the
-//    end, exactly).
-//  * Each activation row is scaled so that its largest magnitude becomes kDigitRange and rounded
-//    to a 22-bit integer n = 16384 d0 + 128 d1 + d2 with balanced base-128 digits; the digits are
-//    three signed-byte MMA columns. One MMA column tile (8 columns) holds two tokens.
-//  * Zero points leave through `block sum - zp * (sum of the block's digits)`, the correction of
-//    onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:208-223; a node without zero points
-//    uses the default 8.
-//  * Block sums are exact int32 (< 2^24), converted to float and combined as
-//    acc[digit] += scale * float(sum); the end computes (16384 acc0 + 128 acc1 + acc2) * undo + bias.
+// Arithmetic and exactness: nbits_digits.cuh. Scales are read in their own layout; zero points from
+// the prepared byte-per-block array (16 x zero point), which rides the same asynchronous copies.
 //
 // Two ways to fill the sixteen MMA rows:
 //  * several tokens: sixteen weight rows x one 128-k segment per step; `ks` warps of a CTA share
@@ -43,34 +32,12 @@
 #include "nbits_ptx.cuh"
 
 #include <cstdint>
-#include <cstdlib>
 #include <type_traits>
-
-#ifdef MNB_TIMELINE
-__device__ unsigned long long g_direct_timeline[512 * 16 * 8];
-__device__ __forceinline__ unsigned long long GlobalTimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define MNB_MARK(slot)                                                                             \
-  if ((threadIdx.x & 31) == 0) {                                                                   \
-    g_direct_timeline[(blockIdx.x * 16 + (threadIdx.x >> 5)) * 8 + (slot)] = GlobalTimer();        \
-  }
-extern "C" int mnb_debug_copy_direct_timeline(unsigned long long *out, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_direct_timeline, sizeof(unsigned long long) * count));
-}
-#else
-#define MNB_MARK(slot)
-#endif
 
 namespace mnb {
 namespace {
 
-struct DirectParams;
-__device__ __forceinline__ int exp_prefetch_mode(const DirectParams &p);
 struct DirectParams {
-  int exp_prefetch;
   WeightView w;
   const float *a;
   OutputView out;
@@ -83,8 +50,6 @@ struct DirectParams {
   int chunk_stride;     // bytes between consecutive segments of the staged digits
   int table_ints;       // ints of the digit-sum table
 };
-
-__device__ __forceinline__ int exp_prefetch_mode(const DirectParams &p) { return p.exp_prefetch; }
 
 // 16 bytes of weights, streamed: read once, no reason to keep them in L1.
 __device__ __forceinline__ uint4 LoadStream16(const unsigned char *ptr) {
@@ -167,7 +132,6 @@ __global__ void __launch_bounds__(512, 1) nbits_decode_direct_kernel(const Direc
 
   // the next kernel of the stream may start filling SMs as soon as this grid's CTAs leave
   ptx::GridDependencyLaunch();
-  MNB_MARK(0)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -298,25 +262,6 @@ __global__ void __launch_bounds__(512, 1) nbits_decode_direct_kernel(const Direc
     }
   };
   issue_stage(0);
-  // The rest of this warp's first tile is asked into L2 only: a prefetch holds no register and no
-  // shared memory, so all of it can be on its way before the dependency wait; the ring stages that
-  // are filled later then come from L2 instead of HBM.
-  if (my_tiles > 0 && exp_prefetch_mode(p) != 0) {
-    const int lines_per_row = supers_per_part * kSegsPerSuper / 2;  // 128-byte lines of this part of K
-    const int first_lines = kSegsPerSuper / 2;                       // already asked for by stage 0
-    const int total = kRowsPerTile * lines_per_row;
-    for (int idx = lane; idx < total; idx += 32) {
-      const int row_in_tile = idx / lines_per_row;
-      const int line = idx - row_in_tile * lines_per_row;
-      int row = tile_first * kRowsPerTile + row_in_tile;
-      row = row < last_row ? row : last_row;
-      if (line >= first_lines) {
-        const unsigned char *at =
-            p.w.b + (static_cast<std::int64_t>(row) * n_blocks + first_seg_of_part) * 64 + line * 128;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(at));
-      }
-    }
-  }
   auto issue_rest = [&]() {
 #pragma unroll
     for (int b = 1; b < RING; ++b) {
@@ -325,13 +270,10 @@ __global__ void __launch_bounds__(512, 1) nbits_decode_direct_kernel(const Direc
   };
 
   // A (and Y) may be produced / still read by the previous kernel in the stream
-  MNB_MARK(1)
   ptx::GridDependencyWait();
-  MNB_MARK(2)
   const DigitGeometry geometry{static_cast<int>(p.w.k), p.segs, p.chunk_stride, p.table_ints};
   StageDigits<ROWPAIR>(geometry, p.a + static_cast<std::int64_t>(m_base) * p.w.k, tokens, NT, digits, table, undo, red,
                        tid, static_cast<int>(blockDim.x), [] { __syncthreads(); }, issue_rest);
-  MNB_MARK(3)
 
   // ---- per-lane constants ----
   // MMA column g as activation operand: digit g % 3 of the first (g < 3) or second (3 <= g < 6)
@@ -452,11 +394,6 @@ __global__ void __launch_bounds__(512, 1) nbits_decode_direct_kernel(const Direc
       CopyAsyncCommit();  // one group per superstep consumed, empty or not
       stage_offset = stage_offset + kStageBytes == RING * kStageBytes ? 0u : stage_offset + kStageBytes;
     }
-#ifdef MNB_TIMELINE
-    if (it == 0) { MNB_MARK(4) }
-    if (it == 1) { MNB_MARK(5) }
-    if (it == 2) { MNB_MARK(6) }
-#endif
 
     if (++super == supers_per_part) {
       super = 0;
@@ -559,7 +496,6 @@ __global__ void __launch_bounds__(512, 1) nbits_decode_direct_kernel(const Direc
   if constexpr (RING > 0) {
     CopyAsyncWait<0>();  // nothing of this thread is in flight when it leaves
   }
-  MNB_MARK(7)
 }
 
 // out[row * n_blocks + block] = 16 * zero point, one byte per block: what the ring copies beside
@@ -616,8 +552,6 @@ cudaError_t LaunchRing(int ring, const DirectParams &p, dim3 grid, int threads, 
     return LaunchOne<ROWPAIR, NT, 0>(p, grid, threads, smem, dependent, stream);
   case 2:
     return LaunchOne<ROWPAIR, NT, 2>(p, grid, threads, smem, dependent, stream);
-  case 3:
-    return LaunchOne<ROWPAIR, NT, 3>(p, grid, threads, smem, dependent, stream);
   default:
     return cudaErrorInvalidValue;
   }
@@ -649,7 +583,10 @@ bool LaunchExpandZeroPoints(const WeightView &w, unsigned char *out, cudaStream_
 }
 
 bool DecodeDirectSupports(const WeightView &w, std::int64_t m) {
-  if (!GeometryFits(w) || m < 1 || m > kMaxTokens || (w.zp != nullptr && w.zp16 == nullptr)) {
+  // One column tile (two tokens). The same code with 2, 4 or 8 column tiles per pass was measured
+  // against the fp16 tensor-core decode kernels on N = 14336, K = 4096 and lost from M = 2 on (M = 4:
+  // 17.1 vs 15.3 us, M = 16: 54.4 vs 38.5 us), so only the one-tile form is built.
+  if (!GeometryFits(w) || m < 1 || m > 2 || (w.zp != nullptr && w.zp16 == nullptr)) {
     return false;
   }
   return (reinterpret_cast<std::uintptr_t>(w.b) & 15u) == 0 && (reinterpret_cast<std::uintptr_t>(w.scales) & 15u) == 0 &&
@@ -676,12 +613,7 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
   constexpr size_t kOnePerSm = 226 * 1024;
 
   const int rows_per_tile = row_pair ? 8 : 16;
-  // column tiles per pass: as many tokens per pass over the weights as shared memory holds
   int column_tiles = 1;
-  if (!row_pair) {
-    const int wanted = static_cast<int>((m + 1) / 2);
-    column_tiles = wanted <= 1 ? 1 : (wanted <= 2 ? 2 : (wanted <= 4 ? 4 : 8));
-  }
   // Preference: two resident CTAs per SM (the next node's CTAs then start while this node
   // drains) with a deep shared-memory ring, then one large CTA, then the register ring; fewer
   // tokens per pass when even that does not fit.
@@ -689,34 +621,18 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
     int threads;
     int ring;
   };
-  // 224 threads: seven warps leave room for a ring of three supersteps beside the digits of one
-  // token at K = 4096; taken when seven warps per CTA cover all tiles in one round.
-  const Shape shapes[] = {{224, 3}, {256, 3}, {256, 2}, {416, 3}, {448, 3}, {512, 3}, {512, 2}, {512, 0}};
+  // Measured (one token, N = 14336, K = 4096, us per launch in a CUDA graph): 256 threads with a
+  // ring of two stages 9.0, 512 threads with the register ring 9.0, 512 / ring 2: 9.2, rings of
+  // three stages 9.8 ... 10.2 (what a warp asks for ahead of time is also in front of its own later
+  // requests).
+  const Shape shapes[] = {{256, 2}, {512, 2}, {512, 0}};
   int threads = 0;
   int ring = 0;
   size_t smem = 0;
-  // EXPERIMENT KNOBS (temporary)
-  static const int exp_threads = std::getenv("MNB_X_THREADS") ? std::atoi(std::getenv("MNB_X_THREADS")) : 0;
-  static const int exp_ring = std::getenv("MNB_X_RING") ? std::atoi(std::getenv("MNB_X_RING")) : -1;
-  static const int exp_pdl = std::getenv("MNB_X_PDL") ? std::atoi(std::getenv("MNB_X_PDL")) : 1;
-  static const int exp_ks = std::getenv("MNB_X_KS") ? std::atoi(std::getenv("MNB_X_KS")) : 0;
-  static const int exp_ctas = std::getenv("MNB_X_CTAS") ? std::atoi(std::getenv("MNB_X_CTAS")) : 0;
-  if (exp_pdl == 0) {
-    dependent = false;
-  }
-  static const int exp_prefetch = std::getenv("MNB_X_PREFETCH") ? std::atoi(std::getenv("MNB_X_PREFETCH")) : 1;
-  p.exp_prefetch = exp_prefetch;
   for (;;) {
     p.chunk_stride = row_pair ? kDigits * kChunkBytes : column_tiles * kTileColumnBytes;
     p.table_ints = row_pair ? (p.segs / 2) * 8 : p.segs * column_tiles * 8;
     for (const Shape &shape : shapes) {
-      if ((exp_threads != 0 && shape.threads != exp_threads) || (exp_ring >= 0 && shape.ring != exp_ring)) {
-        continue;
-      }
-      if (shape.threads == 224 &&
-          (w.n + rows_per_tile - 1) / rows_per_tile > static_cast<std::int64_t>(2 * sms) * 7) {
-        continue;
-      }
       const size_t need = SharedBytes(p, column_tiles, shape.threads / 32, shape.ring);
       if (need <= (shape.threads <= 256 ? kTwoPerSm : kOnePerSm)) {
         threads = shape.threads;
@@ -748,12 +664,6 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
          static_cast<std::int64_t>(p.tiles) * ks * 4 < static_cast<std::int64_t>(ctas) * warps * 3) {
     ks *= 2;
   }
-  if (exp_ks != 0 && (supers % exp_ks) == 0 && (warps % exp_ks) == 0) {
-    ks = exp_ks;
-  }
-  if (exp_ctas != 0) {
-    ctas = exp_ctas;
-  }
   p.ks = ks;
   p.supers_per_part = supers / ks;
   // tiles go round the CTAs first (tile = group * CTAs + CTA), so every SM gets its share whatever
@@ -765,14 +675,8 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
   cudaError_t err = cudaErrorInvalidValue;
   if (row_pair) {
     err = LaunchRing<true, 1>(ring, p, grid, threads, smem, dependent, stream);
-  } else if (column_tiles == 1) {
-    err = LaunchRing<false, 1>(ring, p, grid, threads, smem, dependent, stream);
-  } else if (column_tiles == 2) {
-    err = LaunchRing<false, 2>(ring, p, grid, threads, smem, dependent, stream);
-  } else if (column_tiles == 4) {
-    err = LaunchRing<false, 4>(ring, p, grid, threads, smem, dependent, stream);
   } else {
-    err = LaunchRing<false, 8>(ring, p, grid, threads, smem, dependent, stream);
+    err = LaunchRing<false, 1>(ring, p, grid, threads, smem, dependent, stream);
   }
   if (err != cudaSuccess) {
     cudaGetLastError();

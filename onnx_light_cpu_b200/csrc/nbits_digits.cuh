@@ -116,9 +116,10 @@ __device__ __forceinline__ int ChunkOffset(int seg, int token, int digit, int ch
 // Biased integer u = n + 64 + 64 * 128 + 128 * 16384 (0 < u < 2^22): its plain base-128 digits are
 // the balanced digits of n plus 64, 64 and 128. One fused multiply-add and one conversion per
 // value; u << 1 and u << 2 put the middle and high digit on byte boundaries.
+// sums[d] receives the sum of the eight digits d.
 template <bool ROWPAIR>
 __device__ __forceinline__ void ConvertWord(const float (&x)[8], float lift, float up, int word, int token,
-                                            unsigned char *digits, int chunk_stride) {
+                                            unsigned char *digits, int chunk_stride, int (&sums)[kDigits]) {
   std::uint32_t u0[8], u1[8], u2[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
@@ -140,6 +141,10 @@ __device__ __forceinline__ void ConvertWord(const float (&x)[8], float lift, flo
     packed[1][h] = ((mid & 0x7f7f7f7fu) + 0x40404040u) ^ 0x80808080u;
     packed[2][h] = ((low & 0x7f7f7f7fu) + 0x40404040u) ^ 0x80808080u;
   }
+#pragma unroll
+  for (int d = 0; d < kDigits; ++d) {
+    sums[d] = __dp4a(static_cast<int>(packed[d][0]), 0x01010101, __dp4a(static_cast<int>(packed[d][1]), 0x01010101, 0));
+  }
   const int seg = word >> 4;
   const int quad_lane = (word >> 2) & 3;
   const int word_in_lane = word & 3;
@@ -158,18 +163,23 @@ __device__ __forceinline__ void ConvertWord(const float (&x)[8], float lift, flo
 
 // What takes a row maximum to the digit scale: `up` multiplies the (lifted) activations, `undo`
 // takes the integer result back (NaN for a row with a non-finite entry: all its outputs are NaN).
+// Neither factor needs to be correctly rounded (a relative error of 1e-7 in `up` moves an integer
+// that may reach kDigitRange by less than one, and the digits hold up to 2,023,359; `undo` scales
+// every output of the row alike), so the reciprocal is the fast one.
 __device__ __forceinline__ void DigitFactors(float amax, float *lift, float *up, float *undo) {
   const bool finite = amax < 3.0e38f;  // false for an infinite entry and for NaN
   // rows of very small magnitude are lifted by an exact power of two first, so that `up` stays finite
-  *lift = amax < 1.0e-18f ? 1.8446744e19f /* 2^64 */ : 1.0f;
+  const bool tiny = amax < 1.0e-18f;
+  *lift = tiny ? 1.8446744e19f /* 2^64 */ : 1.0f;
+  const float unlift = tiny ? 5.4210109e-20f /* 2^-64 */ : 1.0f;
   const float lifted = amax * *lift;
-  *up = (finite && lifted > 0.0f) ? kDigitRange / lifted : 0.0f;
+  *up = (finite && lifted > 0.0f) ? __fdividef(kDigitRange, lifted) : 0.0f;
   // the factor 16 of the merged even / odd block sums is taken out here
-  *undo = finite ? ((lifted / kDigitRange) / *lift) * 0.0625f : __int_as_float(0x7fc00000);
+  *undo = finite ? (lifted * (1.0f / kDigitRange)) * unlift * 0.0625f : __int_as_float(0x7fc00000);
 }
 
 // Stages `tokens` activation rows as digit bytes and builds the digit-sum table. All threads of
-// the CTA take part (three barriers). undo[token] takes the integer result back to the
+// the CTA take part (two or three barriers). undo[token] takes the integer result back to the
 // row's scale. Byte order inside a chunk (128 k of one segment): the lane t = k / 32 of a quad owns
 // units 2t (even k) and 2t + 1 (odd k); inside a unit the word k % 32 / 8 owns four bytes.
 // `issue_rest` is called once, right behind the first loads of A: the caller queues the rest of
@@ -230,6 +240,10 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
       held[j][4] = hi.x, held[j][5] = hi.y, held[j][6] = hi.z, held[j][7] = hi.w;
     }
     issue_rest();
+    // the table entries nothing writes below (unused MMA columns) are cleared while A is on its way
+    for (int entry = tid; entry < geo.table_ints; entry += threads) {
+      table[entry] = 0;
+    }
     float amax = 0.0f;  // NaN as soon as the row holds one (max.NaN)
 #pragma unroll
     for (int j = 0; j < kHeld; ++j) {
@@ -255,13 +269,33 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
     if (tid == 0) {
       undo[0] = back;
     }
+    // digit sums ride along: a 128-k segment is sixteen words = one half warp
 #pragma unroll
     for (int j = 0; j < kHeld; ++j) {
       const int word = tid + j * threads;
-      if (word < words_pad) {
-        ConvertWord<ROWPAIR>(held[j], lift, up, word, 0, digits, geo.chunk_stride);
+      const bool valid = word < words_pad;  // the same for the sixteen lanes of a segment
+      int sums[kDigits] = {0, 0, 0};
+      if (valid) {
+        ConvertWord<ROWPAIR>(held[j], lift, up, word, 0, digits, geo.chunk_stride, sums);
+      }
+#pragma unroll
+      for (int offset = 8; offset > 0; offset >>= 1) {
+#pragma unroll
+        for (int d = 0; d < kDigits; ++d) {
+          sums[d] += __shfl_xor_sync(0xffffffffu, sums[d], offset);
+        }
+      }
+      if (valid && (lane & 15) == 0) {
+        const int seg = word >> 4;
+        // entry (step, column): row-pair mode keeps the even segment in columns 0..2, the odd one in 3..5
+        int *entry = ROWPAIR ? table + (seg >> 1) * 8 + (seg & 1) * kDigits : table + seg * column_tiles * 8;
+        entry[0] = -sums[0];
+        entry[1] = -sums[1];
+        entry[2] = -sums[2];
       }
     }
+    sync();
+    return;
   } else {
     for (int token = 0; token < tokens; ++token) {
       const float *src = a_rows + static_cast<std::int64_t>(token) * k;
@@ -298,7 +332,8 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
       for (int word = tid; word < words_pad; word += threads) {
         float x[8];
         load_word(src, word, x);
-        ConvertWord<ROWPAIR>(x, lift, up, word, token, digits, geo.chunk_stride);
+        int unused[kDigits];
+        ConvertWord<ROWPAIR>(x, lift, up, word, token, digits, geo.chunk_stride, unused);
       }
     }
   }
