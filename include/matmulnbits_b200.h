@@ -152,7 +152,9 @@ int mnb_weights_poll_status(mnb_weights *weights, int *status);
  * be bit-exact (integer_gemm_vnni.cc:60-93 nibble order, :208-223 exact integers). */
 int mnb_dequant_int_device(mnb_weights *weights, int32_t *out_dev, void *stream);
 
-/* accuracy_level 4 stage 1: per (row, block) scale = max|A|/127, aq = clamp(rne(A/scale)). */
+/* accuracy_level 4 stage 1: per (row, block) scale = max|A|/127, aq = clamp(rne(A/scale)).
+ * A block that holds a NaN or an infinity gets scale NaN and codes 0: every output of that token
+ * is then NaN, like at accuracy_level 0 (a NaN is not clamped to -127 behind the caller's back). */
 int mnb_quantize_a_device(const float *a_dev, int64_t m, int64_t k, int block_size,
                           int8_t *aq_dev, float *a_scales_dev, void *stream);
 
@@ -161,6 +163,16 @@ int mnb_quantize_a_device(const float *a_dev, int64_t m, int64_t k, int block_si
  * integer_gemm_vnni.cc:48-56). */
 int mnb_int8_block_dots_device(mnb_weights *weights, const int8_t *aq_dev, int64_t m,
                                int32_t *dots_dev, void *stream);
+
+/* The same block dots, but produced by the production integer-MMA kernel of accuracy_level 4 itself
+ * (an instrumented instantiation of it: same fragment layout, swizzled tiles, signed-code form and
+ * zero-point correction, plus a store of every block sum before it is scaled). A is quantized on
+ * the device exactly as mnb_matmul_device(accuracy_level = 4) does it; y_dev [m, N] receives the
+ * ordinary result, dots_dev [m, N, n_blocks] the sums (cleared by the call). m <= 8 and a shape
+ * the integer-MMA kernel takes, else MNB_ERR_UNSUPPORTED. Exactness to compare with:
+ * IntegerDotU8S8Scalar, onnx_light_cpu/impl/math/gemm/vnni/integer_gemm_vnni.cc:48-56. */
+int mnb_int8_mma_block_dots_device(mnb_weights *weights, const float *a_dev, int64_t m, float *y_dev,
+                                   int32_t *dots_dev, void *stream);
 
 /* accuracy_level-4 product Y = MatMulNBits(A) that allocates nothing. It has no counterpart in
  * the reference. It is meant for callers that are not allowed to reach cudaMalloc while they

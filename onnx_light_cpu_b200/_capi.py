@@ -57,6 +57,7 @@ EXPORTED_SYMBOLS = (
     "mnb_dequant_int_device",
     "mnb_quantize_a_device",
     "mnb_int8_block_dots_device",
+    "mnb_int8_mma_block_dots_device",
     "mnb_matmul_int8_static",
     "mnb_launch_count",
     "mnb_last_kernel",
@@ -111,6 +112,7 @@ def load() -> ctypes.CDLL:
     lib.mnb_dequant_int_device.argtypes = [vp, vp, vp]
     lib.mnb_quantize_a_device.argtypes = [vp, i64, i64, i32, vp, vp, vp]
     lib.mnb_int8_block_dots_device.argtypes = [vp, vp, i64, vp, vp]
+    lib.mnb_int8_mma_block_dots_device.argtypes = [vp, vp, i64, vp, vp, vp]
     lib.mnb_matmul_int8_static.argtypes = [vp, vp, i64, vp, vp]
     lib.mnb_launch_count.restype = i64
     for name in ("mnb_weights_n", "mnb_weights_k"):

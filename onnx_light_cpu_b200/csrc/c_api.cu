@@ -1036,6 +1036,36 @@ int mnb_int8_block_dots_device(mnb_weights *h, const int8_t *aq_dev, int64_t m, 
   return MNB_OK;
 }
 
+int mnb_int8_mma_block_dots_device(mnb_weights *h, const float *a_dev, int64_t m, float *y_dev, int32_t *dots_dev,
+                                   void *stream) {
+  if (h == nullptr || a_dev == nullptr || y_dev == nullptr || dots_dev == nullptr || m <= 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_int8_mma_block_dots_device: bad argument.");
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  const std::size_t need = m <= 8 ? mnb::Int8MmaScratchBytes(h->view, m) : 0;
+  const char *name = nullptr;
+  if (need != 0) {
+    const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    OutputView out{y_dev, h->view.n, 0};
+    name = mnb::LaunchInt8MmaBlockDots(h->view, a_dev, m, static_cast<unsigned char *>(h->scratch_a), out, dots_dev,
+                                       h->status_dev, static_cast<cudaStream_t>(stream), h->sm_count);
+  }
+  if (name == nullptr) {
+    return Fail(MNB_ERR_UNSUPPORTED,
+                "mnb_int8_mma_block_dots_device: needs M <= 8 and a shape of the integer-MMA path (bits=4, "
+                "32 <= block_size <= 1024, packed rows a multiple of 128 bytes).");
+  }
+  mnb::t_last_kernel = name;
+  return MNB_OK;
+}
+
 // ---- accuracy_level 4 without any allocation ------------------------------------------------
 // The quantized activations and their block scales live in a fixed array inside the library
 // image instead of cudaMalloc'ed scratch. Every GPU that loads the library carries the array

@@ -217,6 +217,12 @@ std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m);
 const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
                           OutputView out, int *status_word, cudaStream_t stream, int sm_count);
 
+// Parity instrument (m <= 8): the same quantization and the instrumented form of the same kernel,
+// which also adds its exact int32 block dots to dots[m, n, n_blocks] (zeroed by the call).
+const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                                   OutputView out, std::int32_t *dots, int *status_word, cudaStream_t stream,
+                                   int sm_count);
+
 // accuracy_level 0 through the sixteen-row integer-MMA kernel: every token enters as three rows of
 // base-128 digits (22 bits of its row maximum), the three partial results are added behind it.
 // `scratch`: DigitsInt8MmaScratchBytes (0 when the shape is outside what the kernel takes).

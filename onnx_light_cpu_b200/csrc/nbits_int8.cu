@@ -32,16 +32,22 @@ __global__ void __launch_bounds__(256)
   const std::int64_t k0 = static_cast<std::int64_t>(block) * block_size;
   const float *src = a + static_cast<std::int64_t>(row) * k;
   float amax = 0.0f;
+  bool bad = false;  // a NaN or an infinity in the block
   for (int e = lane; e < block_size; e += 32) {
     if (k0 + e < k) {
-      amax = fmaxf(amax, fabsf(src[k0 + e]));
+      const float v = fabsf(src[k0 + e]);
+      amax = fmaxf(amax, v);
+      bad = bad || !(v <= 3.4028235e38f);
     }
   }
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) {
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
   }
-  const float sa = __fdiv_rn(amax, 127.0f);
+  bad = __any_sync(0xffffffffu, bad);
+  // A block with a non-finite activation has no int8 form: its scale is NaN and its codes are 0,
+  // so that every output of the token comes out NaN (what accuracy_level 0 gives for such a row).
+  const float sa = bad ? __int_as_float(0x7fc00000) : __fdiv_rn(amax, 127.0f);
   if (lane == 0) {
     a_scales[static_cast<std::int64_t>(row) * n_blocks + block] = sa;
   }

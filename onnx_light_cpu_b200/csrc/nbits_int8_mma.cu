@@ -67,6 +67,7 @@ struct ImmaParams {
   int table_offset;    // byte offset of the scale / sum table inside a pass
   int pass_bytes;
   int groups_per_block; // 128-k groups per quantization block (block_size >= 256), else 1
+  std::int32_t *dots;   // DOTS instantiations only: [m, n, n_blocks] exact block dots, zero before the launch
 };
 static_assert(kTaskK == kWarps * 128, "one 128-k group of a task per consumer warp");
 
@@ -154,10 +155,13 @@ __global__ void __launch_bounds__(256)
   const bool live = row < m_total;
   const float *src = a + static_cast<std::int64_t>(row) * k;
   float amax = 0.0f;
+  bool bad = false;  // a NaN or an infinity in the block
   if (live) {
     for (int e = lane; e < block_size; e += 32) {
       if (k0 + e < k) {
-        amax = fmaxf(amax, fabsf(src[k0 + e]));
+        const float v = fabsf(src[k0 + e]);
+        amax = fmaxf(amax, v);
+        bad = bad || !(v <= 3.4028235e38f);
       }
     }
   }
@@ -165,7 +169,9 @@ __global__ void __launch_bounds__(256)
   for (int offset = 16; offset > 0; offset >>= 1) {
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
   }
-  const float sa = __fdiv_rn(amax, 127.0f);
+  bad = __any_sync(0xffffffffu, bad);
+  // a block with a non-finite activation: scale NaN, codes 0, every output of the token NaN
+  const float sa = bad ? __int_as_float(0x7fc00000) : __fdiv_rn(amax, 127.0f);
   unsigned char *base = act + static_cast<std::int64_t>(pass) * pass_bytes;
   std::int8_t *dst = reinterpret_cast<std::int8_t *>(base) + static_cast<std::int64_t>(token) * act_row_bytes;
   int sum = 0;
@@ -200,7 +206,11 @@ __global__ void __launch_bounds__(256)
 // number of row tiles of the CTA, and the pipeline starts with the first task that lands. The
 // price is a sum over the sixteen warps per row tile, done through shared memory by NT warps
 // (rotating with the tile index) while the others go on with the next tile.
-template <int NT, int SPB, bool HAS_ZP>
+// DOTS: parity instrument, small shapes only. The int32 sum of every table entry (after the zero
+// point has been taken out, before any scale is applied) is also added to p.dots, so that the
+// block dots of THIS kernel - fragment layout, swizzled box, signed-code form and zero-point
+// correction included - can be compared bit for bit with the CPU restatement.
+template <int NT, int SPB, bool HAS_ZP, bool DOTS = false>
 __global__ void __launch_bounds__(kThreads, 1)
     nbits_int8_mma_kernel(const __grid_constant__ CUtensorMap map_b, const ImmaParams p) {
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
@@ -455,6 +465,21 @@ __global__ void __launch_bounds__(kThreads, 1)
                 e2 -= zp_hi[idx] * sum.x;
                 e3 -= zp_hi[idx] * sum.y;
               }
+              if constexpr (DOTS) {
+                // entry -> quantization block; signed codes carry a factor 16
+                const std::int64_t k0 = static_cast<std::int64_t>(s) * kTaskK + warp * 128 + idx * 32 * SPB;
+                const std::int64_t block = k0 / p.w.block_size;
+                const int shift = HAS_ZP ? 0 : 4;
+                const int values[4] = {e0 >> shift, e1 >> shift, e2 >> shift, e3 >> shift};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const std::int64_t row = row0 + g + 8 * (i >> 1);
+                  const std::int64_t token = static_cast<std::int64_t>(blockIdx.y) * p.tp + nt * 8 + 2 * t + (i & 1);
+                  if (row < row_limit && token < p.m_total && block < p.w.n_blocks) {
+                    atomicAdd(p.dots + (token * p.w.n + row) * p.w.n_blocks + block, values[i]);
+                  }
+                }
+              }
               acc[nt][0] = fmaf(sa.x * ws_lo[idx], static_cast<float>(e0), acc[nt][0]);
               acc[nt][1] = fmaf(sa.y * ws_lo[idx], static_cast<float>(e1), acc[nt][1]);
               acc[nt][2] = fmaf(sa.x * ws_hi[idx], static_cast<float>(e2), acc[nt][2]);
@@ -600,7 +625,8 @@ std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m) {
 
 namespace {
 const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
-                           OutputView out, int *status_word, cudaStream_t stream, int sm_count);
+                           OutputView out, int *status_word, cudaStream_t stream, int sm_count,
+                           std::int32_t *dots = nullptr);
 } // namespace
 
 // Quantizes `a` into `scratch` (Int8MmaScratchBytes) and runs the integer-MMA kernel.
@@ -621,11 +647,35 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   return LaunchMultiply(w, geo, m, scratch, out, status_word, stream, sm_count);
 }
 
+// Parity instrument: quantizes `a` like LaunchInt8Mma and runs the instrumented form of the kernel,
+// which also adds its exact int32 block dots to `dots` ([m, n, n_blocks], zeroed here). m <= 8.
+const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
+                                   OutputView out, std::int32_t *dots, int *status_word, cudaStream_t stream,
+                                   int sm_count) {
+  const ImmaGeometry geo = ImmaGeometryOf(w, m);
+  if (!geo.ok || w.meta == nullptr || scratch == nullptr || dots == nullptr || geo.tp != 8) {
+    return nullptr;
+  }
+  if (cudaMemsetAsync(dots, 0, static_cast<size_t>(m) * w.n * w.n_blocks * sizeof(std::int32_t), stream) !=
+      cudaSuccess) {
+    return nullptr;
+  }
+  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
+  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return LaunchMultiply(w, geo, m, scratch, out, status_word, stream, sm_count, dots);
+}
+
 namespace {
 // The integer-MMA kernel over activations that the kernel launched just before has laid out in
 // `scratch` (it is launched with programmatic stream serialization behind that kernel).
 const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
-                           OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+                           OutputView out, int *status_word, cudaStream_t stream, int sm_count, std::int32_t *dots) {
   const MetaGeometry meta = MetaGeometryOf(w);
   ImmaParams p{};
   p.w = w;
@@ -646,6 +696,10 @@ const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::in
   p.table_offset = geo.table_offset;
   p.pass_bytes = geo.pass_bytes;
   p.groups_per_block = w.block_size >= 256 ? w.block_size / 128 : 1;
+  p.dots = dots;
+  if (dots != nullptr && geo.tp != 8) {
+    return nullptr;  // the instrumented form exists for one column tile per pass only
+  }
   const int spb = geo.entry_k / 32;
 
   CUtensorMap map_b;
@@ -662,6 +716,9 @@ const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::in
 #define MNB_IMMA_CASE(NT_, SPB_, ZP_)                                                            \
   if (geo.tp == 8 * NT_ && spb == SPB_ && (w.zp != nullptr) == ZP_) {                            \
     auto kernel = nbits_int8_mma_kernel<NT_, SPB_, ZP_>;                                         \
+    if (dots != nullptr) {                                                                       \
+      kernel = nbits_int8_mma_kernel<1, SPB_, ZP_, true>;                                        \
+    }                                                                                            \
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
                                static_cast<int>(geo.smem));                                      \
     if (err == cudaSuccess) {                                                                    \

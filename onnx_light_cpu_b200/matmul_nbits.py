@@ -157,6 +157,16 @@ class MatMulNBitsWeights:
         m = aq.numel() // self.k
         _capi.check(self._lib.mnb_int8_block_dots_device(self._handle, aq.data_ptr(), m, dots.data_ptr(), raw))
 
+    def int8_mma_block_dots(self, a, y, dots, stream=None) -> None:
+        """accuracy_level-4 product through the instrumented form of the integer-MMA kernel: ``y``
+        [m, N] fp32 as usual, ``dots`` [m, N, n_blocks] int32 = the kernel's exact block sums."""
+        import torch
+
+        raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
+        m = a.numel() // self.k
+        _capi.check(self._lib.mnb_int8_mma_block_dots_device(self._handle, a.data_ptr(), m, y.data_ptr(),
+                                                             dots.data_ptr(), raw))
+
     def close(self) -> None:
         if getattr(self, "_handle", None):
             self._lib.mnb_weights_destroy(self._handle)

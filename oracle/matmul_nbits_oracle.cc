@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <limits>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -245,10 +246,15 @@ int nbits_oracle_quantize_a(const float *a, std::int64_t m, std::int64_t k, int 
       const std::int64_t k0 = block * block_size;
       const std::int64_t k1 = std::min<std::int64_t>(k, k0 + block_size);
       float amax = 0.0f;
+      bool bad = false; // a NaN or an infinity in the block
       for (std::int64_t kk = k0; kk < k1; ++kk) {
-        amax = std::fmax(amax, std::fabs(a[row * k + kk]));
+        const float v = std::fabs(a[row * k + kk]);
+        amax = std::fmax(amax, v);
+        bad = bad || !(v <= std::numeric_limits<float>::max());
       }
-      const float sa = amax / 127.0f;
+      // A block with a non-finite activation has no int8 form: scale NaN, codes 0, so that every
+      // output of the token is NaN (as at accuracy_level 0).
+      const float sa = bad ? std::numeric_limits<float>::quiet_NaN() : amax / 127.0f;
       a_scales[row * n_blocks + block] = sa;
       for (std::int64_t kk = k0; kk < k1; ++kk) {
         int q = 0;

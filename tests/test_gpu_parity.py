@@ -729,3 +729,60 @@ def test_llama_layer_shapes_both_accuracy_levels(cuda_device):
             else:
                 ref = o.matmul_int8(case.a, case.b, case.scales, None, None, n, case.k, 4, 32)
                 assert rel_err(y, ref) <= TOL_FP32
+
+
+# ---- the production integer-MMA kernel's own block dots: bit-exact --------------------------------
+@pytest.mark.parametrize("m,k,n,bs,zp", [
+    (8, 4096, 96, 32, True), (8, 4096, 50, 32, False), (5, 2048, 77, 64, True), (3, 2304, 33, 64, False),
+    (8, 4096, 64, 128, True), (1, 4096, 40, 128, False), (7, 4096, 24, 256, True), (2, 4096, 16, 1024, False),
+    (4, 2000, 21, 128, True),      # K ends inside a block
+])
+def test_int8_mma_kernel_block_dots_bit_exact(cuda_device, m, k, n, bs, zp):
+    """The instrumented instantiation of nbits_int8_mma_kernel stores every block sum before it is
+    scaled: same fragment layout, swizzled tiles, signed-code form (no zero points) and zero-point
+    correction as the production kernel. Bit-exact against the CPU restatement, whose int32 dots
+    are themselves pinned to the reference's IntegerMatMul2D."""
+    import torch
+
+    case = syn.make_case("mma_dots", m, k, n, 4, bs, seed=m + k + n + bs, zero_points=zp, bias=True)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=k, N=n, bits=4, block_size=bs)
+    a = torch.from_numpy(case.a).cuda()
+    y = torch.empty((m, n), device="cuda")
+    dots = torch.full((m, n, case.n_blocks), 12345, dtype=torch.int32, device="cuda")
+    weights.int8_mma_block_dots(a, y, dots)
+    torch.cuda.synchronize()
+    assert weights.poll_status() == 0 and _capi.last_kernel() == "nbits_int8_mma_kernel"
+    aq, _ = o.quantize_a(case.a, k, bs)
+    assert np.array_equal(dots.cpu().numpy(), o.int8_block_dots(aq, case.b, case.zero_points, n, k, 4, bs))
+    # and the instrumented run gives the ordinary result
+    y_plain = torch.empty((m, n), device="cuda")
+    weights.matmul_device(a, y_plain, accuracy_level=4, path=_capi.PATH_INT8_MMA)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), y_plain.cpu().numpy())
+    weights.close()
+
+
+def test_int8_paths_non_finite_activations(cuda_device):
+    """accuracy_level 4: a NaN or an infinity in A gives NaN for every output of that token (scale
+    NaN, codes 0) on both kernels and in the CPU restatement; the other tokens are untouched."""
+    import torch
+
+    case = syn.make_case("lvl4_nan", 4, 4096, 64, 4, 32, seed=21, bias=True)
+    clean = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, 64, 4096, 4, 32)
+    case.a[1, 100] = np.nan
+    case.a[3, 4000] = -np.inf
+    ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, 64, 4096, 4, 32)
+    assert np.isnan(ref[1]).all() and np.isnan(ref[3]).all()
+    assert np.array_equal(ref[0], clean[0]) and np.array_equal(ref[2], clean[2])
+    aq, sa = o.quantize_a(case.a, 4096, 32)
+    assert np.isnan(sa[1, 100 // 32]) and np.isnan(sa[3, 4000 // 32]) and not aq[1, 96:128].any()
+    for path in (_capi.PATH_INT8_MMA, _capi.PATH_INT8):
+        y, _ = run_device(case, accuracy_level=4, path=path)
+        assert np.isnan(y[1]).all() and np.isnan(y[3]).all()
+        assert rel_err(y[0], clean[0]) <= TOL_FP32 and rel_err(y[2], clean[2]) <= TOL_FP32
+    aq_dev = torch.empty((4, 4096), dtype=torch.int8, device="cuda")
+    sa_dev = torch.empty((4, 128), device="cuda")
+    quantize_a(torch.from_numpy(case.a).cuda(), aq_dev, sa_dev, 32)
+    torch.cuda.synchronize()
+    assert np.array_equal(aq_dev.cpu().numpy(), aq)
+    assert np.array_equal(sa_dev.cpu().numpy(), sa, equal_nan=True)
