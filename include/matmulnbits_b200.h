@@ -184,7 +184,10 @@ int mnb_int8_mma_block_dots_device(mnb_weights *weights, const float *a_dev, int
  * the process exits).
  *   - limits: 1 <= m <= MNB_STATIC_MAX_TOKENS and ceil(K/block_size)*block_size <=
  *     MNB_STATIC_MAX_PADDED_K; anything larger is refused with MNB_ERR_INVALID_ARGUMENT;
- *   - a_dev [m, K] and y_dev [m, N] are device pointers, the work is queued on `stream`;
+ *   - a_dev [m, K] and y_dev [m, N] are device pointers of the GPU that holds the weights (plain
+ *     host memory or another GPU's memory is refused with MNB_ERR_INVALID_ARGUMENT, as by the
+ *     other device-pointer entry points); the work is queued on `stream`, the quantization and
+ *     the product of a call as a pair, also against calls from other host threads;
  *   - the first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress with that device current); make that first call outside any
  *     stream capture;

@@ -59,6 +59,7 @@ def _host_lib() -> ctypes.CDLL:
     lib.olc_session_last_device_kernel.argtypes = [c.c_void_p]
     lib.olc_session_last_device_kernel.restype = c.c_char_p
     lib.olc_session_destroy.argtypes = [c.c_void_p]
+    lib.olc_session_overwrite_b.argtypes = [c.c_void_p, c.c_void_p, c.c_int64]
     _host = lib
     return lib
 

@@ -465,6 +465,38 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
   return MNB_OK;
 }
 
+// Device memory of another GPU would be read through an address this GPU cannot reach, and
+// plain host memory through no address at all (a fault, not an error code): checks where A and Y
+// live, once per pointer pair of the handle. Allocates nothing. The caller holds h->mutex.
+int CheckDeviceOperands(mnb_weights *h, const void *a_dev, const void *y_dev) {
+  if (a_dev == h->checked_a && y_dev == h->checked_y) {
+    return MNB_OK;
+  }
+  for (const void *ptr : {a_dev, y_dev}) {
+    cudaPointerAttributes attributes{};
+    const cudaError_t query = cudaPointerGetAttributes(&attributes, ptr);
+    if (query != cudaSuccess) {
+      cudaGetLastError();
+      continue; // not known to the runtime: leave the decision to the launch
+    }
+    if (attributes.type == cudaMemoryTypeDevice && attributes.device != h->device) {
+      char text[160];
+      std::snprintf(text, sizeof(text),
+                    "MatMulNBits: A and Y must be memory of GPU %d, where the weights are (got memory of GPU %d).",
+                    h->device, attributes.device);
+      return Fail(MNB_ERR_INVALID_ARGUMENT, text);
+    }
+    if (attributes.type == cudaMemoryTypeUnregistered) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT,
+                  "MatMulNBits: the device-pointer entry points take device memory; use mnb_matmul_host for "
+                  "host buffers.");
+    }
+  }
+  h->checked_a = a_dev;
+  h->checked_y = y_dev;
+  return MNB_OK;
+}
+
 } // namespace
 
 extern "C" {
@@ -640,31 +672,11 @@ int mnb_matmul_device_strided(mnb_weights *h, const float *a_dev, int64_t m, int
   if (err != cudaSuccess) {
     return FailCuda("cudaSetDevice", err);
   }
-  // Device memory of another GPU would be read through an address this GPU cannot reach (a
-  // fault, not an error code): check where A and Y live, once per pointer pair.
-  if (m > 0 && (a_dev != h->checked_a || y_dev != h->checked_y)) {
-    for (const void *ptr : {static_cast<const void *>(a_dev), static_cast<const void *>(y_dev)}) {
-      cudaPointerAttributes attributes{};
-      const cudaError_t query = cudaPointerGetAttributes(&attributes, ptr);
-      if (query != cudaSuccess) {
-        cudaGetLastError();
-        continue; // not known to the runtime: leave the decision to the launch
-      }
-      if (attributes.type == cudaMemoryTypeDevice && attributes.device != h->device) {
-        char text[160];
-        std::snprintf(text, sizeof(text),
-                      "MatMulNBits: A and Y must be memory of GPU %d, where the weights are (got memory of GPU %d).",
-                      h->device, attributes.device);
-        return Fail(MNB_ERR_INVALID_ARGUMENT, text);
-      }
-      if (attributes.type == cudaMemoryTypeUnregistered) {
-        return Fail(MNB_ERR_INVALID_ARGUMENT,
-                    "MatMulNBits: the device-pointer entry points take device memory; use mnb_matmul_host for "
-                    "host buffers.");
-      }
+  if (m > 0) {
+    const int rc = CheckDeviceOperands(h, a_dev, y_dev);
+    if (rc != MNB_OK) {
+      return rc;
     }
-    h->checked_a = a_dev;
-    h->checked_y = y_dev;
   }
   OutputView out{y_dev, ld_y, col_offset};
   return Dispatch(h, a_dev, m, accuracy_level, path, out, static_cast<cudaStream_t>(stream));
@@ -1083,6 +1095,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticAqBytes +
 
 namespace {
 std::mutex g_static_mutex;
+std::mutex g_static_launch_mutex;
 unsigned char *g_static_address[kStaticMaxDevices] = {};
 
 // In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
@@ -1095,8 +1108,11 @@ int StaticScratchFor(int device, unsigned char **out) {
   if (g_static_address[device] == nullptr) {
     unsigned char *ptr = nullptr;
     const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
-    if (err != cudaSuccess || ptr == nullptr) {
+    if (err != cudaSuccess) {
       return FailCuda("cudaGetSymbolAddress(static scratch)", err);
+    }
+    if (ptr == nullptr) {
+      return Fail(MNB_ERR_CUDA, "matmulnbits_b200: cudaGetSymbolAddress(static scratch) gave a null address.");
     }
     g_static_address[device] = ptr;
   }
@@ -1125,8 +1141,12 @@ int mnb_matmul_int8_static(mnb_weights *h, const float *a_dev, int64_t m, float 
   if (err != cudaSuccess) {
     return FailCuda("cudaSetDevice", err);
   }
+  int rc = CheckDeviceOperands(h, a_dev, y_dev);
+  if (rc != MNB_OK) {
+    return rc;
+  }
   unsigned char *scratch = nullptr;
-  const int rc = StaticScratchFor(h->device, &scratch);
+  rc = StaticScratchFor(h->device, &scratch);
   if (rc != MNB_OK) {
     return rc;
   }
@@ -1135,6 +1155,9 @@ int mnb_matmul_int8_static(mnb_weights *h, const float *a_dev, int64_t m, float 
   std::int8_t *aq = reinterpret_cast<std::int8_t *>(scratch);
   float *a_scales = reinterpret_cast<float *>(scratch + kStaticAqBytes);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The two launches of a call are queued as a pair: another host thread (another handle, the
+  // same stream) must not get its quantization between this call's quantization and product.
+  std::lock_guard<std::mutex> pair_guard(g_static_launch_mutex);
   const char *name = mnb::LaunchQuantizeAPadded(a_dev, m, w.k, w.block_size, aq, a_scales, s);
   if (name != nullptr) {
     OutputView out{y_dev, w.n, 0};

@@ -9,6 +9,8 @@
 #include "onnx_core/symbolic/sym_tensor.h"
 
 #include <atomic>
+#include <cstdint>
+#include <cstring>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -50,7 +52,50 @@ void Check(int status) {
 
 } // namespace
 
-// The uploaded constants of the node, rebuilt only when the initializer tensors change.
+namespace {
+
+// Fingerprint of a constant operand: its size and 64-bit words sampled at up to 512 evenly spaced
+// places (always the first and the last), FNV-1a. A microsecond per Run; it tells a buffer that
+// was rewritten in place, or freed and reallocated at the same address with other contents, from
+// the one that was uploaded. (A rewrite that leaves every sampled word as it was goes unnoticed:
+// the constant operands of this operator are initializers, which a runtime does not modify.)
+std::uint64_t Fingerprint(const std::uint8_t *data, std::size_t bytes) {
+  std::uint64_t h = 1469598103934665603ull ^ bytes;
+  if (data == nullptr || bytes == 0) {
+    return h;
+  }
+  auto mix = [&h](std::uint64_t v) {
+    h ^= v;
+    h *= 1099511628211ull;
+  };
+  const std::size_t words = bytes / 8;
+  if (words == 0) {
+    for (std::size_t i = 0; i < bytes; ++i) {
+      mix(data[i]);
+    }
+    return h;
+  }
+  const std::size_t samples = words < 512 ? words : 512;
+  for (std::size_t i = 0; i < samples; ++i) {
+    const std::size_t at = samples > 1 ? i * (words - 1) / (samples - 1) : 0;
+    std::uint64_t v;
+    std::memcpy(&v, data + at * 8, 8);
+    mix(v);
+  }
+  for (std::size_t i = words * 8; i < bytes; ++i) {
+    mix(data[i]);
+  }
+  return h;
+}
+
+std::uint64_t FingerprintOf(const Tensor *t) {
+  return t != nullptr ? Fingerprint(reinterpret_cast<const std::uint8_t *>(t->bytes()), t->size_bytes()) : 0;
+}
+
+} // namespace
+
+// The uploaded constants of the node, rebuilt when the initializer tensors change: another
+// address, other attributes, or another fingerprint of their contents.
 struct MatMulNBitsKernel::DeviceWeights {
   std::mutex mutex;
   mnb_weights *handle = nullptr;
@@ -59,6 +104,7 @@ struct MatMulNBitsKernel::DeviceWeights {
   const void *key_zp = nullptr;
   const void *key_bias = nullptr;
   MatMulNBitsAttributes key_attrs;
+  std::uint64_t stamp[4] = {0, 0, 0, 0};
   const char *last_kernel = "";
 
   ~DeviceWeights() { mnb_weights_destroy(handle); }
@@ -68,7 +114,9 @@ struct MatMulNBitsKernel::DeviceWeights {
     return handle != nullptr && key_b == b.bytes() && key_scales == scales.bytes() &&
            key_zp == (zp != nullptr ? zp->bytes() : nullptr) &&
            key_bias == (bias != nullptr ? bias->bytes() : nullptr) && key_attrs.k == a.k &&
-           key_attrs.n == a.n && key_attrs.bits == a.bits && key_attrs.block_size == a.block_size;
+           key_attrs.n == a.n && key_attrs.bits == a.bits && key_attrs.block_size == a.block_size &&
+           stamp[0] == FingerprintOf(&b) && stamp[1] == FingerprintOf(&scales) && stamp[2] == FingerprintOf(zp) &&
+           stamp[3] == FingerprintOf(bias);
   }
 };
 
@@ -158,6 +206,10 @@ Tensor MatMulNBitsKernel::operator()(const Tensor &a, const Tensor &b, const Ten
     cache.key_zp = zero_points != nullptr ? zero_points->bytes() : nullptr;
     cache.key_bias = bias != nullptr ? bias->bytes() : nullptr;
     cache.key_attrs = attrs;
+    cache.stamp[0] = FingerprintOf(&b);
+    cache.stamp[1] = FingerprintOf(&scales);
+    cache.stamp[2] = FingerprintOf(zero_points);
+    cache.stamp[3] = FingerprintOf(bias);
   }
   Check(mnb_matmul_host(cache.handle, a.AsFloat(), m, static_cast<int>(attrs.accuracy_level),
                         MNB_PATH_AUTO, y.AsFloat()));

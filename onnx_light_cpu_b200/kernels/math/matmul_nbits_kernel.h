@@ -55,7 +55,10 @@ public:
 
 private:
   struct DeviceWeights;
-  std::unique_ptr<DeviceWeights> weights_; // per-node cache of the uploaded constants
+  // Per-node cache of the uploaded constants (constant-weight policy: B, scales, zero_points and
+  // bias are initializers). Keyed on their addresses, the attributes and a fingerprint of sampled
+  // contents, so a buffer rewritten in place or recycled at the same address is uploaded again.
+  std::unique_ptr<DeviceWeights> weights_;
 };
 
 /// CUDA device used by kernels constructed after the call (default 0).

@@ -54,6 +54,14 @@ class MatMulNBitsSession:
             _register._raise_last(code)
         return y
 
+    def overwrite_b(self, b) -> None:
+        """Rewrites the session's initializer ``B`` in place (same buffer): the next :meth:`run`
+        must notice and upload the new weights."""
+        b = np.ascontiguousarray(b, dtype=np.uint8)
+        code = self._lib.olc_session_overwrite_b(self._handle, _ptr(b), b.size)
+        if code != 0:
+            _register._raise_last(code)
+
     @property
     def last_device_kernel(self) -> str:
         return self._lib.olc_session_last_device_kernel(self._handle).decode()
@@ -68,6 +76,21 @@ class MatMulNBitsSession:
             self.close()
         except Exception:
             pass
+
+
+def _check_device_tensor(what, tensor, dtype_name, device, min_elements=0):
+    """The C ABI takes raw addresses: a tensor of the wrong dtype, on the host, on another GPU, not
+    contiguous or too small would become an out-of-bounds device access, so it is refused here."""
+    if not getattr(tensor, "is_cuda", False):
+        raise ValueError(f"{what} must be a CUDA tensor")
+    if str(tensor.dtype) != "torch." + dtype_name:
+        raise ValueError(f"{what} must have dtype {dtype_name}, got {tensor.dtype}")
+    if not tensor.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    if (tensor.device.index or 0) != device:
+        raise ValueError(f"{what} is on GPU {tensor.device.index}, the weights are on GPU {device}")
+    if tensor.numel() < min_elements:
+        raise ValueError(f"{what} holds {tensor.numel()} elements, {min_elements} are needed")
 
 
 class MatMulNBitsWeights:
@@ -123,7 +146,11 @@ class MatMulNBitsWeights:
         ``torch.cuda.Stream``; default: the current stream)."""
         import torch
 
-        m = a.numel() // self.k
+        m = self._rows_of(a)
+        ld = self.n if ld_y is None else int(ld_y)
+        if col_offset < 0 or col_offset + self.n > ld:
+            raise ValueError("the output window [col_offset, col_offset + N) does not fit a row of ld_y elements")
+        _check_device_tensor("y", y, "float32", self.device, (m - 1) * ld + col_offset + self.n if m > 0 else 0)
         raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
         _capi.check(self._lib.mnb_matmul_device_strided(
             self._handle, a.data_ptr(), m, accuracy_level, path, y.data_ptr(),
@@ -135,9 +162,16 @@ class MatMulNBitsWeights:
         ``a`` [m, K] and ``y`` [m, N] are torch CUDA fp32 tensors."""
         import torch
 
-        m = a.numel() // self.k
+        m = self._rows_of(a)
+        _check_device_tensor("y", y, "float32", self.device, m * self.n)
         raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
         _capi.check(self._lib.mnb_matmul_int8_static(self._handle, a.data_ptr(), m, y.data_ptr(), raw))
+
+    def _rows_of(self, a) -> int:
+        _check_device_tensor("a", a, "float32", self.device)
+        if a.numel() % self.k != 0:
+            raise ValueError(f"a holds {a.numel()} elements, not a multiple of K = {self.k}")
+        return a.numel() // self.k
 
     def poll_status(self) -> int:
         status = ctypes.c_int(0)
@@ -147,14 +181,20 @@ class MatMulNBitsWeights:
     def dequant_int(self, out, stream=None) -> None:
         import torch
 
+        _check_device_tensor("out", out, "int32", self.device, self.n * self.k)
         raw = (stream or torch.cuda.current_stream(out.device)).cuda_stream
         _capi.check(self._lib.mnb_dequant_int_device(self._handle, out.data_ptr(), raw))
 
     def int8_block_dots(self, aq, dots, stream=None) -> None:
         import torch
 
+        _check_device_tensor("aq", aq, "int8", self.device)
+        if aq.numel() % self.k != 0:
+            raise ValueError(f"aq holds {aq.numel()} elements, not a multiple of K = {self.k}")
         raw = (stream or torch.cuda.current_stream(aq.device)).cuda_stream
         m = aq.numel() // self.k
+        n_blocks = -(-self.k // self.block_size)
+        _check_device_tensor("dots", dots, "int32", self.device, m * self.n * n_blocks)
         _capi.check(self._lib.mnb_int8_block_dots_device(self._handle, aq.data_ptr(), m, dots.data_ptr(), raw))
 
     def int8_mma_block_dots(self, a, y, dots, stream=None) -> None:
@@ -162,8 +202,11 @@ class MatMulNBitsWeights:
         [m, N] fp32 as usual, ``dots`` [m, N, n_blocks] int32 = the kernel's exact block sums."""
         import torch
 
+        m = self._rows_of(a)
+        n_blocks = -(-self.k // self.block_size)
+        _check_device_tensor("y", y, "float32", self.device, m * self.n)
+        _check_device_tensor("dots", dots, "int32", self.device, m * self.n * n_blocks)
         raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
-        m = a.numel() // self.k
         _capi.check(self._lib.mnb_int8_mma_block_dots_device(self._handle, a.data_ptr(), m, y.data_ptr(),
                                                              dots.data_ptr(), raw))
 

@@ -246,6 +246,26 @@ int olc_session_run(void *handle, const float *a, const std::int64_t *shape, int
   });
 }
 
+// Test hook: overwrites the bytes of the session's initializer B in place (same buffer, same
+// address), as a runtime that recycles an initializer's storage would.
+int olc_session_overwrite_b(void *handle, const std::uint8_t *b, std::int64_t b_bytes) {
+  return Guard([&] {
+    auto *session = static_cast<Session *>(handle);
+    if (session == nullptr) {
+      throw std::invalid_argument("null session");
+    }
+    auto it = session->rt.tensors().find("B");
+    if (it == session->rt.tensors().end()) {
+      throw std::invalid_argument("olc_session_overwrite_b: the session has no B");
+    }
+    rt_ns::Tensor &tensor = it->second;
+    if (static_cast<std::int64_t>(tensor.size_bytes()) != b_bytes) {
+      throw std::invalid_argument("olc_session_overwrite_b: size mismatch");
+    }
+    std::memcpy(tensor.mutable_bytes(), b, static_cast<std::size_t>(b_bytes));
+  });
+}
+
 const char *olc_session_last_device_kernel(void *handle) {
   auto *session = static_cast<Session *>(handle);
   auto *kernel = session != nullptr ? dynamic_cast<onnx_light_cuda::MatMulNBitsKernel *>(session->kernel.get())

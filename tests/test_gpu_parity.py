@@ -786,3 +786,20 @@ def test_int8_paths_non_finite_activations(cuda_device):
     torch.cuda.synchronize()
     assert np.array_equal(aq_dev.cpu().numpy(), aq)
     assert np.array_equal(sa_dev.cpu().numpy(), sa, equal_nan=True)
+
+
+def test_registered_operator_notices_rewritten_weights(cuda_device):
+    """The per-node cache of uploaded constants is keyed on a fingerprint of their contents too: an
+    initializer rewritten in place (same address, other bytes) is uploaded again."""
+    pkg.register_kernels()
+    case = syn.make_case("cache", 2, 1024, 96, 4, 32, seed=5, bias=True)
+    session = pkg.MatMulNBitsSession(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n, bits=4,
+                                     block_size=32)
+    y1 = session.run(case.a)
+    assert rel_err(y1, oracle_f64(case)) <= TOL_FP32
+    other = syn.make_case("cache", 2, 1024, 96, 4, 32, seed=6, bias=True)
+    session.overwrite_b(other.b)
+    y2 = session.run(case.a)
+    ref2 = o.matmul_f64(case.a, other.b, case.scales, case.zero_points, case.bias, case.n, case.k, 4, 32)
+    assert rel_err(y2, ref2) <= TOL_FP32 and rel_err(y2, y1) > 1e-2
+    assert np.array_equal(session.run(case.a), y2)   # unchanged weights: the cached upload is used

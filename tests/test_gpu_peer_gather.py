@@ -104,3 +104,43 @@ def test_device_entry_point_refuses_memory_of_another_gpu():
         weights.matmul_device(a, y)
     assert info.value.status == _capi.MNB_ERR_INVALID_ARGUMENT
     weights.close()
+
+
+def test_gather_wait_gives_up_and_reports(cuda_device):
+    """Failure detection without a fault: a gathered step whose second "rank" never raises its flag
+    (both ranks' buffers are plain local memory here, nobody plays rank 1). The bounded wait of the
+    flag exchange runs out after about a second, the kernel returns, the status word reads 5
+    (peer flag) once and 0 afterwards, and the context is usable: an ordinary product is correct."""
+    import ctypes
+
+    import torch
+
+    import onnx_light_cpu_b200 as pkg
+    from onnx_light_cpu_b200 import _capi
+    from onnx_light_cpu_b200.tools import synthetic as syn
+    from oracle import nbits_oracle as o
+
+    case = syn.make_case("gather_timeout", 1, 4096, 256, 4, 128, seed=31, bias=True)
+    weights = pkg.MatMulNBitsWeights(case.b, case.scales, case.zero_points, case.bias, K=case.k, N=case.n, bits=4,
+                                     block_size=128)
+    a = torch.from_numpy(case.a).cuda()
+    results = [torch.zeros((1, case.n), device="cuda") for _ in range(2)]
+    flags = [torch.zeros(_capi.MAX_GATHER_RANKS + 1, dtype=torch.int32, device="cuda") for _ in range(2)]
+    y_ranks = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in results])
+    flag_ranks = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in flags])
+    raw = torch.cuda.current_stream().cuda_stream
+    _capi.check(_capi.load().mnb_matmul_device_gather(weights._handle, a.data_ptr(), 1, y_ranks, flag_ranks, 2, 0,
+                                                      case.n, 0, 1, raw))
+    assert weights.poll_status() == 5       # kDeviceTimeoutPeerFlag; the poll waits for the device
+    assert weights.poll_status() == 0       # read once, then cleared
+    ref = o.matmul_f64(case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, 4, 128)
+    for got in results:                     # the columns were stored into both buffers before the wait
+        err = float(np.abs(got.cpu().numpy() - ref).max() / np.abs(ref).max())
+        assert err <= TOL_FP32
+    assert int(flags[1][0].item()) == 1     # this rank's flag was raised on the "peer"
+    y = torch.zeros((1, case.n), device="cuda")
+    weights.matmul_device(a, y)
+    torch.cuda.synchronize()
+    assert weights.poll_status() == 0
+    assert float(np.abs(y.cpu().numpy() - ref).max() / np.abs(ref).max()) <= TOL_FP32
+    weights.close()

@@ -133,3 +133,25 @@ def test_path_and_status_constants_match_the_header():
     for name, value in re.findall(r"\b(MNB_(?:OK|ERR_[A-Z_]+))\s*=\s*(-?\d+)", header):
         if hasattr(_capi, name):
             assert getattr(_capi, name) == int(value), name
+
+
+def test_device_tensor_checks_reject_bad_arguments():
+    """The Python layer refuses tensors that would turn into out-of-bounds device accesses behind
+    the C ABI (wrong dtype, host memory, too small, strided, wrong GPU). Needs no GPU: the checks
+    look at tensor metadata only."""
+    import types
+
+    import pytest
+    import torch
+
+    from onnx_light_cpu_b200.matmul_nbits import _check_device_tensor
+
+    def fake(dtype=torch.float32, cuda=True, contiguous=True, index=0, numel=16):
+        return types.SimpleNamespace(is_cuda=cuda, dtype=dtype, is_contiguous=lambda: contiguous,
+                                     device=types.SimpleNamespace(index=index), numel=lambda: numel)
+
+    _check_device_tensor("a", fake(), "float32", 0, 16)
+    for bad, match in ((fake(cuda=False), "CUDA tensor"), (fake(dtype=torch.float16), "dtype float32"),
+                       (fake(contiguous=False), "contiguous"), (fake(index=1), "GPU 1"), (fake(numel=8), "are needed")):
+        with pytest.raises(ValueError, match=match):
+            _check_device_tensor("a", bad, "float32", 0, 16)
