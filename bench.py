@@ -12,8 +12,11 @@ N = 1   workload = the decode configuration the metric is quoted on: M=1, K=4096
         weight copies (252 MB, twice the 126 MB L2, so every launch streams from HBM),
         captured as one CUDA graph.
 N > 1   workload = the large-N output projection (K=4096, N=128256, bits=4, block 32, M=1),
-        weight columns sharded across ranks, output columns all-gathered over NCCL; strong
-        scaling (the total problem is fixed). A step is one pass over R=2 weight copies.
+        weight columns sharded across ranks, every rank's columns stored into every rank's gathered
+        result by the kernel itself (peer-mapped memory; `--gather nccl`: an all-gather behind the
+        kernel); strong scaling (the total problem is fixed). A step is one pass over R=2 weight
+        copies. Before timing, one gathered step is compared with the ranks' own products. The line
+        carries `scaling_base`: the same node unsharded on one GPU, timed by rank 0 in the same run.
 
 `value` times device-resident inputs; `e2e` goes through the host-buffer C ABI call (pinned
 host A in, pinned host Y out, copies inside the timed region). `--impl reference` times the CPU
@@ -42,12 +45,24 @@ PREFILL = dict(m=2048, k=4096, n=4096, bits=4, block_size=64)
 LMHEAD = dict(k=4096, n=128256, bits=4, block_size=32)
 L2_BYTES = 126 * 1024 * 1024
 
-# DRAM bytes per launch of the decode kernels on the decode workload, from the ncu captures
-# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the decode kernels on the
+# decode workload, each from one ncu capture of that kernel on this workload. A constant, not a
+# measurement of the run: reported as `traffic`, with `traffic_source` saying so.
 NCU_DECODE_TRAFFIC_BYTES = {
-    "nbits_gemv_imma_kernel": 31_796_480,  # profiles/decode_imma_cfg2.md
-    "nbits_gemv_mma_kernel": 32_258_304,   # profiles/decode_mma_cfg2.md
+    "nbits_decode_resident_kernel": None,
+    "nbits_decode_direct_kernel": 31_538_688,
+    "nbits_gemv_imma_kernel": 31_796_480,
+    "nbits_gemv_mma_kernel": 32_258_304,
 }
+WORKLOAD_DECODE = "cfg2 decode M=1 K=4096 N=14336 bits=4 block=128 zp+bias"
+WORKLOAD_LMHEAD = "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column shards gathered"
+
+
+def workload_config(multi: bool, copies: int, bytes_per_launch: int) -> dict:
+    """The `config` object, identical in both arms of a run."""
+    return {"workload": WORKLOAD_LMHEAD if multi else WORKLOAD_DECODE, "weight_copies": copies,
+            "bytes_per_launch": int(bytes_per_launch),
+            "l2_defeat": f"{copies} weight copies = {copies * bytes_per_launch / 1e6:.0f} MB > 126 MB L2"}
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -117,6 +132,13 @@ class ClockSampler:
         return out
 
 
+def cpu_threading(o) -> str:
+    """Turns on the reference's own threading for the CPU legs where oracle/_ref carries it."""
+    if o.use_reference_execute_ranges(True):
+        return "reference ExecuteRanges + persistent std::thread executor (ExecutionExecutorScope)"
+    return "checker's own persistent worker pool (oracle/_ref absent)"
+
+
 def cpu_port_baseline(seconds: float = 3.0) -> dict:
     """Times the CPU restatement (oracle port) on this host: M=1 decode workload, all threads."""
     from onnx_light_cpu_b200.tools import synthetic as syn
@@ -124,8 +146,10 @@ def cpu_port_baseline(seconds: float = 3.0) -> dict:
 
     case = syn.config2(1)
     threads = o.hardware_threads()
+    threading_kind = cpu_threading(o)
     args = (case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits, case.block_size)
-    o.matmul_f32_fast(*args, threads=threads)
+    for _ in range(3):   # the first call starts the worker threads
+        o.matmul_f32_fast(*args, threads=threads)
     calls, start = 0, time.perf_counter()
     samples = []
     while time.perf_counter() - start < seconds or calls < 7:
@@ -133,37 +157,36 @@ def cpu_port_baseline(seconds: float = 3.0) -> dict:
         o.matmul_f32_fast(*args, threads=threads)
         samples.append(time.perf_counter() - t0)
         calls += 1
-    from onnx_light_cpu_b200 import _capi
-
-    nbytes = _capi.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size, True, True)
+    nbytes = syn.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size, True, True)
     median = statistics.median(samples)
     return {"value": nbytes / median / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "threading": threading_kind,
             "sample": f"{calls} calls of the full M=1 K=4096 N=14336 workload, median of per-call times",
             "ms_per_call": median * 1e3}
 
 
 def run_reference(args, rank: int) -> None:
     """The reference arm: the CPU implementation of this path on the host cores. The reference
-    project has no MatMulNBits kernel, so this is the CPU restatement (kind "port")."""
+    project has no MatMulNBits kernel, so this is the CPU restatement (kind "port"), its column
+    panels dispatched through the reference's ExecuteRanges. Loads nothing of the CUDA product."""
     if rank != 0:
         return
-    from onnx_light_cpu_b200 import _capi
     from onnx_light_cpu_b200.tools import synthetic as syn
     from oracle import nbits_oracle as o
 
     o.build(reference=False)
     multi = args.gpus > 1
     copies = 2 if multi else 8
-    case = syn.config5(1, 4, n=LMHEAD["n"] // 8) if multi else syn.config2(1)
+    case = syn.config5(1, 4) if multi else syn.config2(1)   # the full workload in both cases
     threads = o.hardware_threads()
+    threading_kind = cpu_threading(o)
     call_args = (case.a, case.b, case.scales, case.zero_points, case.bias, case.n, case.k, case.bits,
                  case.block_size)
-    per_call_bytes = _capi.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size,
-                                             case.zero_points is not None, case.bias is not None)
-    scale = (LMHEAD["n"] / case.n) if multi else 1.0   # the lm-head sample is 1/8 of the columns
-    # bound the run: a step is `copies` calls on the sample
-    steps = max(1, min(args.steps, 50))
-    warmup = max(1, min(args.warmup, 5))
+    per_call_bytes = syn.algorithmic_bytes(1, case.n, case.k, case.bits, case.block_size,
+                                           case.zero_points is not None, case.bias is not None)
+    # bound the run: a step is `copies` calls
+    steps = max(1, min(args.steps, 10 if multi else 50))
+    warmup = max(1, min(args.warmup, 3 if multi else 5))
     for _ in range(warmup):
         o.matmul_f32_fast(*call_args, threads=threads)
     start = time.perf_counter()
@@ -171,16 +194,14 @@ def run_reference(args, rank: int) -> None:
         o.matmul_f32_fast(*call_args, threads=threads)
     elapsed = time.perf_counter() - start
     value = per_call_bytes * steps * copies / elapsed / 1e9
-    workload = ("cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32" if multi
-                else "cfg2 decode M=1 K=4096 N=14336 bits=4 block=128 zp+bias")
-    sample = (f"{steps} steps x {copies} calls on a 1/8 column sample (N={case.n}); per-call bytes counted for "
-              "the sample" if multi else f"{steps} steps x {copies} calls of the full workload")
+    sample = f"{steps} steps x {copies} calls of the full workload (same weights each call)"
     line = {
         "impl": "reference", "metric": "MatMulNBits 4-bit M=1 HBM GB/s", "value": value, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": elapsed / steps * 1e3 * scale,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": elapsed / steps * 1e3,
         "higher_is_better": True, "scaling": "strong" if multi else "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": workload, "weight_copies": copies},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "data": "synthetic", "config": workload_config(multi, copies, per_call_bytes),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "threading": threading_kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference ships no MatMulNBits kernel; this is the CPU restatement used as the oracle",
     }
@@ -329,12 +350,11 @@ def main() -> None:
         gpu_launches = args.steps * copies if graphed else _capi.launch_count() - launches_before
         value = per_launch_bytes * copies * args.steps / seconds / 1e9
         launch_us = seconds / (args.steps * copies) * 1e6
-        workload = "cfg2 decode M=1 K=4096 N=14336 bits=4 block=128 zp+bias"
-        config = {"workload": workload, "weight_copies": copies, "bytes_per_launch": per_launch_bytes,
-                  "l2_defeat": f"{copies} weight copies = {copies * per_launch_bytes / 1e6:.0f} MB > 126 MB L2",
-                  "cuda_graph": graphed, "kernel": kernel_name}
+        config = workload_config(False, copies, per_launch_bytes)
+        details = {"cuda_graph": graphed, "kernel": kernel_name}
         roofline = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": value / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES.get(kernel_name),
+                    "traffic_source": "constant from one ncu capture of this kernel on this workload, not this run",
                     "peak_kind": f"of {peak_kind} (copy bandwidth)", "kernel": kernel_name,
                     "us_per_launch": launch_us, "algorithmic_bytes_per_launch": per_launch_bytes}
         scaling = "weak"
@@ -507,6 +527,24 @@ def main() -> None:
         step()
         torch.cuda.synchronize()
         kernel_name = _capi.last_kernel()
+        # ---- before any timing: the gathered result of one step against every rank's own product ----
+        # Rank r's columns must sit in slot [r, :, :] of the gathered result on EVERY rank. Each rank
+        # computes its shard once more into plain local memory, the shards travel over an all-gather,
+        # and every rank compares its gathered buffers with them, value by value.
+        own = torch.empty(m, shard_cfg["n"], device="cuda")
+        mismatch = 0
+        for i, w in enumerate(weights):
+            w.matmul_device(a, own)
+            expected = torch.empty(world, m, shard_cfg["n"], device="cuda")
+            dist.all_gather_into_tensor(expected, own)
+            torch.cuda.synchronize()
+            if not torch.equal(expected, y_full[i][:, :m, :]):
+                mismatch += 1
+        bad = torch.tensor([mismatch], device="cuda")
+        dist.all_reduce(bad, op=dist.ReduceOp.SUM)
+        if int(bad.item()) != 0:
+            raise SystemExit(f"bench: gathered result differs from the ranks' own products ({int(bad.item())} buffers)")
+        gather_checked = True
         # The peer-store step is kernels only and replays from a CUDA graph. With NCCL the pair is
         # launched per step: capturing kernel + all-gather did not complete on this stack.
         if gather is not None and not args.no_graph:
@@ -525,11 +563,9 @@ def main() -> None:
         gpu_launches = launches_timed * world
         value = full_bytes * copies * args.steps / seconds / 1e9
         how = "peer-store gather inside the kernel" if gather is not None else "NCCL all-gather"
-        workload = f"cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, column-sharded + {how}"
-        config = {"workload": workload, "weight_copies": copies, "shard_columns": shard_cfg["n"],
-                  "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name, "cuda_graph": graphed,
-                  "gather": args.gather,
-                  "l2_defeat": f"{copies} weight copies per rank"}
+        config = workload_config(True, copies, full_bytes)
+        details = {"shard_columns": shard_cfg["n"], "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name,
+                   "cuda_graph": graphed, "gather": args.gather, "gather_how": how, "gather_checked": gather_checked}
         shard_bytes = weights[0].algorithmic_bytes(m)
         roofline = {"bound": "hbm", "achieved": value / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": value / world / peaks["hbm_gbs"], "traffic": None,
@@ -562,13 +598,67 @@ def main() -> None:
         e2e = {"value": full_bytes * copies * host_steps / host_seconds / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": copies * a_host.numel() * 4, "d2h_bytes_per_step": copies * y_host.numel() * 4}
 
+        if not args.skip_extras:
+            # ---- M = 8 through the same gathered path (cfg5 lists M in {1, 8, 256}) ----
+            if gather is not None:
+                gather8 = sharded.PeerGather(dist, local_rank, m_max=8, n_shard=shard_cfg["n"], slots=copies)
+                a8 = torch.randn(8, cfg["k"], device="cuda")
+                dist.broadcast(a8, src=0)
+
+                def step8():
+                    for i, w in enumerate(weights):
+                        gather8.run(w, a8, i)
+
+                step8()
+                torch.cuda.synchronize()
+                name8 = _capi.last_kernel()
+                rep8, graphed8 = capture_graph(torch, step8)
+                ok8 = torch.tensor([1 if graphed8 else 0], device="cuda")
+                dist.all_reduce(ok8, op=dist.ReduceOp.MIN)
+                if int(ok8.item()) == 1:
+                    steps8 = max(5, args.steps // 4)
+                    sec8 = time_steps(torch, dist, rep8, steps8, 3, world)
+                    bytes8 = _capi.algorithmic_bytes(8, cfg["n"], cfg["k"], cfg["bits"], cfg["block_size"], True, False)
+                    extras["lmhead_m8"] = {"gbs": bytes8 * copies * steps8 / sec8 / 1e9,
+                                           "us_per_node": sec8 / (copies * steps8) * 1e6, "kernel": name8,
+                                           "workload": "cfg5 lm-head M=8, same shards and gather"}
+                torch.cuda.synchronize()
+                dist.barrier()
+                gather8.close()
+            # ---- like-for-like base of the scaling curve: the same node, unsharded, on one GPU ----
+            # Timed by rank 0 alone in this very run (337 MB of operands fit); the other ranks wait.
+            del weights
+            torch.cuda.empty_cache()
+            dist.barrier()
+            if rank == 0:
+                base_w = device_weights(torch, pkg, cfg, copies, seed=1499, zp=True, bias=False)
+                base_y = [torch.empty(m, cfg["n"], device="cuda") for _ in range(copies)]
+
+                def base_step():
+                    for w, y in zip(base_w, base_y):
+                        w.matmul_device(a, y)
+
+                base_step()
+                torch.cuda.synchronize()
+                base_name = _capi.last_kernel()
+                base_rep, _ = capture_graph(torch, base_step)
+                base_steps = max(5, args.steps // 4)
+                base_sec = time_steps(torch, dist, base_rep, base_steps, 3, 1)
+                extras["scaling_base"] = {
+                    "workload": "cfg5 lm-head M=1 K=4096 N=128256 bits=4 block=32 zp, unsharded on one GPU",
+                    "value": full_bytes * copies * base_steps / base_sec / 1e9, "unit": "GB/s",
+                    "us_per_node": base_sec / (copies * base_steps) * 1e6, "kernel": base_name,
+                    "note": "divide `value` of this line by this value for the like-for-like speed-up over one GPU"}
+                del base_w, base_y
+            dist.barrier()
+
     if rank == 0:
         line = {
             "metric": "MatMulNBits 4-bit M=1 HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config, "roofline": roofline, "e2e": e2e, "gpu_launches": int(gpu_launches),
-            "clocks": clocks.summary(),
+            "config": config, "details": details, "roofline": roofline, "e2e": e2e,
+            "gpu_launches": int(gpu_launches), "clocks": clocks.summary(),
         }
         line.update(extras)
         if not multi and not args.skip_extras:

@@ -99,3 +99,17 @@ def shard_columns(case: Case, world_size: int, rank: int) -> Case:
                 None if case.zero_points is None else case.zero_points[lo:hi],
                 None if case.bias is None else case.bias[lo:hi], case.accuracy_level,
                 dict(case.meta, col_offset=lo))
+
+
+def algorithmic_bytes(m: int, n: int, k: int, bits: int, block_size: int, has_zero_points: bool,
+                      has_bias: bool) -> int:
+    """Bytes the operator must read and write once per call (packed weights, scales, zero points,
+    bias, A, Y): the figure every roofline number is computed from. Same formula as the C ABI's
+    ``mnb_algorithmic_bytes``; restated here so that the CPU legs need not load the CUDA library."""
+    n_blocks = -(-k // block_size)
+    total = n * n_blocks * (block_size * bits // 8) + 4 * n * n_blocks
+    if has_zero_points:
+        total += n * ((n_blocks * bits + 7) // 8)
+    if has_bias:
+        total += 4 * n
+    return total + 4 * m * k + 4 * m * n

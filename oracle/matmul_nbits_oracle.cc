@@ -15,6 +15,10 @@
 #include <cmath>
 #include <limits>
 #include <cstring>
+#include <atomic>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -78,6 +82,117 @@ inline int ReadZeroPoint(const QuantView &v, std::int64_t row, std::int64_t bloc
   return (block & 1) ? (byte >> 4) : (byte & 0x0f);
 }
 
+// Worker threads that live as long as the process: started on first use (and again when another
+// thread count is asked for), parked on a condition variable between calls. A call hands out
+// block indices through an atomic counter and returns when every block is done; the calling
+// thread takes blocks too. Thread start-up is therefore outside any timed call after the first.
+class WorkerPool {
+public:
+  using BlockFn = void (*)(void *, std::int64_t);
+
+  static WorkerPool &Get(int threads) {
+    static std::mutex guard;
+    static std::unique_ptr<WorkerPool> pool;
+    std::lock_guard<std::mutex> lock(guard);
+    if (pool == nullptr || pool->threads_ != threads) {
+      pool.reset(new WorkerPool(threads));
+    }
+    return *pool;
+  }
+
+  ~WorkerPool() {
+    {
+      std::lock_guard<std::mutex> lock(mutex_);
+      stop_ = true;
+      ++generation_;
+    }
+    wake_.notify_all();
+    for (auto &t : workers_) {
+      t.join();
+    }
+  }
+
+  int threads() const { return threads_; }
+
+  void Run(std::int64_t blocks, void *context, BlockFn fn) {
+    if (blocks <= 0) {
+      return;
+    }
+    std::lock_guard<std::mutex> serial(run_mutex_);  // one parallel region at a time
+    {
+      std::lock_guard<std::mutex> lock(mutex_);
+      context_ = context;
+      fn_ = fn;
+      blocks_ = blocks;
+      next_.store(0);
+      pending_ = static_cast<int>(workers_.size());
+      ++generation_;
+    }
+    wake_.notify_all();
+    Drain();
+    std::unique_lock<std::mutex> lock(mutex_);
+    done_.wait(lock, [this] { return pending_ == 0; });
+  }
+
+private:
+  explicit WorkerPool(int threads) : threads_(threads) {
+    for (int i = 1; i < threads; ++i) {
+      workers_.emplace_back([this] { Loop(); });
+    }
+  }
+
+  void Drain() {
+    for (;;) {
+      const std::int64_t block = next_.fetch_add(1);
+      if (block >= blocks_) {
+        return;
+      }
+      fn_(context_, block);
+    }
+  }
+
+  void Loop() {
+    std::uint64_t seen = 0;
+    for (;;) {
+      {
+        std::unique_lock<std::mutex> lock(mutex_);
+        wake_.wait(lock, [&] { return generation_ != seen; });
+        seen = generation_;
+        if (stop_) {
+          return;
+        }
+      }
+      Drain();
+      {
+        std::lock_guard<std::mutex> lock(mutex_);
+        --pending_;
+      }
+      done_.notify_one();
+    }
+  }
+
+  const int threads_;
+  std::vector<std::thread> workers_;
+  std::mutex mutex_, run_mutex_;
+  std::condition_variable wake_, done_;
+  std::uint64_t generation_ = 0;
+  bool stop_ = false;
+  int pending_ = 0;
+  void *context_ = nullptr;
+  BlockFn fn_ = nullptr;
+  std::int64_t blocks_ = 0;
+  std::atomic<std::int64_t> next_{0};
+};
+
+// Optional outside dispatcher for the column panels: runner(total, threads, context, fn) must call
+// fn(context, begin, end) over disjoint ranges that cover [0, total). Set from the test harness to
+// the bridge that goes through the reference's ExecuteRanges (onnx_light_cpu/impl/execution.h:146-176).
+using RangeFn = void (*)(void *, std::int64_t, std::int64_t);
+using RangeRunner = void (*)(std::int64_t, int, void *, RangeFn);
+std::atomic<RangeRunner> g_range_runner{nullptr};
+
+// Splits the n output columns into one contiguous panel per worker ("stream B once, partition N",
+// onnx_light_cpu/impl/math/gemm_kernel.cc:1219-1258).
 template <typename Fn> void ForColumnPanels(std::int64_t n, int threads, Fn fn) {
   const int hw = std::max(1, threads);
   const std::int64_t workers = std::min<std::int64_t>(hw, std::max<std::int64_t>(n, 1));
@@ -85,20 +200,22 @@ template <typename Fn> void ForColumnPanels(std::int64_t n, int threads, Fn fn) 
     fn(std::int64_t{0}, n);
     return;
   }
-  std::vector<std::thread> pool;
-  pool.reserve(static_cast<std::size_t>(workers));
+  if (const RangeRunner runner = g_range_runner.load()) {
+    runner(n, hw, &fn, [](void *context, std::int64_t begin, std::int64_t end) {
+      (*static_cast<Fn *>(context))(begin, end);
+    });
+    return;
+  }
   const std::int64_t panel = (n + workers - 1) / workers;
-  for (std::int64_t w = 0; w < workers; ++w) {
-    const std::int64_t begin = w * panel;
-    const std::int64_t end = std::min(n, begin + panel);
-    if (begin >= end) {
-      break;
-    }
-    pool.emplace_back([=] { fn(begin, end); });
-  }
-  for (auto &t : pool) {
-    t.join();
-  }
+  struct Task {
+    Fn *fn;
+    std::int64_t panel, n;
+  } task{&fn, panel, n};
+  WorkerPool::Get(hw).Run((n + panel - 1) / panel, &task, [](void *context, std::int64_t block) {
+    auto *t = static_cast<Task *>(context);
+    const std::int64_t begin = block * t->panel;
+    (*t->fn)(begin, std::min(t->n, begin + t->panel));
+  });
 }
 
 inline std::uint16_t ToBf16(float value) {
@@ -122,6 +239,11 @@ inline float FromBf16(std::uint16_t bits) {
 } // namespace
 
 extern "C" {
+
+// Installs (or, with nullptr, removes) the outside dispatcher of the column panels.
+void nbits_oracle_set_range_runner(void (*runner)(std::int64_t, int, void *, void (*)(void *, std::int64_t, std::int64_t))) {
+  g_range_runner.store(runner);
+}
 
 std::uint16_t nbits_oracle_float_to_bf16_bits(float value) { return ToBf16(value); }
 float nbits_oracle_bf16_bits_to_float(std::uint16_t bits) { return FromBf16(bits); }

@@ -30,7 +30,8 @@ _ref = None
 def build(reference: bool = True) -> None:
     """Compiles the checker (and, when the reference checkout exists, oracle/_ref)."""
     targets = ["oracle"] + (["ref"] if reference else [])
-    subprocess.run(["make", "-C", str(HERE), *targets], check=True, capture_output=True)
+    subprocess.run(["make", "-C", str(HERE), f"REFERENCE_ROOT={reference_root()}", *targets], check=True,
+                   capture_output=True)
 
 
 def lib() -> ctypes.CDLL:
@@ -54,6 +55,38 @@ def ref_lib():
         _ref.ref_float_to_bf16_bits.restype = ctypes.c_uint16
         _ref.ref_float_to_bf16_bits.argtypes = [ctypes.c_float]
     return _ref
+
+
+def reference_root() -> Path:
+    """The reference checkout: environment variable REFERENCE_ROOT, else ``reference`` beside the repository."""
+    import os
+
+    return Path(os.environ.get("REFERENCE_ROOT", HERE.parent.parent / "reference"))
+
+
+def use_reference_execute_ranges(enable: bool = True) -> bool:
+    """Routes the column panels of the threaded checker functions through the reference's own
+    ``ExecuteRanges`` (onnx_light_cpu/impl/execution.h:146-176) with a persistent ``std::thread``
+    executor injected through ``ExecutionExecutorScope`` - how the reference's CPU kernels get their
+    threads. Needs oracle/_ref; returns whether it is in effect. ``enable=False`` goes back to the
+    checker's own persistent worker pool."""
+    setter = lib().nbits_oracle_set_range_runner
+    setter.argtypes = [ctypes.c_void_p]
+    setter.restype = None
+    ref = ref_lib() if enable else None
+    if ref is None or not hasattr(ref, "ref_execute_ranges"):
+        setter(None)
+        return False
+    setter(ctypes.cast(ref.ref_execute_ranges, ctypes.c_void_p))
+    return True
+
+
+def reference_execute_ranges_calls() -> int:
+    ref = ref_lib()
+    if ref is None or not hasattr(ref, "ref_execute_ranges_calls"):
+        return 0
+    ref.ref_execute_ranges_calls.restype = ctypes.c_longlong
+    return int(ref.ref_execute_ranges_calls())
 
 
 def _p(x):

@@ -21,7 +21,7 @@ def native_libraries():
     build.build_all()
     from oracle import nbits_oracle
 
-    nbits_oracle.build(reference=os.path.isdir("/root/reference"))
+    nbits_oracle.build(reference=nbits_oracle.reference_root().is_dir())
     return True
 
 
