@@ -364,9 +364,11 @@ def main() -> None:
         y_host = torch.empty(m, cfg["n"]).pin_memory()
         host_steps = max(3, min(args.steps, 50))
 
+        a_pointer, y_pointer = a_host.data_ptr(), y_host.data_ptr()
+
         def host_step():
             for w in weights:
-                w.matmul_host_ptr(a_host.data_ptr(), m, y_host.data_ptr())
+                w.matmul_host_ptr(a_pointer, m, y_pointer)
 
         for _ in range(3):
             host_step()

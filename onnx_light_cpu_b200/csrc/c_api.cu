@@ -99,6 +99,14 @@ struct mnb_weights {
   // last (A, Y) pair of the device-pointer entry points whose location has been checked
   const void *checked_a = nullptr;
   const void *checked_y = nullptr;
+  // last (A, Y) pair of the host-buffer entry point and what the runtime said about it: the
+  // device aliases of page-locked buffers (nullptr = stage through device memory)
+  const void *host_a = nullptr;
+  const void *host_y = nullptr;
+  std::size_t host_a_bytes = 0;
+  std::size_t host_y_bytes = 0;
+  const float *host_a_alias = nullptr;
+  float *host_y_alias = nullptr;
 };
 
 namespace {
@@ -631,6 +639,7 @@ int mnb_weights_destroy(mnb_weights *h) {
     return MNB_OK;
   }
   cudaSetDevice(h->device);
+  mnb::ForgetDecodeResidentPlans(h->view);
   if (h->stream != nullptr) {
     cudaStreamSynchronize(h->stream);
     cudaStreamDestroy(h->stream);
@@ -910,15 +919,32 @@ int mnb_matmul_host(mnb_weights *h, const float *a_host, int64_t m, int accuracy
     return rc;
   }
   constexpr std::size_t kDirectLimit = 1u << 20;
-  cudaPointerAttributes attributes{};
-  const float *a_alias = nullptr;
-  if (a_bytes <= kDirectLimit && (reinterpret_cast<std::uintptr_t>(a_host) & 15u) == 0 &&
-      cudaPointerGetAttributes(&attributes, a_host) == cudaSuccess && attributes.type == cudaMemoryTypeHost &&
-      attributes.devicePointer != nullptr) {
-    a_alias = static_cast<const float *>(attributes.devicePointer);
-  } else {
-    cudaGetLastError(); // an unregistered pointer reports an error on some drivers: not a failure here
+  // Where the caller's buffers live is asked once per (A, Y, sizes): two cudaPointerGetAttributes
+  // per call cost about as much as a kernel launch. A buffer that is freed and another one
+  // page-locked at the same address between two calls of the same sizes is a caller error here.
+  if (a_host != h->host_a || y_host != h->host_y || a_bytes != h->host_a_bytes || y_bytes != h->host_y_bytes) {
+    cudaPointerAttributes attributes{};
+    h->host_a_alias = nullptr;
+    h->host_y_alias = nullptr;
+    if (a_bytes <= kDirectLimit && (reinterpret_cast<std::uintptr_t>(a_host) & 15u) == 0 &&
+        cudaPointerGetAttributes(&attributes, a_host) == cudaSuccess && attributes.type == cudaMemoryTypeHost &&
+        attributes.devicePointer != nullptr) {
+      h->host_a_alias = static_cast<const float *>(attributes.devicePointer);
+    } else {
+      cudaGetLastError(); // an unregistered pointer reports an error on some drivers: not a failure here
+    }
+    if (y_bytes <= kDirectLimit && cudaPointerGetAttributes(&attributes, y_host) == cudaSuccess &&
+        attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
+      h->host_y_alias = static_cast<float *>(attributes.devicePointer);
+    } else {
+      cudaGetLastError();
+    }
+    h->host_a = a_host;
+    h->host_y = y_host;
+    h->host_a_bytes = a_bytes;
+    h->host_y_bytes = y_bytes;
   }
+  const float *a_alias = h->host_a_alias;
   if (a_alias != nullptr) {
     const int count16 = static_cast<int>(a_bytes / 16);
     const int tail = static_cast<int>((a_bytes - static_cast<std::size_t>(count16) * 16) / sizeof(float));
@@ -940,15 +966,7 @@ int mnb_matmul_host(mnb_weights *h, const float *a_host, int64_t m, int accuracy
   // decode-sized result), the kernels store straight into it through its device alias, which
   // saves a copy launch per call; any other buffer gets a device staging buffer and a
   // device-to-host copy, which keeps the SMs from waiting on the host link for large results.
-  float *y_alias = nullptr;
-  if (y_bytes > kDirectLimit) {
-    // staged below
-  } else if (cudaPointerGetAttributes(&attributes, y_host) == cudaSuccess &&
-             attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
-    y_alias = static_cast<float *>(attributes.devicePointer);
-  } else {
-    cudaGetLastError(); // an unregistered pointer reports an error on some drivers: not a failure here
-  }
+  float *y_alias = h->host_y_alias;
   if (y_alias == nullptr) {
     rc = Grow(reinterpret_cast<void **>(&h->y_dev), &h->y_dev_bytes, y_bytes);
     if (rc != MNB_OK) {

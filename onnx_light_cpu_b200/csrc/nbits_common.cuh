@@ -193,6 +193,8 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
                                  cudaStream_t stream, int sm_count);
+// Drops the launch plans (tensor maps, slot shapes) cached for a node whose weights are going away.
+void ForgetDecodeResidentPlans(const WeightView &w);
 
 // Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,

@@ -39,6 +39,10 @@
 #include "nbits_common.cuh"
 
 #include <cstdint>
+#include <memory>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "nbits_digits.cuh"
 #include "nbits_ptx.cuh"
@@ -485,17 +489,35 @@ bool DecodeResidentSupports(const WeightView &w, std::int64_t m) {
          w.n < (std::int64_t{1} << 31);
 }
 
-const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
-                                 cudaStream_t stream, int sm_count) {
-  if (!DecodeResidentSupports(w, m)) {
-    return nullptr;
+namespace {
+
+// Everything of a launch that depends on the node only: slot shape, tensor maps, grid. Built once
+// per node (six cuTensorMapEncodeTiled calls and a cudaFuncSetAttribute cost several microseconds,
+// as much as the kernel's share of a host-buffer call) and kept until the node's weights go.
+struct ResidentPlan {
+  ResidentMaps maps;
+  ResidentParams params;  // a, out and status are filled per launch
+  size_t smem = 0;
+  int ctas = 0;
+  int threads = 0;
+};
+
+struct PlanKey {
+  const void *b, *scales, *zp16;
+  std::int64_t n, k;
+  int sms;
+  bool operator==(const PlanKey &o) const {
+    return b == o.b && scales == o.scales && zp16 == o.zp16 && n == o.n && k == o.k && sms == o.sms;
   }
-  const int sms = sm_count > 0 ? sm_count : 148;
-  ResidentParams p{};
+};
+
+std::mutex g_plan_mutex;
+std::vector<std::pair<PlanKey, std::unique_ptr<ResidentPlan>>> g_plans;
+
+bool BuildPlan(const WeightView &w, int sms, ResidentPlan *plan) {
+  ResidentParams &p = plan->params;
+  p = ResidentParams{};
   p.w = w;
-  p.a = a;
-  p.out = out;
-  p.status = status_word;
   p.segs = w.n_blocks;
   p.table_ints = (p.segs / 2) * 8;
   p.tiles = static_cast<int>((w.n + 7) / 8);
@@ -545,30 +567,32 @@ const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64
       }
     }
     if (steps == 0) {
-      return nullptr;
+      return false;
     }
     warps = most_warps(2, steps, 1);
     if (warps < 1) {
-      return nullptr;
+      return false;
     }
   }
   if ((chunks % steps) != 0 || (steps % kStepsPerSuper) != 0 || steps > 256) {
-    return nullptr;
+    return false;
   }
   p.steps_per_task = steps;
   p.parts = chunks / steps;
   p.groups = warps / group_tiles;
   p.slots_per_group = slots_per_group;
   if (p.groups * slots_per_group > kMaxGroupSlots) {
-    return nullptr;
+    return false;
   }
   p.strided = 1;
   p.early_groups = 2;
-  const size_t smem = fixed + static_cast<size_t>(warps) * slots_per_group * steps * per_step;
+  plan->smem = fixed + static_cast<size_t>(warps) * slots_per_group * steps * per_step;
+  plan->ctas = ctas;
+  plan->threads = (warps + 1) * 32;
 
-  ResidentMaps maps;
+  ResidentMaps &maps = plan->maps;
   if (!EncodeWeightTileMap(&maps.w_tile, w, steps)) {
-    return nullptr;
+    return false;
   }
   p.group_tiles = group_tiles;
   p.group_boxes = (group_tiles > 1 && EncodeWeightGroupMap(&maps.w_group, w, steps, group_tiles)) ? 1 : 0;
@@ -587,32 +611,82 @@ const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64
                              static_cast<std::uint32_t>(rows), CU_TENSOR_MAP_SWIZZLE_NONE);
   };
   if (!rows_map(&maps.s_tile, false, 8) || !rows_map(&maps.s_group, false, 8 * group_tiles)) {
-    return nullptr;
+    return false;
   }
   maps.z_tile = maps.s_tile;
   maps.z_group = maps.s_group;
   if (w.zp != nullptr && (!rows_map(&maps.z_tile, true, 8) || !rows_map(&maps.z_group, true, 8 * group_tiles))) {
+    return false;
+  }
+  // The function attribute belongs to the kernel, not to the node: it is raised to the most any
+  // plan can ask for, so that plans of different sizes do not undo one another.
+  const int most = static_cast<int>(limit);
+  const cudaError_t err =
+      w.zp != nullptr
+          ? cudaFuncSetAttribute(nbits_decode_resident_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most)
+          : cudaFuncSetAttribute(nbits_decode_resident_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+  return err == cudaSuccess;
+}
+
+// The plan of a node, built on first use. nullptr when the node's shape has none.
+const ResidentPlan *PlanFor(const WeightView &w, int sms) {
+  const PlanKey key{w.b, w.scales, w.zp != nullptr ? w.zp16 : nullptr, w.n, w.k, sms};
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  for (const auto &entry : g_plans) {
+    if (entry.first == key) {
+      return entry.second.get();
+    }
+  }
+  auto plan = std::make_unique<ResidentPlan>();
+  if (!BuildPlan(w, sms, plan.get())) {
+    cudaGetLastError();
     return nullptr;
   }
-  auto launch = [&](auto kernel) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) {
-      return err;
+  g_plans.emplace_back(key, std::move(plan));
+  return g_plans.back().second.get();
+}
+
+} // namespace
+
+// Called when a node's weights are destroyed: its plan names their addresses.
+void ForgetDecodeResidentPlans(const WeightView &w) {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  for (size_t i = 0; i < g_plans.size();) {
+    if (g_plans[i].first.b == w.b) {
+      g_plans.erase(g_plans.begin() + static_cast<std::ptrdiff_t>(i));
+    } else {
+      ++i;
     }
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
-    config.blockDim = dim3(static_cast<unsigned>((warps + 1) * 32), 1, 1);
-    config.dynamicSmemBytes = smem;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, maps, p);
-  };
-  const cudaError_t err =
-      w.zp != nullptr ? launch(nbits_decode_resident_kernel<true>) : launch(nbits_decode_resident_kernel<false>);
+  }
+}
+
+const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
+                                 cudaStream_t stream, int sm_count) {
+  if (!DecodeResidentSupports(w, m)) {
+    return nullptr;
+  }
+  const ResidentPlan *plan = PlanFor(w, sm_count > 0 ? sm_count : 148);
+  if (plan == nullptr) {
+    return nullptr;
+  }
+  ResidentParams p = plan->params;
+  p.w = w;
+  p.a = a;
+  p.out = out;
+  p.status = status_word;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(plan->ctas), 1, 1);
+  config.blockDim = dim3(static_cast<unsigned>(plan->threads), 1, 1);
+  config.dynamicSmemBytes = plan->smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t err = w.zp != nullptr
+                              ? cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<true>, plan->maps, p)
+                              : cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<false>, plan->maps, p);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return nullptr;

@@ -100,8 +100,13 @@ def test_device_entry_point_refuses_memory_of_another_gpu():
     weights = pkg.MatMulNBitsWeights(case.b, case.scales, None, None, K=4096, N=64, bits=4, block_size=128, device=0)
     a = torch.from_numpy(case.a).to("cuda:1")
     y = torch.zeros((1, 64), device="cuda:1")
-    with pytest.raises(_capi.MatMulNBitsError, match="must be memory of GPU 0") as info:
+    # the Python wrapper refuses the tensors, and the C entry point refuses the raw addresses
+    with pytest.raises(ValueError, match="the weights are on GPU 0"):
         weights.matmul_device(a, y)
+    with pytest.raises(_capi.MatMulNBitsError, match="must be memory of GPU 0") as info:
+        _capi.check(weights._lib.mnb_matmul_device_strided(
+            weights._handle, a.data_ptr(), 1, 0, _capi.PATH_AUTO, y.data_ptr(), 64, 0,
+            torch.cuda.current_stream(0).cuda_stream))
     assert info.value.status == _capi.MNB_ERR_INVALID_ARGUMENT
     weights.close()
 
