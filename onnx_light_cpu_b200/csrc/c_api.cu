@@ -24,14 +24,7 @@ thread_local const char *t_last_kernel = "";
 
 void CountLaunch(int launches) { g_launches.fetch_add(launches, std::memory_order_relaxed); }
 
-int WantedProducers(int kernel_default) {
-  static const int wanted = [] {
-    const char *value = std::getenv("MNB_GEMV_PRODUCERS");
-    const int v = value != nullptr ? std::atoi(value) : 0;
-    return (v == 1 || v == 2 || v == 4) ? v : 0;
-  }();
-  return wanted != 0 ? wanted : kernel_default;
-}
+int WantedProducers(int kernel_default) { return kernel_default; }
 
 thread_local bool t_dependent_launch_hint = false;
 void SetDependentLaunchHint(bool allowed) { t_dependent_launch_hint = allowed; }
@@ -837,17 +830,9 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   if (m > per_pass) {
     name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
   }
-  // off by default: on two GPUs the fused form measured slower than the separate flag kernel
-  // (56.7 vs 48.2 us per lm-head node, same box); MNB_GATHER_FUSED=1 turns it on
-  static const bool fuse_tail = [] {
-    const char *value = std::getenv("MNB_GATHER_FUSED");
-    return value != nullptr && value[0] == '1';
-  }();
-  if (name == nullptr && m <= per_pass && fuse_tail) {
-    // one pass over the weights: the kernel's last CTA runs the flag exchange itself
-    name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &tail);
-    fused = name != nullptr;
-  }
+  // The flag exchange is a kernel of its own behind the decode kernel: a fused form (the decode
+  // kernel's last CTA publishing the flags) measured slower on two GPUs, 56.7 vs 48.2 us per
+  // lm-head node on one box.
   if (name == nullptr) {
     name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
   }
@@ -858,10 +843,7 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   }
   if (!fused) {
     cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
-    static const bool early_launch = [] {
-      const char *value = std::getenv("MNB_GATHER_PDL");
-      return value == nullptr || value[0] != '0';
-    }();
+    // launched early (programmatic stream serialization): 43.3 vs 43.9 us per node on two GPUs
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(1, 1, 1);
     config.blockDim = dim3(32, 1, 1);
@@ -871,7 +853,7 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = early_launch ? 1 : 0;
+    config.numAttrs = 1;
     cudaError_t launch_err = cudaLaunchKernelEx(&config, nbits_publish_wait_kernel, tail, h->status_dev);
     if (launch_err == cudaSuccess) {
       launch_err = cudaGetLastError();

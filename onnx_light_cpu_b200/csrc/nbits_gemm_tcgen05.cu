@@ -334,19 +334,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 // weights for twice the MMA work of the 128-row kernel, which halves the L2 traffic per flop
 // and lets four stages in flight cover the TMA latency. The dequantized tile is transient, so
 // it lives in its own two buffers instead of the TMA ring.
-#ifdef MNB_TIMELINE
-// Debug builds only: event times (globaltimer ns) of CTA 0 for offline inspection.
-__device__ unsigned long long g_gemm_timeline[4 * 80];
-__device__ __forceinline__ unsigned long long GemmNowNs() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define MNB_GEMM_MARK(row_, ks_) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && (ks_) < 80) g_gemm_timeline[(row_) * 80 + (ks_)] = GemmNowNs(); } while (0)
-#else
-#define MNB_GEMM_MARK(row_, ks_) do { } while (0)
-#endif
 
 constexpr int kWideRows = 256;
 constexpr int kWideTokens = 256;
@@ -415,7 +402,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           *abort_flag = 1;
           break;
         }
-        MNB_GEMM_MARK(0, ks);
         ptx::MbarArriveExpectTx(&full_tma[s], kWideStageA + kWideStageP);
         ptx::TmaLoad2D(ring_a + s * kWideStageA, &map_a, ks * kTileK, m0, &full_tma[s]);
         ptx::TmaLoad2D(ring_p + s * kWideStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
@@ -442,7 +428,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         ptx::TcFenceAfter();
-        MNB_GEMM_MARK(3, ks);
         const std::uint32_t sa = ptx::SmemAddr(ring_a + s * kWideStageA);
         const std::uint32_t sw = ptx::SmemAddr(buf_w + b * kWideBufW);
 #pragma unroll
@@ -531,7 +516,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       if (tid == 64) {
-        MNB_GEMM_MARK(1, ks);
       }
       const unsigned char *packed = ring_p + s * kWideStageP + packed_offset;
       unsigned char *dst = buf_w + b * kWideBufW;
@@ -550,7 +534,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::MbarArrive(&w_full[b]);
       }
       if (tid == 64) {
-        MNB_GEMM_MARK(2, ks);
       }
       if (++s == kWideStages) {
         s = 0;
@@ -654,15 +637,6 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
                    : (BT == 128 ? "nbits_gemm_tcgen05_kernel<128>" : "nbits_gemm_tcgen05_kernel<64>");
 }
 
-// MNB_GEMM_NARROW=1 keeps the 128-row tiles for every size (A/B measurements).
-bool ForceNarrowTiles() {
-  static const bool value = [] {
-    const char *env = std::getenv("MNB_GEMM_NARROW");
-    return env != nullptr && env[0] == '1';
-  }();
-  return value;
-}
-
 const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
                        int *status_word, cudaStream_t stream) {
   CUtensorMap map_a, map_p;
@@ -700,11 +674,6 @@ const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t 
 
 } // namespace
 
-#ifdef MNB_TIMELINE
-extern "C" int mnb_debug_copy_gemm_timeline(unsigned long long *host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_gemm_timeline, sizeof(unsigned long long) * count));
-}
-#endif
 
 std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k) {
   return static_cast<std::size_t>(m) * static_cast<std::size_t>(k) * 2;
@@ -738,7 +707,7 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   const int sms = sm_count > 0 ? sm_count : 148;
   // large problems: 256 x 256 tiles (half the operand traffic per flop)
   const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
-  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8 && !ForceNarrowTiles())) {
+  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8)) {
     return LaunchWide(w, m, a_bf16, out, status_word, stream);
   }
   // otherwise the widest token tile that still gives every SM a tile

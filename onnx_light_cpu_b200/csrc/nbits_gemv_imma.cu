@@ -689,11 +689,7 @@ const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, 
     return nullptr;
   }
   p.act_row_bytes = p.k_pad + 16; // 16: the two digit rows read by a quarter warp fall on different banks
-  static const bool allow_full_rows = [] {
-    const char *value = std::getenv("MNB_GEMV_FULL_ROWS");
-    return value == nullptr || value[0] != '0';
-  }();
-  p.full_rows = (allow_full_rows && w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
+  p.full_rows = (w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
                  w.row_bytes >= 1024) ? 1 : 0;
   if (p.full_rows != 0) {
     p.row_stride = w.row_bytes;
@@ -737,13 +733,9 @@ const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, 
                    static_cast<std::uint32_t>(p.slice_b_bytes / 4), 16, CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return nullptr;
   }
-  // Programmatic dependent launch behind the previous kernel of the stream (its weight stream
-  // starts while that kernel drains; A is read after the dependency wait): only with
-  // MNB_IMMA_DEPENDENT_LAUNCH=1 or behind the host-buffer call's fetch kernel.
-  static const bool dependent_launch = [] {
-    const char *value = std::getenv("MNB_IMMA_DEPENDENT_LAUNCH");
-    return value != nullptr && value[0] == '1';
-  }();
+  // Programmatic dependent launch (the weight stream starts while the previous kernel drains; A is
+  // read after the dependency wait) only behind the host-buffer call's fetch kernel: between
+  // consecutive nodes it measured slower (11.3-12.1 vs 10.2-10.5 us per node).
   dim3 grid(static_cast<unsigned>(ctas),
             static_cast<unsigned>((m + p.tokens_per_pass - 1) / p.tokens_per_pass), 1);
   cudaError_t err = cudaErrorInvalidValue;
@@ -762,7 +754,7 @@ const char *LaunchGemvImma(const WeightView &w, const float *a, std::int64_t m, 
       attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
-      config.numAttrs = (dependent_launch || DependentLaunchHint()) ? 1 : 0;                     \
+      config.numAttrs = DependentLaunchHint() ? 1 : 0;                                          \
       err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
     }                                                                                            \
   }

@@ -44,19 +44,6 @@ namespace {
 
 using namespace mma_decode;
 
-#ifdef MNB_TIMELINE
-// Debug builds only: per-CTA event times (globaltimer ns) for offline inspection.
-__device__ unsigned long long g_timeline[148 * 64];
-__device__ __forceinline__ unsigned long long NowNs() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define MNB_MARK(slot_) \
-  do { if (blockIdx.y == 0 && (slot_) < 64) g_timeline[blockIdx.x * 64 + (slot_)] = NowNs(); } while (0)
-#else
-#define MNB_MARK(slot_) do { } while (0)
-#endif
 
 constexpr int kPairs = 8;                 // 16-row tiles in flight per CTA
 constexpr int kWarps = 2 * kPairs;        // consumer warps: two per tile, alternating k slices
@@ -142,7 +129,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
   if (tid == 0) {
-    MNB_MARK(0);
   }
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
@@ -197,7 +183,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
             unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
             slot_task[slot] = task;
-            MNB_MARK(32 + task);
             ptx::MbarArriveExpectTx(&full_bar[slot], row_bytes_total + static_cast<std::uint32_t>(p.slices) * meta_bytes);
             ptx::BulkLoad(dst, p.w.b + first_row * p.row_stride, row_bytes_total, &full_bar[slot]);
             const unsigned char *meta_src = p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes;
@@ -230,7 +215,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
               unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
               slot_task[slot] = task;
-              MNB_MARK(32 + task);
               ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
               ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
               ptx::BulkLoad(dst + box_bytes, meta_src, meta_bytes, &full_bar[slot]);
@@ -277,7 +261,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   // activations staged and (through the producer's arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
   if (tid == 0) {
-    MNB_MARK(1);
   }
 
   const int g = lane >> 2;
@@ -335,7 +318,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         return false;
       }
       if (lane == 0) {
-        MNB_MARK(2 + task);
       }
       return true;
     };
@@ -442,14 +424,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0 && p.full_rows == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
-        MNB_MARK(17 + task);
       }
     }
     if (p.full_rows != 0 && !dead) {
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&empty_bar[slot]);
-        MNB_MARK(17 + tile);
       }
     }
     // blocks of one supergroup sit in neighbouring lanes of the quad: add them up
@@ -551,23 +531,8 @@ __global__ void __launch_bounds__(256) nbits_prepare_meta_kernel(const WeightVie
   }
 }
 
-// Programmatic dependent launch is off unless MNB_DEPENDENT_LAUNCH=1: on the decode benchmark
-// (back-to-back launches in a CUDA graph) it measured 7 % slower than plain serialization.
-bool UseDependentLaunch() {
-  static const bool enabled = [] {
-    const char *value = std::getenv("MNB_DEPENDENT_LAUNCH");
-    return value != nullptr && value[0] == '1';
-  }();
-  return enabled;
-}
-
 } // namespace
 
-#ifdef MNB_TIMELINE
-extern "C" int mnb_debug_copy_timeline(unsigned long long *host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_timeline, sizeof(unsigned long long) * count));
-}
-#endif
 
 MetaGeometry MetaGeometryOf(const WeightView &w) {
   MetaGeometry geo{};
@@ -577,13 +542,6 @@ MetaGeometry MetaGeometryOf(const WeightView &w) {
   }
   // a task covers 2048 k of 16 rows (16 KB of packed weights): 64 / 32 / 16 / 8 ... blocks
   int bpt = 2048 / w.block_size;
-  const char *override_bpt = std::getenv("MNB_GEMV_BLOCKS_PER_TASK");
-  if (override_bpt != nullptr) {
-    const int v = std::atoi(override_bpt);
-    if (v >= 2 && v <= 64 && (v & (v - 1)) == 0 && v * w.block_size >= 512 && v * w.block_size <= 2048) {
-      bpt = v;
-    }
-  }
   geo.bpt = bpt;
   geo.slices = (w.n_blocks + bpt - 1) / bpt;
   geo.scale_row_floats = bpt + (((bpt * 4) % 128) == 0 ? 4 : 0);
@@ -658,12 +616,8 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
   }
   p.act_row_bytes = p.k_pad * 2 + 64; // 64: bank spread between the two piece rows
   // Whole-row tasks when a row is exactly one or two slices long (K = 2048 or 4096): 16 rows are
-  // then one contiguous copy of 16 or 32 KB. MNB_GEMV_FULL_ROWS=0 keeps the sliced TMA boxes.
-  static const bool allow_full_rows = [] {
-    const char *value = std::getenv("MNB_GEMV_FULL_ROWS");
-    return value == nullptr || value[0] != '0';
-  }();
-  p.full_rows = (allow_full_rows && w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
+  // then one contiguous copy of 16 or 32 KB (13 % faster than sliced boxes on K = 4096).
+  p.full_rows = (w.row_bytes == p.slices * p.slice_b_bytes && p.slices <= 2 &&
                  w.row_bytes >= 1024) ? 1 : 0;
   if (p.full_rows != 0) {
     p.row_stride = w.row_bytes;
@@ -724,7 +678,7 @@ const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, O
       attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
-      config.numAttrs = (UseDependentLaunch() || DependentLaunchHint()) ? 1 : 0;                                            \
+      config.numAttrs = DependentLaunchHint() ? 1 : 0;                                                                     \
       err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
     }                                                                                            \
   }

@@ -33,7 +33,6 @@ namespace {
 
 using namespace mma_decode;
 
-#define MNB_MARK(slot_) do { } while (0)
 
 constexpr int kWarps = 16;                // consumer warps = 128-k supergroups of a task
 constexpr int kConsumerThreads = kWarps * 32;
@@ -106,7 +105,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
   if (tid == 0) {
-    MNB_MARK(0);
   }
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
@@ -161,7 +159,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
         unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
         if (task < 15) {
-          MNB_MARK(32 + task);
         }
         ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
         ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
@@ -197,7 +194,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   // activations staged and (through the producer's arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
   if (tid == 0) {
-    MNB_MARK(1);
   }
 
   const int g = lane >> 2;
@@ -255,7 +251,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!dead) {
         if (lane == 0 && warp == 0) {
-          MNB_MARK(2 + task);
         }
         const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
         const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + weight_off);
@@ -307,7 +302,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           acc1[nt] = fmaf(s1, (da[nt][2] + da[nt][3]) + (db[nt][2] + db[nt][3]), acc1[nt]);
         }
         if (lane == 0 && warp == 0) {
-          MNB_MARK(17 + task);
         }
       }
       if (++slot == p.num_slots) {

@@ -60,29 +60,24 @@ def _worker(rank: int, world: int, port: int) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", ["0", "1"])
-def test_gather_entry_point_single_rank(fused, monkeypatch):
-    """World size 1: the entry point, the flag exchange (as its own kernel, and run by the decode
-    kernel's last CTA) and the buffer views without any peer."""
+def test_gather_entry_point_single_rank():
+    """World size 1: the entry point, the flag exchange and the buffer views without any peer."""
     import torch
 
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     import torch.multiprocessing as mp
 
-    monkeypatch.setenv("MNB_GATHER_FUSED", fused)   # read once per process: the child starts fresh
     mp.spawn(_worker, args=(1, _free_port()), nprocs=1, join=True)
 
 
-@pytest.mark.parametrize("fused", ["0", "1"])
-def test_peer_store_gather_two_gpus(fused, monkeypatch):
+def test_peer_store_gather_two_gpus():
     import torch
 
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs on one box")
     import torch.multiprocessing as mp
 
-    monkeypatch.setenv("MNB_GATHER_FUSED", fused)
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
 
 
