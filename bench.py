@@ -450,6 +450,67 @@ def main() -> None:
             del iw, ys_i8
             torch.cuda.empty_cache()
 
+            # ---- sibling nodes in one call: gate + up of the decode workload, M = 1, one launch per pair ----
+            from onnx_light_cpu_b200.matmul_nbits import matmul_device_group
+            pairs = 4
+            gw = device_weights(torch, pkg, cfg, 2 * pairs, seed=1211, zp=True, bias=True)
+            gy = [torch.empty(1, cfg["n"], device="cuda") for _ in range(2 * pairs)]
+            a_g = torch.randn(1, cfg["k"], device="cuda").half().float()
+
+            def group_step():
+                for i in range(pairs):
+                    matmul_device_group(gw[2 * i:2 * i + 2], a_g, gy[2 * i:2 * i + 2])
+
+            group_step()
+            torch.cuda.synchronize()
+            gname = _capi.last_kernel()
+            gstatus = max(w.poll_status() for w in gw)
+            rep, _ = capture_graph(torch, group_step)
+            gsteps = max(5, args.steps // 2)
+            sec = time_steps(torch, dist, rep, gsteps, 3, 1)
+            gbytes = gw[0].algorithmic_bytes(1)
+            ggbs = gbytes * 2 * pairs * gsteps / sec / 1e9
+            extras["group_gate_up_m1"] = {
+                "workload": "two M=1 K=4096 N=14336 bits=4 block=128 zp+bias nodes that share A, one call per pair",
+                "gbs": ggbs, "frac_of_hbm_peak": ggbs / peaks["hbm_gbs"],
+                "us_per_pair": sec / (pairs * gsteps) * 1e6, "us_per_node": sec / (2 * pairs * gsteps) * 1e6,
+                "kernel": gname, "launches_per_pair": 1, "device_status": gstatus}
+            del gw, gy
+            torch.cuda.empty_cache()
+
+            # ---- the seven projections of a decoder layer (cfg4), M = 16, both accuracy levels ----
+            from onnx_light_cpu_b200.tools.decoder_layer import DecoderLayerProjections
+            layers = [DecoderLayerProjections.synthetic(16, 0) for _ in range(2)]   # 2 x 136 MB > L2
+            layer_inputs = [layer.inputs_from_cases() for layer in layers]
+            layer_bytes = layers[0].algorithmic_bytes(16)
+            layer_extra = {"workload": "cfg4 decoder layer: q k v o gate up down, M=16 bits=4 block=32, "
+                                       "q/k/v and gate/up as grouped calls",
+                           "algorithmic_bytes": layer_bytes, "layers_rotated": len(layers)}
+            for level in (0, 4):
+                for grouped in (True, False):
+                    def layer_step():
+                        for layer, inputs in zip(layers, layer_inputs):
+                            layer.run(inputs, accuracy_level=level, grouped=grouped)
+
+                    before = _capi.launch_count()
+                    layer_step()
+                    torch.cuda.synchronize()
+                    launches = (_capi.launch_count() - before) // len(layers)
+                    lstatus = max(layer.poll_status() for layer in layers)
+                    rep, _ = capture_graph(torch, layer_step)
+                    lsteps = max(5, args.steps // 4)
+                    sec = time_steps(torch, dist, rep, lsteps, 3, 1)
+                    us = sec / (len(layers) * lsteps) * 1e6
+                    layer_extra[f"level{level}" + ("" if grouped else "_node_by_node")] = {
+                        "us_per_layer": us, "gbs": layer_bytes / us / 1e3,
+                        "frac_of_hbm_peak": layer_bytes / us / 1e3 / peaks["hbm_gbs"],
+                        "launches_per_layer": launches, "device_status": lstatus}
+            extras["layer_cfg4"] = layer_extra
+            for layer in layers:
+                layer.close()
+            del layers, layer_inputs
+            torch.cuda.empty_cache()
+
             # ---- prefill M = 2048 (bf16 tcgen05 path) ----
             pw = device_weights(torch, pkg, PREFILL, 1, seed=1301, zp=True, bias=False)[0]
             pm = PREFILL["m"]

@@ -102,6 +102,21 @@ int mnb_matmul_host(mnb_weights *weights, const float *a_host, int64_t m, int ac
 int mnb_matmul_device(mnb_weights *weights, const float *a_dev, int64_t m, int accuracy_level,
                       int path, float *y_dev, void *stream);
 
+/* Sibling nodes in one call: `count` (1..MNB_MAX_GROUPED_NODES) nodes that take the SAME
+ * activations - the q / k / v or the gate / up projections of a decoder layer - write
+ * y_dev[i] = MatMulNBits_i(A), each a dense row-major [m, N_i] device matrix. Same K and same GPU
+ * for all nodes, no node or output twice. What the nodes share is done once: at M = 1
+ * (accuracy_level 0, 4-bit, block_size 128) one kernel streams all nodes' weights behind
+ * activations staged once; at accuracy_level 4 the activations are quantized once; for 5..16
+ * tokens on small blocks the digit rows are made once. Any other group runs node by node with
+ * the same results as separate mnb_matmul_device calls. Asynchronous on `stream`; bounded waits
+ * of a grouped launch report through handles[0] (mnb_weights_poll_status).
+ * Replaces: the consecutive MatMul nodes over one input that the reference's graph runs one by
+ * one (q/k/v and gate/up of docs/next_steps/2026/2026_08_qwen3_inference.rst:374-380). */
+#define MNB_MAX_GROUPED_NODES 3
+int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float *a_dev, int64_t m,
+                            int accuracy_level, float *const *y_dev, void *stream);
+
 /* Column-sharded form: writes this shard's N columns into a row-major [m, ld_y] matrix
  * starting at column `col_offset`, so g shards tile one [m, g*N] output. */
 int mnb_matmul_device_strided(mnb_weights *weights, const float *a_dev, int64_t m,

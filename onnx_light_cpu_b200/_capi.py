@@ -48,6 +48,7 @@ EXPORTED_SYMBOLS = (
     "mnb_matmul_host",
     "mnb_matmul_device",
     "mnb_matmul_device_strided",
+    "mnb_matmul_device_group",
     "mnb_peer_buffer_create",
     "mnb_peer_buffer_open",
     "mnb_peer_buffer_close",
@@ -103,6 +104,7 @@ def load() -> ctypes.CDLL:
     lib.mnb_matmul_host.argtypes = [vp, vp, i64, i32, i32, vp]
     lib.mnb_matmul_device.argtypes = [vp, vp, i64, i32, i32, vp, vp]
     lib.mnb_matmul_device_strided.argtypes = [vp, vp, i64, i32, i32, vp, i64, i64, vp]
+    lib.mnb_matmul_device_group.argtypes = [c.POINTER(vp), i32, vp, i64, i32, c.POINTER(vp), vp]
     lib.mnb_peer_buffer_create.argtypes = [i32, c.c_size_t, c.POINTER(vp), vp]
     lib.mnb_peer_buffer_open.argtypes = [i32, vp, c.POINTER(vp)]
     lib.mnb_peer_buffer_close.argtypes = [i32, vp]

@@ -6,6 +6,7 @@
 
 #include "nbits_common.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -682,6 +683,125 @@ int mnb_matmul_device_strided(mnb_weights *h, const float *a_dev, int64_t m, int
   }
   OutputView out{y_dev, ld_y, col_offset};
   return Dispatch(h, a_dev, m, accuracy_level, path, out, static_cast<cudaStream_t>(stream));
+}
+
+static_assert(MNB_MAX_GROUPED_NODES == mnb::kMaxGroupedNodes, "header and kernels agree on the group size");
+
+int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float *a_dev, int64_t m,
+                            int accuracy_level, float *const *y_dev, void *stream) {
+  if (handles == nullptr || y_dev == nullptr || count < 1 || count > MNB_MAX_GROUPED_NODES) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_group: takes 1 to 3 nodes.");
+  }
+  if (accuracy_level != 0 && accuracy_level != 4) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits accuracy_level must be 0 or 4.");
+  }
+  if (m < 0) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits requires M >= 0.");
+  }
+  for (int i = 0; i < count; ++i) {
+    if (handles[i] == nullptr) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null weights handle.");
+    }
+    if (m > 0 && (a_dev == nullptr || y_dev[i] == nullptr)) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: null A or Y.");
+    }
+    if (handles[i]->device != handles[0]->device || handles[i]->view.k != handles[0]->view.k) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT,
+                  "mnb_matmul_device_group: the nodes of a group take the same A: same K, same GPU.");
+    }
+    for (int j = 0; j < i; ++j) {
+      if (handles[j] == handles[i] || y_dev[j] == y_dev[i]) {
+        return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_group: a node or an output is named twice.");
+      }
+    }
+  }
+  // every node's lock, in address order so that two groups over the same nodes cannot block each other
+  mnb_weights *ordered[MNB_MAX_GROUPED_NODES];
+  for (int i = 0; i < count; ++i) {
+    ordered[i] = handles[i];
+  }
+  std::sort(ordered, ordered + count);
+  std::unique_lock<std::mutex> locks[MNB_MAX_GROUPED_NODES];
+  for (int i = 0; i < count; ++i) {
+    locks[i] = std::unique_lock<std::mutex>(ordered[i]->mutex);
+  }
+  mnb_weights *first = handles[0];
+  const cudaError_t err = cudaSetDevice(first->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  if (m == 0) {
+    mnb::t_last_kernel = "none";
+    return MNB_OK;
+  }
+  WeightView nodes[MNB_MAX_GROUPED_NODES];
+  OutputView outs[MNB_MAX_GROUPED_NODES];
+  for (int i = 0; i < count; ++i) {
+    const int rc = CheckDeviceOperands(handles[i], a_dev, y_dev[i]);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    nodes[i] = handles[i]->view;
+    outs[i] = OutputView{y_dev[i], handles[i]->view.n, 0};
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char *name = nullptr;
+  // Bounded waits of a grouped launch report through the first node's status word.
+  if (accuracy_level == 0 && m == 1) {
+    // one launch: the nodes' tiles form one sequence behind activations staged once
+    name = mnb::LaunchDecodeResidentGroup(nodes, outs, count, a_dev, m, first->status_dev, s, first->sm_count);
+  } else if (accuracy_level == 4 && count > 1) {
+    // activations quantized once, then one integer-MMA launch per node
+    std::size_t need = 0;
+    for (int i = 0; i < count; ++i) {
+      const std::size_t bytes = mnb::Int8MmaScratchBytes(nodes[i], m);
+      need = bytes == 0 ? 0 : (bytes > need ? bytes : need);
+      if (bytes == 0) {
+        break;
+      }
+    }
+    if (need != 0) {
+      const int rc = Grow(&first->scratch_a, &first->scratch_a_bytes, need);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchInt8MmaGroup(nodes, outs, count, a_dev, m, static_cast<unsigned char *>(first->scratch_a),
+                                     first->status_dev, s, first->sm_count);
+    }
+  } else if (accuracy_level == 0 && count > 1 && m <= 16 &&
+             ((nodes[0].block_size == 32 && m >= 5) || (nodes[0].block_size == 64 && m >= 9))) {
+    // digit rows made once, then the three-pass integer-MMA product and its combine per node
+    std::size_t need = 0;
+    for (int i = 0; i < count; ++i) {
+      const std::size_t bytes = mnb::DigitsInt8MmaScratchBytes(nodes[i], m);
+      need = bytes == 0 ? 0 : (bytes > need ? bytes : need);
+      if (bytes == 0) {
+        break;
+      }
+    }
+    if (need != 0) {
+      const int rc = Grow(&first->scratch_a, &first->scratch_a_bytes, need);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchDigitsInt8MmaGroup(nodes, outs, count, a_dev, m,
+                                           static_cast<unsigned char *>(first->scratch_a), first->status_dev, s,
+                                           first->sm_count);
+    }
+  }
+  if (name != nullptr) {
+    mnb::t_last_kernel = name;
+    return MNB_OK;
+  }
+  cudaGetLastError();
+  // no shared form for this group: node by node, as separate calls would run
+  for (int i = 0; i < count; ++i) {
+    const int rc = Dispatch(handles[i], a_dev, m, accuracy_level, MNB_PATH_AUTO, outs[i], s);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+  }
+  return MNB_OK;
 }
 
 int mnb_peer_buffer_create(int device, size_t bytes, void **dev_ptr, unsigned char *handle_out) {

@@ -31,6 +31,8 @@ struct WeightView {
 };
 
 // Where a kernel writes its [m, n] result inside a possibly wider row-major matrix.
+// Nodes that one grouped launch can serve (sibling projections sharing their activations).
+constexpr int kMaxGroupedNodes = 3;
 constexpr int kMaxPeers = 7;
 struct OutputView {
   float *y;
@@ -193,6 +195,11 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
                                  cudaStream_t stream, int sm_count);
+// Up to kMaxGroupedNodes nodes that take the same activations (same K, zero points in all or in
+// none) in one launch; nullptr when the group has no such kernel.
+bool DecodeResidentGroupSupports(const WeightView *nodes, int count, std::int64_t m);
+const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count);
 // Drops the launch plans (tensor maps, slot shapes) cached for a node whose weights are going away.
 void ForgetDecodeResidentPlans(const WeightView &w);
 
@@ -231,6 +238,13 @@ const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int
 std::size_t DigitsInt8MmaScratchBytes(const WeightView &w, std::int64_t m);
 const char *LaunchDigitsInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
                                 OutputView out, int *status_word, cudaStream_t stream, int sm_count);
+// Sibling nodes that take the same activations: quantization / digit rows made once for the group.
+const char *LaunchInt8MmaGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                               std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                               int sm_count);
+const char *LaunchDigitsInt8MmaGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                     std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                     int sm_count);
 
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 

@@ -56,19 +56,29 @@ constexpr int kMaxGroupSlots = 32;
 constexpr int kProducerLanes = 4;         // lanes of the producer warp that issue copies
 constexpr int kChunkRowsBytes = 8 * 128;  // one tile's share of a chunk in shared memory: 8 rows x 128 B
 
-struct ResidentParams {
+// One launch serves up to three nodes that take the same activations (the q / k / v or the gate /
+// up projections of a decoder layer): their tile groups form one sequence, node after node, that
+// goes round the CTAs, so the activations are staged once and no kernel boundary separates the
+// nodes' weight streams.
+struct ResidentNode {
   WeightView w;
-  const float *a;
   OutputView out;
-  int *status;
   int tiles;            // eight-row tiles of the node
+  int groups_end;       // tile groups of the launch below this number belong to this node or an earlier one
+  int group_boxes;      // 1: a full group is fetched by one copy per operand (needs N % 8 == 0)
+};
+
+struct ResidentParams {
+  ResidentNode node[kMaxGroupedNodes];
+  int nodes;
+  const float *a;
+  int *status;
+  int k;
   int steps_per_task;   // 128-byte chunks of a row per task = MMA steps of two segments each
   int parts;            // tasks per tile group (parts of K)
   int group_tiles;      // G: tiles (= consumer warps) whose weights one copy fetches
   int groups;           // consumer warp groups (G warps each)
   int slots_per_group;
-  int strided;          // 1: tile groups go round the CTAs (group x of the node belongs to CTA x % grid)
-  int group_boxes;      // 1: a full group is fetched by one copy per operand (needs N % 8 == 0)
   int early_groups;     // first-round group tasks the producer asks for before the consumers have asked for A
   int segs;             // 128-k segments per weight row
   int table_ints;
@@ -119,15 +129,26 @@ __device__ __forceinline__ void TmaLoadBox4D(std::uint32_t smem_dst, const void 
                : "memory");
 }
 
-// The six tensor maps of a launch: packed weights, scales and prepared zero-point bytes, each for a
-// whole group of tiles (one copy) and for a single tile (the last, short group of a CTA).
-struct ResidentMaps {
+// The six tensor maps of a node: packed weights, scales and prepared zero-point bytes, each for a
+// whole group of tiles (one copy) and for a single tile (the last, short group of a node).
+struct ResidentNodeMaps {
   CUtensorMap w_group;  // 4-D {32 words, 8 rows, chunks, tiles}, box {32, 8, steps, G}
   CUtensorMap w_tile;   // 3-D {32 words, rows, chunks}, box {32, 8, steps}
   CUtensorMap s_group;  // 2-D {blocks, rows}, box {2 steps, 8 G}
   CUtensorMap s_tile;   //                     box {2 steps, 8}
   CUtensorMap z_group;
   CUtensorMap z_tile;
+};
+
+struct ResidentMaps {
+  ResidentNodeMaps node[kMaxGroupedNodes];
+};
+
+// A tile group of the launch: whose it is, its first tile there and how many tiles it has.
+struct GroupPlace {
+  int node;
+  int tile0;
+  int count;
 };
 
 template <bool HAS_ZP>
@@ -165,26 +186,27 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   const int lane = tid & 31;
   const int grid = static_cast<int>(gridDim.x);
   const int cta = static_cast<int>(blockIdx.x);
-  // this CTA's tiles: a contiguous range, split as evenly as the grid allows
-  const int tile_begin = static_cast<int>(static_cast<std::int64_t>(cta) * p.tiles / grid);
-  const int tile_end = static_cast<int>(static_cast<std::int64_t>(cta + 1) * p.tiles / grid);
-  int local_tiles = tile_end - tile_begin;
-  const int node_groups = (p.tiles + G - 1) / G;
-  if (p.strided != 0) {
-    // groups cta, cta + grid, ... of the node; the node's last group may be short
-    const int my_groups = cta < node_groups ? (node_groups - cta + grid - 1) / grid : 0;
-    local_tiles = my_groups * G;
-    if (my_groups > 0 && (cta + (my_groups - 1) * grid) == node_groups - 1) {
-      local_tiles -= node_groups * G - p.tiles;
+  // the launch's tile groups cta, cta + grid, ... are this CTA's; the last group of a node may be short
+  const int total_groups = p.node[p.nodes - 1].groups_end;
+  const int my_groups = cta < total_groups ? (total_groups - cta + grid - 1) / grid : 0;
+  auto place_of = [&](int local_group) {
+    const int id = cta + local_group * grid;
+    GroupPlace at{0, 0, 0};
+    int first = 0;
+#pragma unroll
+    for (int i = 0; i + 1 < kMaxGroupedNodes; ++i) {
+      if (i + 1 < p.nodes && id >= p.node[i].groups_end) {
+        at.node = i + 1;
+        first = p.node[i].groups_end;
+      }
     }
-  }
-  // first tile of the node behind this CTA's local tile index (a multiple of G)
-  auto node_tile = [&](int first_local) {
-    return p.strided != 0 ? (cta + (first_local / G) * grid) * G : tile_begin + first_local;
+    at.tile0 = (id - first) * G;
+    const int left = p.node[at.node].tiles - at.tile0;
+    at.count = left < G ? left : G;
+    return at;
   };
-  // round r gives group j the local tiles (r * groups + j) * G ... + G - 1
-  const int tiles_per_round = consumers;
-  const int rounds = (local_tiles + tiles_per_round - 1) / tiles_per_round;
+  // round r gives consumer group j the CTA's local tile group r * groups + j
+  const int rounds = (my_groups + groups - 1) / groups;
   const int consumer_threads = consumers * 32;
 
   if (warp == consumers) {
@@ -208,11 +230,13 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
     auto issue_tasks = [&](int q, int j_begin, int j_end) -> bool {
       bool any = false;
       for (int j = j_begin + lane; j < j_end && ok; j += kProducerLanes) {
-        const int first_local = ((q / p.parts) * groups + j) * G;
-        if (first_local >= local_tiles) {
+        const int local_group = (q / p.parts) * groups + j;
+        if (local_group >= my_groups) {
           continue;
         }
         any = true;
+        const GroupPlace at = place_of(local_group);
+        const ResidentNodeMaps &node_maps = maps.node[at.node];
         const int part = q % p.parts;
         const int slot = j * p.slots_per_group + (q % p.slots_per_group);
         const int use = q / p.slots_per_group;  // how often this slot has been filled before
@@ -221,27 +245,27 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
           ok = false;
           break;
         }
-        const int count = local_tiles - first_local < G ? local_tiles - first_local : G;
-        const int tile0 = node_tile(first_local);
+        const int count = at.count;
+        const int tile0 = at.tile0;
         const std::uint32_t w_at = ptx::SmemAddr(weight_slots) + slot * weight_slot_bytes;
         const std::uint32_t s_at = ptx::SmemAddr(scale_slots) + slot * scale_slot_bytes;
         const std::uint32_t z_at = ptx::SmemAddr(zero_slots) + slot * zero_slot_bytes;
         ptx::MbarArriveExpectTx(&full_bar[slot], static_cast<std::uint32_t>(count) * tile_bytes);
-        if (count == G && p.group_boxes != 0) {
+        if (count == G && p.node[at.node].group_boxes != 0) {
           // the whole group in one copy per operand
-          TmaLoadBox4D(w_at, &maps.w_group, 0, 0, part * steps, tile0, &full_bar[slot]);
-          TmaLoadBox2D(s_at, &maps.s_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
+          TmaLoadBox4D(w_at, &node_maps.w_group, 0, 0, part * steps, tile0, &full_bar[slot]);
+          TmaLoadBox2D(s_at, &node_maps.s_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
           if constexpr (HAS_ZP) {
-            TmaLoadBox2D(z_at, &maps.z_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
+            TmaLoadBox2D(z_at, &node_maps.z_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
           }
         } else {
           // a short group (the end of this CTA's range): tile by tile, same places in the slot
           for (int i = 0; i < count; ++i) {
             const int row0 = (tile0 + i) * 8;
-            TmaLoadBox3D(w_at + i * weight_tile_bytes, &maps.w_tile, 0, row0, part * steps, &full_bar[slot]);
-            TmaLoadBox2D(s_at + i * scale_tile_bytes, &maps.s_tile, part * steps * 2, row0, &full_bar[slot]);
+            TmaLoadBox3D(w_at + i * weight_tile_bytes, &node_maps.w_tile, 0, row0, part * steps, &full_bar[slot]);
+            TmaLoadBox2D(s_at + i * scale_tile_bytes, &node_maps.s_tile, part * steps * 2, row0, &full_bar[slot]);
             if constexpr (HAS_ZP) {
-              TmaLoadBox2D(z_at + i * zero_tile_bytes, &maps.z_tile, part * steps * 2, row0, &full_bar[slot]);
+              TmaLoadBox2D(z_at + i * zero_tile_bytes, &node_maps.z_tile, part * steps * 2, row0, &full_bar[slot]);
             }
           }
         }
@@ -250,13 +274,15 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
     };
     const int early = p.early_groups < groups ? p.early_groups : groups;
     if (lane < kProducerLanes) {
-      ptx::PrefetchTensorMap(&maps.w_group);
-      ptx::PrefetchTensorMap(&maps.s_group);
-      ptx::PrefetchTensorMap(&maps.w_tile);
-      ptx::PrefetchTensorMap(&maps.s_tile);
-      if constexpr (HAS_ZP) {
-        ptx::PrefetchTensorMap(&maps.z_group);
-        ptx::PrefetchTensorMap(&maps.z_tile);
+      for (int i = 0; i < p.nodes; ++i) {
+        ptx::PrefetchTensorMap(&maps.node[i].w_group);
+        ptx::PrefetchTensorMap(&maps.node[i].s_group);
+        ptx::PrefetchTensorMap(&maps.node[i].w_tile);
+        ptx::PrefetchTensorMap(&maps.node[i].s_tile);
+        if constexpr (HAS_ZP) {
+          ptx::PrefetchTensorMap(&maps.node[i].z_group);
+          ptx::PrefetchTensorMap(&maps.node[i].z_tile);
+        }
       }
       issue_tasks(0, 0, early);
     }
@@ -275,7 +301,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         // tasks of group j: rounds in which it has at least one tile, times parts
         int my_rounds = 0;
         for (int r = 0; r < rounds; ++r) {
-          if ((r * groups + j) * G < local_tiles) {
+          if (r * groups + j < my_groups) {
             ++my_rounds;
           }
         }
@@ -296,7 +322,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   // A (and Y) may be produced / still read by the previous kernel in the stream: from here on the
   // consumers depend on it. The producer above only touches the constant weights.
   ptx::GridDependencyWait();
-  const DigitGeometry geometry{static_cast<int>(p.w.k), p.segs, kDigits * kChunkBytes, p.table_ints};
+  const DigitGeometry geometry{p.k, p.segs, kDigits * kChunkBytes, p.table_ints};
   StageDigits<true>(
       geometry, p.a, 1, 1, digits, table, undo, red, tid, consumer_threads,
       [&] { asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory"); },
@@ -333,12 +359,12 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
 
   int q = 0;  // this group's task counter
   for (int round = 0; round < rounds; ++round) {
-    const int first_local = (round * groups + group) * G;
-    if (first_local >= local_tiles) {
+    const int local_group = round * groups + group;
+    if (local_group >= my_groups) {
       break;  // the whole group is done (all its warps see the same)
     }
-    const int local_tile = first_local + member;
-    const bool has_tile = local_tile < local_tiles;  // the last group of a CTA may be short of tiles
+    const GroupPlace at = place_of(local_group);
+    const bool has_tile = member < at.count;  // the last group of a node may be short of tiles
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     bool dead = false;
     for (int part = 0; part < p.parts; ++part, ++q) {
@@ -438,10 +464,11 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
                        : 0.0f;
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
-    const std::int64_t row = static_cast<std::int64_t>(node_tile(first_local) + member) * 8 + rho;
-    if (!dead && t == 0 && row < p.w.n) {
-      const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + row) : 0.0f;
-      StoreOutput(p.out, p.out.col_offset + row, fmaf(v, undo[0], bias));
+    const ResidentNode &node = p.node[at.node];
+    const std::int64_t row = static_cast<std::int64_t>(at.tile0 + member) * 8 + rho;
+    if (!dead && t == 0 && row < node.w.n) {
+      const float bias = node.w.bias != nullptr ? __ldg(node.w.bias + row) : 0.0f;
+      StoreOutput(node.out, node.out.col_offset + row, fmaf(v, undo[0], bias));
     }
   }
 }
@@ -491,38 +518,57 @@ bool DecodeResidentSupports(const WeightView &w, std::int64_t m) {
 
 namespace {
 
-// Everything of a launch that depends on the node only: slot shape, tensor maps, grid. Built once
-// per node (six cuTensorMapEncodeTiled calls and a cudaFuncSetAttribute cost several microseconds,
-// as much as the kernel's share of a host-buffer call) and kept until the node's weights go.
+// Everything of a launch that depends on the nodes only: slot shape, tensor maps, grid. Built once
+// per node group (six cuTensorMapEncodeTiled calls per node and a cudaFuncSetAttribute cost several
+// microseconds, as much as the kernel's share of a host-buffer call) and kept until the weights go.
 struct ResidentPlan {
   ResidentMaps maps;
-  ResidentParams params;  // a, out and status are filled per launch
+  ResidentParams params;  // a, the outputs and status are filled per launch
   size_t smem = 0;
   int ctas = 0;
   int threads = 0;
 };
 
 struct PlanKey {
-  const void *b, *scales, *zp16;
-  std::int64_t n, k;
+  const void *b[kMaxGroupedNodes];
+  const void *scales[kMaxGroupedNodes];
+  const void *zp16[kMaxGroupedNodes];
+  std::int64_t n[kMaxGroupedNodes];
+  std::int64_t k;
+  int nodes;
   int sms;
   bool operator==(const PlanKey &o) const {
-    return b == o.b && scales == o.scales && zp16 == o.zp16 && n == o.n && k == o.k && sms == o.sms;
+    if (nodes != o.nodes || k != o.k || sms != o.sms) {
+      return false;
+    }
+    for (int i = 0; i < nodes; ++i) {
+      if (b[i] != o.b[i] || scales[i] != o.scales[i] || zp16[i] != o.zp16[i] || n[i] != o.n[i]) {
+        return false;
+      }
+    }
+    return true;
   }
 };
 
 std::mutex g_plan_mutex;
 std::vector<std::pair<PlanKey, std::unique_ptr<ResidentPlan>>> g_plans;
 
-bool BuildPlan(const WeightView &w, int sms, ResidentPlan *plan) {
+bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) {
   ResidentParams &p = plan->params;
   p = ResidentParams{};
-  p.w = w;
+  const WeightView &w = nodes[0];  // K, block size and the presence of zero points are the group's
+  p.nodes = count;
+  p.k = static_cast<int>(w.k);
   p.segs = w.n_blocks;
   p.table_ints = (p.segs / 2) * 8;
-  p.tiles = static_cast<int>((w.n + 7) / 8);
-  const int ctas = sms < p.tiles ? sms : p.tiles;
-  const int tiles_per_cta = (p.tiles + ctas - 1) / ctas;
+  std::int64_t tiles = 0;
+  for (int i = 0; i < count; ++i) {
+    p.node[i].w = nodes[i];
+    p.node[i].tiles = static_cast<int>((nodes[i].n + 7) / 8);
+    tiles += p.node[i].tiles;
+  }
+  const int ctas = sms < tiles ? sms : static_cast<int>(tiles);
+  const int tiles_per_cta = static_cast<int>((tiles + ctas - 1) / ctas);
   const int chunks = w.row_bytes / 128;  // MMA steps of a whole row
   const size_t fixed = static_cast<size_t>(p.segs) * kDigits * kChunkBytes + static_cast<size_t>(p.table_ints) * 4 +
                        (kMaxTokens + kMaxTokens * kMaxWarps) * sizeof(float) +
@@ -544,19 +590,21 @@ bool BuildPlan(const WeightView &w, int sms, ResidentPlan *plan) {
     }
     return c;
   };
-  // First choice: a whole row of K per task, tiles fetched in groups of two, one slot per group,
-  // taken when (nearly) every tile of the CTA then has a place of its own. Else tasks of at most
-  // sixteen chunks, single tiles, two slots each, so that a warp's next task is on its way while
-  // it works.
+  // First choice: a whole row of K per task, tiles fetched in groups of two, one slot per group;
+  // a CTA with more tile groups than slots refills a slot as soon as its group has released it
+  // (with twelve warps at work about half of the slots are in flight at any time, which covers the
+  // memory latency). Rows too long for that: tasks of at most sixteen chunks, single tiles, two
+  // slots each.
   // Measured on the decoder projection (N = 14336, K = 4096, us per launch in a CUDA graph, one
   // box): groups of 2 / 4 / 1 tiles 8.47 / 8.48 / 8.95 with the groups going round the CTAs, 9.5 /
   // 9.6 / 9.1 with a contiguous range of tiles per CTA; 2 groups asked for before the activations
-  // 8.47, 1: 8.71, 3: 9.07, none: 9.5.
+  // 8.47, 1: 8.71, 3: 9.07, none: 9.5. Two such nodes in one launch (25 tiles per CTA): 6.77 per
+  // node with this shape, 7.55 with the two-slot shape.
   int group_tiles = 2;
   int steps = chunks;
   int slots_per_group = 1;
   int warps = chunks <= 256 ? most_warps(1, steps, group_tiles) : 0;
-  if (warps < group_tiles || tiles_per_cta > warps + (warps + 3) / 4) {
+  if (warps < group_tiles) {
     group_tiles = 1;
     slots_per_group = 2;
     steps = 0;
@@ -579,44 +627,55 @@ bool BuildPlan(const WeightView &w, int sms, ResidentPlan *plan) {
   }
   p.steps_per_task = steps;
   p.parts = chunks / steps;
+  p.group_tiles = group_tiles;
   p.groups = warps / group_tiles;
   p.slots_per_group = slots_per_group;
   if (p.groups * slots_per_group > kMaxGroupSlots) {
     return false;
   }
-  p.strided = 1;
   p.early_groups = 2;
   plan->smem = fixed + static_cast<size_t>(warps) * slots_per_group * steps * per_step;
   plan->ctas = ctas;
   plan->threads = (warps + 1) * 32;
 
-  ResidentMaps &maps = plan->maps;
-  if (!EncodeWeightTileMap(&maps.w_tile, w, steps)) {
-    return false;
+  int groups_end = 0;
+  for (int i = 0; i < count; ++i) {
+    const WeightView &node = nodes[i];
+    ResidentNodeMaps &maps = plan->maps.node[i];
+    groups_end += (p.node[i].tiles + group_tiles - 1) / group_tiles;
+    p.node[i].groups_end = groups_end;
+    if (!EncodeWeightTileMap(&maps.w_tile, node, steps)) {
+      return false;
+    }
+    p.node[i].group_boxes =
+        (group_tiles > 1 && EncodeWeightGroupMap(&maps.w_group, node, steps, group_tiles)) ? 1 : 0;
+    if (p.node[i].group_boxes == 0) {
+      maps.w_group = maps.w_tile;
+    }
+    auto rows_map = [&](CUtensorMap *map, bool zero_points, int rows) {
+      return zero_points
+                 ? EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, node.zp16,
+                               static_cast<std::uint64_t>(node.n_blocks), static_cast<std::uint64_t>(node.n),
+                               static_cast<std::uint64_t>(node.n_blocks), static_cast<std::uint32_t>(2 * steps),
+                               static_cast<std::uint32_t>(rows), CU_TENSOR_MAP_SWIZZLE_NONE)
+                 : EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, node.scales,
+                               static_cast<std::uint64_t>(node.n_blocks), static_cast<std::uint64_t>(node.n),
+                               static_cast<std::uint64_t>(node.n_blocks) * 4, static_cast<std::uint32_t>(2 * steps),
+                               static_cast<std::uint32_t>(rows), CU_TENSOR_MAP_SWIZZLE_NONE);
+    };
+    if (!rows_map(&maps.s_tile, false, 8) || !rows_map(&maps.s_group, false, 8 * group_tiles)) {
+      return false;
+    }
+    maps.z_tile = maps.s_tile;
+    maps.z_group = maps.s_group;
+    if (node.zp != nullptr && (!rows_map(&maps.z_tile, true, 8) || !rows_map(&maps.z_group, true, 8 * group_tiles))) {
+      return false;
+    }
   }
-  p.group_tiles = group_tiles;
-  p.group_boxes = (group_tiles > 1 && EncodeWeightGroupMap(&maps.w_group, w, steps, group_tiles)) ? 1 : 0;
-  if (p.group_boxes == 0) {
-    maps.w_group = maps.w_tile;
-  }
-  auto rows_map = [&](CUtensorMap *map, bool zero_points, int rows) {
-    return zero_points
-               ? EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.zp16, static_cast<std::uint64_t>(w.n_blocks),
-                             static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.n_blocks),
-                             static_cast<std::uint32_t>(2 * steps), static_cast<std::uint32_t>(rows),
-                             CU_TENSOR_MAP_SWIZZLE_NONE)
-               : EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, w.scales,
-                             static_cast<std::uint64_t>(w.n_blocks), static_cast<std::uint64_t>(w.n),
-                             static_cast<std::uint64_t>(w.n_blocks) * 4, static_cast<std::uint32_t>(2 * steps),
-                             static_cast<std::uint32_t>(rows), CU_TENSOR_MAP_SWIZZLE_NONE);
-  };
-  if (!rows_map(&maps.s_tile, false, 8) || !rows_map(&maps.s_group, false, 8 * group_tiles)) {
-    return false;
-  }
-  maps.z_tile = maps.s_tile;
-  maps.z_group = maps.s_group;
-  if (w.zp != nullptr && (!rows_map(&maps.z_tile, true, 8) || !rows_map(&maps.z_group, true, 8 * group_tiles))) {
-    return false;
+  for (int i = count; i < kMaxGroupedNodes; ++i) {
+    plan->maps.node[i] = plan->maps.node[0];
+    p.node[i] = p.node[0];
+    p.node[i].groups_end = groups_end;
   }
   // The function attribute belongs to the kernel, not to the node: it is raised to the most any
   // plan can ask for, so that plans of different sizes do not undo one another.
@@ -628,9 +687,18 @@ bool BuildPlan(const WeightView &w, int sms, ResidentPlan *plan) {
   return err == cudaSuccess;
 }
 
-// The plan of a node, built on first use. nullptr when the node's shape has none.
-const ResidentPlan *PlanFor(const WeightView &w, int sms) {
-  const PlanKey key{w.b, w.scales, w.zp != nullptr ? w.zp16 : nullptr, w.n, w.k, sms};
+// The plan of a node group, built on first use. nullptr when the shape has none.
+const ResidentPlan *PlanFor(const WeightView *nodes, int count, int sms) {
+  PlanKey key{};
+  key.nodes = count;
+  key.k = nodes[0].k;
+  key.sms = sms;
+  for (int i = 0; i < count; ++i) {
+    key.b[i] = nodes[i].b;
+    key.scales[i] = nodes[i].scales;
+    key.zp16[i] = nodes[i].zp != nullptr ? nodes[i].zp16 : nullptr;
+    key.n[i] = nodes[i].n;
+  }
   std::lock_guard<std::mutex> lock(g_plan_mutex);
   for (const auto &entry : g_plans) {
     if (entry.first == key) {
@@ -638,7 +706,7 @@ const ResidentPlan *PlanFor(const WeightView &w, int sms) {
     }
   }
   auto plan = std::make_unique<ResidentPlan>();
-  if (!BuildPlan(w, sms, plan.get())) {
+  if (!BuildPlan(nodes, count, sms, plan.get())) {
     cudaGetLastError();
     return nullptr;
   }
@@ -648,11 +716,15 @@ const ResidentPlan *PlanFor(const WeightView &w, int sms) {
 
 } // namespace
 
-// Called when a node's weights are destroyed: its plan names their addresses.
+// Called when a node's weights are destroyed: the plans it takes part in name their addresses.
 void ForgetDecodeResidentPlans(const WeightView &w) {
   std::lock_guard<std::mutex> lock(g_plan_mutex);
   for (size_t i = 0; i < g_plans.size();) {
-    if (g_plans[i].first.b == w.b) {
+    bool names = false;
+    for (int x = 0; x < g_plans[i].first.nodes; ++x) {
+      names = names || g_plans[i].first.b[x] == w.b;
+    }
+    if (names) {
       g_plans.erase(g_plans.begin() + static_cast<std::ptrdiff_t>(i));
     } else {
       ++i;
@@ -660,19 +732,35 @@ void ForgetDecodeResidentPlans(const WeightView &w) {
   }
 }
 
-const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
-                                 cudaStream_t stream, int sm_count) {
-  if (!DecodeResidentSupports(w, m)) {
+bool DecodeResidentGroupSupports(const WeightView *nodes, int count, std::int64_t m) {
+  if (count < 1 || count > kMaxGroupedNodes) {
+    return false;
+  }
+  for (int i = 0; i < count; ++i) {
+    if (!DecodeResidentSupports(nodes[i], m) || nodes[i].k != nodes[0].k ||
+        (nodes[i].zp != nullptr) != (nodes[0].zp != nullptr)) {
+      return false;
+    }
+  }
+  return true;
+}
+
+const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count) {
+  if (!DecodeResidentGroupSupports(nodes, count, m)) {
     return nullptr;
   }
-  const ResidentPlan *plan = PlanFor(w, sm_count > 0 ? sm_count : 148);
+  const ResidentPlan *plan = PlanFor(nodes, count, sm_count > 0 ? sm_count : 148);
   if (plan == nullptr) {
     return nullptr;
   }
   ResidentParams p = plan->params;
-  p.w = w;
+  for (int i = 0; i < kMaxGroupedNodes; ++i) {
+    const int from = i < count ? i : 0;
+    p.node[i].w = nodes[from];  // bias may differ between calls; the addresses in the maps do not
+    p.node[i].out = outs[from];
+  }
   p.a = a;
-  p.out = out;
   p.status = status_word;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(plan->ctas), 1, 1);
@@ -684,7 +772,7 @@ const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  const cudaError_t err = w.zp != nullptr
+  const cudaError_t err = nodes[0].zp != nullptr
                               ? cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<true>, plan->maps, p)
                               : cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<false>, plan->maps, p);
   if (err != cudaSuccess) {
@@ -693,6 +781,11 @@ const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64
   }
   CountLaunch();
   return "nbits_decode_resident_kernel";
+}
+
+const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
+                                 cudaStream_t stream, int sm_count) {
+  return LaunchDecodeResidentGroup(&w, &out, 1, a, m, status_word, stream, sm_count);
 }
 
 } // namespace mnb

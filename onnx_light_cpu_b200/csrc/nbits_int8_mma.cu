@@ -647,6 +647,50 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
   return LaunchMultiply(w, geo, m, scratch, out, status_word, stream, sm_count);
 }
 
+namespace {
+// Nodes of a group share one activation layout when the layout's sizes and the table scale agree.
+bool SameActivationLayout(const WeightView &a, const ImmaGeometry &ga, const WeightView &b, const ImmaGeometry &gb) {
+  return a.k == b.k && a.block_size == b.block_size && (a.zp != nullptr) == (b.zp != nullptr) && ga.tp == gb.tp &&
+         ga.passes == gb.passes && ga.act_row_bytes == gb.act_row_bytes && ga.table_offset == gb.table_offset &&
+         ga.pass_bytes == gb.pass_bytes && ga.entry_k == gb.entry_k && ga.entries_pad == gb.entries_pad;
+}
+} // namespace
+
+// Sibling nodes (same K, block size, zero points in all or none): the activations are quantized
+// once into `scratch` and every node's integer-MMA kernel reads them from there.
+const char *LaunchInt8MmaGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                               std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                               int sm_count) {
+  if (count < 1 || count > kMaxGroupedNodes || scratch == nullptr) {
+    return nullptr;
+  }
+  const WeightView &w = nodes[0];
+  const ImmaGeometry geo = ImmaGeometryOf(w, m);
+  if (!geo.ok) {
+    return nullptr;
+  }
+  for (int i = 0; i < count; ++i) {
+    if (nodes[i].meta == nullptr || !SameActivationLayout(w, geo, nodes[i], ImmaGeometryOf(nodes[i], m))) {
+      return nullptr;
+    }
+  }
+  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
+  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  for (int i = 0; i < count; ++i) {
+    if (LaunchMultiply(nodes[i], ImmaGeometryOf(nodes[i], m), m, scratch, outs[i], status_word, stream, sm_count) ==
+        nullptr) {
+      return nullptr;
+    }
+  }
+  return "nbits_int8_mma_kernel";
+}
+
 // Parity instrument: quantizes `a` like LaunchInt8Mma and runs the instrumented form of the kernel,
 // which also adds its exact int32 block dots to `dots` ([m, n, n_blocks], zeroed here). m <= 8.
 const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
@@ -896,6 +940,75 @@ std::size_t AlignUp(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
 
 } // namespace
 
+namespace {
+
+struct DigitsScratch {
+  unsigned char *act;
+  float *factors;
+  float *partial;
+};
+
+DigitsScratch DigitsScratchOf(const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch) {
+  DigitsScratch at{};
+  at.act = scratch;
+  at.factors = reinterpret_cast<float *>(scratch + AlignUp(static_cast<std::size_t>(geo.passes) * geo.pass_bytes));
+  at.partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(at.factors) + AlignUp(3 * m * sizeof(float)));
+  return at;
+}
+
+// Row factors and digit rows of `a` into the scratch area: the part that sibling nodes share.
+bool LaunchDigitRows(const WeightView &w, const ImmaGeometry &geo, const float *a, std::int64_t m,
+                     const DigitsScratch &at, cudaStream_t stream) {
+  nbits_digit_row_factors_kernel<<<static_cast<unsigned>(m), 256, 0, stream>>>(a, static_cast<int>(m), w.k, at.factors);
+  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
+  nbits_digits_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
+      a, at.factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, at.act);
+  if (cudaGetLastError() != cudaSuccess) {
+    return false;
+  }
+  CountLaunch(2);
+  return true;
+}
+
+// One node over digit rows that are already in the scratch area: three partial rows per token,
+// then their sum plus the bias.
+bool LaunchDigitsNode(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, const DigitsScratch &at,
+                      OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+  WeightView no_bias = w;
+  no_bias.bias = nullptr;
+  OutputView to_partial{};
+  to_partial.y = at.partial;
+  to_partial.ld = w.n;
+  to_partial.col_offset = 0;
+  if (LaunchMultiply(no_bias, geo, 3 * m, at.act, to_partial, status_word, stream, sm_count) == nullptr) {
+    return false;
+  }
+  const bool vector_ok = (w.n % 4) == 0 && (out.ld % 4) == 0 && (out.col_offset % 4) == 0 && out.n_peers == 0 &&
+                         (reinterpret_cast<std::uintptr_t>(out.y) & 15u) == 0 &&
+                         (reinterpret_cast<std::uintptr_t>(w.bias) & 15u) == 0;
+  if (vector_ok) {
+    const std::int64_t n4 = w.n / 4;
+    std::int64_t blocks_x = (n4 + 255) / 256;
+    blocks_x = blocks_x > 148 ? 148 : blocks_x;
+    nbits_digits_combine_vec_kernel<<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(m)), 256, 0, stream>>>(
+        reinterpret_cast<const float4 *>(at.partial), reinterpret_cast<const float4 *>(w.bias), n4, out);
+  } else {
+    const std::int64_t total = m * w.n;
+    std::int64_t blocks = (total + 255) / 256;
+    blocks = blocks > 148 * 8 ? 148 * 8 : blocks;
+    nbits_digits_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(at.partial, w.bias,
+                                                                                static_cast<int>(m), w.n, out);
+  }
+  if (cudaGetLastError() != cudaSuccess) {
+    return false;
+  }
+  CountLaunch();
+  return true;
+}
+
+} // namespace
+
 std::size_t DigitsInt8MmaScratchBytes(const WeightView &w, std::int64_t m) {
   const ImmaGeometry geo = ImmaGeometryOf(w, 3 * m);
   if (!geo.ok) {
@@ -907,51 +1020,36 @@ std::size_t DigitsInt8MmaScratchBytes(const WeightView &w, std::int64_t m) {
 
 const char *LaunchDigitsInt8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch,
                                 OutputView out, int *status_word, cudaStream_t stream, int sm_count) {
+  return LaunchDigitsInt8MmaGroup(&w, &out, 1, a, m, scratch, status_word, stream, sm_count);
+}
+
+// Sibling nodes: the digit rows are made once; `scratch` holds DigitsInt8MmaScratchBytes of the
+// node with the most columns.
+const char *LaunchDigitsInt8MmaGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                     std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                     int sm_count) {
+  if (count < 1 || count > kMaxGroupedNodes || scratch == nullptr || m < 1 || m > 16) {
+    return nullptr;
+  }
+  const WeightView &w = nodes[0];
   const ImmaGeometry geo = ImmaGeometryOf(w, 3 * m);
-  if (!geo.ok || w.meta == nullptr || scratch == nullptr || m < 1 || m > 16) {
+  if (!geo.ok) {
     return nullptr;
   }
-  unsigned char *act = scratch;
-  float *factors = reinterpret_cast<float *>(scratch + AlignUp(static_cast<std::size_t>(geo.passes) * geo.pass_bytes));
-  float *partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(factors) + AlignUp(3 * m * sizeof(float)));
-  nbits_digit_row_factors_kernel<<<static_cast<unsigned>(m), 256, 0, stream>>>(a, static_cast<int>(m), w.k, factors);
-  const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
-  nbits_digits_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-      a, factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
-      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, act);
-  if (cudaGetLastError() != cudaSuccess) {
+  for (int i = 0; i < count; ++i) {
+    if (nodes[i].meta == nullptr || !SameActivationLayout(w, geo, nodes[i], ImmaGeometryOf(nodes[i], 3 * m))) {
+      return nullptr;
+    }
+  }
+  const DigitsScratch at = DigitsScratchOf(geo, m, scratch);
+  if (!LaunchDigitRows(w, geo, a, m, at, stream)) {
     return nullptr;
   }
-  CountLaunch(2);
-  WeightView no_bias = w;
-  no_bias.bias = nullptr;
-  OutputView to_partial{};
-  to_partial.y = partial;
-  to_partial.ld = w.n;
-  to_partial.col_offset = 0;
-  if (LaunchMultiply(no_bias, geo, 3 * m, act, to_partial, status_word, stream, sm_count) == nullptr) {
-    return nullptr;
+  for (int i = 0; i < count; ++i) {
+    if (!LaunchDigitsNode(nodes[i], ImmaGeometryOf(nodes[i], 3 * m), m, at, outs[i], status_word, stream, sm_count)) {
+      return nullptr;
+    }
   }
-  const bool vector_ok = (w.n % 4) == 0 && (out.ld % 4) == 0 && (out.col_offset % 4) == 0 && out.n_peers == 0 &&
-                         (reinterpret_cast<std::uintptr_t>(out.y) & 15u) == 0 &&
-                         (reinterpret_cast<std::uintptr_t>(w.bias) & 15u) == 0;
-  if (vector_ok) {
-    const std::int64_t n4 = w.n / 4;
-    std::int64_t blocks_x = (n4 + 255) / 256;
-    blocks_x = blocks_x > 148 ? 148 : blocks_x;
-    nbits_digits_combine_vec_kernel<<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(m)), 256, 0, stream>>>(
-        reinterpret_cast<const float4 *>(partial), reinterpret_cast<const float4 *>(w.bias), n4, out);
-  } else {
-    const std::int64_t total = m * w.n;
-    std::int64_t blocks = (total + 255) / 256;
-    blocks = blocks > 148 * 8 ? 148 * 8 : blocks;
-    nbits_digits_combine_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, w.bias,
-                                                                                static_cast<int>(m), w.n, out);
-  }
-  if (cudaGetLastError() != cudaSuccess) {
-    return nullptr;
-  }
-  CountLaunch();
   return "nbits_int8_mma_kernel(digits)";
 }
 

@@ -93,6 +93,33 @@ def _check_device_tensor(what, tensor, dtype_name, device, min_elements=0):
         raise ValueError(f"{what} holds {tensor.numel()} elements, {min_elements} are needed")
 
 
+MAX_GROUPED_NODES = 3
+
+
+def matmul_device_group(nodes, a, ys, accuracy_level=0, stream=None) -> None:
+    """Sibling nodes that take the same activations (q / k / v, gate / up) in one call:
+    ``ys[i] = nodes[i](a)``, each ``ys[i]`` a dense fp32 CUDA tensor [m, N_i]. One to three
+    :class:`MatMulNBitsWeights` with the same K on the same GPU. Asynchronous on ``stream``."""
+    import ctypes
+
+    import torch
+
+    nodes = list(nodes)
+    ys = list(ys)
+    if not 1 <= len(nodes) <= MAX_GROUPED_NODES or len(ys) != len(nodes):
+        raise ValueError(f"a group takes 1 to {MAX_GROUPED_NODES} nodes and as many outputs")
+    first = nodes[0]
+    m = first._rows_of(a)
+    for node, y in zip(nodes, ys):
+        if node.k != first.k or node.device != first.device:
+            raise ValueError("the nodes of a group take the same activations: same K, same GPU")
+        _check_device_tensor("y", y, "float32", node.device, m * node.n)
+    raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
+    handles = (ctypes.c_void_p * len(nodes))(*[node._handle for node in nodes])
+    outputs = (ctypes.c_void_p * len(nodes))(*[y.data_ptr() for y in ys])
+    _capi.check(first._lib.mnb_matmul_device_group(handles, len(nodes), a.data_ptr(), m, accuracy_level, outputs, raw))
+
+
 class MatMulNBitsWeights:
     """Device-resident weights of one node plus the device-pointer entry points.
 
