@@ -576,8 +576,11 @@ def main() -> None:
             y_full = [gather.result(i) for i in range(copies)]
 
             def step():
+                # every node pushes its columns to the peers and publishes "stored" from its own last
+                # CTA; only the step's last node then waits for the other ranks' flags (seeing a rank's
+                # flag of a node implies its earlier nodes: every rank runs the nodes in this order)
                 for i, w in enumerate(weights):
-                    gather.run(w, a, i)
+                    gather.run(w, a, i, wait=(i == copies - 1))
         else:
             y_shard = [torch.empty(m, shard_cfg["n"], device="cuda") for _ in range(copies)]
             y_full = [torch.empty(world, m, shard_cfg["n"], device="cuda") for _ in range(copies)]
@@ -625,7 +628,8 @@ def main() -> None:
             clocks.hold(replay, torch)
         gpu_launches = launches_timed * world
         value = full_bytes * copies * args.steps / seconds / 1e9
-        how = "peer-store gather inside the kernel" if gather is not None else "NCCL all-gather"
+        how = ("peer stores, flag publish and the step's one flag wait inside the nodes' kernels"
+               if gather is not None else "NCCL all-gather")
         config = workload_config(True, copies, full_bytes)
         details = {"shard_columns": shard_cfg["n"], "gathered_layout": "[ranks, M, N/ranks]", "kernel": kernel_name,
                    "cuda_graph": graphed, "gather": args.gather, "gather_how": how, "gather_checked": gather_checked}
@@ -662,32 +666,56 @@ def main() -> None:
                "h2d_bytes_per_step": copies * a_host.numel() * 4, "d2h_bytes_per_step": copies * y_host.numel() * 4}
 
         if not args.skip_extras:
-            # ---- M = 8 through the same gathered path (cfg5 lists M in {1, 8, 256}) ----
+            # ---- the other sizes of the configuration through the same gathered path: M in {8, 256},
+            # 8-bit weights (shapes the decode kernels do not take run through the ordinary dispatch
+            # and one kernel that copies the local window to the peers) ----
             if gather is not None:
-                gather8 = sharded.PeerGather(dist, local_rank, m_max=8, n_shard=shard_cfg["n"], slots=copies)
-                a8 = torch.randn(8, cfg["k"], device="cuda")
-                dist.broadcast(a8, src=0)
+                for key, m_x, bits_x in (("lmhead_m8", 8, 4), ("lmhead_m256", 256, 4), ("lmhead_bits8_m1", 1, 8),
+                                         ("lmhead_bits8_m8", 8, 8)):
+                    cfg_x = dict(shard_cfg, bits=bits_x)
+                    w_x = weights if bits_x == cfg["bits"] else device_weights(torch, pkg, cfg_x, copies,
+                                                                               seed=1580 + rank, zp=True, bias=False)
+                    gather_x = sharded.PeerGather(dist, local_rank, m_max=m_x, n_shard=shard_cfg["n"], slots=copies)
+                    a_x = torch.randn(m_x, cfg["k"], device="cuda")
+                    dist.broadcast(a_x, src=0)
 
-                def step8():
-                    for i, w in enumerate(weights):
-                        gather8.run(w, a8, i)
+                    def step_x():
+                        for i, w in enumerate(w_x):
+                            gather_x.run(w, a_x, i, wait=(i == copies - 1))
 
-                step8()
-                torch.cuda.synchronize()
-                name8 = _capi.last_kernel()
-                rep8, graphed8 = capture_graph(torch, step8)
-                ok8 = torch.tensor([1 if graphed8 else 0], device="cuda")
-                dist.all_reduce(ok8, op=dist.ReduceOp.MIN)
-                if int(ok8.item()) == 1:
-                    steps8 = max(5, args.steps // 4)
-                    sec8 = time_steps(torch, dist, rep8, steps8, 3, world)
-                    bytes8 = _capi.algorithmic_bytes(8, cfg["n"], cfg["k"], cfg["bits"], cfg["block_size"], True, False)
-                    extras["lmhead_m8"] = {"gbs": bytes8 * copies * steps8 / sec8 / 1e9,
-                                           "us_per_node": sec8 / (copies * steps8) * 1e6, "kernel": name8,
-                                           "workload": "cfg5 lm-head M=8, same shards and gather"}
-                torch.cuda.synchronize()
-                dist.barrier()
-                gather8.close()
+                    step_x()
+                    torch.cuda.synchronize()
+                    name_x = _capi.last_kernel()
+                    # the gathered values against the ranks' own products, as for the headline
+                    own_x = torch.empty(m_x, shard_cfg["n"], device="cuda")
+                    w_x[0].matmul_device(a_x, own_x)
+                    expected_x = torch.empty(world, m_x, shard_cfg["n"], device="cuda")
+                    dist.all_gather_into_tensor(expected_x, own_x)
+                    torch.cuda.synchronize()
+                    # (the gathered path and the plain call may pick different kernels: compare to 2e-5)
+                    worst_x = float((expected_x - gather_x.result(0)).abs().max() / expected_x.abs().max())
+                    same_x = torch.tensor([1 if worst_x <= 2e-5 else 0], device="cuda")
+                    dist.all_reduce(same_x, op=dist.ReduceOp.MIN)
+                    rep_x, graphed_x = capture_graph(torch, step_x)
+                    ok_x = torch.tensor([1 if graphed_x else 0], device="cuda")
+                    dist.all_reduce(ok_x, op=dist.ReduceOp.MIN)
+                    if int(ok_x.item()) == 1:
+                        steps_x = max(5, args.steps // 4)
+                        sec_x = time_steps(torch, dist, rep_x, steps_x, 3, world)
+                        bytes_x = _capi.algorithmic_bytes(m_x, cfg["n"], cfg["k"], bits_x, cfg["block_size"], True, False)
+                        extras[key] = {"gbs": bytes_x * copies * steps_x / sec_x / 1e9,
+                                       "us_per_node": sec_x / (copies * steps_x) * 1e6, "kernel": name_x,
+                                       "gather_checked": bool(int(same_x.item())),
+                                       "workload": f"cfg5 lm-head M={m_x} bits={bits_x}, same shards and gather"}
+                        if m_x >= 64:
+                            extras[key]["tflops"] = 2.0 * m_x * cfg["n"] * cfg["k"] * copies * steps_x / sec_x / 1e12
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    gather_x.close()
+                    if w_x is not weights:
+                        del w_x
+                    del a_x, own_x, expected_x
+                    torch.cuda.empty_cache()
             # ---- like-for-like base of the scaling curve: the same node, unsharded, on one GPU ----
             # Timed by rank 0 alone in this very run (337 MB of operands fit); the other ranks wait.
             del weights

@@ -141,20 +141,40 @@ int mnb_peer_buffer_open(int device, const unsigned char *handle, void **peer_pt
 int mnb_peer_buffer_close(int device, void *peer_ptr);
 int mnb_peer_buffer_destroy(int device, void *dev_ptr);
 
-/* Decode product (M <= 16, accuracy_level 0, 4-bit shapes the tensor-core decode kernels take)
- * whose [m, N] result is stored at the same window (ld_y, col_offset) of `ranks` buffers:
+/* Product whose [m, N] result is stored at the same window (ld_y, col_offset) of `ranks` buffers:
  * y_ranks[r] is rank r's gathered result as mapped in this process (y_ranks[rank] is the local
- * one). Afterwards a one-warp kernel sets flags_ranks[r][rank] = epoch on every rank and waits,
- * bounded, until the local flags_ranks[rank][0..ranks) all carry `epoch`: when the stream
- * reaches that point every rank's columns of this step are in the local buffer. `epoch` must
- * grow by one per step on all ranks, or be 0 on all ranks and all steps: then the step number is
- * kept on the device in flags_ranks[rank][MNB_MAX_GATHER_RANKS] and incremented by the call
- * itself, which is what a captured and replayed CUDA graph needs. Each flags array holds at
- * least MNB_MAX_GATHER_RANKS + 1 ints, zero at start. Every rank must make the same sequence of calls. A wait that gives up sets the status
- * word (mnb_weights_poll_status). */
+ * one). Decode shapes of the tensor-core decode kernels (accuracy_level 0, M <= 16, 4-bit) store
+ * to every buffer from the kernel itself; every other shape (8-bit weights, more tokens,
+ * accuracy_level 4) runs through the ordinary dispatch into the local window, which one more
+ * kernel then copies to the peers. Either way each CTA pushes its part of the window to the
+ * peers with coalesced stores as it finishes, and the last CTA to finish sets
+ * flags_ranks[r][rank] = epoch on every rank ("my columns of this step are stored"): no separate
+ * kernel. With `wait` non-zero that CTA then waits, bounded, until the local
+ * flags_ranks[rank][0..ranks) all carry the epoch, so that the result is complete when the stream
+ * has passed the call. A rank's flag for one call implies its earlier calls (every rank makes the
+ * same sequence of calls), so a run of nodes needs the wait on its last node only, or none and
+ * one mnb_gather_wait where the gathered results are first read: consecutive nodes then do not
+ * each pay a round trip
+ * between GPUs. `epoch` must grow by one per step on all ranks, or be 0 on all ranks and all
+ * steps: then the step number is kept on the device in flags_ranks[rank][MNB_MAX_GATHER_RANKS]
+ * and incremented by the call itself, which is what a captured and replayed CUDA graph needs.
+ * Each flags array holds at least MNB_MAX_GATHER_RANKS + 1 ints, zero at start. Every rank must
+ * make the same sequence of calls. A wait that gives up sets the status word
+ * (mnb_weights_poll_status).
+ * mnb_matmul_device_gather is the accuracy_level 0, wait = 1 form. */
+int mnb_matmul_device_gather_ex(mnb_weights *weights, const float *a_dev, int64_t m, int accuracy_level,
+                                float *const *y_ranks, int *const *flags_ranks, int ranks, int rank,
+                                int64_t ld_y, int64_t col_offset, int epoch, int wait, void *stream);
 int mnb_matmul_device_gather(mnb_weights *weights, const float *a_dev, int64_t m,
                              float *const *y_ranks, int *const *flags_ranks, int ranks, int rank,
                              int64_t ld_y, int64_t col_offset, int epoch, void *stream);
+
+/* Waits (one small kernel on `stream`, bounded, status word of `weights`) until each of the
+ * `count` LOCAL flag arrays carries its epoch for all `ranks` ranks; epochs == NULL or an epoch of
+ * 0 means the step this rank itself published last through that array (self-counting mode). */
+#define MNB_MAX_GATHER_WAITS 8
+int mnb_gather_wait(mnb_weights *weights, int *const *flags_local, const int *epochs, int count, int ranks,
+                    void *stream);
 
 /* Waits for the device and reads the status word that kernels with bounded waits write when
  * they give up (0 = fine, see MNB_ERR_DEVICE_TIMEOUT). Clears it after reading. The

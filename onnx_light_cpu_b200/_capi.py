@@ -54,6 +54,8 @@ EXPORTED_SYMBOLS = (
     "mnb_peer_buffer_close",
     "mnb_peer_buffer_destroy",
     "mnb_matmul_device_gather",
+    "mnb_matmul_device_gather_ex",
+    "mnb_gather_wait",
     "mnb_weights_poll_status",
     "mnb_dequant_int_device",
     "mnb_quantize_a_device",
@@ -110,6 +112,9 @@ def load() -> ctypes.CDLL:
     lib.mnb_peer_buffer_close.argtypes = [i32, vp]
     lib.mnb_peer_buffer_destroy.argtypes = [i32, vp]
     lib.mnb_matmul_device_gather.argtypes = [vp, vp, i64, c.POINTER(vp), c.POINTER(vp), i32, i32, i64, i64, i32, vp]
+    lib.mnb_matmul_device_gather_ex.argtypes = [vp, vp, i64, i32, c.POINTER(vp), c.POINTER(vp), i32, i32, i64, i64, i32,
+                                                i32, vp]
+    lib.mnb_gather_wait.argtypes = [vp, c.POINTER(vp), c.POINTER(i32), i32, i32, vp]
     lib.mnb_weights_poll_status.argtypes = [vp, c.POINTER(i32)]
     lib.mnb_dequant_int_device.argtypes = [vp, vp, vp]
     lib.mnb_quantize_a_device.argtypes = [vp, i64, i64, i32, vp, vp, vp]

@@ -60,6 +60,20 @@ def _host_lib() -> ctypes.CDLL:
     lib.olc_session_last_device_kernel.restype = c.c_char_p
     lib.olc_session_destroy.argtypes = [c.c_void_p]
     lib.olc_session_overwrite_b.argtypes = [c.c_void_p, c.c_void_p, c.c_int64]
+    i64p, u64p = c.POINTER(c.c_int64), c.POINTER(c.c_uint64)
+    lib.olc_peer_gather_layout.argtypes = [c.c_int, c.c_int, c.c_int64, c.c_int64, c.c_int, i64p]
+    lib.olc_peer_gather_tables.argtypes = [c.c_int, c.c_int, c.c_int64, c.c_int64, c.c_int, c.c_int, u64p, u64p, u64p]
+    lib.olc_shard_bounds.argtypes = [c.c_int64, c.c_int, c.c_int, i64p, i64p]
+    lib.olc_peer_gather_create.restype = c.c_void_p
+    lib.olc_peer_gather_create.argtypes = [c.c_int, c.c_int, c.c_int64, c.c_int64, c.c_int, c.c_int, c.c_void_p]
+    lib.olc_peer_gather_open.argtypes = [c.c_void_p, c.c_void_p]
+    lib.olc_peer_gather_result.restype = c.c_void_p
+    lib.olc_peer_gather_result.argtypes = [c.c_void_p, c.c_int]
+    lib.olc_peer_gather_run.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_int64, c.c_int, c.c_int, c.c_int,
+                                        c.c_void_p]
+    lib.olc_peer_gather_wait.argtypes = [c.c_void_p, c.c_void_p, c.POINTER(c.c_int), c.c_int, c.c_void_p]
+    lib.olc_peer_gather_close_peers.argtypes = [c.c_void_p]
+    lib.olc_peer_gather_destroy.argtypes = [c.c_void_p]
     _host = lib
     return lib
 

@@ -37,6 +37,7 @@ HOST_SOURCES = [
     "kernels/kernel_usage.cc",
     "kernels/register_kernels.cc",
     "kernels/math/matmul_nbits_kernel.cc",
+    "kernels/parallel/peer_gather.cc",
     "onnx_py/cudaregister_capi.cc",
 ]
 HOST_HEADERS = [
@@ -44,6 +45,7 @@ HOST_HEADERS = [
     "kernels/kernel_usage.h",
     "kernels/register_kernels.h",
     "kernels/math/matmul_nbits_kernel.h",
+    "kernels/parallel/peer_gather.h",
     "shim/onnx_core/onnx_light_shim.h",
     "../include/matmulnbits_b200.h",
 ]

@@ -243,14 +243,58 @@ __global__ void __launch_bounds__(256) nbits_fetch_kernel(const uint4 *src, uint
   }
 }
 
-// Stand-alone form of the flag exchange, launched behind kernels that do not run it themselves.
-// The stores of the kernels before it in the stream have completed when it starts.
-// When it is launched with programmatic stream serialization (the decode kernels trigger their
-// dependents as they start) its one warp is already resident and waits here for the decode grid
-// to complete and its stores to be visible, which saves the launch latency after that grid.
-__global__ void __launch_bounds__(32) nbits_publish_wait_kernel(mnb::GatherTail tail, int *status) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  mnb::PublishAndWait(tail, threadIdx.x, status);
+// Waiting half of a gathered step, as a kernel of its own so that a caller can put it where the
+// gathered result is first needed: warp i waits, bounded, until the local flag array i carries
+// its epoch for every rank (epoch 0: the step count this rank itself published last).
+struct GatherWaitList {
+  int *flags[MNB_MAX_GATHER_WAITS];
+  int epoch[MNB_MAX_GATHER_WAITS];
+  int count;
+  int ranks;
+};
+
+__global__ void __launch_bounds__(32 * MNB_MAX_GATHER_WAITS) nbits_gather_wait_kernel(GatherWaitList list, int *status) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= list.count) {
+    return;
+  }
+  int epoch = list.epoch[warp];
+  if (epoch == 0) {
+    epoch = *reinterpret_cast<volatile int *>(list.flags[warp] + mnb::kMaxGatherRanks);
+  }
+  mnb::WaitStep(list.flags[warp], list.ranks, epoch, lane, status);
+}
+
+// Gathered step of a product that only wrote the local window (any kernel of the dispatcher): the
+// window [m, n] is copied to the same place of every peer's buffer with plain stores, then the
+// last CTA publishes the flags like the decode kernels do.
+__global__ void __launch_bounds__(256)
+    nbits_gather_push_kernel(mnb::OutputView out, std::int64_t m, std::int64_t n, int vector, mnb::GatherTail tail,
+                             int *status) {
+  const std::int64_t stride = static_cast<std::int64_t>(gridDim.x) * 256;
+  const std::int64_t first = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (vector != 0) {
+    const std::int64_t n4 = n / 4;
+    for (std::int64_t i = first; i < m * n4; i += stride) {
+      const std::int64_t row = i / n4;
+      const std::int64_t at = row * out.ld + out.col_offset + (i - row * n4) * 4;
+      const float4 v = *reinterpret_cast<const float4 *>(out.y + at);
+      for (int r = 0; r < tail.n_peers; ++r) {
+        *reinterpret_cast<float4 *>(tail.peers[r] + at) = v;
+      }
+    }
+  } else {
+    for (std::int64_t i = first; i < m * n; i += stride) {
+      const std::int64_t row = i / n;
+      const std::int64_t at = row * out.ld + out.col_offset + (i - row * n);
+      const float v = out.y[at];
+      for (int r = 0; r < tail.n_peers; ++r) {
+        tail.peers[r][at] = v;
+      }
+    }
+  }
+  mnb::PublishWhenGridDone(tail, static_cast<int>(threadIdx.x), 256, 1, gridDim.x, status);
 }
 
 // AUTO sends at most this many tokens to the integer-digit decode kernel (two tokens per pass).
@@ -303,7 +347,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     // column tile, so 16 tokens are four / two passes over the weights; three digit rows per token
     // through the sixteen-row integer kernel are fewer passes from M = 5 (block 32) / M = 9 (block 64)
     // on (measured: block 32 M = 16 80.8 -> 49.4 us, M = 5 40.2 -> 22.2 us; block 64 M = 16 63.1 -> 50.7 us).
-    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && out.n_peers == 0 &&
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO &&
         ((w.block_size == 32 && m >= 5) || (w.block_size == 64 && m >= 9))) {
       const std::size_t need = mnb::DigitsInt8MmaScratchBytes(w, m);
       if (need != 0) {
@@ -371,7 +415,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     break;
   }
   case MNB_PATH_GEMV_DIGITS: {
-    const std::size_t need = m <= 16 && out.n_peers == 0 ? mnb::DigitsInt8MmaScratchBytes(w, m) : 0;
+    const std::size_t need = m <= 16 ? mnb::DigitsInt8MmaScratchBytes(w, m) : 0;
     if (need != 0) {
       const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
       if (rc != MNB_OK) {
@@ -892,17 +936,43 @@ int mnb_peer_buffer_destroy(int device, void *dev_ptr) {
   return err == cudaSuccess ? MNB_OK : FailCuda("cudaFree(peer buffer)", err);
 }
 
-int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, float *const *y_ranks,
-                             int *const *flags_ranks, int ranks, int rank, int64_t ld_y, int64_t col_offset,
-                             int epoch, void *stream_ptr) {
+namespace {
+
+int LaunchGatherWait(mnb_weights *h, int *const *flags_local, const int *epochs, int count, int ranks,
+                     cudaStream_t stream) {
+  GatherWaitList list{};
+  list.count = count;
+  list.ranks = ranks;
+  for (int i = 0; i < count; ++i) {
+    list.flags[i] = flags_local[i];
+    list.epoch[i] = epochs != nullptr ? epochs[i] : 0;
+  }
+  cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
+  nbits_gather_wait_kernel<<<1, 32 * count, 0, stream>>>(list, h->status_dev);
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    return FailCuda("launch of the gather wait kernel", err);
+  }
+  mnb::CountLaunch();
+  return MNB_OK;
+}
+
+} // namespace
+
+int mnb_matmul_device_gather_ex(mnb_weights *h, const float *a_dev, int64_t m, int accuracy_level,
+                                float *const *y_ranks, int *const *flags_ranks, int ranks, int rank, int64_t ld_y,
+                                int64_t col_offset, int epoch, int wait, void *stream_ptr) {
   if (h == nullptr || a_dev == nullptr || y_ranks == nullptr || flags_ranks == nullptr) {
     return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: null argument.");
   }
   if (ranks < 1 || ranks > MNB_MAX_GATHER_RANKS || rank < 0 || rank >= ranks) {
     return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: 1 <= ranks <= 8 and 0 <= rank < ranks.");
   }
-  if (m < 1 || m > 16) {
-    return Fail(MNB_ERR_UNSUPPORTED, "mnb_matmul_device_gather: decode sizes only (1 <= M <= 16).");
+  if (m < 1) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_matmul_device_gather: M >= 1.");
+  }
+  if (accuracy_level != 0 && accuracy_level != 4) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits accuracy_level must be 0 or 4.");
   }
   if (ld_y < h->view.n || col_offset < 0 || col_offset + h->view.n > ld_y) {
     return Fail(MNB_ERR_INVALID_ARGUMENT, "MatMulNBits: output window does not fit its row.");
@@ -936,55 +1006,85 @@ int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, floa
   tail.ranks = ranks;
   tail.rank = rank;
   tail.epoch = epoch;
+  tail.wait = 0;
   tail.arrivals = h->arrivals_dev;
   for (int r = 0; r < ranks; ++r) {
     tail.flags[r] = flags_ranks[r];
     if (r != rank) {
-      out.peers[out.n_peers++] = y_ranks[r];
+      tail.peers[tail.n_peers++] = y_ranks[r];
     }
   }
   const WeightView &w = h->view;
-  const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
   const char *name = nullptr;
-  bool fused = false;
-  if (m > per_pass) {
-    name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
-  }
-  // The flag exchange is a kernel of its own behind the decode kernel: a fused form (the decode
-  // kernel's last CTA publishing the flags) measured slower on two GPUs, 56.7 vs 48.2 us per
-  // lm-head node on one box.
-  if (name == nullptr) {
-    name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
-  }
-  if (name == nullptr) {
-    return Fail(MNB_ERR_UNSUPPORTED,
-                "mnb_matmul_device_gather: only shapes of the tensor-core decode kernels (bits=4, "
-                "32 <= block_size <= 1024, 16-byte aligned rows) store to peers.");
-  }
-  if (!fused) {
-    cudaGetLastError(); // drop any stale, non-sticky error so that the check below reads this launch
-    // launched early (programmatic stream serialization): 43.3 vs 43.9 us per node on two GPUs
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(1, 1, 1);
-    config.blockDim = dim3(32, 1, 1);
-    config.dynamicSmemBytes = 0;
-    config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attribute;
-    config.numAttrs = 1;
-    cudaError_t launch_err = cudaLaunchKernelEx(&config, nbits_publish_wait_kernel, tail, h->status_dev);
-    if (launch_err == cudaSuccess) {
-      launch_err = cudaGetLastError();
+  if (accuracy_level == 0 && m <= 16) {
+    mnb::GatherTail fused_tail = tail;
+    fused_tail.wait = wait != 0 ? 1 : 0;
+    // The tensor-core decode kernels push each CTA's rows to the peers as the CTA finishes, and the
+    // last CTA to finish publishes the flags: one launch per node, no pass over the result.
+    const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
+    if (m > per_pass) {
+      name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &fused_tail);
     }
+    if (name == nullptr) {
+      name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &fused_tail);
+    }
+  }
+  if (name == nullptr) {
+    // Any other shape (8-bit weights, prefill sizes, accuracy_level 4): the product goes to the local
+    // window through the ordinary dispatch, then one kernel copies the window to the peers and
+    // publishes.
+    cudaGetLastError();
+    OutputView local{y_ranks[rank], ld_y, col_offset};
+    const int rc = Dispatch(h, a_dev, m, accuracy_level, MNB_PATH_AUTO, local, stream);
+    if (rc != MNB_OK) {
+      return rc;
+    }
+    name = mnb::t_last_kernel;
+    bool vector = (w.n % 4) == 0 && (ld_y % 4) == 0 && (col_offset % 4) == 0;
+    for (int r = 0; r < ranks; ++r) {
+      vector = vector && (reinterpret_cast<std::uintptr_t>(y_ranks[r]) & 15u) == 0;
+    }
+    const std::int64_t items = vector ? m * (w.n / 4) : m * w.n;
+    std::int64_t blocks = (items + 255) / 256;
+    const std::int64_t most = 2 * static_cast<std::int64_t>(h->sm_count > 0 ? h->sm_count : 148);
+    blocks = blocks > most ? most : (blocks < 1 ? 1 : blocks);
+    tail.wait = wait != 0 ? 1 : 0;
+    nbits_gather_push_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(out, m, w.n, vector ? 1 : 0, tail,
+                                                                               h->status_dev);
+    const cudaError_t launch_err = cudaGetLastError();
     if (launch_err != cudaSuccess) {
-      return FailCuda("launch of the publish kernel", launch_err);
+      return FailCuda("launch of the gather push kernel", launch_err);
     }
     mnb::CountLaunch();
   }
   mnb::t_last_kernel = name;
   return MNB_OK;
+}
+
+int mnb_matmul_device_gather(mnb_weights *h, const float *a_dev, int64_t m, float *const *y_ranks,
+                             int *const *flags_ranks, int ranks, int rank, int64_t ld_y, int64_t col_offset,
+                             int epoch, void *stream_ptr) {
+  return mnb_matmul_device_gather_ex(h, a_dev, m, 0, y_ranks, flags_ranks, ranks, rank, ld_y, col_offset, epoch, 1,
+                                     stream_ptr);
+}
+
+int mnb_gather_wait(mnb_weights *h, int *const *flags_local, const int *epochs, int count, int ranks,
+                    void *stream_ptr) {
+  if (h == nullptr || flags_local == nullptr || count < 1 || count > MNB_MAX_GATHER_WAITS || ranks < 1 ||
+      ranks > MNB_MAX_GATHER_RANKS) {
+    return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_gather_wait: 1 to 8 flag arrays of 1 to 8 ranks.");
+  }
+  for (int i = 0; i < count; ++i) {
+    if (flags_local[i] == nullptr) {
+      return Fail(MNB_ERR_INVALID_ARGUMENT, "mnb_gather_wait: null flag array.");
+    }
+  }
+  std::lock_guard<std::mutex> guard(h->mutex);
+  const cudaError_t err = cudaSetDevice(h->device);
+  if (err != cudaSuccess) {
+    return FailCuda("cudaSetDevice", err);
+  }
+  return LaunchGatherWait(h, flags_local, epochs, count, ranks, static_cast<cudaStream_t>(stream_ptr));
 }
 
 int mnb_matmul_device(mnb_weights *h, const float *a_dev, int64_t m, int accuracy_level, int path,

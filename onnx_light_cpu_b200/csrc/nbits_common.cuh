@@ -30,27 +30,20 @@ struct WeightView {
   int zp_row_bytes; // ceil(n_blocks * bits / 8)
 };
 
-// Where a kernel writes its [m, n] result inside a possibly wider row-major matrix.
 // Nodes that one grouped launch can serve (sibling projections sharing their activations).
 constexpr int kMaxGroupedNodes = 3;
+// Other GPUs whose result buffers a gathered step writes to.
 constexpr int kMaxPeers = 7;
+
+// Where a kernel writes its [m, n] result inside a possibly wider row-major matrix.
 struct OutputView {
   float *y;
   std::int64_t ld;         // leading dimension in elements
   std::int64_t col_offset; // first column written
-  // Column-sharded gather without a collective: the same window of `n_peers` other GPUs' result
-  // buffers (peer-mapped device memory, same ld / col_offset), written with plain stores next to
-  // the local one. Only the tensor-core decode kernels honour it; the dispatcher refuses the
-  // others when n_peers > 0.
-  float *peers[kMaxPeers];
-  int n_peers;
 };
 
 __device__ __forceinline__ void StoreOutput(const OutputView &out, std::int64_t index, float value) {
   out.y[index] = value;
-  for (int r = 0; r < out.n_peers; ++r) {
-    out.peers[r][index] = value;
-  }
 }
 
 // Error word written by kernels whose bounded waits gave up (0 = fine).
@@ -72,22 +65,42 @@ __device__ __forceinline__ void ReportStatus(int *word, int code) {
   __threadfence_system();
 }
 
-// Flag exchange that ends a gathered step (column shards stored into every rank's result
-// through peer memory): one warp tells every rank that this rank's columns of step `epoch` are
-// stored and waits, bounded (about a second), until the local flag of every rank carries the
-// epoch. flags[r] is rank r's flag array as mapped here: kMaxGatherRanks flags, then the step
-// counter used when epoch == 0 (self-counting mode, what a replayed CUDA graph needs: the step
-// number grows by one per call, in lockstep on all ranks).
+// Flag exchange of a gathered step (column shards stored into every rank's result through peer
+// memory). Publishing: one warp tells every rank that this rank's columns of step `epoch` are
+// stored. Waiting: a warp waits, bounded (about a second), until the local flag of every rank
+// carries the epoch. flags[r] is rank r's flag array as mapped here: kMaxGatherRanks flags, then
+// the step counter used when epoch == 0 (self-counting mode, what a replayed CUDA graph needs: the
+// step number grows by one per call, in lockstep on all ranks).
 constexpr int kMaxGatherRanks = 8;
 struct GatherTail {
   int *flags[kMaxGatherRanks];
   int ranks;         // 0 = no gather
   int rank;
   int epoch;
-  unsigned *arrivals; // device counter of finished CTAs, zero between launches (fused variant only)
+  int wait;          // 1: the publishing warp also waits for everybody's flag
+  unsigned *arrivals; // device counter of finished CTAs, zero between launches
+  float *peers[kMaxPeers]; // the other ranks' result buffers (same window as the local one)
+  int n_peers;
 };
 
-__device__ __forceinline__ void PublishAndWait(const GatherTail &tail, int lane, int *status) {
+// Release / acquire fence at system scope. The sequentially consistent form (__threadfence_system)
+// is not needed anywhere in the flag protocol and costs more; three of those in a row on the last
+// CTA's path measured 7.8 us per node.
+__device__ __forceinline__ void FenceSystem() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
+__device__ __forceinline__ void StoreFlagSystem(int *address, int value) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ int LoadFlagSystem(const int *address) {
+  int value;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+  return value;
+}
+
+// The caller has fenced (FenceSystem) after the stores the flags stand for and nothing needs
+// ordering in between: the flags are plain system-scope stores. Returns the epoch.
+__device__ __forceinline__ int PublishStep(const GatherTail &tail, int lane) {
   int epoch = tail.epoch;
   if (epoch == 0) {
     int *counter = tail.flags[tail.rank] + kMaxGatherRanks;
@@ -98,21 +111,86 @@ __device__ __forceinline__ void PublishAndWait(const GatherTail &tail, int lane,
     }
   }
   if (lane < tail.ranks) {
-    __threadfence_system();
-    *reinterpret_cast<volatile int *>(tail.flags[lane] + tail.rank) = epoch;
-    volatile int *mine = tail.flags[tail.rank] + lane;
+    StoreFlagSystem(tail.flags[lane] + tail.rank, epoch);
+  }
+  return epoch;
+}
+
+// Lane r waits for rank r's flag in the local array. Every wait is bounded; giving up sets the
+// status word and returns, so the context stays usable.
+__device__ __forceinline__ void WaitStep(int *local_flags, int ranks, int epoch, int lane, int *status) {
+  if (lane < ranks) {
     bool arrived = false;
     for (std::uint32_t spin = 0; spin < (1u << 22); ++spin) {
-      if (*mine - epoch >= 0) {
+      if (LoadFlagSystem(local_flags + lane) - epoch >= 0) {
         arrived = true;
         break;
       }
       __nanosleep(200);
     }
     if (!arrived) {
-      ReportStatus(status, 5 /* kDeviceTimeoutPeerFlag */);
+      ReportStatus(status, kDeviceTimeoutPeerFlag);
     }
-    __threadfence_system();
+    FenceSystem(); // acquire: what the flags stand for is visible to whatever follows
+  }
+}
+
+__device__ __forceinline__ void PublishAndWait(const GatherTail &tail, int lane, int *status) {
+  const int epoch = PublishStep(tail, lane);
+  WaitStep(tail.flags[tail.rank], tail.ranks, epoch, lane, status);
+}
+
+// Copies the rows [row0, row1) of `tokens` token rows of the local result to the same place of
+// every peer's buffer, warp-coalesced (consecutive lanes, consecutive columns: one 128-byte
+// transaction over NVLink per warp instead of one packet per output). Scattered 4-byte stores from
+// the arithmetic loop cost 8 us on a 36 us shard of the large-N projection; this costs under one.
+// The caller has made the CTA's local stores visible to the CTA (a barrier).
+__device__ __forceinline__ void PushRowsToPeers(const OutputView &out, const GatherTail &tail, std::int64_t token0,
+                                                int tokens, std::int64_t row0, std::int64_t row1, int tid,
+                                                int threads) {
+  const std::int64_t rows = row1 - row0;
+  if (tail.n_peers == 0) {
+    return;
+  }
+  for (int token = 0; token < tokens; ++token) {
+    const std::int64_t base = (token0 + token) * out.ld + out.col_offset + row0;
+    for (std::int64_t i = tid; i < rows; i += threads) {
+      const float v = __ldcg(out.y + base + i);
+      for (int r = 0; r < tail.n_peers; ++r) {
+        tail.peers[r][base + i] = v;
+      }
+    }
+  }
+}
+
+// End of a kernel whose CTAs stored a gathered step: called by the `threads` threads (whole warps,
+// numbered tid = 0 ...) of every CTA that stored outputs, after their last store. The CTA meets at
+// the named barrier, ONE thread fences at system scope (cumulative over the stores the barrier
+// ordered before it) and counts the CTA in; the warp of the last CTA to arrive publishes the flags
+// (and waits, when tail.wait is set). No thread other than that one pays a system fence.
+__device__ __forceinline__ void PublishWhenGridDone(const GatherTail &tail, int tid, int threads, int barrier_id,
+                                                    unsigned ctas, int *status) {
+  asm volatile("bar.sync %0, %1;" ::"r"(barrier_id), "r"(threads) : "memory");
+  if (tid < 32) {
+    unsigned last = 0;
+    if (tid == 0) {
+      // release at GPU scope: the CTA's stores (ordered before this thread by the barrier) before
+      // its arrival. The one system-scope fence of the step is the last CTA's, below; it is
+      // cumulative over what the arrivals it has observed stand for.
+      __threadfence();
+      last = atomicAdd(tail.arrivals, 1u) == ctas - 1 ? 1u : 0u;
+      if (last != 0) {
+        *tail.arrivals = 0; // everybody has arrived: ready for the next launch
+      }
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last != 0) {
+      FenceSystem(); // acquire the other CTAs' arrivals, release towards the flags
+      const int epoch = PublishStep(tail, tid);
+      if (tail.wait != 0) {
+        WaitStep(tail.flags[tail.rank], tail.ranks, epoch, tid, status);
+      }
+    }
   }
 }
 
@@ -162,15 +240,16 @@ struct MetaGeometry {
 };
 MetaGeometry MetaGeometryOf(const WeightView &w);
 bool LaunchPrepareMeta(const WeightView &w, unsigned char *meta, cudaStream_t stream);
-// `tail` (optional): the last CTA to finish runs the flag exchange of a gathered step itself, so
-// no second kernel is needed.
+// `tail` (optional): the last CTA to finish publishes the flags of a gathered step itself (and
+// waits for the other ranks' flags when tail->wait is set), so no second kernel is needed.
 const char *LaunchGemvMma(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                           int *status_word, cudaStream_t stream, int sm_count,
                           const GatherTail *tail = nullptr);
 // Same arithmetic with two or four column tiles of tokens per pass over the weights; nullptr
 // when one column tile is enough for `m` or the shape is outside what the kernel takes.
 const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                               int *status_word, cudaStream_t stream, int sm_count);
+                               int *status_word, cudaStream_t stream, int sm_count,
+                               const GatherTail *tail = nullptr);
 
 // Decode for one or two tokens per pass on integer MMA: the activations enter as three base-128
 // digits (22 bits of the row maximum), block dots are exact int32. block_size 128 ... 1024.

@@ -515,8 +515,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ok = false;
         break;
       }
-      if (tid == 64) {
-      }
       const unsigned char *packed = ring_p + s * kWideStageP + packed_offset;
       unsigned char *dst = buf_w + b * kWideBufW;
 #pragma unroll
@@ -532,8 +530,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&w_full[b]);
-      }
-      if (tid == 64) {
       }
       if (++s == kWideStages) {
         s = 0;

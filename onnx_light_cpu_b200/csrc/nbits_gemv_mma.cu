@@ -128,8 +128,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::int64_t row_limit =
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
-  if (tid == 0) {
-  }
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
 
@@ -260,8 +258,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                            act, p.act_row_bytes, inv_scale, scratch, tid);
   // activations staged and (through the producer's arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
-  if (tid == 0) {
-  }
 
   const int g = lane >> 2;
   const int t = lane & 3;
@@ -316,8 +312,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!assigned || !ptx::MbarWait(&full_bar[slot], round & 1u)) {
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         return false;
-      }
-      if (lane == 0) {
       }
       return true;
     };
@@ -472,29 +466,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   }
-  // ---- gathered step: the last CTA of the grid exchanges the flags ---------------------------
+  // ---- gathered step: the last CTA of the grid publishes this rank's flags --------------------
   if (p.tail.ranks > 0) {
-    // every consumer thread fences its own stores (local and peer), then the CTA meets
-    __threadfence_system();
+    // gathered step: the arithmetic stored locally only; now this CTA's rows go to the peers
     asm volatile("bar.sync 12, %0;" ::"n"(kConsumerThreads) : "memory");
-    if (warp == 0) {
-      unsigned last = 0;
-      if (lane == 0) {
-        __threadfence_system(); // cumulative: the CTA's fenced stores before its arrival
-        const unsigned total = gridDim.x * gridDim.y;
-        last = atomicAdd(p.tail.arrivals, 1u) == total - 1 ? 1u : 0u;
-        if (last != 0) {
-          *p.tail.arrivals = 0; // everybody has arrived: ready for the next launch
-        }
-      }
-      last = __shfl_sync(0xffffffffu, last, 0);
-      if (last != 0) {
-        __threadfence_system(); // the other CTAs' fenced stores before the flags
-        PublishAndWait(p.tail, lane, p.status);
-      }
-    }
+    PushRowsToPeers(p.out, p.tail, m_base, tokens, static_cast<std::int64_t>(h_begin) * 8, row_limit, tid, kConsumerThreads);
+    PublishWhenGridDone(p.tail, tid, kConsumerThreads, 12, gridDim.x * gridDim.y, p.status);
   }
-
 }
 
 // ---- prepared side array -----------------------------------------------------------------

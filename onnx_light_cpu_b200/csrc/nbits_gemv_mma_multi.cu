@@ -66,6 +66,7 @@ struct MultiParams {
   int tokens_per_pass;  // activation rows per grid.y pass: NT * (4 / blocks-per-supergroup)
   int token_rows;       // activation rows staged in shared memory: min(M, tokens_per_pass)
   std::uint32_t magic;  // 0x64006400, passed at run time so that it stays in a register
+  GatherTail tail;      // gathered step: the last CTA publishes this rank's flags (ranks == 0: none)
 };
 
 // NB_SG_LOG2: log2 of quantization blocks per 128-k supergroup (block 128+: 0, 64: 1, 32: 2).
@@ -104,8 +105,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::int64_t row_limit =
       static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
 
-  if (tid == 0) {
-  }
   // the next kernel in the stream may start filling SMs as they free up
   ptx::GridDependencyLaunch();
 
@@ -158,8 +157,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes + s * meta_slice_stride;
         const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
         unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
-        if (task < 15) {
-        }
         ptx::MbarArriveExpectTx(&full_bar[slot], box_bytes + meta_bytes);
         ptx::TmaLoad2D(dst, &map_b, s * x_step, h0 * 8, &full_bar[slot]);
         ptx::BulkLoad(dst + box_bytes, meta_src, meta_bytes, &full_bar[slot]);
@@ -193,8 +190,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                            act, p.act_row_bytes, inv_scale, scratch, tid);
   // activations staged and (through the producer's arrival) barriers initialised
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory");
-  if (tid == 0) {
-  }
 
   const int g = lane >> 2;
   const int t = lane & 3;
@@ -250,8 +245,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         dead = true;
       }
       if (!dead) {
-        if (lane == 0 && warp == 0) {
-        }
         const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
         const uint4 q0 = *reinterpret_cast<const uint4 *>(sb + weight_off);
         const uint4 q1 = *reinterpret_cast<const uint4 *>(sb + weight_off + 8 * p.slice_b_bytes);
@@ -300,8 +293,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int nt = 0; nt < NT; ++nt) {
           acc0[nt] = fmaf(s0, (da[nt][0] + da[nt][1]) + (db[nt][0] + db[nt][1]), acc0[nt]);
           acc1[nt] = fmaf(s1, (da[nt][2] + da[nt][3]) + (db[nt][2] + db[nt][3]), acc1[nt]);
-        }
-        if (lane == 0 && warp == 0) {
         }
       }
       if (++slot == p.num_slots) {
@@ -371,12 +362,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   }
+  if (p.tail.ranks > 0) {
+    // gathered step: the arithmetic stored locally only; now this CTA's rows go to the peers
+    asm volatile("bar.sync 12, %0;" ::"n"(kConsumerThreads) : "memory");
+    PushRowsToPeers(p.out, p.tail, m_base, tokens, static_cast<std::int64_t>(h_begin) * 8, row_limit, tid, kConsumerThreads);
+    PublishWhenGridDone(p.tail, tid, kConsumerThreads, 12, gridDim.x * gridDim.y, p.status);
+  }
 }
 
 } // namespace
 
 const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                          int *status_word, cudaStream_t stream, int sm_count) {
+                               int *status_word, cudaStream_t stream, int sm_count, const GatherTail *tail) {
   const MetaGeometry geo = MetaGeometryOf(w);
   if (geo.bytes == 0 || w.meta == nullptr || m < 1 || (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0 ||
       geo.bpt * w.block_size != kTaskK) {
@@ -389,6 +386,9 @@ const char *LaunchGemvMmaMulti(const WeightView &w, const float *a, std::int64_t
   p.out = out;
   p.status = status_word;
   p.magic = 0x64006400u;
+  if (tail != nullptr) {
+    p.tail = *tail;
+  }
   p.half_tiles = geo.half_tiles;
   p.bpt = geo.bpt;
   p.slices = geo.slices;

@@ -984,7 +984,7 @@ bool LaunchDigitsNode(const WeightView &w, const ImmaGeometry &geo, std::int64_t
   if (LaunchMultiply(no_bias, geo, 3 * m, at.act, to_partial, status_word, stream, sm_count) == nullptr) {
     return false;
   }
-  const bool vector_ok = (w.n % 4) == 0 && (out.ld % 4) == 0 && (out.col_offset % 4) == 0 && out.n_peers == 0 &&
+  const bool vector_ok = (w.n % 4) == 0 && (out.ld % 4) == 0 && (out.col_offset % 4) == 0 &&
                          (reinterpret_cast<std::uintptr_t>(out.y) & 15u) == 0 &&
                          (reinterpret_cast<std::uintptr_t>(w.bias) & 15u) == 0;
   if (vector_ok) {

@@ -8,6 +8,7 @@
 #include "onnx_light_cpu_b200/kernels/kernel_registration.h"
 #include "onnx_light_cpu_b200/kernels/kernel_usage.h"
 #include "onnx_light_cpu_b200/kernels/math/matmul_nbits_kernel.h"
+#include "onnx_light_cpu_b200/kernels/parallel/peer_gather.h"
 #include "onnx_light_cpu_b200/kernels/register_kernels.h"
 
 #include "onnx_core/runtime/kernels/kernel_dispatch_table.h"
@@ -274,5 +275,85 @@ const char *olc_session_last_device_kernel(void *handle) {
 }
 
 void olc_session_destroy(void *handle) { delete static_cast<Session *>(handle); }
+
+// ---- column-sharded nodes: buffer layout (no GPU needed) and the buffers themselves ----------
+
+// out[0..3] = floats per slot, byte offset of the first flag array, bytes of the whole buffer,
+// bytes of one writer's window.
+int olc_peer_gather_layout(int world, int rank, std::int64_t m_max, std::int64_t n_shard, int slots,
+                           std::int64_t *out) {
+  return Guard([&] {
+    const auto layout = onnx_light_cuda::PeerGatherLayout::Make(world, rank, m_max, n_shard, slots);
+    out[0] = layout.SlotFloats();
+    out[1] = layout.FlagsOffsetBytes();
+    out[2] = layout.Bytes();
+    out[3] = m_max * n_shard * 4;
+  });
+}
+
+// Pointer tables of one call of `rank`: y_ranks[r] / flags_ranks[r] from the buffers' base addresses.
+int olc_peer_gather_tables(int world, int rank, std::int64_t m_max, std::int64_t n_shard, int slots, int slot,
+                           const std::uint64_t *bases, std::uint64_t *y_ranks, std::uint64_t *flags_ranks) {
+  return Guard([&] {
+    const auto layout = onnx_light_cuda::PeerGatherLayout::Make(world, rank, m_max, n_shard, slots);
+    std::vector<std::uintptr_t> in(static_cast<size_t>(world)), y(static_cast<size_t>(world)),
+        flags(static_cast<size_t>(world));
+    for (int r = 0; r < world; ++r) {
+      in[static_cast<size_t>(r)] = static_cast<std::uintptr_t>(bases[r]);
+    }
+    layout.Tables(in.data(), slot, y.data(), flags.data());
+    for (int r = 0; r < world; ++r) {
+      y_ranks[r] = y[static_cast<size_t>(r)];
+      flags_ranks[r] = flags[static_cast<size_t>(r)];
+    }
+  });
+}
+
+int olc_shard_bounds(std::int64_t n, int world, int rank, std::int64_t *lo, std::int64_t *hi) {
+  return Guard([&] { onnx_light_cuda::ShardBounds(n, world, rank, lo, hi); });
+}
+
+// Allocates this rank's buffer; handle_out receives the 64 bytes the peers need to map it.
+void *olc_peer_gather_create(int world, int rank, std::int64_t m_max, std::int64_t n_shard, int slots, int device,
+                             unsigned char *handle_out) {
+  onnx_light_cuda::PeerGatherBuffers *buffers = nullptr;
+  const int code = Guard([&] {
+    const auto layout = onnx_light_cuda::PeerGatherLayout::Make(world, rank, m_max, n_shard, slots);
+    buffers = new onnx_light_cuda::PeerGatherBuffers(layout, device);
+    std::memcpy(handle_out, buffers->Handle(), onnx_light_cuda::kIpcHandleBytes);
+  });
+  return code == 0 ? buffers : nullptr;
+}
+
+int olc_peer_gather_open(void *buffers, const unsigned char *handles) {
+  return Guard([&] { static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers)->Open(handles); });
+}
+
+void *olc_peer_gather_result(void *buffers, int slot) {
+  void *result = nullptr;
+  Guard([&] { result = static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers)->Result(slot); });
+  return result;
+}
+
+int olc_peer_gather_run(void *buffers, void *weights, const float *a_dev, std::int64_t m, int accuracy_level,
+                        int slot, int wait, void *stream) {
+  return Guard([&] {
+    static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers)->Run(static_cast<mnb_weights *>(weights), a_dev, m,
+                                                                     accuracy_level, slot, wait != 0, stream);
+  });
+}
+
+int olc_peer_gather_wait(void *buffers, void *weights, const int *slots, int count, void *stream) {
+  return Guard([&] {
+    static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers)->Wait(static_cast<mnb_weights *>(weights), slots, count,
+                                                                      stream);
+  });
+}
+
+int olc_peer_gather_close_peers(void *buffers) {
+  return Guard([&] { static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers)->ClosePeers(); });
+}
+
+void olc_peer_gather_destroy(void *buffers) { delete static_cast<onnx_light_cuda::PeerGatherBuffers *>(buffers); }
 
 } // extern "C"

@@ -15,18 +15,42 @@ import numpy as np
 
 
 def shard_bounds(n: int, world: int, rank: int) -> tuple[int, int]:
-    if n % world != 0:
-        raise ValueError(f"N={n} does not divide by the number of shards {world}")
-    per = n // world
-    return rank * per, (rank + 1) * per
+    """Columns [lo, hi) of rank ``rank``. N need not divide by ``world``: the first ``N % world``
+    ranks take one column more (the C++ helper ``ShardBounds`` is the implementation)."""
+    import ctypes
+
+    from .._register import _host_lib, _raise_last
+
+    lo, hi = ctypes.c_int64(), ctypes.c_int64()
+    code = _host_lib().olc_shard_bounds(n, world, rank, ctypes.byref(lo), ctypes.byref(hi))
+    if code != 0:
+        _raise_last(code)
+    return lo.value, hi.value
 
 
-def assemble(gathered):
-    """[world, M, N/world] -> [M, N] (numpy array or torch tensor)."""
+def assemble(gathered, n: int | None = None):
+    """[world, M, width] -> [M, N] (numpy array or torch tensor). ``n``: the node's N when it does
+    not divide by the number of shards: ``width`` is then the widest shard and rank r's valid
+    columns are the first ``hi - lo`` of its window."""
     world, m, per = gathered.shape
+    if n is None or n == world * per:
+        if isinstance(gathered, np.ndarray):
+            return np.ascontiguousarray(gathered.transpose(1, 0, 2)).reshape(m, world * per)
+        return gathered.permute(1, 0, 2).reshape(m, world * per)
+    parts = []
+    for rank in range(world):
+        lo, hi = shard_bounds(n, world, rank)
+        parts.append(gathered[rank][:, :hi - lo])
     if isinstance(gathered, np.ndarray):
-        return np.ascontiguousarray(gathered.transpose(1, 0, 2)).reshape(m, world * per)
-    return gathered.permute(1, 0, 2).reshape(m, world * per)
+        return np.concatenate(parts, axis=1)
+    import torch
+
+    return torch.cat(parts, dim=1)
+
+
+def widest_shard(n: int, world: int) -> int:
+    """Columns of the widest shard: what the gather buffers are sized for."""
+    return -(-n // world)
 
 
 def gather_shards(y_shard, dist, out=None):
@@ -74,15 +98,19 @@ class _DeviceArray:
 
 
 class PeerGather:
-    """Gathered decode results without a collective.
+    """Gathered results without a collective.
 
     Every rank owns one buffer that the other ranks map (CUDA inter-process handles exchanged over
     the process group, any backend): ``slots`` gathered results ``[world, m_max, n_shard]`` fp32 and
-    one flag array per slot. :meth:`run` launches the decode kernel, which stores this rank's
-    columns into all ``world`` buffers, and a one-warp kernel that raises this rank's flag on every
-    rank and waits for everybody's flag locally. When the stream reaches the end of :meth:`run`
-    the slot's local result is complete. Use at least two slots and alternate them, so that a fast
-    rank writing step i+1 never touches what a slow rank still reads of step i.
+    one flag array per slot. :meth:`run` launches this rank's shard of a node: its kernels store
+    the rank's columns into all ``world`` buffers and the last of their CTAs raises this rank's
+    flag on every rank. With ``wait=True`` a one-warp kernel behind it waits for everybody's flag,
+    and when the stream reaches the end of :meth:`run` the slot's local result is complete; with
+    ``wait=False`` the caller puts :meth:`wait` where the results are first read, so consecutive
+    nodes do not each pay a round trip between GPUs. Use at least two slots and alternate them,
+    so that a fast rank writing step i+1 never touches what a slow rank still reads of step i.
+    The layout arithmetic, the buffers and the calls live in the C++ helper
+    (``kernels/parallel/peer_gather.h``); only the handle exchange uses the process group.
     """
 
     def __init__(self, dist, device_index: int, m_max: int, n_shard: int, slots: int = 2):
@@ -90,64 +118,59 @@ class PeerGather:
 
         import torch
 
-        from onnx_light_cpu_b200 import _capi
+        from .._register import _host_lib, _raise_last
 
-        self._capi, self._ctypes, self._torch = _capi, ctypes, torch
-        self.lib = _capi.load()
+        self._ctypes, self._torch, self._raise = ctypes, torch, _raise_last
+        self.lib = _host_lib()
         self.dist, self.device = dist, device_index
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
-        if self.world > _capi.MAX_GATHER_RANKS:
-            raise ValueError(f"at most {_capi.MAX_GATHER_RANKS} ranks")
         self.m_max, self.n_shard, self.slots = m_max, n_shard, slots
-        self.slot_floats = self.world * m_max * n_shard
-        self.flags_offset = (slots * self.slot_floats * 4 + 255) // 256 * 256
-        self.bytes = self.flags_offset + slots * 256
-        own = ctypes.c_void_p()
-        handle = (ctypes.c_ubyte * _capi.IPC_HANDLE_BYTES)()
-        _capi.check(self.lib.mnb_peer_buffer_create(device_index, self.bytes, ctypes.byref(own), handle))
-        self.own = own.value
+        handle = (ctypes.c_ubyte * 64)()
+        self.own = self.lib.olc_peer_gather_create(self.world, self.rank, m_max, n_shard, slots, device_index, handle)
+        if not self.own:
+            _raise_last(1)
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(handle))
-        self.bases = []
-        for r, raw in enumerate(handles):
-            if r == self.rank:
-                self.bases.append(self.own)
-                continue
-            ptr = ctypes.c_void_p()
-            buf = (ctypes.c_ubyte * _capi.IPC_HANDLE_BYTES).from_buffer_copy(raw)
-            _capi.check(self.lib.mnb_peer_buffer_open(device_index, buf, ctypes.byref(ptr)))
-            self.bases.append(ptr.value)
-        self._views = [torch.as_tensor(_DeviceArray(self.own + s * self.slot_floats * 4,
+        table = (ctypes.c_ubyte * (64 * self.world)).from_buffer_copy(b"".join(handles))
+        self._check(self.lib.olc_peer_gather_open(self.own, table))
+        self._views = [torch.as_tensor(_DeviceArray(self.lib.olc_peer_gather_result(self.own, s),
                                                     (self.world, m_max, n_shard), "<f4"),
                                        device=torch.device("cuda", device_index)) for s in range(slots)]
         dist.barrier()
+
+    def _check(self, code: int) -> None:
+        if code != 0:
+            self._raise(code)
 
     def result(self, slot: int):
         """Local gathered result of ``slot`` as a torch tensor ``[world, m_max, n_shard]`` (a view)."""
         return self._views[slot]
 
-    def run(self, weights, a, slot: int, stream=None) -> None:
+    def run(self, weights, a, slot: int, stream=None, accuracy_level: int = 0, wait: bool = True) -> None:
         """``weights``: this rank's :class:`MatMulNBitsWeights` shard; ``a`` [m, K] on this GPU.
         The step number is kept on the device, so the call can be captured in a CUDA graph."""
-        c, torch = self._ctypes, self._torch
+        torch = self._torch
         m = a.numel() // weights.k
-        if m > self.m_max or weights.n != self.n_shard:
-            raise ValueError("shape does not match the gather buffers")
-        window = (slot * self.world + self.rank) * self.m_max * self.n_shard * 4
-        y_ranks = (c.c_void_p * self.world)(*[base + window for base in self.bases])
-        flags = (c.c_void_p * self.world)(*[base + self.flags_offset + slot * 256 for base in self.bases])
         raw = (stream or torch.cuda.current_stream(a.device)).cuda_stream
-        self._capi.check(self.lib.mnb_matmul_device_gather(
-            weights._handle, a.data_ptr(), m, y_ranks, flags, self.world, self.rank, self.n_shard, 0, 0, raw))
+        self._check(self.lib.olc_peer_gather_run(self.own, weights._handle, a.data_ptr(), m, accuracy_level, slot,
+                                                 1 if wait else 0, raw))
+
+    def wait(self, weights, slots, stream=None) -> None:
+        """One small kernel: when the stream has passed it, the named slots hold every rank's
+        columns of their last step. ``weights``: any node of this rank (its status word reports a
+        wait that gave up)."""
+        torch = self._torch
+        slots = list(slots)
+        raw = (stream or torch.cuda.current_stream(torch.device("cuda", self.device))).cuda_stream
+        array = (self._ctypes.c_int * len(slots))(*slots)
+        self._check(self.lib.olc_peer_gather_wait(self.own, weights._handle, array, len(slots), raw))
 
     def close(self) -> None:
         if self.own is None:
             return
         self._torch.cuda.synchronize()
         self.dist.barrier()   # nobody unmaps or frees while a peer may still store
-        for r, base in enumerate(self.bases):
-            if r != self.rank:
-                self.lib.mnb_peer_buffer_close(self.device, base)
+        self.lib.olc_peer_gather_close_peers(self.own)
         self.dist.barrier()
-        self.lib.mnb_peer_buffer_destroy(self.device, self.own)
+        self.lib.olc_peer_gather_destroy(self.own)
         self.own = None

@@ -88,13 +88,13 @@ def config5(m: int = 1, bits: int = 4, n: int = 128256) -> Case:
 
 
 def shard_columns(case: Case, world_size: int, rank: int) -> Case:
-    """Column shard ``rank`` of ``world_size``: contiguous N range, A replicated."""
-    if case.n % world_size != 0:
-        raise ValueError("N must be divisible by the number of shards")
-    per = case.n // world_size
-    lo, hi = rank * per, (rank + 1) * per
+    """Column shard ``rank`` of ``world_size``: contiguous N range, A replicated. When N does not
+    divide, the first ``N % world_size`` shards are one column wider."""
+    per, extra = divmod(case.n, world_size)
+    lo = per * rank + min(rank, extra)
+    hi = lo + per + (1 if rank < extra else 0)
     nb = case.n_blocks
-    return Case(f"{case.name}_shard{rank}of{world_size}", case.m, case.k, per, case.bits, case.block_size,
+    return Case(f"{case.name}_shard{rank}of{world_size}", case.m, case.k, hi - lo, case.bits, case.block_size,
                 case.a, case.b[lo:hi], case.scales.reshape(case.n, nb)[lo:hi].reshape(-1),
                 None if case.zero_points is None else case.zero_points[lo:hi],
                 None if case.bias is None else case.bias[lo:hi], case.accuracy_level,
