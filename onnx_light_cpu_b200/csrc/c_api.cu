@@ -444,7 +444,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
   case MNB_PATH_TCGEN05_WIDE: {
     if (!mnb::GemmTcgen05Supports(w, m)) {
       return Fail(MNB_ERR_UNSUPPORTED,
-                  "MatMulNBits: the tcgen05 path needs bits=4, block_size>=32, K%64==0.");
+                  "MatMulNBits: the tcgen05 path needs bits 4 or 8, block_size>=32, K%64==0.");
     }
     const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, mnb::GemmTcgen05ScratchBytes(m, w.k));
     if (rc != MNB_OK) {

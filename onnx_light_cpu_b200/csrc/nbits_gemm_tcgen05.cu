@@ -27,6 +27,7 @@
 #include "nbits_tma.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <cstdint>
 #include <cstdlib>
@@ -42,19 +43,20 @@ constexpr int kThreads = (2 + kDequantWarps) * 32;
 // Order in which the eight k of a group appear in the bf16 buffers: positions 0..7 hold
 // k = 0,4,1,5,2,6,3,7. Extraction (w >> 4j) & 0x000F000F yields the pair (nibble j, nibble j+4).
 
+// `permute` = 0 keeps the natural order (8-bit codes are whole bytes and come out in order).
 __global__ void __launch_bounds__(256)
-    nbits_a_to_bf16_kernel(const float *a, std::int64_t m, std::int64_t k, __nv_bfloat16 *out) {
+    nbits_a_to_bf16_kernel(const float *a, std::int64_t m, std::int64_t k, __nv_bfloat16 *out, int permute) {
   const std::int64_t groups_per_row = k / 8;
   const std::int64_t total = m * groups_per_row;
   for (std::int64_t g = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
        g += static_cast<std::int64_t>(gridDim.x) * blockDim.x) {
     const float4 lo = __ldg(reinterpret_cast<const float4 *>(a) + 2 * g);
     const float4 hi = __ldg(reinterpret_cast<const float4 *>(a) + 2 * g + 1);
-    // natural k: lo = (0,1,2,3), hi = (4,5,6,7); stored order 0,4,1,5,2,6,3,7
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, hi.x);
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(lo.y, hi.y);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(lo.z, hi.z);
-    __nv_bfloat162 p3 = __floats2bfloat162_rn(lo.w, hi.w);
+    // natural k: lo = (0,1,2,3), hi = (4,5,6,7); stored order 0,4,1,5,2,6,3,7 when permuted
+    __nv_bfloat162 p0 = permute != 0 ? __floats2bfloat162_rn(lo.x, hi.x) : __floats2bfloat162_rn(lo.x, lo.y);
+    __nv_bfloat162 p1 = permute != 0 ? __floats2bfloat162_rn(lo.y, hi.y) : __floats2bfloat162_rn(lo.z, lo.w);
+    __nv_bfloat162 p2 = permute != 0 ? __floats2bfloat162_rn(lo.z, hi.z) : __floats2bfloat162_rn(hi.x, hi.y);
+    __nv_bfloat162 p3 = permute != 0 ? __floats2bfloat162_rn(lo.w, hi.w) : __floats2bfloat162_rn(hi.z, hi.w);
     uint4 packed;
     packed.x = *reinterpret_cast<std::uint32_t *>(&p0);
     packed.y = *reinterpret_cast<std::uint32_t *>(&p1);
@@ -74,10 +76,11 @@ struct GemmParams {
   std::uint32_t magic; // 0x43004300, passed at run time so that it stays in a register
 };
 
-template <int BT> struct GemmSmem {
+template <int BT, int BITS> struct GemmSmem {
+  static constexpr int kRowP = kTileK * BITS / 8; // packed bytes of a row per stage: 32 (4-bit) or 64 (8-bit)
   static constexpr int kStageA = BT * 128;        // activation tile, bf16, swizzled
   static constexpr int kStageW = kTileN * 128;    // dequantized weight tile, bf16, swizzled
-  static constexpr int kStageP = kTileN * 32;     // packed weight tile (4-bit: 32 B per row)
+  static constexpr int kStageP = kTileN * kRowP;  // packed weight tile
   static constexpr int kStage = kStageA + kStageW + kStageP;
   static constexpr int kStages = BT == 256 ? 4 : (BT == 128 ? 5 : 6);
   static constexpr int kBarrierBytes = 256;
@@ -113,6 +116,27 @@ __device__ __forceinline__ void DequantStore(std::uint32_t dst, std::uint32_t w,
                : "memory");
 }
 
+// Eight 8-bit codes (two words, natural k order) into one 16-byte chunk of bf16: 1024 + q as fp16
+// through a byte permute (0x6400 | q), minus 1024 + zp exactly, then (q - zp), an integer of at most
+// eight significant bits and so exact in bf16, times the block scale in bf16: the same two
+// roundings as the 4-bit form (scale to bf16, product to bf16).
+__device__ __forceinline__ void DequantStore8(std::uint32_t dst, std::uint32_t w0, std::uint32_t w1,
+                                              std::uint32_t offset16, std::uint32_t scale) {
+  const __half2 off = *reinterpret_cast<const __half2 *>(&offset16);
+  const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&scale);
+  std::uint32_t x[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const std::uint32_t word = i < 2 ? w0 : w1;
+    const std::uint32_t h = __byte_perm(word, 0x64646464u, (i & 1) ? 0x4342u : 0x4140u);
+    const float2 f = __half22float2(__hsub2(*reinterpret_cast<const __half2 *>(&h), off));
+    const __nv_bfloat162 v = __hmul2(__floats2bfloat162_rn(f.x, f.y), sc);
+    x[i] = *reinterpret_cast<const std::uint32_t *>(&v);
+  }
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3])
+               : "memory");
+}
+
 // bf16 pair (v, v) from a float, round to nearest even.
 __device__ __forceinline__ std::uint32_t Bf16Pair(float v) {
   std::uint32_t d;
@@ -120,11 +144,11 @@ __device__ __forceinline__ std::uint32_t Bf16Pair(float v) {
   return d;
 }
 
-template <int BT>
+template <int BT, int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
     nbits_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                               const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
-  using Smem = GemmSmem<BT>;
+  using Smem = GemmSmem<BT, BITS>;
   constexpr int kStages = Smem::kStages;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms; the pointer stays in the
@@ -181,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         unsigned char *sp = sa + Smem::kStageA + Smem::kStageW;
         ptx::MbarArriveExpectTx(&full_tma[s], Smem::kStageA + Smem::kStageP);
         ptx::TmaLoad2D(sa, &map_a, ks * kTileK, m0, &full_tma[s]);
-        ptx::TmaLoad2D(sp, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
+        ptx::TmaLoad2D(sp, &map_p, ks * Smem::kRowP, n0, &full_tma[s]);
       }
     }
   } else if (warp == 1) {
@@ -227,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int last_block = p.w.n_blocks - 1;
     const std::uint32_t magic = p.magic;
     // fixed shared-memory offsets of this thread inside a stage
-    const int packed_offset = Smem::kStageA + Smem::kStageW + row * 32 + half * 16;
+    const int packed_offset = Smem::kStageA + Smem::kStageW + row * Smem::kRowP + half * (Smem::kRowP / 2);
     int store_offset[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -239,13 +263,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       int block = (ks * kTileK + half * 32) >> p.block_shift;
       block = block > last_block ? last_block : block;
       const float scale = row_valid ? __ldg(scale_row + block) : 0.0f;
-      int zp = 8;
-      if (zp_row != nullptr) {
-        const int byte = __ldg(zp_row + (block >> 1));
-        zp = (byte >> ((block & 1) * 4)) & 0x0f;
-      }
       scale2 = Bf16Pair(scale);
-      offset2 = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
+      if constexpr (BITS == 4) {
+        int zp = 8;
+        if (zp_row != nullptr) {
+          const int byte = __ldg(zp_row + (block >> 1));
+          zp = (byte >> ((block & 1) * 4)) & 0x0f;
+        }
+        offset2 = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
+      } else {
+        const int zp = zp_row != nullptr ? __ldg(zp_row + block) : 128;
+        const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp)); // exact in fp16
+        offset2 = *reinterpret_cast<const std::uint32_t *>(&both);
+      }
     };
 
     std::uint32_t scale_next, offset_next;
@@ -266,12 +296,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       unsigned char *stage = stage0 + s * Smem::kStage;
-      const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset);
       const std::uint32_t base = ptx::SmemAddr(stage);
-      DequantStore(base + store_offset[0], q.x, magic, offset2, scale2);
-      DequantStore(base + store_offset[1], q.y, magic, offset2, scale2);
-      DequantStore(base + store_offset[2], q.z, magic, offset2, scale2);
-      DequantStore(base + store_offset[3], q.w, magic, offset2, scale2);
+      if constexpr (BITS == 4) {
+        const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset);
+        DequantStore(base + store_offset[0], q.x, magic, offset2, scale2);
+        DequantStore(base + store_offset[1], q.y, magic, offset2, scale2);
+        DequantStore(base + store_offset[2], q.z, magic, offset2, scale2);
+        DequantStore(base + store_offset[3], q.w, magic, offset2, scale2);
+      } else {
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(stage + packed_offset);
+        const uint4 q1 = *reinterpret_cast<const uint4 *>(stage + packed_offset + 16);
+        DequantStore8(base + store_offset[0], q0.x, q0.y, offset2, scale2);
+        DequantStore8(base + store_offset[1], q0.z, q0.w, offset2, scale2);
+        DequantStore8(base + store_offset[2], q1.x, q1.y, offset2, scale2);
+        DequantStore8(base + store_offset[3], q1.z, q1.w, offset2, scale2);
+      }
       // make the generic-proxy stores visible to the tensor core (async proxy), then signal
       ptx::FenceProxyAsyncShared();
       __syncwarp();
@@ -593,10 +632,10 @@ int Log2Of(int v) {
   return l;
 }
 
-template <int BT>
-const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16,
-                       OutputView out, int *status_word, cudaStream_t stream) {
-  using Smem = GemmSmem<BT>;
+template <int BT, int BITS>
+const char *LaunchTileBits(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16,
+                           OutputView out, int *status_word, cudaStream_t stream) {
+  using Smem = GemmSmem<BT, BITS>;
   CUtensorMap map_a, map_p;
   if (!EncodeMap2D(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16,
                    static_cast<std::uint64_t>(w.k), static_cast<std::uint64_t>(m),
@@ -605,7 +644,7 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
   }
   if (!EncodeMap2D(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.b,
                    static_cast<std::uint64_t>(w.row_bytes), static_cast<std::uint64_t>(w.n),
-                   static_cast<std::uint64_t>(w.row_bytes), kTileK / 2, kTileN,
+                   static_cast<std::uint64_t>(w.row_bytes), Smem::kRowP, kTileN,
                    CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return nullptr;
   }
@@ -617,7 +656,7 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
   p.status = status_word;
   p.block_shift = Log2Of(w.block_size);
   p.magic = 0x43004300u;
-  auto kernel = nbits_gemm_tcgen05_kernel<BT>;
+  auto kernel = nbits_gemm_tcgen05_kernel<BT, BITS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) !=
       cudaSuccess) {
     return nullptr;
@@ -631,6 +670,13 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
   CountLaunch();
   return BT == 256 ? "nbits_gemm_tcgen05_kernel<256>"
                    : (BT == 128 ? "nbits_gemm_tcgen05_kernel<128>" : "nbits_gemm_tcgen05_kernel<64>");
+}
+
+template <int BT>
+const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
+                       int *status_word, cudaStream_t stream) {
+  return w.bits == 8 ? LaunchTileBits<BT, 8>(w, m, a_bf16, out, status_word, stream)
+                     : LaunchTileBits<BT, 4>(w, m, a_bf16, out, status_word, stream);
 }
 
 const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
@@ -676,7 +722,7 @@ std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k) {
 }
 
 bool GemmTcgen05Supports(const WeightView &w, std::int64_t m) {
-  return m >= 1 && w.bits == 4 && w.block_size >= 32 && (w.k % kTileK) == 0 &&
+  return m >= 1 && (w.bits == 4 || w.bits == 8) && w.block_size >= 32 && (w.k % kTileK) == 0 &&
          (reinterpret_cast<std::uintptr_t>(w.b) & 15u) == 0 && (w.row_bytes % 16) == 0 &&
          GetEncodeTiled() != nullptr;
 }
@@ -693,8 +739,8 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   if (blocks > max_blocks) {
     blocks = max_blocks;
   }
-  nbits_a_to_bf16_kernel<<<blocks, 256, 0, stream>>>(a, m, w.k,
-                                                     reinterpret_cast<__nv_bfloat16 *>(a_bf16));
+  nbits_a_to_bf16_kernel<<<blocks, 256, 0, stream>>>(a, m, w.k, reinterpret_cast<__nv_bfloat16 *>(a_bf16),
+                                                     w.bits == 4 ? 1 : 0);
   if (cudaGetLastError() != cudaSuccess) {
     return nullptr;
   }
@@ -703,7 +749,7 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   const int sms = sm_count > 0 ? sm_count : 148;
   // large problems: 256 x 256 tiles (half the operand traffic per flop)
   const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
-  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8)) {
+  if (w.bits == 4 && (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8))) {
     return LaunchWide(w, m, a_bf16, out, status_word, stream);
   }
   // otherwise the widest token tile that still gives every SM a tile

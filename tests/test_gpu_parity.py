@@ -543,6 +543,23 @@ def test_prefill_tcgen05(cuda_device, m, k, n, bs, zp, bias):
 
 
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (17, 256, 130, 64, True, False),       # 64-token tile, ragged N
+    (64, 1024, 128, 32, True, True),
+    (100, 2048, 300, 128, False, True),    # 128-token tile, default zero point 128
+    (300, 4096, 256, 32, True, False),     # 256-token tile
+    (256, 4096, 1002, 32, True, False),    # the column-shard geometry at reduced N
+])
+def test_prefill_tcgen05_8bit(cuda_device, m, k, n, bs, zp, bias):
+    """8-bit codes through the same kernel: whole bytes, natural k order, (q - zp) exact in bf16."""
+    case = syn.make_case("prefill8", m, k, n, 8, bs, seed=m + k + n + 8, zero_points=zp, bias=bias)
+    y, kernel = run_device(case)   # AUTO: above sixteen tokens 8-bit weights go to the tensor cores too
+    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 8, bs)
+    assert rel_err(y, ref_bf16) <= TOL_BF16
+    assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
     (512, 4096, 512, 64, True, False),
     (300, 1024, 700, 32, True, True),      # ragged in both directions, two row tiles
     (257, 512, 130, 128, False, True),     # one token over a tile boundary
