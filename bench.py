@@ -49,7 +49,7 @@ L2_BYTES = 126 * 1024 * 1024
 # decode workload, each from one ncu capture of that kernel on this workload. A constant, not a
 # measurement of the run: reported as `traffic`, with `traffic_source` saying so.
 NCU_DECODE_TRAFFIC_BYTES = {
-    "nbits_decode_resident_kernel": None,
+    "nbits_decode_resident_kernel": 31_793_920,
     "nbits_decode_direct_kernel": 31_538_688,
     "nbits_gemv_imma_kernel": 31_796_480,
     "nbits_gemv_mma_kernel": 32_258_304,
