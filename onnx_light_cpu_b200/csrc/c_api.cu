@@ -446,7 +446,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       return Fail(MNB_ERR_UNSUPPORTED,
                   "MatMulNBits: the tcgen05 path needs bits 4 or 8, block_size>=32, K%64==0.");
     }
-    const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, mnb::GemmTcgen05ScratchBytes(m, w.k));
+    const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, mnb::GemmTcgen05ScratchBytes(w, m, h->sm_count));
     if (rc != MNB_OK) {
       return rc;
     }

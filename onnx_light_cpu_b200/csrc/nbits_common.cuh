@@ -286,7 +286,8 @@ void ForgetDecodeResidentPlans(const WeightView &w);
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
                               std::uint16_t *a_bf16, OutputView out, int *status_word,
                               cudaStream_t stream, int sm_count, bool force_wide = false);
-std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k);
+// Scratch of one call: bf16 activations, plus partial tiles and arrival counters when K is split.
+std::size_t GemmTcgen05ScratchBytes(const WeightView &w, std::int64_t m, int sm_count);
 bool GemmTcgen05Supports(const WeightView &w, std::int64_t m);
 
 // accuracy_level 4.

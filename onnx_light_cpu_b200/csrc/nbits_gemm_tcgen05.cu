@@ -74,6 +74,7 @@ struct GemmParams {
   int *status;
   int block_shift;
   std::uint32_t magic; // 0x43004300, passed at run time so that it stays in a register
+  float *partial;      // split-K: [parts][m_total][n] partial products, summed by a kernel behind this one
 };
 
 template <int BT, int BITS> struct GemmSmem {
@@ -383,6 +384,11 @@ constexpr int kWideStageP = kWideRows * 32;      // 8 KB
 constexpr int kWideBufW = kWideRows * 128;       // 32 KB, two 16 KB sub-tiles
 constexpr int kWideSmem = kWideStages * (kWideStageA + kWideStageP) + kWideBuffers * kWideBufW + 256 + 1024;
 
+// SPLIT: gridDim.z CTAs share a tile; each takes a consecutive part of K and stores its partial
+// tile, and nbits_split_k_sum_kernel behind this kernel adds the parts in order (+ bias): the
+// result does not depend on timing. (fp32 reductions straight into Y were tried first: 8.4 M
+// element-wise L2 atomics took longer than the product, 112 us against 41 us unsplit on M = 512.)
+template <bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
     nbits_gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a,
                                    const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
@@ -405,6 +411,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = tid & 31;
   const int n0 = blockIdx.x * kWideRows;
   const int m0 = blockIdx.y * kWideTokens;
+  // this CTA's share of K: all of it, or one of gridDim.z consecutive parts
+  const int splits = SPLIT ? static_cast<int>(gridDim.z) : 1;
+  const int split = SPLIT ? static_cast<int>(blockIdx.z) : 0;
+  const int ks_begin = SPLIT ? static_cast<int>(static_cast<std::int64_t>(split) * p.k_steps / splits) : 0;
+  const int ks_end = SPLIT ? static_cast<int>(static_cast<std::int64_t>(split + 1) * p.k_steps / splits) : p.k_steps;
 
   if (tid == 0) {
     for (int s = 0; s < kWideStages; ++s) {
@@ -435,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::PrefetchTensorMap(&map_p);
       int s = 0;
       std::uint32_t phase = 0;
-      for (int ks = 0; ks < p.k_steps; ++ks) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         if (!ptx::MbarWaitHot(&empty[s], phase ^ 1u)) {
           ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
           *abort_flag = 1;
@@ -458,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int s = 0;
       int b = 0;
       std::uint32_t b_phase = 0;
-      for (int ks = 0; ks < p.k_steps; ++ks) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         // the buffer's dequantizers waited for the stage's TMA, so the activations are in too
         if (!ptx::MbarWaitHot(&w_full[b], b_phase)) {
           ReportStatus(p.status, kDeviceTimeoutMmaBarrier);
@@ -475,7 +486,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int kk = 0; kk < kTileK / 16; ++kk) {
             const std::uint64_t desc_w = ptx::UmmaDescKMajorSw128(sw + sub * (kWideBufW / 2) + kk * 32);
             const std::uint64_t desc_a = ptx::UmmaDescKMajorSw128(sa + kk * 32);
-            ptx::UmmaBf16(tmem_base + sub * kWideTokens, desc_w, desc_a, idesc, (ks | kk) != 0 ? 1u : 0u);
+            ptx::UmmaBf16(tmem_base + sub * kWideTokens, desc_w, desc_a, idesc,
+                          (ks != ks_begin || kk != 0) ? 1u : 0u);
           }
         }
         ptx::UmmaCommit(&empty[s]);
@@ -535,16 +547,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     };
 
     std::uint32_t scale_next[2], offset_next[2];
-    load_meta(0, scale_next, offset_next);
+    load_meta(ks_begin, scale_next, offset_next);
     bool ok = true;
     int s = 0;
     std::uint32_t phase = 0;
     int b = 0;
     std::uint32_t b_phase = 0;
-    for (int ks = 0; ks < p.k_steps; ++ks) {
+    for (int ks = ks_begin; ks < ks_end; ++ks) {
       const std::uint32_t scale2[2] = {scale_next[0], scale_next[1]};
       const std::uint32_t offset2[2] = {offset_next[0], offset_next[1]};
-      if (ks + 1 < p.k_steps) {
+      if (ks + 1 < ks_end) {
         load_meta(ks + 1, scale_next, offset_next);
       }
       // packed weights of this stage landed, and the buffer's previous reader has retired
@@ -594,7 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int sub = (warp - 2) >> 2;         // warps 2..5 read sub-tile 0, warps 6..9 sub-tile 1
       const int n_local = sub * 128 + quarter * 32 + lane;
       const std::int64_t col = static_cast<std::int64_t>(n0) + n_local;
-      const float bias = (p.w.bias != nullptr && col < p.w.n) ? __ldg(p.w.bias + col) : 0.0f;
+      const float bias = (!SPLIT && p.w.bias != nullptr && col < p.w.n) ? __ldg(p.w.bias + col) : 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kWideTokens; c0 += 32) {
         std::uint32_t v[32];
@@ -605,8 +617,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int j = 0; j < 32; ++j) {
             const int m = m0 + c0 + j;
             if (m < p.m_total) {
-              p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] =
-                  __uint_as_float(v[j]) + bias;
+              if constexpr (SPLIT) {
+                p.partial[(static_cast<std::int64_t>(split) * p.m_total + m) * p.w.n + col] = __uint_as_float(v[j]);
+              } else {
+                p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] =
+                    __uint_as_float(v[j]) + bias;
+              }
             }
           }
         }
@@ -619,6 +635,24 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 0) {
     ptx::TcFenceAfter();
     ptx::TmemDealloc(tmem_base, 512);
+  }
+}
+
+// Y = part 0 + part 1 + ... (in that order) + bias, for a split-K product. The parts were written
+// by the kernel before it and are still in L2.
+__global__ void __launch_bounds__(256)
+    nbits_split_k_sum_kernel(const float *partial, int parts, std::int64_t m, std::int64_t n, const float *bias,
+                             OutputView out) {
+  const std::int64_t total = m * n;
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * 256) {
+    const std::int64_t row = i / n;
+    const std::int64_t col = i - row * n;
+    float value = __ldcg(partial + i);
+    for (int z = 1; z < parts; ++z) {
+      value += __ldcg(partial + z * total + i);
+    }
+    out.y[row * out.ld + out.col_offset + col] = value + (bias != nullptr ? __ldg(bias + col) : 0.0f);
   }
 }
 
@@ -680,7 +714,7 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
 }
 
 const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
-                       int *status_word, cudaStream_t stream) {
+                       int *status_word, cudaStream_t stream, int splits, float *partial, int sms) {
   CUtensorMap map_a, map_p;
   if (!EncodeMap2D(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16, static_cast<std::uint64_t>(w.k),
                    static_cast<std::uint64_t>(m), static_cast<std::uint64_t>(w.k) * 2, kTileK, kWideTokens,
@@ -700,25 +734,65 @@ const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t 
   p.status = status_word;
   p.block_shift = Log2Of(w.block_size);
   p.magic = 0x43004300u;
-  if (cudaFuncSetAttribute(nbits_gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kWideSmem) != cudaSuccess) {
+  p.partial = partial;
+  auto kernel = splits > 1 ? nbits_gemm_tcgen05_wide_kernel<true> : nbits_gemm_tcgen05_wide_kernel<false>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem) != cudaSuccess) {
     return nullptr;
   }
   dim3 grid(static_cast<unsigned>((w.n + kWideRows - 1) / kWideRows),
-            static_cast<unsigned>((m + kWideTokens - 1) / kWideTokens), 1);
-  nbits_gemm_tcgen05_wide_kernel<<<grid, kThreads, kWideSmem, stream>>>(map_a, map_p, p);
+            static_cast<unsigned>((m + kWideTokens - 1) / kWideTokens), static_cast<unsigned>(splits));
+  kernel<<<grid, kThreads, kWideSmem, stream>>>(map_a, map_p, p);
   if (cudaGetLastError() != cudaSuccess) {
     return nullptr;
   }
   CountLaunch();
-  return "nbits_gemm_tcgen05_wide_kernel";
+  if (splits > 1) {
+    const std::int64_t total = m * w.n;
+    std::int64_t blocks = (total + 255) / 256;
+    blocks = blocks > static_cast<std::int64_t>(sms) * 8 ? static_cast<std::int64_t>(sms) * 8 : blocks;
+    nbits_split_k_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, splits, m, w.n, w.bias, out);
+    if (cudaGetLastError() != cudaSuccess) {
+      return nullptr;
+    }
+    CountLaunch();
+  }
+  return splits > 1 ? "nbits_gemm_tcgen05_wide_kernel(split-k)" : "nbits_gemm_tcgen05_wide_kernel";
 }
+
+// Tile shape of a product. 0: the 128-row kernel. 1: 256 x 256 tiles, whole K per CTA (large
+// problems: half the operand traffic per flop). 2: 256 x 256 tiles with K shared by two CTAs, for
+// products whose tiles alone would cover between a third and a half of the SMs (the lm-head shard
+// at M = 256 is 63 tiles, the decode projection at M = 256 is 56): 70.5 against 78.2 us and 65.9
+// against 73.7 us with the 128-row kernel. Fewer tiles in four parts lost to the 128-row kernel
+// (M = 512 on N = 4096: 49.8 against 41.3 us): the fixed cost of a 256 x 256 tile, its two
+// epilogues and the sum kernel outweigh sixteen k steps.
+int WideSplits(const WeightView &w, std::int64_t m, int sms, bool force_wide) {
+  if (w.bits != 4) {
+    return 0;
+  }
+  const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
+  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8)) {
+    return 1;
+  }
+  const std::int64_t k_steps = w.k / kTileK;
+  if (m > 128 && wide_tiles * 2 <= sms && wide_tiles * 3 > sms && k_steps >= 16) {
+    return 2;
+  }
+  return 0;
+}
+
+std::size_t AlignScratch(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
 
 } // namespace
 
-
-std::size_t GemmTcgen05ScratchBytes(std::int64_t m, std::int64_t k) {
-  return static_cast<std::size_t>(m) * static_cast<std::size_t>(k) * 2;
+// bf16 activations of one call, then (split-K only) the partial products [parts][m][n].
+std::size_t GemmTcgen05ScratchBytes(const WeightView &w, std::int64_t m, int sm_count) {
+  std::size_t bytes = AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2);
+  const int splits = WideSplits(w, m, sm_count > 0 ? sm_count : 148, false);
+  if (splits > 1) {
+    bytes += static_cast<std::size_t>(splits) * static_cast<std::size_t>(m) * static_cast<std::size_t>(w.n) * sizeof(float);
+  }
+  return bytes;
 }
 
 bool GemmTcgen05Supports(const WeightView &w, std::int64_t m) {
@@ -739,6 +813,8 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   if (blocks > max_blocks) {
     blocks = max_blocks;
   }
+  const int sms = sm_count > 0 ? sm_count : 148;
+  const int splits = WideSplits(w, m, sms, force_wide);
   nbits_a_to_bf16_kernel<<<blocks, 256, 0, stream>>>(a, m, w.k, reinterpret_cast<__nv_bfloat16 *>(a_bf16),
                                                      w.bits == 4 ? 1 : 0);
   if (cudaGetLastError() != cudaSuccess) {
@@ -746,11 +822,11 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   }
   CountLaunch();
   const std::int64_t n_tiles = (w.n + kTileN - 1) / kTileN;
-  const int sms = sm_count > 0 ? sm_count : 148;
-  // large problems: 256 x 256 tiles (half the operand traffic per flop)
-  const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
-  if (w.bits == 4 && (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8))) {
-    return LaunchWide(w, m, a_bf16, out, status_word, stream);
+  if (splits >= 1) {
+    float *partial = reinterpret_cast<float *>(
+        reinterpret_cast<unsigned char *>(a_bf16) +
+        AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2));
+    return LaunchWide(w, m, a_bf16, out, status_word, stream, splits, splits > 1 ? partial : nullptr, sms);
   }
   // otherwise the widest token tile that still gives every SM a tile
   if (m > 128 && n_tiles * ((m + 255) / 256) >= sms) {

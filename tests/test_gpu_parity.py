@@ -536,7 +536,8 @@ def test_decode_linearity_at_full_size(cuda_device):
 def test_prefill_tcgen05(cuda_device, m, k, n, bs, zp, bias):
     case = syn.make_case("prefill", m, k, n, 4, bs, seed=m + k + n, zero_points=zp, bias=bias)
     y, kernel = run_device(case, path=_capi.PATH_TCGEN05)
-    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    expected = "nbits_gemm_tcgen05_kernel"   # few tiles: 128-row tiles
+    assert kernel.startswith(expected), kernel
     ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
     assert rel_err(y, ref_bf16) <= TOL_BF16
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
@@ -572,6 +573,29 @@ def test_prefill_tcgen05_wide_tiles(cuda_device, m, k, n, bs, zp, bias):
     ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
     assert rel_err(y, ref_bf16) <= TOL_BF16
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (200, 1024, 12900, 64, True, True),    # 51 tiles of 256 x 256: K in two parts of eight steps, ragged M and N
+    (256, 2048, 16032, 32, True, False),   # the lm-head shard's width: 63 tiles
+])
+def test_prefill_split_k(cuda_device, m, k, n, bs, zp, bias):
+    """Products between decode and prefill whose 256 x 256 tiles alone would leave most SMs idle: K
+    is shared by two CTAs per tile and the partial products are added in part order by a kernel
+    behind them, so two runs give the same bits. Values match the bf16 model like the unsplit
+    kernel's, and the unsplit kernel itself up to the order of the fp32 additions."""
+    case = syn.make_case("splitk", m, k, n, 4, bs, seed=m + k + n + 5, zero_points=zp, bias=bias)
+    y, kernel = run_device(case)
+    again, _ = run_device(case)
+    assert kernel.startswith("nbits_gemm_tcgen05"), kernel
+    assert kernel == "nbits_gemm_tcgen05_wide_kernel(split-k)", kernel
+    np.testing.assert_array_equal(y, again)
+    ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
+    assert rel_err(y, ref_bf16) <= TOL_BF16
+    assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+    whole, name = run_device(case, path=_capi.PATH_TCGEN05_WIDE)
+    assert name == "nbits_gemm_tcgen05_wide_kernel", name
+    assert rel_err(y, whole) <= 1e-5
 
 
 def test_prefill_auto_dispatch_and_full_size_property(cuda_device):
