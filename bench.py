@@ -446,7 +446,7 @@ def main() -> None:
                 "workload": "cfg4 gate/up projection M=16 K=4096 N=14336 bits=4 block=32, accuracy_level=0",
                 "gbs": lgbs, "frac_of_hbm_peak": lgbs / peaks["hbm_gbs"], "us_per_call": sec / (icopies * isteps) * 1e6,
                 "kernel": lname, "device_status": lstatus,
-                "includes": "row factors + digit rows + integer-MMA kernel (three passes of sixteen rows) + combine"}
+                "includes": "digit rows of both K slices + one-pass integer-MMA kernel over 48 digit rows + sum of the slices"}
             del iw, ys_i8
             torch.cuda.empty_cache()
 

@@ -300,6 +300,14 @@ __global__ void __launch_bounds__(256)
 // AUTO sends at most this many tokens to the integer-digit decode kernel (two tokens per pass).
 constexpr std::int64_t kImmaAutoTokens = 2;
 
+// Token counts that AUTO sends to the one-pass digit kernel (nbits_digits_mma_kernel), by block size.
+bool DigitSlicesWanted(const WeightView &w, std::int64_t m) {
+  if (w.bits != 4 || m > 16) {
+    return false;
+  }
+  return (w.block_size == 32 && m >= 6) || (w.block_size == 64 && m >= 5) || (w.block_size >= 128 && m >= 9);
+}
+
 // Core dispatch. The caller holds h->mutex and has made h->device current.
 int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_level, int path,
              OutputView out, cudaStream_t stream) {
@@ -343,10 +351,27 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
       name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
-    // Small blocks with many tokens: the fp16 kernels hold one (block 32) or two (block 64) tokens per
-    // column tile, so 16 tokens are four / two passes over the weights; three digit rows per token
-    // through the sixteen-row integer kernel are fewer passes from M = 5 (block 32) / M = 9 (block 64)
-    // on (measured: block 32 M = 16 80.8 -> 49.4 us, M = 5 40.2 -> 22.2 us; block 64 M = 16 63.1 -> 50.7 us).
+    // Six and more tokens (nine and more on blocks of 128 and above, where the fp16 kernels hold four
+    // tokens per column tile): all digit rows of a 2048-k slice in shared memory, one pass over the
+    // weights (measured against the other paths, us per gate/up-sized node: block 32 M = 8 34.1 -> 22.2,
+    // M = 16 47.1 -> 28.5; block 64 M = 8 32.8 -> 22.1; block 128 M = 16 38.6 -> 29.6, M = 8 21.0 vs 22.5).
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && DigitSlicesWanted(w, m)) {
+      const std::size_t need = mnb::DigitSlicesScratchBytes(w, m);
+      if (need != 0) {
+        const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+        if (rc != MNB_OK) {
+          return rc;
+        }
+        name = mnb::LaunchDigitSlicesGroup(&w, &out, 1, a_dev, m, static_cast<unsigned char *>(h->scratch_a),
+                                           h->status_dev, stream, h->sm_count);
+        if (name == nullptr) {
+          cudaGetLastError();
+        }
+      }
+    }
+    // Five tokens on block 32 (and shapes the sliced kernel does not take): three digit rows per token
+    // through the sixteen-row integer kernel, fewer passes than one token per column tile
+    // (measured: block 32 M = 5 40.2 -> 22.2 us).
     if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO &&
         ((w.block_size == 32 && m >= 5) || (w.block_size == 64 && m >= 9))) {
       const std::size_t need = mnb::DigitsInt8MmaScratchBytes(w, m);
@@ -415,6 +440,19 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     break;
   }
   case MNB_PATH_GEMV_DIGITS: {
+    const std::size_t sliced = m <= 16 ? mnb::DigitSlicesScratchBytes(w, m) : 0;
+    if (sliced != 0) {
+      const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, sliced);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchDigitSlicesGroup(&w, &out, 1, a_dev, m, static_cast<unsigned char *>(h->scratch_a),
+                                         h->status_dev, stream, h->sm_count);
+      if (name != nullptr) {
+        break;
+      }
+      cudaGetLastError();
+    }
     const std::size_t need = m <= 16 ? mnb::DigitsInt8MmaScratchBytes(w, m) : 0;
     if (need != 0) {
       const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
@@ -811,6 +849,24 @@ int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float 
       }
       name = mnb::LaunchInt8MmaGroup(nodes, outs, count, a_dev, m, static_cast<unsigned char *>(first->scratch_a),
                                      first->status_dev, s, first->sm_count);
+    }
+  } else if (accuracy_level == 0 && count > 1 && m <= 16 && DigitSlicesWanted(nodes[0], m)) {
+    // row factors and the digit rows of all K slices made once, then the one-pass product per node
+    std::size_t need = 0;
+    for (int i = 0; i < count; ++i) {
+      const std::size_t bytes = mnb::DigitSlicesScratchBytes(nodes[i], m);
+      need = bytes == 0 ? 0 : (bytes > need ? bytes : need);
+      if (bytes == 0) {
+        break;
+      }
+    }
+    if (need != 0) {
+      const int rc = Grow(&first->scratch_a, &first->scratch_a_bytes, need);
+      if (rc != MNB_OK) {
+        return rc;
+      }
+      name = mnb::LaunchDigitSlicesGroup(nodes, outs, count, a_dev, m, static_cast<unsigned char *>(first->scratch_a),
+                                         first->status_dev, s, first->sm_count);
     }
   } else if (accuracy_level == 0 && count > 1 && m <= 16 &&
              ((nodes[0].block_size == 32 && m >= 5) || (nodes[0].block_size == 64 && m >= 9))) {

@@ -325,6 +325,13 @@ const char *LaunchInt8MmaGroup(const WeightView *nodes, const OutputView *outs, 
 const char *LaunchDigitsInt8MmaGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
                                      std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
                                      int sm_count);
+// accuracy_level 0 for up to sixteen tokens in ONE pass over the weights: each CTA takes one 2048-k
+// slice of K with all digit rows of that slice in shared memory. 0 bytes / nullptr when the shape
+// is outside what the kernel takes.
+std::size_t DigitSlicesScratchBytes(const WeightView &w, std::int64_t m);
+const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                   std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                   int sm_count);
 
 const char *LaunchDequantInt(const WeightView &w, std::int32_t *out, cudaStream_t stream);
 

@@ -816,6 +816,8 @@ constexpr float kDigitRange = 2.0e6f;
 // One CTA per row. factors = {up[m], lift[m], undo[m]} as three arrays of m_total floats.
 __global__ void __launch_bounds__(256)
     nbits_digit_row_factors_kernel(const float *a, int m_total, std::int64_t k, float *factors) {
+  // the digit kernel behind this one may be scheduled right away; it waits before it reads `factors`
+  ptx::GridDependencyLaunch();
   __shared__ float warp_max[8];
   const int row = blockIdx.x;
   const float *src = a + static_cast<std::int64_t>(row) * k;
@@ -937,6 +939,671 @@ __global__ void __launch_bounds__(256)
 }
 
 std::size_t AlignUp(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
+
+// ---- accuracy_level 0, 5 ... 16 tokens, in ONE pass over the weights --------------------------------
+//
+// The three-pass form above keeps sixteen digit rows of the whole K in shared memory. Here a CTA
+// takes ONE 2048-k slice of K (blockIdx.y) for all of its row tiles, so that all 3 x 8 NTOK digit rows
+// of that slice fit (99 KB for sixteen tokens), and the digit rows are laid out digit-major: MMA
+// column tile d * NTOK + j holds digit d of tokens 8 j ... 8 j + 7, which puts the three digits of a
+// token in the same lane and register position. Every weight byte is read once (by the CTA of its
+// slice) and feeds 3 NTOK MMAs. Per quantization block the three exact int32 dots are combined
+//   block_size <= 64:  E = 16384 e0 + 128 e1 + e2 - zp * S   in int32 (|E| < 2^31; S = 16384 s0 + 128 s1 + s2
+//                      comes ready from the digit kernel), one conversion and one FFMA with the scale;
+//   block_size >= 128: e_d - zp * s_d per digit in int32, 16384 f0 + 128 f1 + f2 in fp32
+//                      (the int32 combination could overflow), one FFMA with the scale.
+// The per-token factor `undo` and the bias are applied by the kernel that adds the slices' partial
+// products in slice order. Nodes without zero points use zp = 8 (unsigned codes as they are).
+struct DigitsParams {
+  WeightView w;
+  const unsigned char *act;   // [slices][slice_bytes]: digit rows of a slice, then its table of sums
+  float *partial;             // [slices][tokens_pad][n]
+  int m_total;
+  int *status;
+  int half_tiles;
+  int bpt;
+  int slices;
+  int rec_bytes;
+  int rec_scale_bytes;
+  int slot_bytes;
+  int num_slots;
+  int producers;
+  int act_row_bytes;
+  int table_offset;
+  int slice_bytes;
+  int groups_per_block;
+};
+
+template <int NTOK, int SPB, bool HAS_ZP>
+__global__ void __launch_bounds__(kThreads, 1)
+    nbits_digits_mma_kernel(const __grid_constant__ CUtensorMap map_b, const DigitsParams p) {
+  constexpr int NT = 3 * NTOK;           // MMA column tiles: digit-major
+  constexpr int kRows = 8 * NT;          // digit rows
+  constexpr int kTableInts = SPB == 4 ? kRows : 8 * NTOK;   // per entry: sums per digit row, or combined per token
+  extern __shared__ __align__(1024) unsigned char smem_dyn[];
+  unsigned char *smem_raw = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
+  unsigned char *slots = smem_raw;
+  unsigned char *act = smem_raw + static_cast<size_t>(p.num_slots) * p.slot_bytes;
+  float4 *partial = reinterpret_cast<float4 *>(act + p.slice_bytes); // [2][kWarps][NTOK][32]
+  std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(partial + 2 * kWarps * NTOK * 32);
+  std::uint64_t *empty_bar = full_bar + kMaxSlots;
+  std::uint64_t *act_bar = empty_bar + kMaxSlots;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int slice = blockIdx.y;
+  // the kernel that adds the slices up may be scheduled as SMs free up; it waits for this grid
+  ptx::GridDependencyLaunch();
+
+  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * p.half_tiles / gridDim.x);
+  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * p.half_tiles / gridDim.x);
+  const int n_tiles = (h_end - h_begin + 1) >> 1;
+  const std::int64_t row_limit =
+      static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
+
+  if (warp >= kWarps) {
+    // ------------------------------ producers ------------------------------
+    const int producer = warp - kWarps;
+    if (producer == 0 && lane == 0) {
+      for (int s = 0; s < p.num_slots; ++s) {
+        ptx::MbarInit(&full_bar[s], 1);
+        ptx::MbarInit(&empty_bar[s], kWarps);
+      }
+      ptx::MbarInit(act_bar, 1);
+      ptx::FenceMbarInit();
+    }
+    asm volatile("bar.sync 11, %0;" ::"n"(kProducers * 32) : "memory"); // barriers initialised
+    asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
+    if (lane == 0) {
+      ptx::PrefetchTensorMap(&map_b);
+      const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
+      bool ok = true;
+      bool act_issued = producer != 0;
+      // the digit rows come from the kernel launched just before (programmatic dependent launch);
+      // the weights do not depend on it: a first ring of tiles is requested before waiting for it
+      auto issue_activations = [&]() {
+        ptx::GridDependencyWait();
+        ptx::MbarArriveExpectTx(act_bar, static_cast<std::uint32_t>(p.slice_bytes));
+        ptx::BulkLoad(act, p.act + static_cast<std::int64_t>(slice) * p.slice_bytes,
+                      static_cast<std::uint32_t>(p.slice_bytes), act_bar);
+        act_issued = true;
+      };
+      for (int task = producer; producer < p.producers && task < n_tiles && ok; task += p.producers) {
+        const int slot = task % p.num_slots;
+        const std::uint32_t round = static_cast<std::uint32_t>(task / p.num_slots);
+        if (round != 0) {
+          if (!act_issued) {
+            issue_activations();
+          }
+          if (!ptx::MbarWait(&empty_bar[slot], (round & 1u) ^ 1u)) {
+            ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
+            ok = false;
+            break;
+          }
+        }
+        const int h0 = h_begin + 2 * task;
+        const unsigned char *meta_src =
+            p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes + slice * meta_slice_stride;
+        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+        unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
+        ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
+        TmaLoad3D(dst, &map_b, 0, h0 * 8, slice * kSegments, &full_bar[slot]);
+        ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
+      }
+      if (!act_issued) {
+        issue_activations();
+      }
+      // stay until every copy this lane issued has been consumed (bounded), so none lands after exit
+      const int first = n_tiles - p.num_slots < 0 ? 0 : n_tiles - p.num_slots;
+      for (int i = first; i < n_tiles && ok; ++i) {
+        if (producer < p.producers && (i % p.producers) == producer &&
+            !ptx::MbarWait(&empty_bar[i % p.num_slots], static_cast<std::uint32_t>(i / p.num_slots) & 1u)) {
+          break;
+        }
+      }
+      if (producer == 0) {
+        ptx::MbarWait(act_bar, 0);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory"); // barriers initialised
+  bool dead = false;
+  if (!ptx::MbarWait(act_bar, 0)) {
+    ReportStatus(p.status, kDeviceTimeoutFullBarrier);
+    dead = true;
+  }
+
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const std::uint32_t nib = 0x0f0f0f0fu;
+  int word_off[4];
+#pragma unroll
+  for (int st = 0; st < 4; ++st) {
+    const int c = (warp & 1) * 4 + st;
+    word_off[st] = (warp >> 1) * 2048 + g * 128 + ((c ^ g) << 4) + 4 * t;
+  }
+  constexpr int kEntriesPerGroup = 4 / SPB;
+  const int scale_row_bytes = p.rec_scale_bytes / 8;
+  const int meta_index = p.groups_per_block > 1 ? warp / p.groups_per_block : warp * kEntriesPerGroup;
+  // sums of this warp's entries: tokens 2 t, 2 t + 1 of every column tile
+  const int *table = reinterpret_cast<const int *>(act + p.table_offset) + warp * kEntriesPerGroup * kTableInts + 2 * t;
+  // digit bytes: row g of every column tile, this warp's 128-k group, this lane's eight k per step
+  const unsigned char *act_lane = act + g * p.act_row_bytes + warp * 128 + t * 32;
+
+  int slot = 0;
+  std::uint32_t round = 0;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int h0 = h_begin + 2 * tile;
+    const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
+    float acc[NTOK][4];
+#pragma unroll
+    for (int j = 0; j < NTOK; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[j][i] = 0.0f;
+      }
+    }
+    if (!dead && !ptx::MbarWait(&full_bar[slot], round & 1u)) {
+      ReportStatus(p.status, kDeviceTimeoutFullBarrier);
+      dead = true;
+    }
+    if (!dead) {
+      const unsigned char *sb = slots + static_cast<size_t>(slot) * p.slot_bytes;
+      std::uint32_t w_lo[4], w_hi[4];
+#pragma unroll
+      for (int st = 0; st < 4; ++st) {
+        w_lo[st] = *reinterpret_cast<const std::uint32_t *>(sb + word_off[st]);
+        w_hi[st] = *reinterpret_cast<const std::uint32_t *>(sb + word_off[st] + 1024);
+      }
+      const unsigned char *meta0 = sb + kTaskBytes;
+      const unsigned char *meta1 = meta0 + p.rec_bytes;
+      const float *sc0 = reinterpret_cast<const float *>(meta0 + g * scale_row_bytes) + meta_index;
+      const float *sc1 = reinterpret_cast<const float *>(meta1 + g * scale_row_bytes) + meta_index;
+      float ws_lo[kEntriesPerGroup], ws_hi[kEntriesPerGroup];
+      int zp_lo[kEntriesPerGroup], zp_hi[kEntriesPerGroup];
+      if constexpr (SPB == 1) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(sc0);
+        const float4 b4 = *reinterpret_cast<const float4 *>(sc1);
+        ws_lo[0] = a4.x, ws_lo[1] = a4.y, ws_lo[2] = a4.z, ws_lo[3] = a4.w;
+        ws_hi[0] = b4.x, ws_hi[1] = b4.y, ws_hi[2] = b4.z, ws_hi[3] = b4.w;
+      } else if constexpr (SPB == 2) {
+        const float2 a2 = *reinterpret_cast<const float2 *>(sc0);
+        const float2 b2 = *reinterpret_cast<const float2 *>(sc1);
+        ws_lo[0] = a2.x, ws_lo[1] = a2.y, ws_hi[0] = b2.x, ws_hi[1] = b2.y;
+      } else {
+        ws_lo[0] = sc0[0], ws_hi[0] = sc1[0];
+      }
+#pragma unroll
+      for (int i = 0; i < kEntriesPerGroup; ++i) {
+        zp_lo[i] = 8;
+        zp_hi[i] = 8;
+      }
+      if constexpr (HAS_ZP) {
+        const unsigned char *zr0 = meta0 + p.rec_scale_bytes + g * p.bpt + meta_index;
+        const unsigned char *zr1 = meta1 + p.rec_scale_bytes + g * p.bpt + meta_index;
+#pragma unroll
+        for (int i = 0; i < kEntriesPerGroup; ++i) {
+          zp_lo[i] = zr0[i];
+          zp_hi[i] = zr1[i];
+        }
+      }
+      // the weights are in registers: hand the slot back before the arithmetic
+      __syncwarp();
+      if (lane == 0) {
+        ptx::MbarArrive(&empty_bar[slot]);
+      }
+      int d[NT][4];
+#pragma unroll
+      for (int st = 0; st < 4; ++st) {
+        const std::uint32_t a0 = w_lo[st] & nib;
+        const std::uint32_t a1 = w_hi[st] & nib;
+        const std::uint32_t a2 = (w_lo[st] >> 4) & nib;
+        const std::uint32_t a3 = (w_hi[st] >> 4) & nib;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint2 b = *reinterpret_cast<const uint2 *>(act_lane + nt * 8 * p.act_row_bytes + st * 8);
+          if ((st % SPB) == 0) {
+            MmaU8S8Zero(d[nt], a0, a1, a2, a3, b.x, b.y);
+          } else {
+            MmaU8S8(d[nt], a0, a1, a2, a3, b.x, b.y);
+          }
+        }
+        if (((st + 1) % SPB) == 0) {
+          const int idx = st / SPB;
+          const int *sums = table + idx * kTableInts;
+#pragma unroll
+          for (int j = 0; j < NTOK; ++j) {
+            float f[4];
+            if constexpr (SPB == 4) {
+              // per digit: take the zero point out in int32, combine the digits in fp32
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                f[i] = 0.0f;
+              }
+#pragma unroll
+              for (int digit = 0; digit < 3; ++digit) {
+                const int2 sd = *reinterpret_cast<const int2 *>(sums + (digit * NTOK + j) * 8);
+                const int *e = d[digit * NTOK + j];
+                const float weight = digit == 0 ? 16384.0f : (digit == 1 ? 128.0f : 1.0f);
+                f[0] = fmaf(weight, static_cast<float>(e[0] - zp_lo[idx] * sd.x), f[0]);
+                f[1] = fmaf(weight, static_cast<float>(e[1] - zp_lo[idx] * sd.y), f[1]);
+                f[2] = fmaf(weight, static_cast<float>(e[2] - zp_hi[idx] * sd.x), f[2]);
+                f[3] = fmaf(weight, static_cast<float>(e[3] - zp_hi[idx] * sd.y), f[3]);
+              }
+            } else {
+              // block_size <= 64: everything in int32, S = 16384 s0 + 128 s1 + s2 from the table
+              const int2 sd = *reinterpret_cast<const int2 *>(sums + j * 8);
+              const int *e0 = d[j], *e1 = d[NTOK + j], *e2 = d[2 * NTOK + j];
+              // (unsigned arithmetic: the parts may wrap, the result fits)
+              auto combine = [](int x0, int x1, int x2, int zp, int s) {
+                const unsigned v = static_cast<unsigned>(x0) * 16384u + static_cast<unsigned>(x1) * 128u +
+                                   static_cast<unsigned>(x2) - static_cast<unsigned>(zp) * static_cast<unsigned>(s);
+                return static_cast<float>(static_cast<int>(v));
+              };
+              f[0] = combine(e0[0], e1[0], e2[0], zp_lo[idx], sd.x);
+              f[1] = combine(e0[1], e1[1], e2[1], zp_lo[idx], sd.y);
+              f[2] = combine(e0[2], e1[2], e2[2], zp_hi[idx], sd.x);
+              f[3] = combine(e0[3], e1[3], e2[3], zp_hi[idx], sd.y);
+            }
+            acc[j][0] = fmaf(ws_lo[idx], f[0], acc[j][0]);
+            acc[j][1] = fmaf(ws_lo[idx], f[1], acc[j][1]);
+            acc[j][2] = fmaf(ws_hi[idx], f[2], acc[j][2]);
+            acc[j][3] = fmaf(ws_hi[idx], f[3], acc[j][3]);
+          }
+        }
+      }
+    }
+    if (++slot == p.num_slots) {
+      slot = 0;
+      ++round;
+    }
+
+    // ---- sum over the sixteen warps (same scheme as the accuracy_level-4 kernel) ----------------
+    const int b = tile & 1;
+    const int reducer0 = (tile * NTOK) & (kWarps - 1);
+    const bool reduces = ((warp - reducer0) & (kWarps - 1)) < NTOK;
+    if (tile >= 2) {
+      const int previous0 = ((tile - 2) * NTOK) & (kWarps - 1);
+      const bool reduced_previous = ((warp - previous0) & (kWarps - 1)) < NTOK;
+      if (!reduced_previous) {
+        asm volatile("bar.sync %0, %1;" ::"r"(4 + b), "n"(kConsumerThreads) : "memory");
+      }
+    }
+    float4 *mine = partial + ((b * kWarps + warp) * NTOK) * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < NTOK; ++j) {
+      mine[j * 32] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    }
+    if (!reduces) {
+      asm volatile("bar.arrive %0, %1;" ::"r"(2 + b), "n"(kConsumerThreads) : "memory");
+    } else {
+      asm volatile("bar.sync %0, %1;" ::"r"(2 + b), "n"(kConsumerThreads) : "memory");
+      const int j = (warp - reducer0) & (kWarps - 1);
+      const float4 *column = partial + (b * kWarps * NTOK + j) * 32 + lane;
+      float4 total = column[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) {
+        const float4 v = column[w * NTOK * 32];
+        total.x += v.x, total.y += v.y, total.z += v.z, total.w += v.w;
+      }
+      if (tile + 2 < n_tiles) {
+        asm volatile("bar.arrive %0, %1;" ::"r"(4 + b), "n"(kConsumerThreads) : "memory");
+      }
+      const std::int64_t r_lo = row0 + g;
+      const std::int64_t r_hi = row0 + g + 8;
+      const std::int64_t m0 = j * 8 + 2 * t;
+      float *y0 = p.partial + (static_cast<std::int64_t>(slice) * (8 * NTOK) + m0) * p.w.n;
+      float *y1 = y0 + p.w.n;
+      if (m0 < p.m_total) {
+        if (r_lo < row_limit) {
+          y0[r_lo] = total.x;
+        }
+        if (r_hi < row_limit) {
+          y0[r_hi] = total.z;
+        }
+      }
+      if (m0 + 1 < p.m_total) {
+        if (r_lo < row_limit) {
+          y1[r_lo] = total.y;
+        }
+        if (r_hi < row_limit) {
+          y1[r_hi] = total.w;
+        }
+      }
+    }
+  }
+}
+
+// Digit rows of every K slice in the layout nbits_digits_mma_kernel reads: CTAs (token, slice,
+// part of the slice's entries). A CTA first finds the row's largest magnitude (all of K: 16 KB per row, an L2 hit for
+// all but the first CTA of a token), then converts its slice, one warp per table entry at a time.
+// Slice layout: [24 NTOK rows][act_row_bytes] signed bytes, row (d NTOK + j) 8 + i = digit d of
+// token 8 j + i, k in the MMA's order inside each 128-k group; then the table
+// [entries of the slice][table_ints]: per digit row its sum (entries of 128 k), or per token the
+// combined 16384 s0 + 128 s1 + s2 (entries of 32 / 64 k). factors[2 m + token] = the factor that
+// takes the integer result back (NaN for a row with a non-finite entry), read by the kernel that adds
+// the slices up.
+__global__ void __launch_bounds__(256)
+    nbits_digit_slices_kernel(const float *a, float *factors, int m_total, std::int64_t k, int entry_k,
+                              int entries_per_slice, int ntok, int act_row_bytes, int table_offset,
+                              int slice_bytes, int table_ints, unsigned char *act) {
+  // the product kernel behind this one may start (barrier set-up, first weight tiles) right away
+  ptx::GridDependencyLaunch();
+  __shared__ float warp_max[8];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x;
+  const int slice = blockIdx.y;
+  const bool live = token < m_total;
+  const float *src = a + static_cast<std::int64_t>(token) * k;
+  float amax = 0.0f;
+  bool bad = false;
+  if (live) {
+    for (std::int64_t i = threadIdx.x; i < k; i += 256) {
+      const float v = src[i];
+      amax = fmaxf(amax, fabsf(v));
+      bad = bad || (v != v);
+    }
+  }
+  if (bad) {
+    amax = __int_as_float(0x7f800000);
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+  }
+  if (lane == 0) {
+    warp_max[warp] = amax;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    amax = fmaxf(amax, warp_max[i]);
+  }
+  const bool finite = amax < 3.0e38f;
+  const float lift = amax < 1.0e-18f ? 1.8446744e19f /* 2^64 */ : 1.0f;
+  const float lifted = amax * lift;
+  const float up = (live && finite && lifted > 0.0f) ? kDigitRange / lifted : 0.0f;
+  if (live && slice == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    factors[2 * m_total + token] = finite ? (lifted / kDigitRange) / lift : __int_as_float(0x7fc00000);
+  }
+  unsigned char *base = act + static_cast<std::int64_t>(slice) * slice_bytes;
+  const int tile = token >> 3;
+  const int within = token & 7;
+  std::int8_t *rows[3];
+#pragma unroll
+  for (int digit = 0; digit < 3; ++digit) {
+    rows[digit] = reinterpret_cast<std::int8_t *>(base) +
+                  static_cast<std::int64_t>((digit * ntok + tile) * 8 + within) * act_row_bytes;
+  }
+  // gridDim.z CTAs share a slice's entries, so that even two slices of sixteen tokens fill the GPU
+  const int entry_begin = static_cast<int>(blockIdx.z) * entries_per_slice / static_cast<int>(gridDim.z);
+  const int entry_end = (static_cast<int>(blockIdx.z) + 1) * entries_per_slice / static_cast<int>(gridDim.z);
+  for (int entry = entry_begin + warp; entry < entry_end; entry += 8) {
+    int sum[3] = {0, 0, 0};
+    for (int e = lane; e < entry_k; e += 32) {
+      const int k_in_slice = entry * entry_k + e;
+      const std::int64_t kk = static_cast<std::int64_t>(slice) * kTaskK + k_in_slice;
+      int q[3] = {0, 0, 0};
+      if (live && kk < k) {
+        int n = __float2int_rn((src[kk] * lift) * up);
+        const int range = static_cast<int>(kDigitRange);
+        n = n > range ? range : (n < -range ? -range : n);
+        q[2] = ((n + 64) & 127) - 64;
+        const int n1 = (n - q[2]) >> 7;
+        q[1] = ((n1 + 64) & 127) - 64;
+        q[0] = (n1 - q[1]) >> 7;
+      }
+      const int at = ActBytePosition(k_in_slice);
+#pragma unroll
+      for (int digit = 0; digit < 3; ++digit) {
+        sum[digit] += q[digit];
+        rows[digit][at] = static_cast<std::int8_t>(q[digit]);
+      }
+    }
+#pragma unroll
+    for (int digit = 0; digit < 3; ++digit) {
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        sum[digit] += __shfl_xor_sync(0xffffffffu, sum[digit], offset);
+      }
+    }
+    if (lane == 0) {
+      int *cell = reinterpret_cast<int *>(base + table_offset) + static_cast<std::int64_t>(entry) * table_ints;
+      if (table_ints == 8 * ntok) {
+        cell[token] = static_cast<int>(static_cast<unsigned>(sum[0]) * 16384u + static_cast<unsigned>(sum[1]) * 128u +
+                                       static_cast<unsigned>(sum[2]));
+      } else {
+#pragma unroll
+        for (int digit = 0; digit < 3; ++digit) {
+          cell[(digit * ntok + tile) * 8 + within] = sum[digit];
+        }
+      }
+    }
+  }
+}
+
+// Y[token][n] = undo[token] * (P_0 + P_1 + ... in slice order)[token][n] + bias[n].
+__global__ void __launch_bounds__(256)
+    nbits_digit_slices_sum_kernel(const float *partial, int slices, int tokens_pad, const float *factors, int m_total,
+                                  std::int64_t n, const float *bias, OutputView out) {
+  const std::int64_t total = static_cast<std::int64_t>(m_total) * n;
+  const std::int64_t slice_stride = static_cast<std::int64_t>(tokens_pad) * n;
+  ptx::GridDependencyWait();   // the partial products come from the kernel before this one
+  for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<std::int64_t>(gridDim.x) * 256) {
+    const std::int64_t token = i / n;
+    const std::int64_t col = i - token * n;
+    float sum = partial[token * n + col];
+    for (int s = 1; s < slices; ++s) {
+      sum += partial[s * slice_stride + token * n + col];
+    }
+    const float undo = factors[2 * m_total + token];
+    out.y[token * out.ld + out.col_offset + col] = fmaf(sum, undo, bias != nullptr ? bias[col] : 0.0f);
+  }
+}
+
+struct DigitsGeometry {
+  bool ok;
+  int ntok;
+  int spb;
+  int entry_k;
+  int entries_per_slice;
+  int table_ints;
+  int act_row_bytes;
+  int table_offset;
+  int slice_bytes;
+  int slot_bytes;
+  int num_slots;
+  std::size_t smem;
+  std::size_t act_bytes;      // all slices
+  std::size_t partial_bytes;  // [slices][tokens_pad][n]
+};
+
+DigitsGeometry DigitsGeometryOf(const WeightView &w, std::int64_t m) {
+  DigitsGeometry geo{};
+  const MetaGeometry meta = MetaGeometryOf(w);
+  if (meta.bytes == 0 || meta.bpt * w.block_size != kTaskK || (w.row_bytes % 128) != 0 || m < 1 || m > 16 ||
+      (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0) {
+    return geo;
+  }
+  geo.ntok = m > 8 ? 2 : 1;
+  geo.entry_k = w.block_size < 128 ? w.block_size : 128;
+  geo.spb = geo.entry_k / 32;
+  geo.entries_per_slice = kTaskK / geo.entry_k;
+  geo.table_ints = geo.spb == 4 ? 24 * geo.ntok : 8 * geo.ntok;
+  geo.act_row_bytes = kTaskK + 16;
+  geo.table_offset = 24 * geo.ntok * geo.act_row_bytes;
+  geo.slice_bytes = geo.table_offset + geo.entries_per_slice * geo.table_ints * 4;
+  geo.slot_bytes = (kTaskBytes + 2 * meta.rec_bytes + 1023) & ~1023;
+  const std::size_t limit = 225 * 1024;
+  const std::size_t fixed = static_cast<std::size_t>(geo.slice_bytes) + 2 * kWarps * geo.ntok * 32 * sizeof(float4) +
+                            (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64 + 1024;
+  if ((geo.slice_bytes % 16) != 0 || fixed + 3 * static_cast<std::size_t>(geo.slot_bytes) > limit) {
+    return geo;
+  }
+  int slots = static_cast<int>((limit - fixed) / geo.slot_bytes);
+  geo.num_slots = slots > kMaxSlots ? kMaxSlots : slots;
+  geo.smem = static_cast<std::size_t>(geo.num_slots) * geo.slot_bytes + fixed;
+  geo.act_bytes = static_cast<std::size_t>(meta.slices) * geo.slice_bytes;
+  geo.partial_bytes = static_cast<std::size_t>(meta.slices) * 8 * geo.ntok * static_cast<std::size_t>(w.n) * sizeof(float);
+  geo.ok = true;
+  return geo;
+}
+
+} // namespace
+
+std::size_t DigitSlicesScratchBytes(const WeightView &w, std::int64_t m) {
+  const DigitsGeometry geo = DigitsGeometryOf(w, m);
+  if (!geo.ok) {
+    return 0;
+  }
+  return AlignUp(geo.act_bytes) + AlignUp(3 * m * sizeof(float)) + geo.partial_bytes;
+}
+
+namespace {
+
+const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo, std::int64_t m, unsigned char *act,
+                                  const float *factors, float *partial, OutputView out, int *status_word,
+                                  cudaStream_t stream, int sm_count) {
+  const MetaGeometry meta = MetaGeometryOf(w);
+  DigitsParams p{};
+  p.w = w;
+  p.act = act;
+  p.partial = partial;
+  p.m_total = static_cast<int>(m);
+  p.status = status_word;
+  p.half_tiles = meta.half_tiles;
+  p.bpt = meta.bpt;
+  p.slices = meta.slices;
+  p.rec_bytes = meta.rec_bytes;
+  p.rec_scale_bytes = meta.rec_scale_bytes;
+  p.slot_bytes = geo.slot_bytes;
+  p.num_slots = geo.num_slots;
+  p.producers = geo.num_slots < kProducers ? geo.num_slots : kProducers;
+  p.act_row_bytes = geo.act_row_bytes;
+  p.table_offset = geo.table_offset;
+  p.slice_bytes = geo.slice_bytes;
+  p.groups_per_block = w.block_size >= 256 ? w.block_size / 128 : 1;
+  CUtensorMap map_b;
+  if (!EncodeWeightsMap3D(&map_b, w)) {
+    return nullptr;
+  }
+  int ctas = sm_count > 0 ? sm_count : 148;
+  const int tiles = (meta.half_tiles + 1) / 2;
+  // slices run side by side: share the SMs between them so that one wave covers the node
+  ctas = ctas / meta.slices > 0 ? ctas / meta.slices : 1;
+  if (ctas > tiles) {
+    ctas = tiles;
+  }
+  dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(meta.slices), 1);
+  cudaError_t err = cudaErrorInvalidValue;
+#define MNB_DIGITS_CASE(NTOK_, SPB_, ZP_)                                                        \
+  if (geo.ntok == NTOK_ && geo.spb == SPB_ && (w.zp != nullptr) == ZP_) {                        \
+    auto kernel = nbits_digits_mma_kernel<NTOK_, SPB_, ZP_>;                                     \
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                               static_cast<int>(geo.smem));                                      \
+    if (err == cudaSuccess) {                                                                    \
+      cudaLaunchConfig_t config = {};                                                            \
+      config.gridDim = grid;                                                                     \
+      config.blockDim = dim3(kThreads, 1, 1);                                                    \
+      config.dynamicSmemBytes = geo.smem;                                                        \
+      config.stream = stream;                                                                    \
+      cudaLaunchAttribute attribute[1];                                                          \
+      attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
+      attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
+      config.attrs = attribute;                                                                  \
+      config.numAttrs = 1;                                                                       \
+      err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
+    }                                                                                            \
+  }
+#define MNB_DIGITS_CASES(SPB_)                                                                   \
+  MNB_DIGITS_CASE(1, SPB_, true)                                                                 \
+  MNB_DIGITS_CASE(1, SPB_, false)                                                                \
+  MNB_DIGITS_CASE(2, SPB_, true)                                                                 \
+  MNB_DIGITS_CASE(2, SPB_, false)
+  MNB_DIGITS_CASES(1)
+  MNB_DIGITS_CASES(2)
+  MNB_DIGITS_CASES(4)
+#undef MNB_DIGITS_CASES
+#undef MNB_DIGITS_CASE
+  if (err != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  const std::int64_t total = m * w.n;
+  std::int64_t blocks = (total + 255) / 256;
+  blocks = blocks > 148 * 4 ? 148 * 4 : blocks;
+  {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    config.blockDim = dim3(256, 1, 1);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    if (cudaLaunchKernelEx(&config, nbits_digit_slices_sum_kernel, static_cast<const float *>(partial), meta.slices,
+                           8 * geo.ntok, factors, static_cast<int>(m), w.n, w.bias, out) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+  }
+  CountLaunch();
+  return "nbits_digits_mma_kernel";
+}
+
+} // namespace
+
+// accuracy_level 0 for up to sixteen tokens in one pass over the weights: the digit rows of all K
+// slices once (one kernel, shared by sibling nodes), then per node the sliced integer-MMA product and
+// the sum of its slices. `scratch`: DigitSlicesScratchBytes of the node with the most columns.
+const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
+                                   std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                   int sm_count) {
+  if (count < 1 || count > kMaxGroupedNodes || scratch == nullptr) {
+    return nullptr;
+  }
+  const WeightView &w = nodes[0];
+  const DigitsGeometry geo = DigitsGeometryOf(w, m);
+  if (!geo.ok) {
+    return nullptr;
+  }
+  for (int i = 0; i < count; ++i) {
+    const DigitsGeometry other = DigitsGeometryOf(nodes[i], m);
+    if (!other.ok || nodes[i].meta == nullptr || nodes[i].k != w.k || nodes[i].block_size != w.block_size ||
+        other.slice_bytes != geo.slice_bytes || other.table_ints != geo.table_ints) {
+      return nullptr;
+    }
+  }
+  const MetaGeometry meta = MetaGeometryOf(w);
+  unsigned char *act = scratch;
+  float *factors = reinterpret_cast<float *>(scratch + AlignUp(geo.act_bytes));
+  float *partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(factors) + AlignUp(3 * m * sizeof(float)));
+  const unsigned parts = geo.entries_per_slice >= 32 ? 8u : 4u;
+  nbits_digit_slices_kernel<<<dim3(static_cast<unsigned>(8 * geo.ntok), static_cast<unsigned>(meta.slices), parts), 256,
+                              0, stream>>>(a, factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_per_slice,
+                                        geo.ntok, geo.act_row_bytes, geo.table_offset, geo.slice_bytes, geo.table_ints,
+                                        act);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  for (int i = 0; i < count; ++i) {
+    if (LaunchDigitSlicesNode(nodes[i], DigitsGeometryOf(nodes[i], m), m, act, factors, partial, outs[i], status_word,
+                              stream, sm_count) == nullptr) {
+      return nullptr;
+    }
+  }
+  return "nbits_digits_mma_kernel";
+}
+
+namespace {
 
 } // namespace
 

@@ -52,21 +52,22 @@ def resident_takes(case):
             (case.zero_points is None or blocks % 16 == 0))
 
 
-RESIDENT = "nbits_decode_resident_kernel"
-
-
-def resident_takes(case):
-    """Shapes AUTO sends to the one-token kernel that asks for all of its weights at kernel start."""
-    blocks = -(-case.k // case.block_size)
-    return (case.bits == 4 and case.block_size == 128 and case.m == 1 and blocks % 8 == 0 and
-            (case.zero_points is None or blocks % 16 == 0))
-
-
 def direct_takes(case):
     """Shapes AUTO sends to the direct-stream decode kernel: one token, 4-bit, block 128, blocks per
     row a multiple of four (and the resident kernel does not take them)."""
     return (case.bits == 4 and case.block_size == 128 and case.m == 1 and
             (-(-case.k // case.block_size)) % 4 == 0 and not resident_takes(case))
+
+
+def sliced_digits_take(case):
+    """Token counts AUTO sends to the one-pass digit kernel, by block size (4-bit, packed rows that are
+    whole 128-byte units)."""
+    m, bs = case.m, case.block_size
+    wanted = (bs == 32 and m >= 6) or (bs == 64 and m >= 5) or (bs >= 128 and m >= 9)
+    return case.bits == 4 and m <= 16 and wanted and (case.k // 2) % 128 == 0 and 32 <= bs <= 1024
+
+
+SLICED = "nbits_digits_mma_kernel"
 
 
 def oracle_f64(case):
@@ -104,7 +105,7 @@ def test_config1_single_node(cuda_device):
 def test_config2_decode_sweep(cuda_device, m):
     case = syn.config2(m)
     y, kernel = run_device(case)
-    expected = {1: RESIDENT, 4: "nbits_gemv_mma_kernel", 16: "nbits_gemv_mma_multi_kernel"}[m]
+    expected = {1: RESIDENT, 4: "nbits_gemv_mma_kernel", 16: SLICED}[m]
     assert kernel == expected, kernel
     ref = oracle_f64(case)
     assert rel_err(y, ref) <= TOL_FP32
@@ -189,8 +190,11 @@ def test_decode_mma_multi_tile_path(cuda_device, m, k, n, bs, zp, bias):
     y_auto, kernel_auto = run_device(case)
     if direct_takes(case):
         assert kernel_auto == DIRECT and rel_err(y, y_auto) <= TOL_FP32
-    elif (bs == 32 and m >= 5) or (bs == 64 and m >= 9):
-        # AUTO sends many tokens over small blocks through the digit rows of the integer kernel
+    elif sliced_digits_take(case):
+        # AUTO sends many tokens through the one-pass digit kernel
+        assert kernel_auto == SLICED and rel_err(y, y_auto) <= TOL_FP32
+    elif bs == 32 and m == 5:
+        # five tokens over block 32: digit rows through the sixteen-row integer kernel
         assert kernel_auto == "nbits_int8_mma_kernel(digits)" and rel_err(y, y_auto) <= TOL_FP32
     else:   # AUTO picks the same kernel for these shapes
         assert kernel_auto == kernel and np.array_equal(y, y_auto)
@@ -446,13 +450,11 @@ DIGIT_ROW_CASES = [
 def test_decode_digit_rows_path(cuda_device, m, k, n, bs, zp, bias):
     case = syn.make_case("digit_rows", m, k, n, 4, bs, seed=m * 17 + k + n + bs, zero_points=zp, bias=bias)
     y, kernel = run_device(case, path=_capi.PATH_GEMV_DIGITS)
-    assert kernel == "nbits_int8_mma_kernel(digits)"
+    assert kernel == "nbits_digits_mma_kernel"
     ref = oracle_f64(case)
     for row in range(m):
         assert rel_err(y[row], ref[row]) <= TOL_FP32, row
     y_auto, kernel_auto = run_device(case)
-    picked = ((bs == 32 and m >= 5) or (bs == 64 and m >= 9)) and not direct_takes(case)
-    assert (kernel_auto == kernel) == picked
     assert rel_err(y, y_auto) <= TOL_FP32
 
 
