@@ -1072,7 +1072,10 @@ int mnb_matmul_device_gather_ex(mnb_weights *h, const float *a_dev, int64_t m, i
   }
   const WeightView &w = h->view;
   const char *name = nullptr;
-  if (accuracy_level == 0 && m <= 16) {
+  // (token counts that AUTO sends to the one-pass digit kernel take the general path below: that
+  // kernel plus the push is faster than the decode kernels with their own push, 100 against 157 us
+  // per lm-head half at M = 8)
+  if (accuracy_level == 0 && m <= 16 && !(DigitSlicesWanted(w, m) && mnb::DigitSlicesScratchBytes(w, m) != 0)) {
     mnb::GatherTail fused_tail = tail;
     fused_tail.wait = wait != 0 ? 1 : 0;
     // The tensor-core decode kernels push each CTA's rows to the peers as the CTA finishes, and the
