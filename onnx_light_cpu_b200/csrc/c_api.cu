@@ -305,7 +305,7 @@ bool DigitSlicesWanted(const WeightView &w, std::int64_t m) {
   if (w.bits != 4 || m > 16) {
     return false;
   }
-  return (w.block_size == 32 && m >= 6) || (w.block_size == 64 && m >= 5) || (w.block_size >= 128 && m >= 9);
+  return m >= 5;
 }
 
 // Core dispatch. The caller holds h->mutex and has made h->device current.
@@ -351,10 +351,10 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
       name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
-    // Six and more tokens (nine and more on blocks of 128 and above, where the fp16 kernels hold four
-    // tokens per column tile): all digit rows of a 2048-k slice in shared memory, one pass over the
-    // weights (measured against the other paths, us per gate/up-sized node: block 32 M = 8 34.1 -> 22.2,
-    // M = 16 47.1 -> 28.5; block 64 M = 8 32.8 -> 22.1; block 128 M = 16 38.6 -> 29.6, M = 8 21.0 vs 22.5).
+    // Five and more tokens: all digit rows of a 2048-k slice in shared memory, one pass over the
+    // weights (measured against the other paths, us per gate/up-sized node: block 32 M = 5 21.5 -> 20.2,
+    // M = 8 34.1 -> 20.2, M = 16 47.1 -> 24.9; block 64 M = 8 32.8 -> 20.4; block 128 M = 5 20.3 -> 19.5,
+    // M = 8 21.0 -> 19.5, M = 16 38.6 -> 25.7; four tokens stay on the fp16 kernel: 15.3 against 19.5).
     if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && DigitSlicesWanted(w, m)) {
       const std::size_t need = mnb::DigitSlicesScratchBytes(w, m);
       if (need != 0) {
@@ -369,9 +369,8 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
         }
       }
     }
-    // Five tokens on block 32 (and shapes the sliced kernel does not take): three digit rows per token
-    // through the sixteen-row integer kernel, fewer passes than one token per column tile
-    // (measured: block 32 M = 5 40.2 -> 22.2 us).
+    // Shapes the sliced kernel does not take: three digit rows per token through the sixteen-row
+    // integer kernel in up to three passes, still fewer than one token per column tile on small blocks.
     if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO &&
         ((w.block_size == 32 && m >= 5) || (w.block_size == 64 && m >= 9))) {
       const std::size_t need = mnb::DigitsInt8MmaScratchBytes(w, m);

@@ -1436,7 +1436,10 @@ DigitsGeometry DigitsGeometryOf(const WeightView &w, std::int64_t m) {
   geo.spb = geo.entry_k / 32;
   geo.entries_per_slice = kTaskK / geo.entry_k;
   geo.table_ints = geo.spb == 4 ? 24 * geo.ntok : 8 * geo.ntok;
-  geo.act_row_bytes = kTaskK + 16;
+  // 8 bytes of padding: the sixteen lanes of a half warp (four rows, four 32-byte positions) read
+  // eight bytes each per step, and with rows 2056 bytes apart they fall on 32 different banks
+  // (2064 made it a two-way conflict: 1.45 M conflicts in 4.12 M wavefronts)
+  geo.act_row_bytes = kTaskK + 8;
   geo.table_offset = 24 * geo.ntok * geo.act_row_bytes;
   geo.slice_bytes = geo.table_offset + geo.entries_per_slice * geo.table_ints * 4;
   geo.slot_bytes = (kTaskBytes + 2 * meta.rec_bytes + 1023) & ~1023;

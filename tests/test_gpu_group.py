@@ -108,9 +108,8 @@ def test_small_block_group_shares_its_prologue(cuda_device, m, accuracy_level):
     matmul_device_group(nodes, a, ys, accuracy_level=accuracy_level)
     torch.cuda.synchronize()
     launches = _capi.launch_count() - before
-    # level 0: six and more tokens take the one-pass digit kernel (digit rows once, then product + sum per
-    # node); five tokens the three-pass form (row factors + digit rows once, then product + combine per node)
-    expected = 4 if accuracy_level == 4 else (7 if m >= 6 else 8)
+    # level 0: the one-pass digit kernel (digit rows once, then product + sum of the slices per node)
+    expected = 4 if accuracy_level == 4 else 7
     assert launches == expected, launches
     for case, node, y in zip(cases, nodes, ys):
         assert node.poll_status() == 0

@@ -60,11 +60,10 @@ def direct_takes(case):
 
 
 def sliced_digits_take(case):
-    """Token counts AUTO sends to the one-pass digit kernel, by block size (4-bit, packed rows that are
-    whole 128-byte units)."""
+    """Shapes AUTO sends to the one-pass digit kernel: five to sixteen tokens, 4-bit, packed rows that
+    are whole 128-byte units."""
     m, bs = case.m, case.block_size
-    wanted = (bs == 32 and m >= 6) or (bs == 64 and m >= 5) or (bs >= 128 and m >= 9)
-    return case.bits == 4 and m <= 16 and wanted and (case.k // 2) % 128 == 0 and 32 <= bs <= 1024
+    return case.bits == 4 and 5 <= m <= 16 and (case.k // 2) % 128 == 0 and 32 <= bs <= 1024
 
 
 SLICED = "nbits_digits_mma_kernel"
@@ -193,9 +192,6 @@ def test_decode_mma_multi_tile_path(cuda_device, m, k, n, bs, zp, bias):
     elif sliced_digits_take(case):
         # AUTO sends many tokens through the one-pass digit kernel
         assert kernel_auto == SLICED and rel_err(y, y_auto) <= TOL_FP32
-    elif bs == 32 and m == 5:
-        # five tokens over block 32: digit rows through the sixteen-row integer kernel
-        assert kernel_auto == "nbits_int8_mma_kernel(digits)" and rel_err(y, y_auto) <= TOL_FP32
     else:   # AUTO picks the same kernel for these shapes
         assert kernel_auto == kernel and np.array_equal(y, y_auto)
     y_single, _ = run_device(case, path=_capi.PATH_GEMV_MMA)   # one column tile per pass
