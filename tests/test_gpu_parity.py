@@ -429,16 +429,19 @@ def test_decode_direct_path_rejects_other_blocks(cuda_device):
     weights.close()
 
 
-# shapes for the digit rows through the sixteen-row integer kernel: (m, k, n, block, zp, bias)
+# shapes for the digit kernels (PATH_GEMV_DIGITS: the one-pass kernel where it fits): (m, k, n, block, zp, bias)
 DIGIT_ROW_CASES = [
-    (16, 4096, 128, 32, False, True),      # three passes of sixteen rows, signed codes
-    (5, 4096, 77, 64, True, True),         # fifteen rows: one pass
-    (3, 2048, 200, 128, True, False),      # nine rows: one pass of sixteen, seven of them empty
+    (16, 4096, 128, 32, False, True),      # 48 digit rows, two slices, default zero point
+    (5, 4096, 77, 64, True, True),         # five tokens: 24 digit rows, nine of them empty
+    (3, 2048, 200, 128, True, False),      # three tokens, one slice
     (16, 4096, 300, 128, True, True),
     (1, 4096, 64, 32, True, False),        # three rows: one pass of eight
     (7, 8192, 40, 256, False, False),      # block spans two 128-k table entries
     (11, 14336, 96, 32, True, True),       # wide K: seven slices; 33 rows = three passes, last one ragged
     (16, 4096, 14336, 32, False, False),   # cfg4 gate / up projection at full size
+    (16, 1024, 256, 32, False, False),     # K shorter than one 2048-k slice: the rest of the slice is zeros
+    (9, 6144, 100, 128, True, True),       # three slices, the SMs do not divide by them
+    (12, 4096, 24, 1024, True, False),     # one quantization block spans eight 128-k table entries
 ]
 
 
