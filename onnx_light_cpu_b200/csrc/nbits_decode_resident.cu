@@ -567,6 +567,8 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
     p.node[i].tiles = static_cast<int>((nodes[i].n + 7) / 8);
     tiles += p.node[i].tiles;
   }
+  // one CTA per SM: two CTAs of half the slots each (so that the next launch's CTAs could move in
+  // as this launch's leave) measured 11.7 against 8.3 us per node: twice the staging, half the warps
   const int ctas = sms < tiles ? sms : static_cast<int>(tiles);
   const int tiles_per_cta = static_cast<int>((tiles + ctas - 1) / ctas);
   const int chunks = w.row_bytes / 128;  // MMA steps of a whole row
