@@ -105,10 +105,12 @@ int mnb_matmul_device(mnb_weights *weights, const float *a_dev, int64_t m, int a
 /* Sibling nodes in one call: `count` (1..MNB_MAX_GROUPED_NODES) nodes that take the SAME
  * activations - the q / k / v or the gate / up projections of a decoder layer - write
  * y_dev[i] = MatMulNBits_i(A), each a dense row-major [m, N_i] device matrix. Same K and same GPU
- * for all nodes, no node or output twice. What the nodes share is done once: at M = 1
- * (accuracy_level 0, 4-bit, block_size 128) one kernel streams all nodes' weights behind
- * activations staged once; at accuracy_level 4 the activations are quantized once; for 5..16
- * tokens on small blocks the digit rows are made once. Any other group runs node by node with
+ * for all nodes, no node or output twice. What the nodes share is done once and the nodes' row
+ * tiles form one sequence over the CTAs of a single kernel launch: at M = 1 (accuracy_level 0,
+ * 4-bit, block_size 128) one kernel streams all nodes' weights behind activations staged once; at
+ * accuracy_level 4 the activations are quantized once and one integer-MMA launch covers the
+ * group; for 5..16 tokens at accuracy_level 0 the digit rows are made once and one launch of the
+ * one-pass digit kernel covers the group. Any other group runs node by node with
  * the same results as separate mnb_matmul_device calls. Asynchronous on `stream`; bounded waits
  * of a grouped launch report through handles[0] (mnb_weights_poll_status).
  * Replaces: the consecutive MatMul nodes over one input that the reference's graph runs one by

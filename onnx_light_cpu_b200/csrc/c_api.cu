@@ -850,15 +850,8 @@ int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float 
                                      first->status_dev, s, first->sm_count);
     }
   } else if (accuracy_level == 0 && count > 1 && m <= 16 && DigitSlicesWanted(nodes[0], m)) {
-    // row factors and the digit rows of all K slices made once, then the one-pass product per node
-    std::size_t need = 0;
-    for (int i = 0; i < count; ++i) {
-      const std::size_t bytes = mnb::DigitSlicesScratchBytes(nodes[i], m);
-      need = bytes == 0 ? 0 : (bytes > need ? bytes : need);
-      if (bytes == 0) {
-        break;
-      }
-    }
+    // the digit rows of all K slices made once, one product launch for all nodes, then a sum per node
+    const std::size_t need = mnb::DigitSlicesGroupScratchBytes(nodes, count, m);
     if (need != 0) {
       const int rc = Grow(&first->scratch_a, &first->scratch_a_bytes, need);
       if (rc != MNB_OK) {

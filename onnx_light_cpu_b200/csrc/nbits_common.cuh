@@ -329,6 +329,7 @@ const char *LaunchDigitsInt8MmaGroup(const WeightView *nodes, const OutputView *
 // slice of K with all digit rows of that slice in shared memory. 0 bytes / nullptr when the shape
 // is outside what the kernel takes.
 std::size_t DigitSlicesScratchBytes(const WeightView &w, std::int64_t m);
+std::size_t DigitSlicesGroupScratchBytes(const WeightView *nodes, int count, std::int64_t m);
 const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
                                    std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
                                    int sm_count);

@@ -48,13 +48,75 @@ constexpr int kTaskK = 2048;                 // k per task
 constexpr int kTaskBytes = 16 * kTaskK / 2;  // packed weights of a task: 16 rows
 constexpr int kSegments = kTaskK / 256;      // 128-byte segments per row inside a task
 
+// Up to three sibling nodes (same K, block size, zero points in all or none) in one launch: their
+// half tiles (8 rows) form one sequence that is split over the CTAs, so the activation prologue, the
+// ramp-up and the tail are paid once for the group. A row tile never straddles two nodes.
+constexpr int kMaxGroupTiles = 256;   // row tiles of one CTA that the tile table of a grouped launch holds
+
+struct NodeSet {
+  WeightView w[kMaxGroupedNodes];
+  int halves_end[kMaxGroupedNodes];   // half tiles of the launch up to and including the node
+  int nodes;
+};
+
+struct NodeMaps {
+  CUtensorMap b[kMaxGroupedNodes];
+};
+
+struct TilePlace {
+  int node;
+  int h0;       // first half tile inside the node
+  int halves;   // 1 or 2
+};
+
+// The CTA's row tiles when several nodes share the launch, packed node << 28 | halves << 24 | h0;
+// built by one thread. Returns the number of tiles.
+__device__ inline int BuildTileTable(const NodeSet &set, int h_begin, int h_end, int *table) {
+  int h = h_begin;
+  int count = 0;
+  while (h < h_end && count < kMaxGroupTiles) {
+    int node = 0;
+    int start = 0;
+    for (int i = 0; i + 1 < set.nodes; ++i) {
+      if (h >= set.halves_end[i]) {
+        node = i + 1;
+        start = set.halves_end[i];
+      }
+    }
+    int halves = h_end - h < 2 ? h_end - h : 2;
+    halves = set.halves_end[node] - h < halves ? set.halves_end[node] - h : halves;
+    table[count++] = (node << 28) | (halves << 24) | (h - start);
+    h += halves;
+  }
+  return count;
+}
+
+__device__ __forceinline__ TilePlace PlaceOfTile(const NodeSet &set, const int *table, int h_begin, int h_end,
+                                                 int tile) {
+  TilePlace at;
+  if (set.nodes == 1) {
+    at.node = 0;
+    at.h0 = h_begin + 2 * tile;
+    at.halves = h_end - at.h0 < 2 ? h_end - at.h0 : 2;
+  } else {
+    const int packed = table[tile];
+    at.node = static_cast<int>(static_cast<unsigned>(packed) >> 28);
+    at.halves = (packed >> 24) & 15;
+    at.h0 = packed & 0xffffff;
+  }
+  return at;
+}
+
+__device__ __forceinline__ int HalfTilesOf(const NodeSet &set, int node) {
+  return set.halves_end[node] - (node > 0 ? set.halves_end[node - 1] : 0);
+}
+
 struct ImmaParams {
-  WeightView w;
+  NodeSet set;
   const unsigned char *act; // [passes][pass_bytes]: quantized activations, then scales and sums
   int m_total;
-  OutputView out;
+  OutputView out[kMaxGroupedNodes];
   int *status;
-  int half_tiles;
   int bpt;             // quantization blocks per task
   int slices;          // tasks per row tile
   int rec_bytes;
@@ -212,7 +274,7 @@ __global__ void __launch_bounds__(256)
 // correction included - can be compared bit for bit with the CPU restatement.
 template <int NT, int SPB, bool HAS_ZP, bool DOTS = false>
 __global__ void __launch_bounds__(kThreads, 1)
-    nbits_int8_mma_kernel(const __grid_constant__ CUtensorMap map_b, const ImmaParams p) {
+    nbits_int8_mma_kernel(const __grid_constant__ NodeMaps maps, const ImmaParams p) {
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char *smem_raw = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
   // layout: [slots][activations of the pass + table][partial sums: 2 x 16 warps][barriers]
@@ -222,17 +284,16 @@ __global__ void __launch_bounds__(kThreads, 1)
   std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(partial + 2 * kWarps * NT * 32);
   std::uint64_t *empty_bar = full_bar + kMaxSlots;
   std::uint64_t *act_bar = empty_bar + kMaxSlots;
+  int *tile_table = reinterpret_cast<int *>(act_bar + 1);   // [kMaxGroupTiles] + the tile count (grouped launches)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int m_base = blockIdx.y * p.tp;
 
-  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * p.half_tiles / gridDim.x);
-  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * p.half_tiles / gridDim.x);
-  const int n_tiles = (h_end - h_begin + 1) >> 1;
-  const std::int64_t row_limit =
-      static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
+  const int total_halves = p.set.halves_end[p.set.nodes - 1];
+  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * total_halves / gridDim.x);
+  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * total_halves / gridDim.x);
 
   if (warp >= kWarps) {
     // ------------------------------ producers ------------------------------
@@ -245,13 +306,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ptx::MbarInit(act_bar, 1);
       ptx::FenceMbarInit();
+      if (p.set.nodes > 1) {
+        tile_table[kMaxGroupTiles] = BuildTileTable(p.set, h_begin, h_end, tile_table);
+      }
     }
     asm volatile("bar.sync 11, %0;" ::"n"(kProducers * 32) : "memory"); // barriers initialised
     asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
     if (lane == 0) {
-      ptx::PrefetchTensorMap(&map_b);
+      const int n_tiles = p.set.nodes == 1 ? (h_end - h_begin + 1) >> 1 : tile_table[kMaxGroupTiles];
+      for (int i = 0; i < p.set.nodes; ++i) {
+        ptx::PrefetchTensorMap(&maps.b[i]);
+      }
       const int total = n_tiles * p.slices;
-      const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
       bool ok = true;
       bool act_issued = producer != 0;
       // The quantized activations come from the kernel launched just before this one, which may
@@ -288,13 +354,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
         }
-        const int h0 = h_begin + 2 * tile;
-        const unsigned char *meta_src =
-            p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes + s * meta_slice_stride;
-        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+        const TilePlace at = PlaceOfTile(p.set, tile_table, h_begin, h_end, tile);
+        const int h0 = at.h0;
+        const int node_halves = HalfTilesOf(p.set, at.node);
+        const unsigned char *meta_src = p.set.w[at.node].meta + static_cast<std::int64_t>(h0) * p.rec_bytes +
+                                        static_cast<std::int64_t>(s) * node_halves * p.rec_bytes;
+        const std::uint32_t meta_bytes = (h0 + 1 < node_halves ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
         unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
         ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
-        TmaLoad3D(dst, &map_b, 0, h0 * 8, s * kSegments, &full_bar[slot]);
+        TmaLoad3D(dst, &maps.b[at.node], 0, h0 * 8, s * kSegments, &full_bar[slot]);
         ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
       }
       if (!act_issued) {
@@ -317,6 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // ------------------------------ consumers ------------------------------
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory"); // barriers initialised
+  const int n_tiles = p.set.nodes == 1 ? (h_end - h_begin + 1) >> 1 : tile_table[kMaxGroupTiles];
   bool dead = false; // a bounded wait gave up: skip the math, keep the barrier protocol
   if (!ptx::MbarWait(act_bar, 0)) {
     ReportStatus(p.status, kDeviceTimeoutFullBarrier);
@@ -347,8 +416,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   int slot = 0;
   std::uint32_t round = 0;
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int h0 = h_begin + 2 * tile;
-    const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
+    const TilePlace at = PlaceOfTile(p.set, tile_table, h_begin, h_end, tile);
+    const WeightView &node_w = p.set.w[at.node];
+    const std::int64_t row0 = static_cast<std::int64_t>(at.h0) * 8;
+    const std::int64_t row_limit = row0 + at.halves * 8 < node_w.n ? row0 + at.halves * 8 : node_w.n;
     float acc[NT][4];
     int d[NT][4];
 #pragma unroll
@@ -468,15 +539,15 @@ __global__ void __launch_bounds__(kThreads, 1)
               if constexpr (DOTS) {
                 // entry -> quantization block; signed codes carry a factor 16
                 const std::int64_t k0 = static_cast<std::int64_t>(s) * kTaskK + warp * 128 + idx * 32 * SPB;
-                const std::int64_t block = k0 / p.w.block_size;
+                const std::int64_t block = k0 / node_w.block_size;
                 const int shift = HAS_ZP ? 0 : 4;
                 const int values[4] = {e0 >> shift, e1 >> shift, e2 >> shift, e3 >> shift};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const std::int64_t row = row0 + g + 8 * (i >> 1);
                   const std::int64_t token = static_cast<std::int64_t>(blockIdx.y) * p.tp + nt * 8 + 2 * t + (i & 1);
-                  if (row < row_limit && token < p.m_total && block < p.w.n_blocks) {
-                    atomicAdd(p.dots + (token * p.w.n + row) * p.w.n_blocks + block, values[i]);
+                  if (row < row_limit && token < p.m_total && block < node_w.n_blocks) {
+                    atomicAdd(p.dots + (token * node_w.n + row) * node_w.n_blocks + block, values[i]);
                   }
                 }
               }
@@ -530,11 +601,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       const std::int64_t r_lo = row0 + g;
       const std::int64_t r_hi = row0 + g + 8;
-      const float bias_lo = (p.w.bias != nullptr && r_lo < row_limit) ? __ldg(p.w.bias + r_lo) : 0.0f;
-      const float bias_hi = (p.w.bias != nullptr && r_hi < row_limit) ? __ldg(p.w.bias + r_hi) : 0.0f;
+      const float bias_lo = (node_w.bias != nullptr && r_lo < row_limit) ? __ldg(node_w.bias + r_lo) : 0.0f;
+      const float bias_hi = (node_w.bias != nullptr && r_hi < row_limit) ? __ldg(node_w.bias + r_hi) : 0.0f;
       const std::int64_t m0 = m_base + nt * 8 + 2 * t;
-      float *y0 = p.out.y + m0 * p.out.ld + p.out.col_offset;
-      float *y1 = y0 + p.out.ld;
+      const OutputView &node_out = p.out[at.node];
+      float *y0 = node_out.y + m0 * node_out.ld + node_out.col_offset;
+      float *y1 = y0 + node_out.ld;
       if (m0 < p.m_total) {
         if (r_lo < row_limit) {
           y0[r_lo] = total.x + bias_lo;
@@ -603,7 +675,8 @@ ImmaGeometry ImmaGeometryOf(const WeightView &w, std::int64_t m) {
     geo.pass_bytes = geo.table_offset + geo.entries_pad * tp * 8;
     const std::size_t fixed = static_cast<std::size_t>(geo.pass_bytes) +
                               2 * kWarps * (tp / 8) * 32 * sizeof(float4) +
-                              (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64;
+                              (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64 +
+                              (kMaxGroupTiles + 1) * sizeof(int);
     if (geo.pass_bytes < (1 << 20) && fixed + 2 * static_cast<std::size_t>(geo.slot_bytes) + 1024 <= limit) {
       int slots = static_cast<int>((limit - fixed - 1024) / geo.slot_bytes);
       geo.num_slots = slots > kMaxSlots ? kMaxSlots : slots;
@@ -624,9 +697,14 @@ std::size_t Int8MmaScratchBytes(const WeightView &w, std::int64_t m) {
 }
 
 namespace {
+const char *LaunchMultiplyNodes(const WeightView *nodes, const OutputView *outs, int count, const ImmaGeometry &geo,
+                                std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                int sm_count, std::int32_t *dots = nullptr);
 const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
                            OutputView out, int *status_word, cudaStream_t stream, int sm_count,
-                           std::int32_t *dots = nullptr);
+                           std::int32_t *dots = nullptr) {
+  return LaunchMultiplyNodes(&w, &out, 1, geo, m, scratch, status_word, stream, sm_count, dots);
+}
 } // namespace
 
 // Quantizes `a` into `scratch` (Int8MmaScratchBytes) and runs the integer-MMA kernel.
@@ -682,6 +760,11 @@ const char *LaunchInt8MmaGroup(const WeightView *nodes, const OutputView *outs, 
     return nullptr;
   }
   CountLaunch();
+  // one launch for the group: the nodes' row tiles form one sequence over the CTAs
+  if (LaunchMultiplyNodes(nodes, outs, count, geo, m, scratch, status_word, stream, sm_count) != nullptr) {
+    return "nbits_int8_mma_kernel";
+  }
+  cudaGetLastError();
   for (int i = 0; i < count; ++i) {
     if (LaunchMultiply(nodes[i], ImmaGeometryOf(nodes[i], m), m, scratch, outs[i], status_word, stream, sm_count) ==
         nullptr) {
@@ -716,18 +799,53 @@ const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int
 }
 
 namespace {
+// Fills the node table of a launch: the nodes' half tiles one after the other. False when a node
+// has no prepared records or the group is larger than the kernels take.
+bool FillNodeSet(const WeightView *nodes, int count, NodeSet *set, NodeMaps *maps, std::int64_t *tiles) {
+  if (count < 1 || count > kMaxGroupedNodes) {
+    return false;
+  }
+  int halves = 0;
+  *tiles = 0;
+  for (int i = 0; i < kMaxGroupedNodes; ++i) {
+    const WeightView &w = nodes[i < count ? i : 0];
+    set->w[i] = w;
+    if (i < count) {
+      if (w.meta == nullptr || !EncodeWeightsMap3D(&maps->b[i], w)) {
+        return false;
+      }
+      const MetaGeometry meta = MetaGeometryOf(w);
+      halves += meta.half_tiles;
+      *tiles += (meta.half_tiles + 1) / 2;
+    } else {
+      maps->b[i] = maps->b[0];
+    }
+    set->halves_end[i] = halves;
+  }
+  set->nodes = count;
+  return true;
+}
+
 // The integer-MMA kernel over activations that the kernel launched just before has laid out in
-// `scratch` (it is launched with programmatic stream serialization behind that kernel).
-const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::int64_t m, unsigned char *scratch,
-                           OutputView out, int *status_word, cudaStream_t stream, int sm_count, std::int32_t *dots) {
+// `scratch` (it is launched with programmatic stream serialization behind that kernel); one launch
+// for all `count` nodes.
+const char *LaunchMultiplyNodes(const WeightView *nodes, const OutputView *outs, int count, const ImmaGeometry &geo,
+                                std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
+                                int sm_count, std::int32_t *dots) {
+  const WeightView &w = nodes[0];
   const MetaGeometry meta = MetaGeometryOf(w);
   ImmaParams p{};
-  p.w = w;
+  NodeMaps maps;
+  std::int64_t tiles = 0;
+  if (!FillNodeSet(nodes, count, &p.set, &maps, &tiles)) {
+    return nullptr;
+  }
+  for (int i = 0; i < kMaxGroupedNodes; ++i) {
+    p.out[i] = outs[i < count ? i : 0];
+  }
   p.act = scratch;
   p.m_total = static_cast<int>(m);
-  p.out = out;
   p.status = status_word;
-  p.half_tiles = meta.half_tiles;
   p.bpt = meta.bpt;
   p.slices = meta.slices;
   p.rec_bytes = meta.rec_bytes;
@@ -746,14 +864,13 @@ const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::in
   }
   const int spb = geo.entry_k / 32;
 
-  CUtensorMap map_b;
-  if (!EncodeWeightsMap3D(&map_b, w)) {
-    return nullptr;
-  }
   int ctas = sm_count > 0 ? sm_count : 148;
-  const int tiles = (meta.half_tiles + 1) / 2;
   if (ctas > tiles) {
-    ctas = tiles;
+    ctas = static_cast<int>(tiles);
+  }
+  // a grouped launch keeps its row tiles in a table of kMaxGroupTiles entries per CTA
+  if (count > 1 && (p.set.halves_end[count - 1] / ctas + 2) / 2 + count > kMaxGroupTiles) {
+    return nullptr;
   }
   dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(geo.passes), 1);
   cudaError_t err = cudaErrorInvalidValue;
@@ -776,7 +893,7 @@ const char *LaunchMultiply(const WeightView &w, const ImmaGeometry &geo, std::in
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
       config.numAttrs = 1;                                                                       \
-      err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
+      err = cudaLaunchKernelEx(&config, kernel, maps, p);                                        \
     }                                                                                            \
   }
 #define MNB_IMMA_CASES(SPB_)                                                                     \
@@ -955,12 +1072,11 @@ std::size_t AlignUp(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
 // The per-token factor `undo` and the bias are applied by the kernel that adds the slices' partial
 // products in slice order. Nodes without zero points use zp = 8 (unsigned codes as they are).
 struct DigitsParams {
-  WeightView w;
+  NodeSet set;
   const unsigned char *act;   // [slices][slice_bytes]: digit rows of a slice, then its table of sums
-  float *partial;             // [slices][tokens_pad][n]
+  float *partial[kMaxGroupedNodes];   // per node [slices][tokens_pad][n]
   int m_total;
   int *status;
-  int half_tiles;
   int bpt;
   int slices;
   int rec_bytes;
@@ -976,7 +1092,7 @@ struct DigitsParams {
 
 template <int NTOK, int SPB, bool HAS_ZP>
 __global__ void __launch_bounds__(kThreads, 1)
-    nbits_digits_mma_kernel(const __grid_constant__ CUtensorMap map_b, const DigitsParams p) {
+    nbits_digits_mma_kernel(const __grid_constant__ NodeMaps maps, const DigitsParams p) {
   constexpr int NT = 3 * NTOK;           // MMA column tiles: digit-major
   constexpr int kRows = 8 * NT;          // digit rows
   constexpr int kTableInts = SPB == 4 ? kRows : 8 * NTOK;   // per entry: sums per digit row, or combined per token
@@ -988,6 +1104,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   std::uint64_t *full_bar = reinterpret_cast<std::uint64_t *>(partial + 2 * kWarps * NTOK * 32);
   std::uint64_t *empty_bar = full_bar + kMaxSlots;
   std::uint64_t *act_bar = empty_bar + kMaxSlots;
+  int *tile_table = reinterpret_cast<int *>(act_bar + 1);   // [kMaxGroupTiles] + the tile count (grouped launches)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -996,11 +1113,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // the kernel that adds the slices up may be scheduled as SMs free up; it waits for this grid
   ptx::GridDependencyLaunch();
 
-  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * p.half_tiles / gridDim.x);
-  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * p.half_tiles / gridDim.x);
-  const int n_tiles = (h_end - h_begin + 1) >> 1;
-  const std::int64_t row_limit =
-      static_cast<std::int64_t>(h_end) * 8 < p.w.n ? static_cast<std::int64_t>(h_end) * 8 : p.w.n;
+  const int total_halves = p.set.halves_end[p.set.nodes - 1];
+  const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * total_halves / gridDim.x);
+  const int h_end = static_cast<int>(static_cast<std::int64_t>(blockIdx.x + 1) * total_halves / gridDim.x);
 
   if (warp >= kWarps) {
     // ------------------------------ producers ------------------------------
@@ -1012,12 +1127,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       ptx::MbarInit(act_bar, 1);
       ptx::FenceMbarInit();
+      if (p.set.nodes > 1) {
+        tile_table[kMaxGroupTiles] = BuildTileTable(p.set, h_begin, h_end, tile_table);
+      }
     }
     asm volatile("bar.sync 11, %0;" ::"n"(kProducers * 32) : "memory"); // barriers initialised
     asm volatile("bar.arrive 10, %0;" ::"n"(kThreads) : "memory");
     if (lane == 0) {
-      ptx::PrefetchTensorMap(&map_b);
-      const std::int64_t meta_slice_stride = static_cast<std::int64_t>(p.half_tiles) * p.rec_bytes;
+      const int n_tiles = p.set.nodes == 1 ? (h_end - h_begin + 1) >> 1 : tile_table[kMaxGroupTiles];
+      for (int i = 0; i < p.set.nodes; ++i) {
+        ptx::PrefetchTensorMap(&maps.b[i]);
+      }
       bool ok = true;
       bool act_issued = producer != 0;
       // the digit rows come from the kernel launched just before (programmatic dependent launch);
@@ -1042,13 +1162,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
         }
-        const int h0 = h_begin + 2 * task;
-        const unsigned char *meta_src =
-            p.w.meta + static_cast<std::int64_t>(h0) * p.rec_bytes + slice * meta_slice_stride;
-        const std::uint32_t meta_bytes = (h0 + 1 < p.half_tiles ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
+        const TilePlace at = PlaceOfTile(p.set, tile_table, h_begin, h_end, task);
+        const int h0 = at.h0;
+        const int node_halves = HalfTilesOf(p.set, at.node);
+        const unsigned char *meta_src = p.set.w[at.node].meta + static_cast<std::int64_t>(h0) * p.rec_bytes +
+                                        static_cast<std::int64_t>(slice) * node_halves * p.rec_bytes;
+        const std::uint32_t meta_bytes = (h0 + 1 < node_halves ? 2u : 1u) * static_cast<std::uint32_t>(p.rec_bytes);
         unsigned char *dst = slots + static_cast<size_t>(slot) * p.slot_bytes;
         ptx::MbarArriveExpectTx(&full_bar[slot], kTaskBytes + meta_bytes);
-        TmaLoad3D(dst, &map_b, 0, h0 * 8, slice * kSegments, &full_bar[slot]);
+        TmaLoad3D(dst, &maps.b[at.node], 0, h0 * 8, slice * kSegments, &full_bar[slot]);
         ptx::BulkLoad(dst + kTaskBytes, meta_src, meta_bytes, &full_bar[slot]);
       }
       if (!act_issued) {
@@ -1071,6 +1193,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // ------------------------------ consumers ------------------------------
   asm volatile("bar.sync 10, %0;" ::"n"(kThreads) : "memory"); // barriers initialised
+  const int n_tiles = p.set.nodes == 1 ? (h_end - h_begin + 1) >> 1 : tile_table[kMaxGroupTiles];
   bool dead = false;
   if (!ptx::MbarWait(act_bar, 0)) {
     ReportStatus(p.status, kDeviceTimeoutFullBarrier);
@@ -1097,8 +1220,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   int slot = 0;
   std::uint32_t round = 0;
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int h0 = h_begin + 2 * tile;
-    const std::int64_t row0 = static_cast<std::int64_t>(h0) * 8;
+    const TilePlace at = PlaceOfTile(p.set, tile_table, h_begin, h_end, tile);
+    const std::int64_t node_n = p.set.w[at.node].n;
+    const std::int64_t row0 = static_cast<std::int64_t>(at.h0) * 8;
+    const std::int64_t row_limit = row0 + at.halves * 8 < node_n ? row0 + at.halves * 8 : node_n;
     float acc[NTOK][4];
 #pragma unroll
     for (int j = 0; j < NTOK; ++j) {
@@ -1256,8 +1381,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::int64_t r_lo = row0 + g;
       const std::int64_t r_hi = row0 + g + 8;
       const std::int64_t m0 = j * 8 + 2 * t;
-      float *y0 = p.partial + (static_cast<std::int64_t>(slice) * (8 * NTOK) + m0) * p.w.n;
-      float *y1 = y0 + p.w.n;
+      float *y0 = p.partial[at.node] + (static_cast<std::int64_t>(slice) * (8 * NTOK) + m0) * node_n;
+      float *y1 = y0 + node_n;
       if (m0 < p.m_total) {
         if (r_lo < row_limit) {
           y0[r_lo] = total.x;
@@ -1445,7 +1570,8 @@ DigitsGeometry DigitsGeometryOf(const WeightView &w, std::int64_t m) {
   geo.slot_bytes = (kTaskBytes + 2 * meta.rec_bytes + 1023) & ~1023;
   const std::size_t limit = 225 * 1024;
   const std::size_t fixed = static_cast<std::size_t>(geo.slice_bytes) + 2 * kWarps * geo.ntok * 32 * sizeof(float4) +
-                            (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64 + 1024;
+                            (2 * kMaxSlots + 1) * sizeof(std::uint64_t) + 64 + 1024 +
+                            (kMaxGroupTiles + 1) * sizeof(int);
   if ((geo.slice_bytes % 16) != 0 || fixed + 3 * static_cast<std::size_t>(geo.slot_bytes) > limit) {
     return geo;
   }
@@ -1460,27 +1586,58 @@ DigitsGeometry DigitsGeometryOf(const WeightView &w, std::int64_t m) {
 
 } // namespace
 
-std::size_t DigitSlicesScratchBytes(const WeightView &w, std::int64_t m) {
-  const DigitsGeometry geo = DigitsGeometryOf(w, m);
+// Scratch of a group: the digit rows of all K slices, the row factors, every node's partial products.
+std::size_t DigitSlicesGroupScratchBytes(const WeightView *nodes, int count, std::int64_t m) {
+  if (count < 1 || count > kMaxGroupedNodes) {
+    return 0;
+  }
+  const DigitsGeometry geo = DigitsGeometryOf(nodes[0], m);
   if (!geo.ok) {
     return 0;
   }
-  return AlignUp(geo.act_bytes) + AlignUp(3 * m * sizeof(float)) + geo.partial_bytes;
+  std::size_t bytes = AlignUp(geo.act_bytes) + AlignUp(3 * m * sizeof(float));
+  for (int i = 0; i < count; ++i) {
+    const DigitsGeometry other = DigitsGeometryOf(nodes[i], m);
+    if (!other.ok) {
+      return 0;
+    }
+    bytes += other.partial_bytes;
+  }
+  return bytes;
+}
+
+std::size_t DigitSlicesScratchBytes(const WeightView &w, std::int64_t m) {
+  return DigitSlicesGroupScratchBytes(&w, 1, m);
 }
 
 namespace {
 
-const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo, std::int64_t m, unsigned char *act,
-                                  const float *factors, float *partial, OutputView out, int *status_word,
-                                  cudaStream_t stream, int sm_count) {
+// One product launch for all `count` nodes (their row tiles form one sequence over the CTAs of each
+// slice), then per node the sum of its slices. partial: the nodes' [slices][tokens_pad][n] buffers one
+// after the other.
+const char *LaunchDigitSlicesNodes(const WeightView *nodes, const OutputView *outs, int count,
+                                   const DigitsGeometry &geo, std::int64_t m, unsigned char *act, const float *factors,
+                                   float *partial, int *status_word, cudaStream_t stream, int sm_count) {
+  const WeightView &w = nodes[0];
   const MetaGeometry meta = MetaGeometryOf(w);
   DigitsParams p{};
-  p.w = w;
+  NodeMaps maps;
+  std::int64_t tiles = 0;
+  if (!FillNodeSet(nodes, count, &p.set, &maps, &tiles)) {
+    return nullptr;
+  }
+  float *node_partial[kMaxGroupedNodes];
+  float *next = partial;
+  for (int i = 0; i < kMaxGroupedNodes; ++i) {
+    node_partial[i] = i < count ? next : partial;
+    p.partial[i] = node_partial[i];
+    if (i < count) {
+      next += static_cast<std::int64_t>(meta.slices) * 8 * geo.ntok * nodes[i].n;
+    }
+  }
   p.act = act;
-  p.partial = partial;
   p.m_total = static_cast<int>(m);
   p.status = status_word;
-  p.half_tiles = meta.half_tiles;
   p.bpt = meta.bpt;
   p.slices = meta.slices;
   p.rec_bytes = meta.rec_bytes;
@@ -1492,16 +1649,14 @@ const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo
   p.table_offset = geo.table_offset;
   p.slice_bytes = geo.slice_bytes;
   p.groups_per_block = w.block_size >= 256 ? w.block_size / 128 : 1;
-  CUtensorMap map_b;
-  if (!EncodeWeightsMap3D(&map_b, w)) {
-    return nullptr;
-  }
   int ctas = sm_count > 0 ? sm_count : 148;
-  const int tiles = (meta.half_tiles + 1) / 2;
-  // slices run side by side: share the SMs between them so that one wave covers the node
+  // slices run side by side: share the SMs between them so that one wave covers the launch
   ctas = ctas / meta.slices > 0 ? ctas / meta.slices : 1;
   if (ctas > tiles) {
-    ctas = tiles;
+    ctas = static_cast<int>(tiles);
+  }
+  if (count > 1 && (p.set.halves_end[count - 1] / ctas + 2) / 2 + count > kMaxGroupTiles) {
+    return nullptr;
   }
   dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(meta.slices), 1);
   cudaError_t err = cudaErrorInvalidValue;
@@ -1521,7 +1676,7 @@ const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo
       attribute[0].val.programmaticStreamSerializationAllowed = 1;                               \
       config.attrs = attribute;                                                                  \
       config.numAttrs = 1;                                                                       \
-      err = cudaLaunchKernelEx(&config, kernel, map_b, p);                                       \
+      err = cudaLaunchKernelEx(&config, kernel, maps, p);                                        \
     }                                                                                            \
   }
 #define MNB_DIGITS_CASES(SPB_)                                                                   \
@@ -1538,10 +1693,10 @@ const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo
     return nullptr;
   }
   CountLaunch();
-  const std::int64_t total = m * w.n;
-  std::int64_t blocks = (total + 255) / 256;
-  blocks = blocks > 148 * 4 ? 148 * 4 : blocks;
-  {
+  for (int i = 0; i < count; ++i) {
+    const std::int64_t total = m * nodes[i].n;
+    std::int64_t blocks = (total + 255) / 256;
+    blocks = blocks > 148 * 4 ? 148 * 4 : blocks;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
     config.blockDim = dim3(256, 1, 1);
@@ -1551,13 +1706,14 @@ const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    if (cudaLaunchKernelEx(&config, nbits_digit_slices_sum_kernel, static_cast<const float *>(partial), meta.slices,
-                           8 * geo.ntok, factors, static_cast<int>(m), w.n, w.bias, out) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&config, nbits_digit_slices_sum_kernel, static_cast<const float *>(node_partial[i]),
+                           meta.slices, 8 * geo.ntok, factors, static_cast<int>(m), nodes[i].n, nodes[i].bias,
+                           outs[i]) != cudaSuccess) {
       cudaGetLastError();
       return nullptr;
     }
+    CountLaunch();
   }
-  CountLaunch();
   return "nbits_digits_mma_kernel";
 }
 
@@ -1565,7 +1721,7 @@ const char *LaunchDigitSlicesNode(const WeightView &w, const DigitsGeometry &geo
 
 // accuracy_level 0 for up to sixteen tokens in one pass over the weights: the digit rows of all K
 // slices once (one kernel, shared by sibling nodes), then per node the sliced integer-MMA product and
-// the sum of its slices. `scratch`: DigitSlicesScratchBytes of the node with the most columns.
+// the sum of its slices. `scratch`: DigitSlicesGroupScratchBytes of the group.
 const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
                                    std::int64_t m, unsigned char *scratch, int *status_word, cudaStream_t stream,
                                    int sm_count) {
@@ -1580,7 +1736,8 @@ const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *ou
   for (int i = 0; i < count; ++i) {
     const DigitsGeometry other = DigitsGeometryOf(nodes[i], m);
     if (!other.ok || nodes[i].meta == nullptr || nodes[i].k != w.k || nodes[i].block_size != w.block_size ||
-        other.slice_bytes != geo.slice_bytes || other.table_ints != geo.table_ints) {
+        (nodes[i].zp != nullptr) != (w.zp != nullptr) || other.slice_bytes != geo.slice_bytes ||
+        other.table_ints != geo.table_ints) {
       return nullptr;
     }
   }
@@ -1597,13 +1754,7 @@ const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *ou
     return nullptr;
   }
   CountLaunch();
-  for (int i = 0; i < count; ++i) {
-    if (LaunchDigitSlicesNode(nodes[i], DigitsGeometryOf(nodes[i], m), m, act, factors, partial, outs[i], status_word,
-                              stream, sm_count) == nullptr) {
-      return nullptr;
-    }
-  }
-  return "nbits_digits_mma_kernel";
+  return LaunchDigitSlicesNodes(nodes, outs, count, geo, m, act, factors, partial, status_word, stream, sm_count);
 }
 
 namespace {

@@ -96,8 +96,8 @@ def test_one_token_group_of_mixed_nodes_runs_node_by_node(cuda_device):
 @pytest.mark.parametrize("m", [5, 16])
 @pytest.mark.parametrize("accuracy_level", [0, 4])
 def test_small_block_group_shares_its_prologue(cuda_device, m, accuracy_level):
-    """Block size 32, several tokens: level 4 quantizes A once (1 + 3 launches for three nodes),
-    level 0 makes the digit rows once and runs the product and its sum per node (2 each)."""
+    """Block size 32, several tokens: what the nodes share is done once and their row tiles form one
+    sequence over the CTAs of a single product launch."""
     cases = make_nodes((1024, 272, 528), 2048, 32, zero_points=False, bias=True, m=m, seed=9300 + m)
     import torch
 
@@ -108,8 +108,9 @@ def test_small_block_group_shares_its_prologue(cuda_device, m, accuracy_level):
     matmul_device_group(nodes, a, ys, accuracy_level=accuracy_level)
     torch.cuda.synchronize()
     launches = _capi.launch_count() - before
-    # level 0: the one-pass digit kernel (digit rows once, then product + sum of the slices per node)
-    expected = 4 if accuracy_level == 4 else 7
+    # level 4: the quantization and ONE product launch for the three nodes; level 0: the digit rows, ONE
+    # product launch, then the sum of the slices per node
+    expected = 2 if accuracy_level == 4 else 5
     assert launches == expected, launches
     for case, node, y in zip(cases, nodes, ys):
         assert node.poll_status() == 0
