@@ -125,6 +125,27 @@ def test_small_block_group_shares_its_prologue(cuda_device, m, accuracy_level):
         node.close()
 
 
+@pytest.mark.parametrize("accuracy_level", [0, 4])
+@pytest.mark.parametrize("shapes,k,bs,zp", [
+    ((77, 8, 100), 2048, 32, True),        # ragged N in every node: row tiles end at node boundaries
+    ((4096, 1024, 1024), 4096, 32, False),  # q / k / v of the layer at full size
+    ((520, 264), 14336, 128, True),         # seven K slices
+])
+def test_grouped_product_launch_matches_separate_calls(cuda_device, shapes, k, bs, zp, accuracy_level):
+    """Sixteen tokens: one product launch over the nodes' row tiles gives, bit for bit, what one call per
+    node gives, and both match the checker."""
+    cases = make_nodes(shapes, k, bs, zero_points=zp, bias=True, m=16, seed=9500 + k + bs)
+    out, alone, kernel, launches = run_group(cases, accuracy_level=accuracy_level)
+    assert kernel == ("nbits_int8_mma_kernel" if accuracy_level == 4 else "nbits_digits_mma_kernel"), kernel
+    assert launches == (2 if accuracy_level == 4 else 2 + len(shapes))
+    kind = "int8" if accuracy_level == 4 else "f64"
+    for case, y, y1 in zip(cases, out, alone):
+        assert not np.isnan(y).any()
+        np.testing.assert_array_equal(y, y1)
+        columns = sample_columns(case, 91)
+        assert_close(y[:, columns], sampled_reference(case, columns, kind), TOL_FP32, case.name)
+
+
 def test_group_entry_refuses_bad_groups(cuda_device):
     import torch
 
