@@ -46,6 +46,8 @@ constexpr int kThreads = (2 + kDequantWarps) * 32;
 // `permute` = 0 keeps the natural order (8-bit codes are whole bytes and come out in order).
 __global__ void __launch_bounds__(256)
     nbits_a_to_bf16_kernel(const float *a, std::int64_t m, std::int64_t k, __nv_bfloat16 *out, int permute) {
+  // the GEMM behind this kernel may set itself up right away; its copies wait for this grid
+  ptx::GridDependencyLaunch();
   const std::int64_t groups_per_row = k / 8;
   const std::int64_t total = m * groups_per_row;
   for (std::int64_t g = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
@@ -194,6 +196,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_a);
       ptx::PrefetchTensorMap(&map_p);
+      // the bf16 activations come from the pre-pass launched just before (programmatic dependent
+      // launch): TMEM, barriers and descriptors are set up while it runs, the copies wait for it
+      ptx::GridDependencyWait();
       for (int ks = 0; ks < p.k_steps; ++ks) {
         const int s = ks % kStages;
         const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
@@ -444,6 +449,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_a);
       ptx::PrefetchTensorMap(&map_p);
+      // the bf16 activations come from the pre-pass launched just before (programmatic dependent
+      // launch): TMEM, barriers and descriptors are set up while it runs, the copies wait for it
+      ptx::GridDependencyWait();
       int s = 0;
       std::uint32_t phase = 0;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
@@ -666,6 +674,27 @@ int Log2Of(int v) {
   return l;
 }
 
+// Launch with programmatic stream serialization behind the activation pre-pass.
+template <typename Kernel>
+bool LaunchBehindPrePass(Kernel kernel, dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &map_a,
+                         const CUtensorMap &map_p, const GemmParams &p) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, kernel, map_a, map_p, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return true;
+}
+
 template <int BT, int BITS>
 const char *LaunchTileBits(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16,
                            OutputView out, int *status_word, cudaStream_t stream) {
@@ -697,8 +726,7 @@ const char *LaunchTileBits(const WeightView &w, std::int64_t m, const std::uint1
   }
   dim3 grid(static_cast<unsigned>((w.n + kTileN - 1) / kTileN),
             static_cast<unsigned>((m + BT - 1) / BT), 1);
-  kernel<<<grid, kThreads, Smem::kTotal, stream>>>(map_a, map_p, p);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchBehindPrePass(kernel, grid, Smem::kTotal, stream, map_a, map_p, p)) {
     return nullptr;
   }
   CountLaunch();
@@ -741,8 +769,7 @@ const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t 
   }
   dim3 grid(static_cast<unsigned>((w.n + kWideRows - 1) / kWideRows),
             static_cast<unsigned>((m + kWideTokens - 1) / kWideTokens), static_cast<unsigned>(splits));
-  kernel<<<grid, kThreads, kWideSmem, stream>>>(map_a, map_p, p);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchBehindPrePass(kernel, grid, kWideSmem, stream, map_a, map_p, p)) {
     return nullptr;
   }
   CountLaunch();
