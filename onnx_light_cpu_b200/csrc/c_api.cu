@@ -488,7 +488,9 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       return rc;
     }
     name = mnb::LaunchGemmTcgen05(w, a_dev, m, static_cast<std::uint16_t *>(h->scratch_a), out,
-                                  h->status_dev, stream, h->sm_count, chosen == MNB_PATH_TCGEN05_WIDE);
+                                  h->status_dev, stream, h->sm_count,
+                                  path == MNB_PATH_AUTO ? mnb::kGemmTileAuto
+                                                        : (path == MNB_PATH_TCGEN05_WIDE ? mnb::kGemmTilePairs : mnb::kGemmTileRows128));
     break;
   }
   case MNB_PATH_INT8_MMA: {

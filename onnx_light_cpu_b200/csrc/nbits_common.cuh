@@ -282,11 +282,14 @@ const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView 
 // Drops the launch plans (tensor maps, slot shapes) cached for a node whose weights are going away.
 void ForgetDecodeResidentPlans(const WeightView &w);
 
-// Prefill. `a_bf16` is scratch of m*k_padded bf16 elements, k_padded = round_up(k, 64).
+// Prefill. `scratch` holds GemmTcgen05ScratchBytes(...) bytes. `tiles`: which kernel takes the product.
+constexpr int kGemmTileAuto = 0;      // CTA pairs for more than 128 tokens where the cost model prefers them
+constexpr int kGemmTileRows128 = 1;   // the kernel with 128 weight rows per CTA
+constexpr int kGemmTilePairs = 2;     // CTA pairs (4-bit weights; other widths fall back to the 128-row kernel)
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
-                              std::uint16_t *a_bf16, OutputView out, int *status_word,
-                              cudaStream_t stream, int sm_count, bool force_wide = false);
-// Scratch of one call: bf16 activations, plus partial tiles and arrival counters when K is split.
+                              std::uint16_t *scratch, OutputView out, int *status_word,
+                              cudaStream_t stream, int sm_count, int tiles = kGemmTileAuto);
+// Scratch of one call: bf16 activations, plus the partial products when K is shared between CTA pairs.
 std::size_t GemmTcgen05ScratchBytes(const WeightView &w, std::int64_t m, int sm_count);
 bool GemmTcgen05Supports(const WeightView &w, std::int64_t m);
 

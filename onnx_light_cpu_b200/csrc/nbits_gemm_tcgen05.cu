@@ -265,35 +265,44 @@ __global__ void __launch_bounds__(kThreads, 1)
       store_offset[i] = Smem::kStageA + row * 128 + ((c ^ (row & 7)) << 4);
     }
 
-    auto load_meta = [&](int ks, std::uint32_t &scale2, std::uint32_t &offset2) {
-      int block = (ks * kTileK + half * 32) >> p.block_shift;
-      block = block > last_block ? last_block : block;
-      const float scale = row_valid ? __ldg(scale_row + block) : 0.0f;
+    // Scale and zero point of a k step's block. The loads are issued one step ahead and nothing
+    // touches their results before the next step begins (a conversion right behind the load would
+    // expose the L2 latency in every step).
+    auto block_of = [&](int ks) {
+      const int block = (ks * kTileK + half * 32) >> p.block_shift;
+      return block > last_block ? last_block : block;
+    };
+    auto fetch_meta = [&](int ks, float &scale, int &zp_byte) {
+      const int block = block_of(ks);
+      scale = row_valid ? __ldg(scale_row + block) : 0.0f;
+      if constexpr (BITS == 4) {
+        zp_byte = zp_row != nullptr ? __ldg(zp_row + (block >> 1)) : 0x88;
+      } else {
+        zp_byte = zp_row != nullptr ? __ldg(zp_row + block) : 128;
+      }
+    };
+    auto finish_meta = [&](int ks, float scale, int zp_byte, std::uint32_t &scale2, std::uint32_t &offset2) {
       scale2 = Bf16Pair(scale);
       if constexpr (BITS == 4) {
-        int zp = 8;
-        if (zp_row != nullptr) {
-          const int byte = __ldg(zp_row + (block >> 1));
-          zp = (byte >> ((block & 1) * 4)) & 0x0f;
-        }
+        const int zp = (zp_byte >> ((block_of(ks) & 1) * 4)) & 0x0f;
         offset2 = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
       } else {
-        const int zp = zp_row != nullptr ? __ldg(zp_row + block) : 128;
-        const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp)); // exact in fp16
+        const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp_byte)); // exact in fp16
         offset2 = *reinterpret_cast<const std::uint32_t *>(&both);
       }
     };
 
-    std::uint32_t scale_next, offset_next;
-    load_meta(0, scale_next, offset_next);
+    float scale_raw;
+    int zp_raw;
+    fetch_meta(0, scale_raw, zp_raw);
     bool ok = true;
     int s = 0;
     std::uint32_t phase = 0;
     for (int ks = 0; ks < p.k_steps; ++ks) {
-      const std::uint32_t scale2 = scale_next;
-      const std::uint32_t offset2 = offset_next;
+      std::uint32_t scale2, offset2;
+      finish_meta(ks, scale_raw, zp_raw, scale2, offset2);
       if (ks + 1 < p.k_steps) {
-        load_meta(ks + 1, scale_next, offset_next);
+        fetch_meta(ks + 1, scale_raw, zp_raw);
       }
       if (!ptx::MbarWait(&full_tma[s], phase)) {
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
@@ -374,61 +383,94 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Wide variant for large M: one CTA owns 256 weight rows x 256 tokens (two 128-lane accumulators,
-// all 512 TMEM columns). Per 64-k step it brings in 32 KB of activations and 8 KB of packed
-// weights for twice the MMA work of the 128-row kernel, which halves the L2 traffic per flop
-// and lets four stages in flight cover the TMA latency. The dequantized tile is transient, so
-// it lives in its own two buffers instead of the TMA ring.
+// CTA pairs: 512 weight rows x `tokens` (<= 256) per pair of SMs, for every product of more than
+// 128 tokens that is worth it (PairPlanFor below).
+//
+// Two CTAs of a cluster (the same pair of SMs) share every MMA (cta_group::2, 256 x tokens x 16): each
+// CTA dequantizes 256 weight rows of its own (two 128-row sub-tiles = the two 256-column accumulators
+// in its TMEM, all 512 columns) but stages only HALF of the token tile; the tensor cores of both SMs
+// read both halves. Per 64-k step a CTA brings in at most 16 KB of activations and 8 KB of packed
+// weights for 2 x 128 x 256 x 64 multiply-adds. The dequantized tile is transient, so it lives in
+// buffers of its own instead of the TMA ring. (A single CTA with the whole 256-token tile, which this
+// kernel replaced, was bound by shared-memory bandwidth: 176 KB crossed it per k step against 125 KB
+// here, and 953 against 1076 TFLOP/s at M = 2048.)
+//
+// The dequantizers are bound by the latency of their own chain (wait, load, convert, store, proxy
+// fence, arrive), so there are sixteen warps of them in two groups that take alternate k steps: two
+// steps are being dequantized at any time. (Sixteen warps on every step: 1046 TFLOP/s; four groups
+// with four buffers: 1066; five TMA stages: 1030; packed weights loaded from global memory by the
+// dequantizers instead of TMA: 986.)
+//
+// Roles per CTA as in the 128-row kernel; the MMA issuer runs in the even CTA only. What crosses the pair:
+//   w_full[b] of the even CTA collects the dequantizer warps of BOTH CTAs (the odd CTA's arrive
+//     through the cluster address of that barrier). A warp arrives after it has seen its own CTA's
+//     copies land, so one wait tells the issuer that weights and activations are in place in both.
+//   empty[s], w_empty[b], accum_full are signalled in both CTAs by one tcgen05.commit.
+// gridDim.z > 1 shares K between that many pairs per tile: each takes a consecutive part of the k
+// steps and stores its partial tile, and nbits_split_k_sum_kernel behind this kernel adds the parts
+// in order (+ bias), so the result does not depend on timing. (fp32 reductions straight into Y were
+// tried first: 8.4 M element-wise L2 atomics took longer than the product.)
+// TMEM is allocated and released by warp 0 of both CTAs together; a cluster barrier before the
+// release keeps either CTA's shared memory and TMEM alive until both are done.
 
-constexpr int kWideRows = 256;
-constexpr int kWideTokens = 256;
-constexpr int kWideStages = 3;
-constexpr int kWideBuffers = 3; // dequantized-weight buffers: the dequantizers run up to two steps ahead
-constexpr int kWideStageA = kWideTokens * 128;   // 32 KB
-constexpr int kWideStageP = kWideRows * 32;      // 8 KB
-constexpr int kWideBufW = kWideRows * 128;       // 32 KB, two 16 KB sub-tiles
-constexpr int kWideSmem = kWideStages * (kWideStageA + kWideStageP) + kWideBuffers * kWideBufW + 256 + 1024;
+constexpr int kPairRows = 256;      // weight rows per CTA: two 128-row sub-tiles
+constexpr int kPairTokens = 256;    // widest token tile of a pair = columns of one accumulator
+constexpr int kPairDequantWarps = 16;
+constexpr int kPairThreads = (2 + kPairDequantWarps) * 32;
+constexpr int kPairGroups = 2;                                     // groups of dequantizer warps, one k step each
+constexpr int kPairGroupThreads = kPairDequantWarps / kPairGroups * 32;
+static_assert(kPairGroupThreads == 256, "a group covers 128 rows x two halves of a k step");
+constexpr int kPairStages = 4;
+constexpr int kPairBuffers = 3;
+constexpr int kPairStageA = (kPairTokens / 2) * 128;   // half a token tile: 16 KB
+constexpr int kPairStageP = kPairRows * 32;            // packed weights of a k step: 8 KB
+constexpr int kPairBufW = kPairRows * 128;             // dequantized weights of a k step: 32 KB, two 16 KB sub-tiles
+constexpr int kPairSmem = kPairStages * (kPairStageA + kPairStageP) + kPairBuffers * kPairBufW + 256 + 1024;
 
-// SPLIT: gridDim.z CTAs share a tile; each takes a consecutive part of K and stores its partial
-// tile, and nbits_split_k_sum_kernel behind this kernel adds the parts in order (+ bias): the
-// result does not depend on timing. (fp32 reductions straight into Y were tried first: 8.4 M
-// element-wise L2 atomics took longer than the product, 112 us against 41 us unsplit on M = 512.)
-template <bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1)
-    nbits_gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a,
-                                   const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
+struct PairParams {
+  GemmParams g;
+  int tokens;       // token-tile width of the pair: a multiple of 16, <= 256
+  std::uint32_t idesc;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+    nbits_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                   const __grid_constant__ CUtensorMap map_p, const PairParams pp) {
+  const GemmParams &p = pp.g;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
-  unsigned char *ring_a = smem;                                     // [stages][32 KB]
-  unsigned char *buf_w = ring_a + kWideStages * kWideStageA;        // [buffers][32 KB]
-  unsigned char *ring_p = buf_w + kWideBuffers * kWideBufW;                    // [stages][8 KB]
-  std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(ring_p + kWideStages * kWideStageP);
-  std::uint64_t *full_tma = bars;                    // [stages] activations + packed weights landed
-  std::uint64_t *empty = bars + kWideStages;         // [stages] MMAs that read the stage retired
-  std::uint64_t *w_full = bars + 2 * kWideStages;    // [buffers] weights dequantized into the buffer
-  std::uint64_t *w_empty = w_full + kWideBuffers;    // [buffers] MMAs that read the buffer retired
-  std::uint64_t *accum_full = w_empty + kWideBuffers;
+  unsigned char *ring_a = smem;                                     // [stages][16 KB]
+  unsigned char *buf_w = ring_a + kPairStages * kPairStageA;     // [buffers][32 KB]
+  unsigned char *ring_p = buf_w + kPairBuffers * kPairBufW;         // [stages][8 KB]
+  std::uint64_t *bars = reinterpret_cast<std::uint64_t *>(ring_p + kPairStages * kPairStageP);
+  std::uint64_t *full_tma = bars;                    // [stages] this CTA's activations + packed weights landed
+  std::uint64_t *empty = bars + kPairStages;         // [stages] pair MMAs that read the stage retired
+  std::uint64_t *w_full = bars + 2 * kPairStages;    // [buffers] (even CTA) both CTAs' weights dequantized
+  std::uint64_t *w_empty = w_full + kPairBuffers;    // [buffers] pair MMAs that read the buffer retired
+  std::uint64_t *accum_full = w_empty + kPairBuffers;
   std::uint32_t *tmem_slot = reinterpret_cast<std::uint32_t *>(accum_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int n0 = blockIdx.x * kWideRows;
-  const int m0 = blockIdx.y * kWideTokens;
-  // this CTA's share of K: all of it, or one of gridDim.z consecutive parts
-  const int splits = SPLIT ? static_cast<int>(gridDim.z) : 1;
-  const int split = SPLIT ? static_cast<int>(blockIdx.z) : 0;
-  const int ks_begin = SPLIT ? static_cast<int>(static_cast<std::int64_t>(split) * p.k_steps / splits) : 0;
-  const int ks_end = SPLIT ? static_cast<int>(static_cast<std::int64_t>(split + 1) * p.k_steps / splits) : p.k_steps;
+  const std::uint32_t rank = ptx::ClusterCtaRank();      // 0: issues the MMAs
+  const int n0 = blockIdx.x * kPairRows;                 // blockIdx.x = 2 * pair + rank
+  const int m0 = blockIdx.y * pp.tokens;
+  const int half_tokens = pp.tokens / 2;
+  const std::uint32_t stage_a_bytes = static_cast<std::uint32_t>(half_tokens) * 128u;
+  const int parts = static_cast<int>(gridDim.z);
+  const int part = static_cast<int>(blockIdx.z);
+  const int ks_begin = static_cast<int>(static_cast<std::int64_t>(part) * p.k_steps / parts);
+  const int ks_end = static_cast<int>(static_cast<std::int64_t>(part + 1) * p.k_steps / parts);
 
   if (tid == 0) {
-    for (int s = 0; s < kWideStages; ++s) {
+    for (int s = 0; s < kPairStages; ++s) {
       ptx::MbarInit(&full_tma[s], 1);
       ptx::MbarInit(&empty[s], 1);
     }
-    for (int b = 0; b < kWideBuffers; ++b) {
-      ptx::MbarInit(&w_full[b], kDequantWarps);
+    for (int b = 0; b < kPairBuffers; ++b) {
+      ptx::MbarInit(&w_full[b], 2 * kPairDequantWarps / kPairGroups);
       ptx::MbarInit(&w_empty[b], 1);
     }
     ptx::MbarInit(accum_full, 1);
@@ -436,11 +478,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     ptx::FenceMbarInit();
   }
   if (warp == 0) {
-    ptx::TmemAlloc(tmem_slot, 512);
-    ptx::TmemRelinquish();
+    ptx::TmemAllocPair(tmem_slot, 512);
+    ptx::TmemRelinquishPair();
   }
   ptx::TcFenceBefore();
-  __syncthreads();
+  ptx::ClusterSync();   // barriers of both CTAs exist before anything arrives on them
   ptx::TcFenceAfter();
   const std::uint32_t tmem_base = *tmem_slot;
 
@@ -449,9 +491,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       ptx::PrefetchTensorMap(&map_a);
       ptx::PrefetchTensorMap(&map_p);
-      // the bf16 activations come from the pre-pass launched just before (programmatic dependent
-      // launch): TMEM, barriers and descriptors are set up while it runs, the copies wait for it
-      ptx::GridDependencyWait();
+      ptx::GridDependencyWait();   // the bf16 activations come from the pre-pass launched just before
       int s = 0;
       std::uint32_t phase = 0;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
@@ -460,25 +500,24 @@ __global__ void __launch_bounds__(kThreads, 1)
           *abort_flag = 1;
           break;
         }
-        ptx::MbarArriveExpectTx(&full_tma[s], kWideStageA + kWideStageP);
-        ptx::TmaLoad2D(ring_a + s * kWideStageA, &map_a, ks * kTileK, m0, &full_tma[s]);
-        ptx::TmaLoad2D(ring_p + s * kWideStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
-        if (++s == kWideStages) {
+        ptx::MbarArriveExpectTx(&full_tma[s], stage_a_bytes + kPairStageP);
+        ptx::TmaLoad2D(ring_a + s * kPairStageA, &map_a, ks * kTileK, m0 + static_cast<int>(rank) * half_tokens,
+                       &full_tma[s]);
+        ptx::TmaLoad2D(ring_p + s * kPairStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
+        if (++s == kPairStages) {
           s = 0;
           phase ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      constexpr std::uint32_t idesc = ptx::UmmaIdescBf16(128, kWideTokens);
+    // ------------------------------- MMA issuer (even CTA) -------------------------------
+    if (lane == 0 && rank == 0) {
       bool ok = true;
       int s = 0;
       int b = 0;
       std::uint32_t b_phase = 0;
       for (int ks = ks_begin; ks < ks_end; ++ks) {
-        // the buffer's dequantizers waited for the stage's TMA, so the activations are in too
         if (!ptx::MbarWaitHot(&w_full[b], b_phase)) {
           ReportStatus(p.status, kDeviceTimeoutMmaBarrier);
           *abort_flag = 1;
@@ -486,37 +525,38 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         ptx::TcFenceAfter();
-        const std::uint32_t sa = ptx::SmemAddr(ring_a + s * kWideStageA);
-        const std::uint32_t sw = ptx::SmemAddr(buf_w + b * kWideBufW);
+        const std::uint32_t sa = ptx::SmemAddr(ring_a + s * kPairStageA);
+        const std::uint32_t sw = ptx::SmemAddr(buf_w + b * kPairBufW);
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
           for (int kk = 0; kk < kTileK / 16; ++kk) {
-            const std::uint64_t desc_w = ptx::UmmaDescKMajorSw128(sw + sub * (kWideBufW / 2) + kk * 32);
+            const std::uint64_t desc_w = ptx::UmmaDescKMajorSw128(sw + sub * (kPairBufW / 2) + kk * 32);
             const std::uint64_t desc_a = ptx::UmmaDescKMajorSw128(sa + kk * 32);
-            ptx::UmmaBf16(tmem_base + sub * kWideTokens, desc_w, desc_a, idesc,
-                          (ks != ks_begin || kk != 0) ? 1u : 0u);
+            ptx::UmmaBf16Pair(tmem_base + sub * kPairTokens, desc_w, desc_a, pp.idesc, (ks != ks_begin || kk != 0) ? 1u : 0u);
           }
         }
-        ptx::UmmaCommit(&empty[s]);
-        ptx::UmmaCommit(&w_empty[b]);
-        if (++s == kWideStages) {
+        ptx::UmmaCommitPair(&empty[s], 3);
+        ptx::UmmaCommitPair(&w_empty[b], 3);
+        if (++s == kPairStages) {
           s = 0;
         }
-        if (++b == kWideBuffers) {
+        if (++b == kPairBuffers) {
           b = 0;
           b_phase ^= 1u;
         }
       }
       if (ok) {
-        ptx::UmmaCommit(accum_full);
+        ptx::UmmaCommitPair(accum_full, 3);
       }
     }
   } else {
     // ------------------------------- dequantizers -------------------------------
-    const int dq = tid - 64;          // 0..255
-    const int row = dq >> 1;          // weight row inside each 128-row sub-tile
-    const int half = dq & 1;          // which 32 of the 64 k of the stage
+    const int dq = tid - 64;                 // 0..511
+    const int group = dq / kPairGroupThreads;  // takes k steps group, group + 2, ... of this CTA's part
+    const int gdq = dq % kPairGroupThreads;
+    const int row = gdq >> 1;                  // weight row inside each 128-row sub-tile
+    const int half = gdq & 1;                  // which 32 of the 64 k of the stage
     const std::uint32_t magic = p.magic;
     const int last_block = p.w.n_blocks - 1;
     const float *scale_row[2];
@@ -537,49 +577,59 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int c = half * 4 + i; // 16-byte chunk index inside the 128-byte row
       store_offset[i] = row * 128 + ((c ^ (row & 7)) << 4);
     }
+    // where this warp reports a dequantized buffer: the even CTA's barrier (the arrival form that
+    // hands shared memory written by threads to the pair's MMA)
+    const std::uint32_t w_full_even = ptx::MapToCta(ptx::SmemAddr(&w_full[0]), 0);
 
-    auto load_meta = [&](int ks, std::uint32_t (&scale2)[2], std::uint32_t (&offset2)[2]) {
-      int block = (ks * kTileK + half * 32) >> p.block_shift;
-      block = block > last_block ? last_block : block;
+    // Scale and zero point of a k step's block: loaded one step of the group ahead, converted at the
+    // start of the step that uses them (a conversion right behind the load would expose the L2 latency).
+    auto block_of = [&](int ks) {
+      const int block = (ks * kTileK + half * 32) >> p.block_shift;
+      return block > last_block ? last_block : block;
+    };
+    auto fetch_meta = [&](int ks, float (&scale)[2], int (&zp_byte)[2]) {
+      const int block = block_of(ks);
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
-        const float scale = row_valid[sub] ? __ldg(scale_row[sub] + block) : 0.0f;
-        int zp = 8;
-        if (zp_row[sub] != nullptr) {
-          const int byte = __ldg(zp_row[sub] + (block >> 1));
-          zp = (byte >> ((block & 1) * 4)) & 0x0f;
-        }
-        scale2[sub] = Bf16Pair(scale);
-        offset2[sub] = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
+        scale[sub] = row_valid[sub] ? __ldg(scale_row[sub] + block) : 0.0f;
+        zp_byte[sub] = zp_row[sub] != nullptr ? __ldg(zp_row[sub] + (block >> 1)) : 0x88;
       }
     };
 
-    std::uint32_t scale_next[2], offset_next[2];
-    load_meta(ks_begin, scale_next, offset_next);
+    float scale_raw[2];
+    int zp_raw[2];
     bool ok = true;
-    int s = 0;
+    int s = group;                // kPairGroups <= kPairStages, kPairBuffers
     std::uint32_t phase = 0;
-    int b = 0;
+    int b = group;
     std::uint32_t b_phase = 0;
-    for (int ks = ks_begin; ks < ks_end; ++ks) {
-      const std::uint32_t scale2[2] = {scale_next[0], scale_next[1]};
-      const std::uint32_t offset2[2] = {offset_next[0], offset_next[1]};
-      if (ks + 1 < ks_end) {
-        load_meta(ks + 1, scale_next, offset_next);
+    if (ks_begin + group < ks_end) {
+      fetch_meta(ks_begin + group, scale_raw, zp_raw);
+    }
+    for (int ks = ks_begin + group; ks < ks_end; ks += kPairGroups) {
+      const int shift = (block_of(ks) & 1) * 4;
+      std::uint32_t scale2[2], offset2[2];
+#pragma unroll
+      for (int sub = 0; sub < 2; ++sub) {
+        scale2[sub] = Bf16Pair(scale_raw[sub]);
+        offset2[sub] = Bf16Pair(static_cast<float>(128 + ((zp_raw[sub] >> shift) & 0x0f))); // exact in bf16
       }
-      // packed weights of this stage landed, and the buffer's previous reader has retired
+      if (ks + kPairGroups < ks_end) {
+        fetch_meta(ks + kPairGroups, scale_raw, zp_raw);
+      }
+      // this CTA's copies of the stage landed, and the buffer's previous readers have retired
       if (!ptx::MbarWaitHot(&full_tma[s], phase) || !ptx::MbarWaitHot(&w_empty[b], b_phase ^ 1u)) {
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
         break;
       }
-      const unsigned char *packed = ring_p + s * kWideStageP + packed_offset;
-      unsigned char *dst = buf_w + b * kWideBufW;
+      const unsigned char *packed = ring_p + s * kPairStageP + packed_offset;
+      unsigned char *dst = buf_w + b * kPairBufW;
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         const uint4 q = *reinterpret_cast<const uint4 *>(packed + sub * 128 * 32);
-        const std::uint32_t tile = ptx::SmemAddr(dst + sub * (kWideBufW / 2));
+        const std::uint32_t tile = ptx::SmemAddr(dst + sub * (kPairBufW / 2));
         DequantStore(tile + store_offset[0], q.x, magic, offset2[sub], scale2[sub]);
         DequantStore(tile + store_offset[1], q.y, magic, offset2[sub], scale2[sub]);
         DequantStore(tile + store_offset[2], q.z, magic, offset2[sub], scale2[sub]);
@@ -588,14 +638,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       ptx::FenceProxyAsyncShared();
       __syncwarp();
       if (lane == 0) {
-        ptx::MbarArrive(&w_full[b]);
+        ptx::MbarArriveCluster(w_full_even + static_cast<std::uint32_t>(b) * 8u);
       }
-      if (++s == kWideStages) {
-        s = 0;
+      s += kPairGroups;
+      if (s >= kPairStages) {
+        s -= kPairStages;
         phase ^= 1u;
       }
-      if (++b == kWideBuffers) {
-        b = 0;
+      b += kPairGroups;
+      if (b >= kPairBuffers) {
+        b -= kPairBuffers;
         b_phase ^= 1u;
       }
     }
@@ -610,26 +662,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (ok && *abort_flag == 0) {
       ptx::TcFenceAfter();
-      const int quarter = warp & 3;            // TMEM lane quarter this warp may read
-      const int sub = (warp - 2) >> 2;         // warps 2..5 read sub-tile 0, warps 6..9 sub-tile 1
-      const int n_local = sub * 128 + quarter * 32 + lane;
+      // four warps share a TMEM lane quarter: two accumulators x two halves of the token tile
+      const int quarter = warp & 3;
+      const int share = (warp - 2) >> 2;       // 0..3
+      const int acc = share & 1;
+      const int c_begin = (share >> 1) * (kPairTokens / 2);
+      const int n_local = acc * 128 + quarter * 32 + lane;
       const std::int64_t col = static_cast<std::int64_t>(n0) + n_local;
-      const float bias = (!SPLIT && p.w.bias != nullptr && col < p.w.n) ? __ldg(p.w.bias + col) : 0.0f;
+      const bool whole = p.partial == nullptr;   // otherwise the sum kernel adds the bias
+      const float bias = (whole && p.w.bias != nullptr && col < p.w.n) ? __ldg(p.w.bias + col) : 0.0f;
+      float *part_out = whole ? nullptr : p.partial + static_cast<std::int64_t>(part) * p.m_total * p.w.n;
+      const int m_end = (m0 + pp.tokens) < p.m_total ? (m0 + pp.tokens) : p.m_total;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kWideTokens; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_begin + kPairTokens / 2 && c0 < pp.tokens; c0 += 32) {
         std::uint32_t v[32];
-        ptx::TmemLoad32x32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + sub * kWideTokens + c0, v);
+        ptx::TmemLoad32x32(tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) + acc * kPairTokens + c0, v);
         ptx::TmemLoadWait();
         if (col < p.w.n) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int m = m0 + c0 + j;
-            if (m < p.m_total) {
-              if constexpr (SPLIT) {
-                p.partial[(static_cast<std::int64_t>(split) * p.m_total + m) * p.w.n + col] = __uint_as_float(v[j]);
+            if (m < m_end) {
+              if (whole) {
+                p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] = __uint_as_float(v[j]) + bias;
               } else {
-                p.out.y[static_cast<std::int64_t>(m) * p.out.ld + p.out.col_offset + col] =
-                    __uint_as_float(v[j]) + bias;
+                part_out[static_cast<std::int64_t>(m) * p.w.n + col] = __uint_as_float(v[j]);
               }
             }
           }
@@ -638,11 +695,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
+  // both CTAs are done with each other's shared memory and with their TMEM
+  __syncwarp();
   ptx::TcFenceBefore();
-  __syncthreads();
+  ptx::ClusterSync();
   if (warp == 0) {
     ptx::TcFenceAfter();
-    ptx::TmemDealloc(tmem_base, 512);
+    ptx::TmemDeallocPair(tmem_base, 512);
   }
 }
 
@@ -741,83 +800,131 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
                      : LaunchTileBits<BT, 4>(w, m, a_bf16, out, status_word, stream);
 }
 
-const char *LaunchWide(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
-                       int *status_word, cudaStream_t stream, int splits, float *partial, int sms) {
+// Shape of a product on the pair kernel: token-tile width (a multiple of 16, at most 256) and the
+// number of parts K is shared between; parts == 0 sends the product to the 128-row kernel instead.
+// Chosen by a cost model in microseconds under load, fitted to measurements (N = 4096 ... 16032,
+// K = 4096 and 14336, M = 192 ... 8192): a k step of a pair costs 0.30 + 0.0016 per token of the
+// tile, a tile 4 for set-up plus 0.028 per token for its epilogue; the partial products of a shared K
+// cross L2 once more on their way into Y (4 us + bytes at 4 TB/s); a k step of a 128 x 128 tile of
+// the 128-row kernel costs 0.375 and its tile 3.
+struct PairPlan {
+  int tokens;
+  int parts;
+};
+
+PairPlan PairPlanFor(const WeightView &w, std::int64_t m, int sms, bool force_pair) {
+  const std::int64_t pair_rows = (w.n + 2 * kPairRows - 1) / (2 * kPairRows);
+  const std::int64_t slots = sms / 2 > 0 ? sms / 2 : 1;
+  const std::int64_t k_steps = w.k / kTileK;
+  PairPlan best{kPairTokens, 1};
+  double best_cost = -1.0;
+  for (int parts = 1; parts <= 4; parts *= 2) {
+    if (parts > 1 && k_steps / parts < 8) {
+      break;
+    }
+    const double steps = static_cast<double>((k_steps + parts - 1) / parts);
+    for (int tokens = kPairTokens; tokens >= 64; tokens -= 16) {
+      const std::int64_t tiles = pair_rows * ((m + tokens - 1) / tokens) * parts;
+      const double rounds = static_cast<double>((tiles + slots - 1) / slots);
+      double cost = rounds * (4.0 + 0.028 * tokens + steps * (0.30 + 0.0016 * tokens));
+      if (parts > 1) {
+        cost += 4.0 + static_cast<double>(parts + 1) * static_cast<double>(m) * static_cast<double>(w.n) * 4.0 / 4.0e6;
+      }
+      if (best_cost < 0.0 || cost < best_cost) {
+        best_cost = cost;
+        best = PairPlan{tokens, parts};
+      }
+    }
+  }
+  if (!force_pair) {
+    const std::int64_t tiles = ((w.n + kTileN - 1) / kTileN) * ((m + 127) / 128);
+    const double rounds = static_cast<double>((tiles + sms - 1) / sms);
+    if (rounds * (3.0 + 0.375 * static_cast<double>(k_steps)) < best_cost) {
+      best.parts = 0;
+    }
+  }
+  return best;
+}
+
+// Whether a product is considered for the pair kernel at all.
+bool PairShape(const WeightView &w, std::int64_t m, bool force_pair) {
+  return w.bits == 4 && (force_pair || m > 128);
+}
+
+const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
+                       int *status_word, cudaStream_t stream, int sms, float *partial, const PairPlan &plan) {
+  const int tokens = plan.tokens;
   CUtensorMap map_a, map_p;
   if (!EncodeMap2D(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_bf16, static_cast<std::uint64_t>(w.k),
-                   static_cast<std::uint64_t>(m), static_cast<std::uint64_t>(w.k) * 2, kTileK, kWideTokens,
+                   static_cast<std::uint64_t>(m), static_cast<std::uint64_t>(w.k) * 2, kTileK, tokens / 2,
                    CU_TENSOR_MAP_SWIZZLE_128B)) {
     return nullptr;
   }
   if (!EncodeMap2D(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.b, static_cast<std::uint64_t>(w.row_bytes),
                    static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.row_bytes), kTileK / 2,
-                   kWideRows, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+                   kPairRows, CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return nullptr;
   }
-  GemmParams p{};
-  p.w = w;
-  p.out = out;
-  p.m_total = static_cast<int>(m);
-  p.k_steps = static_cast<int>(w.k / kTileK);
-  p.status = status_word;
-  p.block_shift = Log2Of(w.block_size);
-  p.magic = 0x43004300u;
-  p.partial = partial;
-  auto kernel = splits > 1 ? nbits_gemm_tcgen05_wide_kernel<true> : nbits_gemm_tcgen05_wide_kernel<false>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem) != cudaSuccess) {
+  PairParams pp{};
+  pp.g.w = w;
+  pp.g.out = out;
+  pp.g.m_total = static_cast<int>(m);
+  pp.g.k_steps = static_cast<int>(w.k / kTileK);
+  pp.g.status = status_word;
+  pp.g.block_shift = Log2Of(w.block_size);
+  pp.g.magic = 0x43004300u;
+  pp.g.partial = plan.parts > 1 ? partial : nullptr;
+  pp.tokens = tokens;
+  pp.idesc = ptx::UmmaIdescBf16(256, tokens);
+  auto kernel = nbits_gemm_tcgen05_pair_kernel;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess) {
     return nullptr;
   }
-  dim3 grid(static_cast<unsigned>((w.n + kWideRows - 1) / kWideRows),
-            static_cast<unsigned>((m + kWideTokens - 1) / kWideTokens), static_cast<unsigned>(splits));
-  if (!LaunchBehindPrePass(kernel, grid, kWideSmem, stream, map_a, map_p, p)) {
+  const std::int64_t pair_rows = (w.n + 2 * kPairRows - 1) / (2 * kPairRows);
+  dim3 grid(static_cast<unsigned>(2 * pair_rows), static_cast<unsigned>((m + tokens - 1) / tokens),
+            static_cast<unsigned>(plan.parts));
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(kPairThreads, 1, 1);
+  config.dynamicSmemBytes = kPairSmem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, kernel, map_a, map_p, pp) != cudaSuccess) {
+    cudaGetLastError();
     return nullptr;
   }
   CountLaunch();
-  if (splits > 1) {
+  if (plan.parts > 1) {
     const std::int64_t total = m * w.n;
     std::int64_t blocks = (total + 255) / 256;
     blocks = blocks > static_cast<std::int64_t>(sms) * 8 ? static_cast<std::int64_t>(sms) * 8 : blocks;
-    nbits_split_k_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, splits, m, w.n, w.bias, out);
+    nbits_split_k_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, plan.parts, m, w.n, w.bias, out);
     if (cudaGetLastError() != cudaSuccess) {
       return nullptr;
     }
     CountLaunch();
+    return "nbits_gemm_tcgen05_pair_kernel(split-k)";
   }
-  return splits > 1 ? "nbits_gemm_tcgen05_wide_kernel(split-k)" : "nbits_gemm_tcgen05_wide_kernel";
-}
-
-// Tile shape of a product. 0: the 128-row kernel. 1: 256 x 256 tiles, whole K per CTA (large
-// problems: half the operand traffic per flop). 2: 256 x 256 tiles with K shared by two CTAs, for
-// products whose tiles alone would cover between a third and a half of the SMs (the lm-head shard
-// at M = 256 is 63 tiles, the decode projection at M = 256 is 56): 70.5 against 78.2 us and 65.9
-// against 73.7 us with the 128-row kernel. Fewer tiles in four parts lost to the 128-row kernel
-// (M = 512 on N = 4096: 49.8 against 41.3 us): the fixed cost of a 256 x 256 tile, its two
-// epilogues and the sum kernel outweigh sixteen k steps.
-int WideSplits(const WeightView &w, std::int64_t m, int sms, bool force_wide) {
-  if (w.bits != 4) {
-    return 0;
-  }
-  const std::int64_t wide_tiles = ((w.n + kWideRows - 1) / kWideRows) * ((m + kWideTokens - 1) / kWideTokens);
-  if (force_wide || (m >= 1024 && wide_tiles * 10 >= static_cast<std::int64_t>(sms) * 8)) {
-    return 1;
-  }
-  const std::int64_t k_steps = w.k / kTileK;
-  if (m > 128 && wide_tiles * 2 <= sms && wide_tiles * 3 > sms && k_steps >= 16) {
-    return 2;
-  }
-  return 0;
+  return "nbits_gemm_tcgen05_pair_kernel";
 }
 
 std::size_t AlignScratch(std::size_t v) { return (v + 255) & ~std::size_t{255}; }
 
 } // namespace
 
-// bf16 activations of one call, then (split-K only) the partial products [parts][m][n].
+// bf16 activations of one call, then (K shared between pairs only) the partial products [parts][m][n].
 std::size_t GemmTcgen05ScratchBytes(const WeightView &w, std::int64_t m, int sm_count) {
   std::size_t bytes = AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2);
-  const int splits = WideSplits(w, m, sm_count > 0 ? sm_count : 148, false);
-  if (splits > 1) {
-    bytes += static_cast<std::size_t>(splits) * static_cast<std::size_t>(m) * static_cast<std::size_t>(w.n) * sizeof(float);
+  if (PairShape(w, m, true)) {
+    // the widest split either choice of kernel can take (the forced pair path may split where AUTO does not)
+    const PairPlan forced = PairPlanFor(w, m, sm_count > 0 ? sm_count : 148, true);
+    if (forced.parts > 1) {
+      bytes += static_cast<std::size_t>(forced.parts) * static_cast<std::size_t>(m) * static_cast<std::size_t>(w.n) * sizeof(float);
+    }
   }
   return bytes;
 }
@@ -830,7 +937,7 @@ bool GemmTcgen05Supports(const WeightView &w, std::int64_t m) {
 
 const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t m,
                               std::uint16_t *a_bf16, OutputView out, int *status_word,
-                              cudaStream_t stream, int sm_count, bool force_wide) {
+                              cudaStream_t stream, int sm_count, int tiles) {
   if (!GemmTcgen05Supports(w, m) || (reinterpret_cast<std::uintptr_t>(a) & 15u) != 0) {
     return nullptr;
   }
@@ -841,7 +948,6 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
     blocks = max_blocks;
   }
   const int sms = sm_count > 0 ? sm_count : 148;
-  const int splits = WideSplits(w, m, sms, force_wide);
   nbits_a_to_bf16_kernel<<<blocks, 256, 0, stream>>>(a, m, w.k, reinterpret_cast<__nv_bfloat16 *>(a_bf16),
                                                      w.bits == 4 ? 1 : 0);
   if (cudaGetLastError() != cudaSuccess) {
@@ -849,11 +955,15 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
   }
   CountLaunch();
   const std::int64_t n_tiles = (w.n + kTileN - 1) / kTileN;
-  if (splits >= 1) {
-    float *partial = reinterpret_cast<float *>(
-        reinterpret_cast<unsigned char *>(a_bf16) +
-        AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2));
-    return LaunchWide(w, m, a_bf16, out, status_word, stream, splits, splits > 1 ? partial : nullptr, sms);
+  const bool force_pair = tiles == kGemmTilePairs;
+  if (tiles != kGemmTileRows128 && PairShape(w, m, force_pair)) {
+    const PairPlan plan = PairPlanFor(w, m, sms, force_pair);
+    if (plan.parts >= 1) {
+      float *partial = reinterpret_cast<float *>(
+          reinterpret_cast<unsigned char *>(a_bf16) +
+          AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2));
+      return LaunchPair(w, m, a_bf16, out, status_word, stream, sms, partial, plan);
+    }
   }
   // otherwise the widest token tile that still gives every SM a tile
   if (m > 128 && n_tiles * ((m + 255) / 256) >= sms) {

@@ -561,41 +561,48 @@ def test_prefill_tcgen05_8bit(cuda_device, m, k, n, bs, zp, bias):
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
 
 
+PAIR = "nbits_gemm_tcgen05_pair_kernel"
+
+
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", [
     (512, 4096, 512, 64, True, False),
-    (300, 1024, 700, 32, True, True),      # ragged in both directions, two row tiles
-    (257, 512, 130, 128, False, True),     # one token over a tile boundary
+    (300, 1024, 700, 32, True, True),      # ragged in both directions; the odd CTA's second sub-tile is past N
+    (257, 512, 130, 128, False, True),     # one token over a tile boundary; the odd CTA of the pair has no row at all
     (64, 256, 256, 64, True, False),
+    (1024, 1024, 1536, 64, True, True),    # three pairs of row tiles, K whole
+    (250, 2048, 1000, 32, True, True),     # token tile narrower than 256 and not a multiple of 32
 ])
-def test_prefill_tcgen05_wide_tiles(cuda_device, m, k, n, bs, zp, bias):
-    case = syn.make_case("prefill_wide", m, k, n, 4, bs, seed=m + k + n + 1, zero_points=zp, bias=bias)
+def test_prefill_tcgen05_cta_pairs(cuda_device, m, k, n, bs, zp, bias):
+    """The kernel in which two CTAs share every MMA (each with 256 weight rows of its own and half of
+    the token tile), forced for shapes of every raggedness; K whole or shared between pairs as the
+    plan decides."""
+    case = syn.make_case("prefill_pair", m, k, n, 4, bs, seed=m + k + n + 1, zero_points=zp, bias=bias)
     y, kernel = run_device(case, path=_capi.PATH_TCGEN05_WIDE)
-    assert kernel == "nbits_gemm_tcgen05_wide_kernel", kernel
+    assert kernel.startswith(PAIR), kernel
     ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
     assert rel_err(y, ref_bf16) <= TOL_BF16
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
 
 
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", [
-    (200, 1024, 12900, 64, True, True),    # 51 tiles of 256 x 256: K in two parts of eight steps, ragged M and N
-    (256, 2048, 16032, 32, True, False),   # the lm-head shard's width: 63 tiles
+    (200, 4096, 4100, 64, True, True),     # nine pairs of row tiles (the last one ragged), K in four parts
+    (256, 4096, 4096, 32, True, False),
 ])
 def test_prefill_split_k(cuda_device, m, k, n, bs, zp, bias):
-    """Products between decode and prefill whose 256 x 256 tiles alone would leave most SMs idle: K
-    is shared by two CTAs per tile and the partial products are added in part order by a kernel
-    behind them, so two runs give the same bits. Values match the bf16 model like the unsplit
-    kernel's, and the unsplit kernel itself up to the order of the fp32 additions."""
+    """Products between decode and prefill whose tiles alone would leave most SMs idle: K is shared
+    by several CTA pairs per tile and the partial products are added in part order by a kernel
+    behind them, so two runs give the same bits. Values match the bf16 model like the 128-row
+    kernel's, and that kernel itself up to the order of the fp32 additions."""
     case = syn.make_case("splitk", m, k, n, 4, bs, seed=m + k + n + 5, zero_points=zp, bias=bias)
     y, kernel = run_device(case)
     again, _ = run_device(case)
-    assert kernel.startswith("nbits_gemm_tcgen05"), kernel
-    assert kernel == "nbits_gemm_tcgen05_wide_kernel(split-k)", kernel
+    assert kernel == PAIR + "(split-k)", kernel
     np.testing.assert_array_equal(y, again)
     ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 4, bs)
     assert rel_err(y, ref_bf16) <= TOL_BF16
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
-    whole, name = run_device(case, path=_capi.PATH_TCGEN05_WIDE)
-    assert name == "nbits_gemm_tcgen05_wide_kernel", name
+    whole, name = run_device(case, path=_capi.PATH_TCGEN05)
+    assert name.startswith("nbits_gemm_tcgen05_kernel"), name
     assert rel_err(y, whole) <= 1e-5
 
 
