@@ -42,7 +42,7 @@ typedef enum mnb_path {
   MNB_PATH_TCGEN05 = 2, /* TMA + smem dequant to bf16 + tcgen05/TMEM MMA (prefill), 128 weight rows per CTA */
   MNB_PATH_INT8 = 3,    /* accuracy_level 4: per-block int8 A, int32 block dots */
   MNB_PATH_GEMV_MMA = 4, /* decode on warp-level MMA, exact two-piece fp16 split of A */
-  MNB_PATH_TCGEN05_WIDE = 5, /* prefill, tiles of 512 rows x up to 256 tokens on pairs of CTAs for any M (AUTO picks them for M > 128 when they pay) */
+  MNB_PATH_TCGEN05_WIDE = 5, /* prefill, tiles of 512 rows x up to 256 tokens on pairs of CTAs for any M (AUTO picks them for M > 16 when they pay) */
   MNB_PATH_INT8_MMA = 6, /* accuracy_level 4 on integer tensor-core MMA (AUTO picks it when the shape fits) */
   MNB_PATH_GEMV_MMA_MULTI = 7, /* decode on warp-level MMA, several column tiles of tokens per pass */
   MNB_PATH_GEMV_IMMA = 8, /* decode on integer MMA, A as three base-128 digits (block_size >= 128; AUTO picks it for M <= 2) */

@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 // ---------------------------------------------------------------------------------------------
 // CTA pairs: 512 weight rows x `tokens` (<= 256) per pair of SMs, for every product of more than
-// 128 tokens that is worth it (PairPlanFor below).
+// sixteen tokens that is worth it (PairPlanFor below).
 //
 // Two CTAs of a cluster (the same pair of SMs) share every MMA (cta_group::2, 256 x tokens x 16): each
 // CTA dequantizes 256 weight rows of its own (two 128-row sub-tiles = the two 256-column accumulators
@@ -803,10 +803,10 @@ const char *LaunchTile(const WeightView &w, std::int64_t m, const std::uint16_t 
 // Shape of a product on the pair kernel: token-tile width (a multiple of 16, at most 256) and the
 // number of parts K is shared between; parts == 0 sends the product to the 128-row kernel instead.
 // Chosen by a cost model in microseconds under load, fitted to measurements (N = 4096 ... 16032,
-// K = 4096 and 14336, M = 192 ... 8192): a k step of a pair costs 0.30 + 0.0016 per token of the
-// tile, a tile 4 for set-up plus 0.028 per token for its epilogue; the partial products of a shared K
-// cross L2 once more on their way into Y (4 us + bytes at 4 TB/s); a k step of a 128 x 128 tile of
-// the 128-row kernel costs 0.375 and its tile 3.
+// K = 4096 and 14336, M = 17 ... 8192): a k step of a pair costs 0.30 + 0.0016 per token of the
+// tile but at least 0.5 (the dequantization of 2 x 256 rows), a tile 4 for set-up plus 0.028 per
+// token for its epilogue; the partial products of a shared K cross L2 once more on their way into Y
+// (4 us + bytes at 4 TB/s); a k step of a tile of the 128-row kernel costs 0.375 and its tile 3.
 struct PairPlan {
   int tokens;
   int parts;
@@ -818,7 +818,7 @@ PairPlan PairPlanFor(const WeightView &w, std::int64_t m, int sms, bool force_pa
   const std::int64_t k_steps = w.k / kTileK;
   PairPlan best{kPairTokens, 1};
   double best_cost = -1.0;
-  for (int parts = 1; parts <= 4; parts *= 2) {
+  for (int parts = 1; parts <= 8; parts *= 2) {
     if (parts > 1 && k_steps / parts < 8) {
       break;
     }
@@ -826,7 +826,8 @@ PairPlan PairPlanFor(const WeightView &w, std::int64_t m, int sms, bool force_pa
     for (int tokens = kPairTokens; tokens >= 64; tokens -= 16) {
       const std::int64_t tiles = pair_rows * ((m + tokens - 1) / tokens) * parts;
       const double rounds = static_cast<double>((tiles + slots - 1) / slots);
-      double cost = rounds * (4.0 + 0.028 * tokens + steps * (0.30 + 0.0016 * tokens));
+      const double step_cost = 0.30 + 0.0016 * tokens > 0.5 ? 0.30 + 0.0016 * tokens : 0.5;
+      double cost = rounds * (4.0 + 0.028 * tokens + steps * step_cost);
       if (parts > 1) {
         cost += 4.0 + static_cast<double>(parts + 1) * static_cast<double>(m) * static_cast<double>(w.n) * 4.0 / 4.0e6;
       }
@@ -848,7 +849,7 @@ PairPlan PairPlanFor(const WeightView &w, std::int64_t m, int sms, bool force_pa
 
 // Whether a product is considered for the pair kernel at all.
 bool PairShape(const WeightView &w, std::int64_t m, bool force_pair) {
-  return w.bits == 4 && (force_pair || m > 128);
+  return w.bits == 4 && (force_pair || m > 16);
 }
 
 const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,

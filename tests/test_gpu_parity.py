@@ -571,6 +571,8 @@ PAIR = "nbits_gemm_tcgen05_pair_kernel"
     (64, 256, 256, 64, True, False),
     (1024, 1024, 1536, 64, True, True),    # three pairs of row tiles, K whole
     (250, 2048, 1000, 32, True, True),     # token tile narrower than 256 and not a multiple of 32
+    (17, 4096, 520, 64, True, True),       # fewer tokens than the narrowest tile, K in eight parts
+    (40, 14336, 300, 32, False, False),    # 224 k steps in eight parts of 28
 ])
 def test_prefill_tcgen05_cta_pairs(cuda_device, m, k, n, bs, zp, bias):
     """The kernel in which two CTAs share every MMA (each with 256 weight rows of its own and half of
@@ -587,6 +589,7 @@ def test_prefill_tcgen05_cta_pairs(cuda_device, m, k, n, bs, zp, bias):
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", [
     (200, 4096, 4100, 64, True, True),     # nine pairs of row tiles (the last one ragged), K in four parts
     (256, 4096, 4096, 32, True, False),
+    (64, 4096, 4096, 64, True, True),      # the middle regime on a square node: AUTO shares K between pairs
 ])
 def test_prefill_split_k(cuda_device, m, k, n, bs, zp, bias):
     """Products between decode and prefill whose tiles alone would leave most SMs idle: K is shared
