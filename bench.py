@@ -511,36 +511,39 @@ def main() -> None:
             del layers, layer_inputs
             torch.cuda.empty_cache()
 
-            # ---- prefill M = 2048 (bf16 tcgen05 path) ----
+            # ---- prefill M = 2048 and M = 8192 (bf16 tcgen05 path) ----
             pw = device_weights(torch, pkg, PREFILL, 1, seed=1301, zp=True, bias=False)[0]
-            pm = PREFILL["m"]
-            sets = 3  # rotate A/Y so that A + Y + weights exceed L2 between repeats
-            a_p = [torch.randn(pm, PREFILL["k"], device="cuda") for _ in range(sets)]
-            y_p = [torch.empty(pm, PREFILL["n"], device="cuda") for _ in range(sets)]
+            for pm, key in ((PREFILL["m"], "prefill"), (8192, "prefill_m8192")):
+                sets = 3 if pm <= 2048 else 2  # rotate A/Y so that A + Y + weights exceed L2 between repeats
+                a_p = [torch.randn(pm, PREFILL["k"], device="cuda") for _ in range(sets)]
+                y_p = [torch.empty(pm, PREFILL["n"], device="cuda") for _ in range(sets)]
 
-            def prefill_step():
-                for a_i, y_i in zip(a_p, y_p):
-                    pw.matmul_device(a_i, y_i)
+                def prefill_step():
+                    for a_i, y_i in zip(a_p, y_p):
+                        pw.matmul_device(a_i, y_i)
 
-            prefill_step()
-            torch.cuda.synchronize()
-            pname = _capi.last_kernel()
-            status = pw.poll_status()
-            psteps = max(5, args.steps // 10)
-            # events around the whole call: the fp32->bf16 activation pre-pass is inside
-            sec = time_steps(torch, dist, prefill_step, psteps, 3, 1)
-            flops = 2.0 * pm * PREFILL["n"] * PREFILL["k"]
-            tflops = flops * sets * psteps / sec / 1e12
-            extras["prefill"] = {
-                "workload": "cfg3 prefill M=2048 K=4096 N=4096 bits=4 block=64 zp",
-                "tflops": tflops, "us_per_call": sec / (sets * psteps) * 1e6, "kernel": pname,
-                "device_status": status,
-                "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                             "frac": tflops / peaks["bf16_tflops"],
-                             "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],
-                             "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)", "traffic": None},
-                "includes": "fp32->bf16 activation pre-pass + GEMM kernel"}
-            del pw, a_p, y_p
+                prefill_step()
+                torch.cuda.synchronize()
+                pname = _capi.last_kernel()
+                status = pw.poll_status()
+                psteps = max(5, args.steps // 10)
+                prefill_replay, _ = capture_graph(torch, prefill_step)
+                # events around the whole call: the fp32->bf16 activation pre-pass is inside
+                sec = time_steps(torch, dist, prefill_replay, psteps, 3, 1)
+                flops = 2.0 * pm * PREFILL["n"] * PREFILL["k"]
+                tflops = flops * sets * psteps / sec / 1e12
+                extras[key] = {
+                    "workload": f"cfg3 prefill M={pm} K=4096 N=4096 bits=4 block=64 zp",
+                    "tflops": tflops, "us_per_call": sec / (sets * psteps) * 1e6, "kernel": pname,
+                    "device_status": status,
+                    "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                 "frac": tflops / peaks["bf16_tflops"],
+                                 "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"],
+                                 "peak_kind": f"of {peak_kind} (cuBLAS bf16 burst)", "traffic": None},
+                    "includes": "fp32->bf16 activation pre-pass + GEMM kernel, replayed from a CUDA graph"}
+                del a_p, y_p, prefill_replay
+                torch.cuda.empty_cache()
+            del pw
     else:
         # ---- multi-GPU: column-sharded lm-head, NCCL all-gather of the output columns ----
         cfg = dict(LMHEAD)

@@ -423,9 +423,12 @@ static_assert(kPairGroupThreads == 256, "a group covers 128 rows x two halves of
 constexpr int kPairStages = 4;
 constexpr int kPairBuffers = 3;
 constexpr int kPairStageA = (kPairTokens / 2) * 128;   // half a token tile: 16 KB
-constexpr int kPairStageP = kPairRows * 32;            // packed weights of a k step: 8 KB
 constexpr int kPairBufW = kPairRows * 128;             // dequantized weights of a k step: 32 KB, two 16 KB sub-tiles
-constexpr int kPairSmem = kPairStages * (kPairStageA + kPairStageP) + kPairBuffers * kPairBufW + 256 + 1024;
+template <int BITS> struct PairSmem {
+  static constexpr int kRowP = kTileK * BITS / 8;       // packed bytes of a row per k step: 32 (4-bit) or 64 (8-bit)
+  static constexpr int kStageP = kPairRows * kRowP;     // packed weights of a k step: 8 or 16 KB
+  static constexpr int kTotal = kPairStages * (kPairStageA + kStageP) + kPairBuffers * kPairBufW + 256 + 1024;
+};
 
 struct PairParams {
   GemmParams g;
@@ -433,10 +436,13 @@ struct PairParams {
   std::uint32_t idesc;
 };
 
+template <int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     nbits_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                    const __grid_constant__ CUtensorMap map_p, const PairParams pp) {
   const GemmParams &p = pp.g;
+  constexpr int kPairStageP = PairSmem<BITS>::kStageP;
+  constexpr int kRowP = PairSmem<BITS>::kRowP;
   extern __shared__ __align__(1024) unsigned char smem_dyn[];
   unsigned char *smem = smem_dyn + ((1024u - (ptx::SmemAddr(smem_dyn) & 1023u)) & 1023u);
   unsigned char *ring_a = smem;                                     // [stages][16 KB]
@@ -503,7 +509,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         ptx::MbarArriveExpectTx(&full_tma[s], stage_a_bytes + kPairStageP);
         ptx::TmaLoad2D(ring_a + s * kPairStageA, &map_a, ks * kTileK, m0 + static_cast<int>(rank) * half_tokens,
                        &full_tma[s]);
-        ptx::TmaLoad2D(ring_p + s * kPairStageP, &map_p, ks * (kTileK / 2), n0, &full_tma[s]);
+        ptx::TmaLoad2D(ring_p + s * kPairStageP, &map_p, ks * kRowP, n0, &full_tma[s]);
         if (++s == kPairStages) {
           s = 0;
           phase ^= 1u;
@@ -570,7 +576,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       scale_row[sub] = p.w.scales + safe_row * p.w.n_blocks;
       zp_row[sub] = p.w.zp != nullptr ? p.w.zp + safe_row * p.w.zp_row_bytes : nullptr;
     }
-    const int packed_offset = row * 32 + half * 16;
+    const int packed_offset = row * kRowP + half * (kRowP / 2);
     int store_offset[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -592,7 +598,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         scale[sub] = row_valid[sub] ? __ldg(scale_row[sub] + block) : 0.0f;
-        zp_byte[sub] = zp_row[sub] != nullptr ? __ldg(zp_row[sub] + (block >> 1)) : 0x88;
+        if constexpr (BITS == 4) {
+          zp_byte[sub] = zp_row[sub] != nullptr ? __ldg(zp_row[sub] + (block >> 1)) : 0x88;
+        } else {
+          zp_byte[sub] = zp_row[sub] != nullptr ? __ldg(zp_row[sub] + block) : 128;
+        }
       }
     };
 
@@ -607,12 +617,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       fetch_meta(ks_begin + group, scale_raw, zp_raw);
     }
     for (int ks = ks_begin + group; ks < ks_end; ks += kPairGroups) {
-      const int shift = (block_of(ks) & 1) * 4;
+      [[maybe_unused]] const int shift = (block_of(ks) & 1) * 4;
       std::uint32_t scale2[2], offset2[2];
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
         scale2[sub] = Bf16Pair(scale_raw[sub]);
-        offset2[sub] = Bf16Pair(static_cast<float>(128 + ((zp_raw[sub] >> shift) & 0x0f))); // exact in bf16
+        if constexpr (BITS == 4) {
+          offset2[sub] = Bf16Pair(static_cast<float>(128 + ((zp_raw[sub] >> shift) & 0x0f))); // exact in bf16
+        } else {
+          const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp_raw[sub])); // exact in fp16
+          offset2[sub] = *reinterpret_cast<const std::uint32_t *>(&both);
+        }
       }
       if (ks + kPairGroups < ks_end) {
         fetch_meta(ks + kPairGroups, scale_raw, zp_raw);
@@ -628,12 +643,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       unsigned char *dst = buf_w + b * kPairBufW;
 #pragma unroll
       for (int sub = 0; sub < 2; ++sub) {
-        const uint4 q = *reinterpret_cast<const uint4 *>(packed + sub * 128 * 32);
         const std::uint32_t tile = ptx::SmemAddr(dst + sub * (kPairBufW / 2));
-        DequantStore(tile + store_offset[0], q.x, magic, offset2[sub], scale2[sub]);
-        DequantStore(tile + store_offset[1], q.y, magic, offset2[sub], scale2[sub]);
-        DequantStore(tile + store_offset[2], q.z, magic, offset2[sub], scale2[sub]);
-        DequantStore(tile + store_offset[3], q.w, magic, offset2[sub], scale2[sub]);
+        if constexpr (BITS == 4) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(packed + sub * 128 * kRowP);
+          DequantStore(tile + store_offset[0], q.x, magic, offset2[sub], scale2[sub]);
+          DequantStore(tile + store_offset[1], q.y, magic, offset2[sub], scale2[sub]);
+          DequantStore(tile + store_offset[2], q.z, magic, offset2[sub], scale2[sub]);
+          DequantStore(tile + store_offset[3], q.w, magic, offset2[sub], scale2[sub]);
+        } else {
+          const uint4 q0 = *reinterpret_cast<const uint4 *>(packed + sub * 128 * kRowP);
+          const uint4 q1 = *reinterpret_cast<const uint4 *>(packed + sub * 128 * kRowP + 16);
+          DequantStore8(tile + store_offset[0], q0.x, q0.y, offset2[sub], scale2[sub]);
+          DequantStore8(tile + store_offset[1], q0.z, q0.w, offset2[sub], scale2[sub]);
+          DequantStore8(tile + store_offset[2], q1.x, q1.y, offset2[sub], scale2[sub]);
+          DequantStore8(tile + store_offset[3], q1.z, q1.w, offset2[sub], scale2[sub]);
+        }
       }
       ptx::FenceProxyAsyncShared();
       __syncwarp();
@@ -849,10 +873,11 @@ PairPlan PairPlanFor(const WeightView &w, std::int64_t m, int sms, bool force_pa
 
 // Whether a product is considered for the pair kernel at all.
 bool PairShape(const WeightView &w, std::int64_t m, bool force_pair) {
-  return w.bits == 4 && (force_pair || m > 16);
+  return (w.bits == 4 || w.bits == 8) && (force_pair || m > 16);
 }
 
-const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
+template <int BITS>
+const char *LaunchPairBits(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
                        int *status_word, cudaStream_t stream, int sms, float *partial, const PairPlan &plan) {
   const int tokens = plan.tokens;
   CUtensorMap map_a, map_p;
@@ -862,7 +887,7 @@ const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t 
     return nullptr;
   }
   if (!EncodeMap2D(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.b, static_cast<std::uint64_t>(w.row_bytes),
-                   static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.row_bytes), kTileK / 2,
+                   static_cast<std::uint64_t>(w.n), static_cast<std::uint64_t>(w.row_bytes), PairSmem<BITS>::kRowP,
                    kPairRows, CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return nullptr;
   }
@@ -877,7 +902,8 @@ const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t 
   pp.g.partial = plan.parts > 1 ? partial : nullptr;
   pp.tokens = tokens;
   pp.idesc = ptx::UmmaIdescBf16(256, tokens);
-  auto kernel = nbits_gemm_tcgen05_pair_kernel;
+  auto kernel = nbits_gemm_tcgen05_pair_kernel<BITS>;
+  constexpr int kPairSmem = PairSmem<BITS>::kTotal;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) != cudaSuccess) {
     return nullptr;
   }
@@ -911,6 +937,12 @@ const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t 
     return "nbits_gemm_tcgen05_pair_kernel(split-k)";
   }
   return "nbits_gemm_tcgen05_pair_kernel";
+}
+
+const char *LaunchPair(const WeightView &w, std::int64_t m, const std::uint16_t *a_bf16, OutputView out,
+                       int *status_word, cudaStream_t stream, int sms, float *partial, const PairPlan &plan) {
+  return w.bits == 8 ? LaunchPairBits<8>(w, m, a_bf16, out, status_word, stream, sms, partial, plan)
+                     : LaunchPairBits<4>(w, m, a_bf16, out, status_word, stream, sms, partial, plan);
 }
 
 std::size_t AlignScratch(std::size_t v) { return (v + 255) & ~std::size_t{255}; }

@@ -555,13 +555,31 @@ def test_prefill_tcgen05_8bit(cuda_device, m, k, n, bs, zp, bias):
     """8-bit codes through the same kernel: whole bytes, natural k order, (q - zp) exact in bf16."""
     case = syn.make_case("prefill8", m, k, n, 8, bs, seed=m + k + n + 8, zero_points=zp, bias=bias)
     y, kernel = run_device(case)   # AUTO: above sixteen tokens 8-bit weights go to the tensor cores too
-    assert kernel.startswith("nbits_gemm_tcgen05_kernel"), kernel
+    assert kernel.startswith("nbits_gemm_tcgen05"), kernel
     ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 8, bs)
     assert rel_err(y, ref_bf16) <= TOL_BF16
     assert rel_err(y, oracle_f64(case)) <= TOL_BF16
 
 
 PAIR = "nbits_gemm_tcgen05_pair_kernel"
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", [
+    (300, 4096, 700, 32, True, True),      # ragged in both directions, zero points as whole bytes
+    (64, 1024, 128, 64, False, False),     # default zero point 128, a single pair
+    (256, 4096, 1002, 32, True, False),    # the column-shard geometry at reduced N
+])
+def test_prefill_tcgen05_cta_pairs_8bit(cuda_device, m, k, n, bs, zp, bias):
+    """8-bit codes through the pair kernel: 64 packed bytes per row and k step, natural k order."""
+    case = syn.make_case("prefill_pair8", m, k, n, 8, bs, seed=m + k + n + 88, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_TCGEN05_WIDE)
+    assert kernel.startswith(PAIR), kernel
+    rows, name = run_device(case, path=_capi.PATH_TCGEN05)
+    assert name.startswith("nbits_gemm_tcgen05_kernel"), name
+    ref_bf16 = o.matmul_bf16(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 8, bs)
+    assert rel_err(y, ref_bf16) <= TOL_BF16
+    assert rel_err(y, oracle_f64(case)) <= TOL_BF16
+    assert rel_err(y, rows) <= 1e-5        # the same roundings as the 128-row kernel, another order of the fp32 sums
 
 
 @pytest.mark.parametrize("m,k,n,bs,zp,bias", [
