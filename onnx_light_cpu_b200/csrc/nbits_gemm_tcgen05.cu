@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::MbarInit(&full_tma[s], 1);
-      ptx::MbarInit(&full_deq[s], kDequantWarps);
+      ptx::MbarInit(&full_deq[s], kDequantWarps / 2);   // the group of dequantizer warps that takes the step
       ptx::MbarInit(&empty[s], 1);
     }
     ptx::MbarInit(accum_full, 1);
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int ks = 0; ks < p.k_steps; ++ks) {
         const int s = ks % kStages;
         const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
-        if (!ptx::MbarWait(&empty[s], (round & 1u) ^ 1u)) {
+        if (!ptx::MbarWaitHot(&empty[s], (round & 1u) ^ 1u)) {
           ReportStatus(p.status, kDeviceTimeoutEmptyBarrier);
           *abort_flag = 1;
           break;
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int ks = 0; ks < p.k_steps && ok; ++ks) {
         const int s = ks % kStages;
         const std::uint32_t round = static_cast<std::uint32_t>(ks / kStages);
-        if (!ptx::MbarWait(&full_deq[s], round & 1u)) {
+        if (!ptx::MbarWaitHot(&full_deq[s], round & 1u)) {
           ReportStatus(p.status, kDeviceTimeoutMmaBarrier);
           *abort_flag = 1;
           ok = false;
@@ -245,66 +245,83 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------- dequantizers -------------------------------
+    // Two groups of four warps take alternate k steps (a step's chain of wait, load, convert, store,
+    // proxy fence and arrival is latency, not work: two of them run at any time); a thread converts
+    // the same half of two rows 64 apart.
     const int dq = tid - 64;          // 0..255
-    const int row = dq >> 1;          // weight row inside the tile
-    const int half = dq & 1;          // which 32 of the 64 k of the stage
-    const std::int64_t grow = static_cast<std::int64_t>(n0) + row;
-    const bool row_valid = grow < p.w.n;
-    const std::int64_t safe_row = row_valid ? grow : 0;
-    // per-thread views of this row's scales and packed zero points
-    const float *scale_row = p.w.scales + safe_row * p.w.n_blocks;
-    const std::uint8_t *zp_row = p.w.zp != nullptr ? p.w.zp + safe_row * p.w.zp_row_bytes : nullptr;
+    const int group = dq >> 7;
+    const int gdq = dq & 127;
+    const int row0 = gdq >> 1;        // rows row0 and row0 + 64 of the tile
+    const int half = gdq & 1;         // which 32 of the 64 k of the stage
     const int last_block = p.w.n_blocks - 1;
     const std::uint32_t magic = p.magic;
-    // fixed shared-memory offsets of this thread inside a stage
-    const int packed_offset = Smem::kStageA + Smem::kStageW + row * Smem::kRowP + half * (Smem::kRowP / 2);
-    int store_offset[4];
+    const float *scale_row[2];
+    const std::uint8_t *zp_row[2];
+    bool row_valid[2];
+    int packed_offset[2];
+    int store_base[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = half * 4 + i; // 16-byte chunk index inside the 128-byte row
-      store_offset[i] = Smem::kStageA + row * 128 + ((c ^ (row & 7)) << 4);
+    for (int i = 0; i < 2; ++i) {
+      const int row = row0 + i * 64;
+      const std::int64_t grow = static_cast<std::int64_t>(n0) + row;
+      row_valid[i] = grow < p.w.n;
+      const std::int64_t safe_row = row_valid[i] ? grow : 0;
+      scale_row[i] = p.w.scales + safe_row * p.w.n_blocks;
+      zp_row[i] = p.w.zp != nullptr ? p.w.zp + safe_row * p.w.zp_row_bytes : nullptr;
+      packed_offset[i] = Smem::kStageA + Smem::kStageW + row * Smem::kRowP + half * (Smem::kRowP / 2);
+      store_base[i] = Smem::kStageA + row * 128;
+    }
+    int chunk_offset[4];              // 16-byte chunk c of a row sits at c ^ (row & 7); both rows agree in row & 7
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      chunk_offset[c] = ((half * 4 + c) ^ (row0 & 7)) << 4;
     }
 
-    // Scale and zero point of a k step's block. The loads are issued one step ahead and nothing
-    // touches their results before the next step begins (a conversion right behind the load would
-    // expose the L2 latency in every step).
+    // Scale and zero point of a k step's block. The loads are issued one step of the group ahead and
+    // nothing touches their results before that step begins (a conversion right behind the load
+    // would expose the L2 latency in every step).
     auto block_of = [&](int ks) {
       const int block = (ks * kTileK + half * 32) >> p.block_shift;
       return block > last_block ? last_block : block;
     };
-    auto fetch_meta = [&](int ks, float &scale, int &zp_byte) {
+    auto fetch_meta = [&](int ks, float (&scale)[2], int (&zp_byte)[2]) {
       const int block = block_of(ks);
-      scale = row_valid ? __ldg(scale_row + block) : 0.0f;
-      if constexpr (BITS == 4) {
-        zp_byte = zp_row != nullptr ? __ldg(zp_row + (block >> 1)) : 0x88;
-      } else {
-        zp_byte = zp_row != nullptr ? __ldg(zp_row + block) : 128;
-      }
-    };
-    auto finish_meta = [&](int ks, float scale, int zp_byte, std::uint32_t &scale2, std::uint32_t &offset2) {
-      scale2 = Bf16Pair(scale);
-      if constexpr (BITS == 4) {
-        const int zp = (zp_byte >> ((block_of(ks) & 1) * 4)) & 0x0f;
-        offset2 = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
-      } else {
-        const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp_byte)); // exact in fp16
-        offset2 = *reinterpret_cast<const std::uint32_t *>(&both);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        scale[i] = row_valid[i] ? __ldg(scale_row[i] + block) : 0.0f;
+        if constexpr (BITS == 4) {
+          zp_byte[i] = zp_row[i] != nullptr ? __ldg(zp_row[i] + (block >> 1)) : 0x88;
+        } else {
+          zp_byte[i] = zp_row[i] != nullptr ? __ldg(zp_row[i] + block) : 128;
+        }
       }
     };
 
-    float scale_raw;
-    int zp_raw;
-    fetch_meta(0, scale_raw, zp_raw);
+    float scale_raw[2];
+    int zp_raw[2];
+    if (group < p.k_steps) {
+      fetch_meta(group, scale_raw, zp_raw);
+    }
     bool ok = true;
-    int s = 0;
-    std::uint32_t phase = 0;
-    for (int ks = 0; ks < p.k_steps; ++ks) {
-      std::uint32_t scale2, offset2;
-      finish_meta(ks, scale_raw, zp_raw, scale2, offset2);
-      if (ks + 1 < p.k_steps) {
-        fetch_meta(ks + 1, scale_raw, zp_raw);
+    for (int ks = group; ks < p.k_steps; ks += 2) {
+      const int s = ks % kStages;
+      const std::uint32_t phase = static_cast<std::uint32_t>(ks / kStages) & 1u;
+      std::uint32_t scale2[2], offset2[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        scale2[i] = Bf16Pair(scale_raw[i]);
+        if constexpr (BITS == 4) {
+          const int zp = (zp_raw[i] >> ((block_of(ks) & 1) * 4)) & 0x0f;
+          offset2[i] = Bf16Pair(static_cast<float>(128 + zp)); // exact in bf16
+        } else {
+          const __half2 both = __float2half2_rn(static_cast<float>(1024 + zp_raw[i])); // exact in fp16
+          offset2[i] = *reinterpret_cast<const std::uint32_t *>(&both);
+        }
       }
-      if (!ptx::MbarWait(&full_tma[s], phase)) {
+      if (ks + 2 < p.k_steps) {
+        fetch_meta(ks + 2, scale_raw, zp_raw);
+      }
+      if (!ptx::MbarWaitHot(&full_tma[s], phase)) {
         ReportStatus(p.status, kDeviceTimeoutFullBarrier);
         *abort_flag = 1;
         ok = false;
@@ -312,29 +329,29 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       unsigned char *stage = stage0 + s * Smem::kStage;
       const std::uint32_t base = ptx::SmemAddr(stage);
-      if constexpr (BITS == 4) {
-        const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset);
-        DequantStore(base + store_offset[0], q.x, magic, offset2, scale2);
-        DequantStore(base + store_offset[1], q.y, magic, offset2, scale2);
-        DequantStore(base + store_offset[2], q.z, magic, offset2, scale2);
-        DequantStore(base + store_offset[3], q.w, magic, offset2, scale2);
-      } else {
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(stage + packed_offset);
-        const uint4 q1 = *reinterpret_cast<const uint4 *>(stage + packed_offset + 16);
-        DequantStore8(base + store_offset[0], q0.x, q0.y, offset2, scale2);
-        DequantStore8(base + store_offset[1], q0.z, q0.w, offset2, scale2);
-        DequantStore8(base + store_offset[2], q1.x, q1.y, offset2, scale2);
-        DequantStore8(base + store_offset[3], q1.z, q1.w, offset2, scale2);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const std::uint32_t dst = base + store_base[i];
+        if constexpr (BITS == 4) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(stage + packed_offset[i]);
+          DequantStore(dst + chunk_offset[0], q.x, magic, offset2[i], scale2[i]);
+          DequantStore(dst + chunk_offset[1], q.y, magic, offset2[i], scale2[i]);
+          DequantStore(dst + chunk_offset[2], q.z, magic, offset2[i], scale2[i]);
+          DequantStore(dst + chunk_offset[3], q.w, magic, offset2[i], scale2[i]);
+        } else {
+          const uint4 q0 = *reinterpret_cast<const uint4 *>(stage + packed_offset[i]);
+          const uint4 q1 = *reinterpret_cast<const uint4 *>(stage + packed_offset[i] + 16);
+          DequantStore8(dst + chunk_offset[0], q0.x, q0.y, offset2[i], scale2[i]);
+          DequantStore8(dst + chunk_offset[1], q0.z, q0.w, offset2[i], scale2[i]);
+          DequantStore8(dst + chunk_offset[2], q1.x, q1.y, offset2[i], scale2[i]);
+          DequantStore8(dst + chunk_offset[3], q1.z, q1.w, offset2[i], scale2[i]);
+        }
       }
       // make the generic-proxy stores visible to the tensor core (async proxy), then signal
       ptx::FenceProxyAsyncShared();
       __syncwarp();
       if (lane == 0) {
         ptx::MbarArrive(&full_deq[s]);
-      }
-      if (++s == kStages) {
-        s = 0;
-        phase ^= 1u;
       }
     }
 
