@@ -48,6 +48,9 @@ __global__ void __launch_bounds__(256)
     nbits_a_to_bf16_kernel(const float *a, std::int64_t m, std::int64_t k, __nv_bfloat16 *out, int permute) {
   // the GEMM behind this kernel may set itself up right away; its copies wait for this grid
   ptx::GridDependencyLaunch();
+  // this kernel itself is launched behind whatever precedes it in the stream with programmatic
+  // serialization (its blocks may be resident early): A and the scratch buffer are touched after that
+  ptx::GridDependencyWait();
   const std::int64_t groups_per_row = k / 8;
   const std::int64_t total = m * groups_per_row;
   for (std::int64_t g = static_cast<std::int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total;
@@ -171,6 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = tid & 31;
   const int n0 = blockIdx.x * kTileN;
   const int m0 = blockIdx.y * BT;
+  ptx::GridDependencyLaunch();   // what follows in the stream (the next call's pre-pass) may move in as SMs free up
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -478,6 +482,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const std::uint32_t rank = ptx::ClusterCtaRank();      // 0: issues the MMAs
+  ptx::GridDependencyLaunch();   // what follows in the stream (the sum of the parts, the next call's pre-pass) may move in as SMs free up
   const int n0 = blockIdx.x * kPairRows;                 // blockIdx.x = 2 * pair + rank
   const int m0 = blockIdx.y * pp.tokens;
   const int half_tokens = pp.tokens / 2;
@@ -751,6 +756,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 __global__ void __launch_bounds__(256)
     nbits_split_k_sum_kernel(const float *partial, int parts, std::int64_t m, std::int64_t n, const float *bias,
                              OutputView out) {
+  ptx::GridDependencyLaunch();
+  ptx::GridDependencyWait();   // the partial products come from the kernel launched just before
   const std::int64_t total = m * n;
   for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
        i += static_cast<std::int64_t>(gridDim.x) * 256) {
@@ -772,6 +779,28 @@ int Log2Of(int v) {
     ++l;
   }
   return l;
+}
+
+// Launch with programmatic stream serialization: the kernel's blocks may become resident while the
+// kernel before it in the stream drains; it waits (griddepcontrol.wait) before it touches anything
+// that kernel wrote.
+template <typename Kernel, typename... Args>
+bool LaunchDependent(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, kernel, args...) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return true;
 }
 
 // Launch with programmatic stream serialization behind the activation pre-pass.
@@ -946,8 +975,8 @@ const char *LaunchPairBits(const WeightView &w, std::int64_t m, const std::uint1
     const std::int64_t total = m * w.n;
     std::int64_t blocks = (total + 255) / 256;
     blocks = blocks > static_cast<std::int64_t>(sms) * 8 ? static_cast<std::int64_t>(sms) * 8 : blocks;
-    nbits_split_k_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(partial, plan.parts, m, w.n, w.bias, out);
-    if (cudaGetLastError() != cudaSuccess) {
+    if (!LaunchDependent(nbits_split_k_sum_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,
+                         static_cast<const float *>(partial), plan.parts, m, w.n, w.bias, out)) {
       return nullptr;
     }
     CountLaunch();
@@ -998,9 +1027,8 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
     blocks = max_blocks;
   }
   const int sms = sm_count > 0 ? sm_count : 148;
-  nbits_a_to_bf16_kernel<<<blocks, 256, 0, stream>>>(a, m, w.k, reinterpret_cast<__nv_bfloat16 *>(a_bf16),
-                                                     w.bits == 4 ? 1 : 0);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchDependent(nbits_a_to_bf16_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, a, m, w.k,
+                       reinterpret_cast<__nv_bfloat16 *>(a_bf16), w.bits == 4 ? 1 : 0)) {
     return nullptr;
   }
   CountLaunch();
