@@ -4,8 +4,8 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 One JSON line on stdout (rank 0). Headline metric: effective HBM GB/s of the 4-bit decode
-GEMV at M=1 (algorithmic bytes / device time), with the M=2048 prefill TFLOP/s, the decode
-sweep, the roofline fractions and a timed CPU baseline in the same line.
+GEMV at M=1 (algorithmic bytes / device time), with the M=2048 and M=8192 prefill TFLOP/s, the
+decode sweep, the roofline fractions and a timed CPU baseline in the same line.
 
 N = 1   workload = the decode configuration the metric is quoted on: M=1, K=4096, N=14336,
         bits=4, block_size=128, zero points and bias. A step is one pass over R=8 distinct
