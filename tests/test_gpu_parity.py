@@ -627,6 +627,32 @@ def test_prefill_split_k(cuda_device, m, k, n, bs, zp, bias):
     assert rel_err(y, whole) <= 1e-5
 
 
+def test_prefill_kernels_agree_on_random_shapes(cuda_device):
+    """Forty seeded random shapes (4- and 8-bit, every block size, ragged M and N, 17 to 3000 tokens):
+    the pair kernel, whatever AUTO picks, and the 128-row kernel round the same way, so whole-K
+    products agree bit for bit and products with K shared between pairs up to the order of the
+    fp32 additions."""
+    rng = np.random.default_rng(20260)
+    for it in range(40):
+        bits = int(rng.choice([4, 4, 4, 8]))
+        bs = int(rng.choice([32, 64, 128, 256]))
+        k = int(rng.integers(1, 40)) * 64
+        k = -(-k // bs) * bs
+        n = int(rng.integers(1, 1400)) if rng.random() < 0.7 else int(rng.integers(1, 9)) * 512 + int(rng.integers(-3, 4))
+        m = int(rng.integers(17, 700)) if rng.random() < 0.8 else int(rng.integers(700, 3000))
+        zp, bias = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        case = syn.make_case("prefill_random", m, k, n, bits, bs, seed=3000 + it, zero_points=zp, bias=bias)
+        rows, name = run_device(case, path=_capi.PATH_TCGEN05)
+        assert name.startswith("nbits_gemm_tcgen05_kernel"), name
+        scale = float(np.abs(rows).max()) + 1e-30
+        for path in (_capi.PATH_TCGEN05_WIDE, _capi.PATH_AUTO):
+            y, kernel = run_device(case, path=path)
+            assert kernel.startswith("nbits_gemm_tcgen05"), kernel
+            assert not np.isnan(y).any(), (it, kernel)
+            tolerance = 2e-5 if kernel.endswith("(split-k)") else 0.0
+            assert float(np.abs(y - rows).max()) / scale <= tolerance, (it, m, k, n, bits, bs, kernel)
+
+
 def test_prefill_auto_dispatch_and_full_size_property(cuda_device):
     """cfg3 at full size M=2048: a checksum identity instead of a full CPU product. With A = ones
     the result is the per-column sum of the (bf16-rounded) dequantized weights."""
