@@ -191,6 +191,28 @@ __host__ __device__ inline int ActBytePosition(int k) {
   return ((k >> 7) << 7) + (t << 5) + (s << 3) + ((j & 1) ? 4 + (j >> 1) : (j >> 1));
 }
 
+// Launch with programmatic stream serialization: the kernel's blocks may become resident while the
+// kernel before it in the stream drains; it waits (griddepcontrol.wait) before it touches anything
+// that kernel wrote or still reads.
+template <typename Kernel, typename... Args>
+bool LaunchSerialized(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaLaunchKernelEx(&config, kernel, args...) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return true;
+}
+
 // Quantizes one pass layout: one warp per (token slot, table entry) over passes * tp slots and
 // the task-padded entry count. An entry covers min(block_size, 128) consecutive k: a whole
 // quantization block, or a 128-k part of a larger one (same scale, its own sum). Slots beyond
@@ -201,6 +223,9 @@ __global__ void __launch_bounds__(256)
                                  int passes, float table_scale, unsigned char *act) {
   // the multiply kernel behind this one may start (barrier set-up, first weight tiles) right away
   ptx::GridDependencyLaunch();
+  // launched with programmatic serialization itself: A and the scratch are touched once the kernel
+  // before this one in the stream (which may still read the scratch) has completed
+  ptx::GridDependencyWait();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const std::int64_t item = static_cast<std::int64_t>(blockIdx.x) * 8 + warp;
@@ -290,6 +315,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int m_base = blockIdx.y * p.tp;
+  // what follows in the stream (the next call's quantization) may be scheduled as SMs free up
+  ptx::GridDependencyLaunch();
 
   const int total_halves = p.set.halves_end[p.set.nodes - 1];
   const int h_begin = static_cast<int>(static_cast<std::int64_t>(blockIdx.x) * total_halves / gridDim.x);
@@ -710,10 +737,9 @@ const char *LaunchInt8Mma(const WeightView &w, const float *a, std::int64_t m, u
     return nullptr;
   }
   const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
-  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
-      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchSerialized(nbits_quantize_a_imma_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), stream, a,
+                        static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+                        geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch)) {
     return nullptr;
   }
   CountLaunch();
@@ -748,10 +774,9 @@ const char *LaunchInt8MmaGroup(const WeightView *nodes, const OutputView *outs, 
     }
   }
   const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
-  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
-      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchSerialized(nbits_quantize_a_imma_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), stream, a,
+                        static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+                        geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch)) {
     return nullptr;
   }
   CountLaunch();
@@ -783,10 +808,9 @@ const char *LaunchInt8MmaBlockDots(const WeightView &w, const float *a, std::int
     return nullptr;
   }
   const std::int64_t items = static_cast<std::int64_t>(geo.passes) * geo.tp * geo.entries_pad;
-  nbits_quantize_a_imma_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-      a, static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
-      geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchSerialized(nbits_quantize_a_imma_kernel, dim3(static_cast<unsigned>((items + 7) / 8)), dim3(256), stream, a,
+                        static_cast<int>(m), w.k, w.block_size, geo.entry_k, geo.entries_pad, geo.tp, geo.act_row_bytes,
+                        geo.table_offset, geo.pass_bytes, geo.passes, w.zp != nullptr ? 1.0f : 0.0625f, scratch)) {
     return nullptr;
   }
   CountLaunch();
@@ -1405,6 +1429,9 @@ __global__ void __launch_bounds__(256)
                               int slice_bytes, int table_ints, unsigned char *act) {
   // the product kernel behind this one may start (barrier set-up, first weight tiles) right away
   ptx::GridDependencyLaunch();
+  // launched with programmatic serialization itself: A and the scratch are touched once the kernel
+  // before this one in the stream has completed
+  ptx::GridDependencyWait();
   __shared__ float warp_max[8];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -1505,6 +1532,7 @@ __global__ void __launch_bounds__(256)
                                   std::int64_t n, const float *bias, OutputView out) {
   const std::int64_t total = static_cast<std::int64_t>(m_total) * n;
   const std::int64_t slice_stride = static_cast<std::int64_t>(tokens_pad) * n;
+  ptx::GridDependencyLaunch(); // what follows in the stream may be scheduled as SMs free up
   ptx::GridDependencyWait();   // the partial products come from the kernel before this one
   for (std::int64_t i = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
        i += static_cast<std::int64_t>(gridDim.x) * 256) {
@@ -1733,11 +1761,10 @@ const char *LaunchDigitSlicesGroup(const WeightView *nodes, const OutputView *ou
   float *factors = reinterpret_cast<float *>(scratch + AlignUp(geo.act_bytes));
   float *partial = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(factors) + AlignUp(3 * m * sizeof(float)));
   const unsigned parts = geo.entries_per_slice >= 32 ? 8u : 4u;
-  nbits_digit_slices_kernel<<<dim3(static_cast<unsigned>(8 * geo.ntok), static_cast<unsigned>(meta.slices), parts), 256,
-                              0, stream>>>(a, factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_per_slice,
-                                        geo.ntok, geo.act_row_bytes, geo.table_offset, geo.slice_bytes, geo.table_ints,
-                                        act);
-  if (cudaGetLastError() != cudaSuccess) {
+  if (!LaunchSerialized(nbits_digit_slices_kernel,
+                        dim3(static_cast<unsigned>(8 * geo.ntok), static_cast<unsigned>(meta.slices), parts), dim3(256),
+                        stream, a, factors, static_cast<int>(m), w.k, geo.entry_k, geo.entries_per_slice, geo.ntok,
+                        geo.act_row_bytes, geo.table_offset, geo.slice_bytes, geo.table_ints, act)) {
     return nullptr;
   }
   CountLaunch();
