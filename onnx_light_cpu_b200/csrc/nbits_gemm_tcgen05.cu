@@ -1040,7 +1040,11 @@ const char *LaunchGemmTcgen05(const WeightView &w, const float *a, std::int64_t 
       float *partial = reinterpret_cast<float *>(
           reinterpret_cast<unsigned char *>(a_bf16) +
           AlignScratch(static_cast<std::size_t>(m) * static_cast<std::size_t>(w.k) * 2));
-      return LaunchPair(w, m, a_bf16, out, status_word, stream, sms, partial, plan);
+      const char *name = LaunchPair(w, m, a_bf16, out, status_word, stream, sms, partial, plan);
+      if (name != nullptr) {
+        return name;
+      }
+      cudaGetLastError();   // a cluster launch that the device refuses: the 128-row kernel takes the product
     }
   }
   // otherwise the widest token tile that still gives every SM a tile
