@@ -272,6 +272,9 @@ __global__ void __launch_bounds__(32 * MNB_MAX_GATHER_WAITS) nbits_gather_wait_k
 __global__ void __launch_bounds__(256)
     nbits_gather_push_kernel(mnb::OutputView out, std::int64_t m, std::int64_t n, int vector, mnb::GatherTail tail,
                              int *status) {
+  // launched with programmatic stream serialization behind the kernels of the product: its blocks
+  // may be resident early, the window is read once those kernels have completed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const std::int64_t stride = static_cast<std::int64_t>(gridDim.x) * 256;
   const std::int64_t first = static_cast<std::int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (vector != 0) {
@@ -1102,9 +1105,18 @@ int mnb_matmul_device_gather_ex(mnb_weights *h, const float *a_dev, int64_t m, i
     const std::int64_t most = 2 * static_cast<std::int64_t>(h->sm_count > 0 ? h->sm_count : 148);
     blocks = blocks > most ? most : (blocks < 1 ? 1 : blocks);
     tail.wait = wait != 0 ? 1 : 0;
-    nbits_gather_push_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(out, m, w.n, vector ? 1 : 0, tail,
-                                                                               h->status_dev);
-    const cudaError_t launch_err = cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+    config.blockDim = dim3(256, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    const cudaError_t launch_err = cudaLaunchKernelEx(&config, nbits_gather_push_kernel, out, static_cast<std::int64_t>(m),
+                                                      static_cast<std::int64_t>(w.n), vector ? 1 : 0, tail, h->status_dev);
     if (launch_err != cudaSuccess) {
       return FailCuda("launch of the gather push kernel", launch_err);
     }
