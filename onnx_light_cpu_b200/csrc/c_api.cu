@@ -1078,7 +1078,14 @@ int mnb_matmul_device_gather_ex(mnb_weights *h, const float *a_dev, int64_t m, i
     // The tensor-core decode kernels push each CTA's rows to the peers as the CTA finishes, and the
     // last CTA to finish publishes the flags: one launch per node, no pass over the result.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m > per_pass) {
+    if (m == 1 && mnb::DecodeResidentSupports(w, m)) {
+      // one token: the kernel that asks for each SM's whole share of the weights at its start
+      name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &fused_tail);
+      if (name == nullptr) {
+        cudaGetLastError();
+      }
+    }
+    if (name == nullptr && m > per_pass) {
       name = mnb::LaunchGemvMmaMulti(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &fused_tail);
     }
     if (name == nullptr) {

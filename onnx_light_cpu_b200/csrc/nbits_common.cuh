@@ -271,14 +271,17 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
 
 // Decode of one token with the CTA's whole share of the packed weights asked for at kernel start
 // (TMA copies issued by a producer warp into shared-memory slots that are normally written once).
+// block_size 128 or 32. `tail` (single node): the CTAs push their rows to the peers of a gathered
+// step and the last one publishes the flags.
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
-                                 cudaStream_t stream, int sm_count);
+                                 cudaStream_t stream, int sm_count, const GatherTail *tail = nullptr);
 // Up to kMaxGroupedNodes nodes that take the same activations (same K, zero points in all or in
 // none) in one launch; nullptr when the group has no such kernel.
 bool DecodeResidentGroupSupports(const WeightView *nodes, int count, std::int64_t m);
 const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
-                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count);
+                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count,
+                                      const GatherTail *tail = nullptr);
 // Drops the launch plans (tensor maps, slot shapes) cached for a node whose weights are going away.
 void ForgetDecodeResidentPlans(const WeightView &w);
 

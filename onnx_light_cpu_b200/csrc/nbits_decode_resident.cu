@@ -82,6 +82,7 @@ struct ResidentParams {
   int early_groups;     // first-round group tasks the producer asks for before the consumers have asked for A
   int segs;             // 128-k segments per weight row
   int table_ints;
+  GatherTail tail;      // gathered step (ranks > 0, single node): rows pushed to the peers, flags by the last CTA
 };
 
 __device__ __forceinline__ void TmaLoadBox3D(std::uint32_t smem_dst, const void *tensor_map, int x, int y, int z,
@@ -151,7 +152,20 @@ struct GroupPlace {
   int count;
 };
 
-template <bool HAS_ZP>
+__device__ __forceinline__ void LoadMatrixX4(std::uint32_t addr, std::uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// BPS: quantization blocks per 128-k segment: 1 (block_size 128) or 4 (block_size 32). With four,
+// an MMA covers one 32-k block of a row's even segment (MMA rows 0-7) and of its odd segment (rows
+// 8-15): ldmatrix hands lane t of a quad word t of each 16-byte unit (= block) of the row, the low
+// nibbles of that word fill k slots 4t.. and the high nibbles slots 16 + 4t.., the staged digits are
+// kept block by block in the same order, and every block's exact int32 sums leave through its own
+// scale and zero point. Scales arrive as 128-byte-swizzled boxes of four steps (eight rows read by
+// a quarter warp fall on different banks), zero-point bytes as plain rows.
+template <bool HAS_ZP, int BPS>
 __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
     nbits_decode_resident_kernel(const __grid_constant__ ResidentMaps maps, const ResidentParams p) {
   const int G = p.group_tiles;
@@ -163,8 +177,10 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   const int slots = groups * p.slots_per_group;
   const int steps = p.steps_per_task;
   const int weight_tile_bytes = steps * kChunkRowsBytes;      // [chunk][8 rows][128 B] per tile
-  const int scale_tile_bytes = steps * 64;                    // [8 rows][2 segments per step] floats
-  const int zero_tile_bytes = HAS_ZP ? steps * 16 : 0;        // [8 rows][2 segments per step] bytes
+  const int scale_tile_bytes = steps * 64 * BPS;              // [8 rows][2 segments per step][BPS] floats
+  // zero points: [8 rows][2 segments per step] prepared bytes, or (blocks of 32) the operator's own
+  // packed nibbles, [8 rows][8 blocks per step] = four bytes per row and step
+  const int zero_tile_bytes = HAS_ZP ? (BPS == 1 ? steps * 16 : steps * 32) : 0;
   const int weight_slot_bytes = G * weight_tile_bytes;        // a slot holds the G tiles of a group, tile-major
   const int scale_slot_bytes = G * scale_tile_bytes;
   const int zero_slot_bytes = G * zero_tile_bytes;
@@ -254,18 +270,28 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         if (count == G && p.node[at.node].group_boxes != 0) {
           // the whole group in one copy per operand
           TmaLoadBox4D(w_at, &node_maps.w_group, 0, 0, part * steps, tile0, &full_bar[slot]);
-          TmaLoadBox2D(s_at, &node_maps.s_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
+          if constexpr (BPS == 1) {
+            TmaLoadBox2D(s_at, &node_maps.s_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
+          } else {
+            TmaLoadBox4D(s_at, &node_maps.s_group, 0, 0, part * steps / 4, tile0, &full_bar[slot]);
+          }
           if constexpr (HAS_ZP) {
-            TmaLoadBox2D(z_at, &node_maps.z_group, part * steps * 2, tile0 * 8, &full_bar[slot]);
+            TmaLoadBox2D(z_at, &node_maps.z_group, BPS == 1 ? part * steps * 2 : part * steps * 4, tile0 * 8,
+                         &full_bar[slot]);
           }
         } else {
           // a short group (the end of this CTA's range): tile by tile, same places in the slot
           for (int i = 0; i < count; ++i) {
             const int row0 = (tile0 + i) * 8;
             TmaLoadBox3D(w_at + i * weight_tile_bytes, &node_maps.w_tile, 0, row0, part * steps, &full_bar[slot]);
-            TmaLoadBox2D(s_at + i * scale_tile_bytes, &node_maps.s_tile, part * steps * 2, row0, &full_bar[slot]);
+            if constexpr (BPS == 1) {
+              TmaLoadBox2D(s_at + i * scale_tile_bytes, &node_maps.s_tile, part * steps * 2, row0, &full_bar[slot]);
+            } else {
+              TmaLoadBox3D(s_at + i * scale_tile_bytes, &node_maps.s_tile, 0, row0, part * steps / 4, &full_bar[slot]);
+            }
             if constexpr (HAS_ZP) {
-              TmaLoadBox2D(z_at + i * zero_tile_bytes, &node_maps.z_tile, part * steps * 2, row0, &full_bar[slot]);
+              TmaLoadBox2D(z_at + i * zero_tile_bytes, &node_maps.z_tile,
+                           BPS == 1 ? part * steps * 2 : part * steps * 4, row0, &full_bar[slot]);
             }
           }
         }
@@ -323,7 +349,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   // consumers depend on it. The producer above only touches the constant weights.
   ptx::GridDependencyWait();
   const DigitGeometry geometry{p.k, p.segs, kDigits * kChunkBytes, p.table_ints};
-  StageDigits<true>(
+  StageDigits<true, BPS == 4>(
       geometry, p.a, 1, 1, digits, table, undo, red, tid, consumer_threads,
       [&] { asm volatile("bar.sync 1, %0;" ::"r"(consumer_threads) : "memory"); },
       [&] { asm volatile("bar.arrive 3, %0;" ::"r"(consumer_threads + 32) : "memory"); });
@@ -334,6 +360,147 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   const int t = lane & 3;
   const int group = warp / G;
   const int member = warp - group * G;  // which tile of the group's box this warp works on
+  // Gathered step: the arithmetic stores locally only; once all consumer warps of the CTA are done,
+  // the rows of its tile groups go to the same place of every peer's buffer and the CTA counts
+  // itself in; the last CTA of the grid publishes this rank's flags.
+  auto finish_gathered_step = [&]() {
+    if (p.tail.ranks <= 0) {
+      return;
+    }
+    asm volatile("bar.sync 4, %0;" ::"r"(consumer_threads) : "memory");
+    const ResidentNode &node = p.node[0];
+    for (int local_group = 0; local_group < my_groups; ++local_group) {
+      const GroupPlace at = place_of(local_group);
+      const std::int64_t row0 = static_cast<std::int64_t>(at.tile0) * 8;
+      std::int64_t row1 = row0 + static_cast<std::int64_t>(at.count) * 8;
+      row1 = row1 < node.w.n ? row1 : node.w.n;
+      if (row1 > row0) {
+        PushRowsToPeers(node.out, p.tail, 0, 1, row0, row1, tid, consumer_threads);
+      }
+    }
+    PublishWhenGridDone(p.tail, tid, consumer_threads, 4, gridDim.x, p.status);
+  };
+  if constexpr (BPS == 4) {
+    // ---- blocks of 32: one MMA per block, MMA row g = row g of the tile ----
+    const int matrix = lane >> 3;  // ldmatrix: this lane names row (lane & 7) of matrix (lane >> 3) = unit of the segment
+    const int mrow = lane & 7;
+    const std::uint32_t lo_lane = member * weight_tile_bytes + mrow * 128 + ((matrix ^ mrow) << 4);
+    const std::uint32_t hi_lane = member * weight_tile_bytes + mrow * 128 + (((4 + matrix) ^ mrow) << 4);
+    const int column = g < 6 ? g : g - 4;  // MMA columns 6 and 7 are not used: they read columns 2 and 3 again
+    const std::uint32_t digits_lane = LaunderAfterBarrier(ptx::SmemAddr(digits) + column * 32 + t * 8);
+    const std::uint32_t table_lane = LaunderAfterBarrier(ptx::SmemAddr(table) + t * 8);
+    const std::uint32_t weights_group = ptx::SmemAddr(weight_slots) + group * p.slots_per_group * weight_slot_bytes;
+    const std::uint32_t scales_row = ptx::SmemAddr(scale_slots) + group * p.slots_per_group * scale_slot_bytes +
+                                     member * scale_tile_bytes + g * 128;
+    const std::uint32_t zeros_row = ptx::SmemAddr(zero_slots) + group * p.slots_per_group * zero_slot_bytes +
+                                    member * zero_tile_bytes + g * (steps * 4);
+    const int supers = steps / kStepsPerSuper;
+    const ZeroQuad zero = MakeZeroQuad();
+    int q = 0;  // this group's task counter
+    for (int round = 0; round < rounds; ++round) {
+      const int local_group = round * groups + group;
+      if (local_group >= my_groups) {
+        break;
+      }
+      const GroupPlace at = place_of(local_group);
+      const bool has_tile = member < at.count;
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      bool dead = false;
+      for (int part = 0; part < p.parts; ++part, ++q) {
+        const int d = q % p.slots_per_group;
+        const int slot = group * p.slots_per_group + d;
+        if (!dead && !ptx::MbarWait(&full_bar[slot], static_cast<std::uint32_t>(q / p.slots_per_group) & 1u)) {
+          ReportStatus(p.status, kDeviceTimeoutFullBarrier);
+          dead = true;
+        }
+        if (dead) {
+          continue;
+        }
+        if (has_tile) {
+          std::uint32_t lo_at = weights_group + d * weight_slot_bytes + lo_lane;
+          std::uint32_t hi_at = weights_group + d * weight_slot_bytes + hi_lane;
+          std::uint32_t scales_at = scales_row + d * scale_slot_bytes;
+          std::uint32_t zeros_at = zeros_row + d * zero_slot_bytes;
+          std::uint32_t digits_at = digits_lane + part * steps * (4 * kBlock32Bytes);
+          std::uint32_t table_at = table_lane + part * steps * (4 * 32);
+#pragma unroll 1
+          for (int super = 0; super < supers; ++super) {
+            uint4 z_super = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (HAS_ZP) {
+              z_super = LoadSlot16At(zeros_at);  // one word per step: the nibbles of its eight blocks, in k order
+            }
+            auto do_step = [&](auto step_tag) {
+              constexpr int i = decltype(step_tag)::value;
+              std::uint32_t lo[4], hi[4];
+              LoadMatrixX4(lo_at + i * kChunkRowsBytes, lo);
+              LoadMatrixX4(hi_at + i * kChunkRowsBytes, hi);
+              // scales of the four blocks of the even segment and of the odd one (16-byte units 2i and
+              // 2i + 1 of the row's 128 bytes, swizzled with the row)
+              const uint4 u_lo = LoadSlot16At(scales_at + (((2 * i) ^ g) << 4));
+              const uint4 u_hi = LoadSlot16At(scales_at + (((2 * i + 1) ^ g) << 4));
+              const std::uint32_t s_lo_bits[4] = {u_lo.x, u_lo.y, u_lo.z, u_lo.w};
+              const std::uint32_t s_hi_bits[4] = {u_hi.x, u_hi.y, u_hi.z, u_hi.w};
+              const std::uint32_t z_word = i == 0 ? z_super.x : (i == 1 ? z_super.y : (i == 2 ? z_super.z : z_super.w));
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const std::uint32_t a0 = lo[u] & 0x0f0f0f0fu;
+                const std::uint32_t a1 = hi[u] & 0x0f0f0f0fu;
+                const std::uint32_t a2 = (lo[u] >> 4) & 0x0f0f0f0fu;
+                const std::uint32_t a3 = (hi[u] >> 4) & 0x0f0f0f0fu;
+                const uint2 b = LoadSlot8At(digits_at + (i * 4 + u) * kBlock32Bytes);
+                const uint2 sums_bits = LoadSlot8At(table_at + (i * 4 + u) * 32);
+                const int sums_x = static_cast<int>(sums_bits.x);
+                const int sums_y = static_cast<int>(sums_bits.y);
+                int dot[4];
+                ImmaFresh(dot, a0, a1, a2, a3, b.x, b.y, zero);
+                int z_lo = 8, z_hi = 8;
+                if constexpr (HAS_ZP) {
+                  z_lo = static_cast<int>((z_word >> (4 * u)) & 0xfu);
+                  z_hi = static_cast<int>((z_word >> (16 + 4 * u)) & 0xfu);
+                }
+                // block sum - zp * digit sum: exact (the table holds -sum); times 16 with the scale,
+                // because the row's factor takes a sixteenth out again
+                const float s_lo = __uint_as_float(s_lo_bits[u]) * 16.0f;
+                const float s_hi = __uint_as_float(s_hi_bits[u]) * 16.0f;
+                acc[0] = fmaf(s_lo, static_cast<float>(z_lo * sums_x + dot[0]), acc[0]);
+                acc[1] = fmaf(s_lo, static_cast<float>(z_lo * sums_y + dot[1]), acc[1]);
+                acc[2] = fmaf(s_hi, static_cast<float>(z_hi * sums_x + dot[2]), acc[2]);
+                acc[3] = fmaf(s_hi, static_cast<float>(z_hi * sums_y + dot[3]), acc[3]);
+              }
+            };
+            ForEachIndex<kStepsPerSuper>(do_step);
+            lo_at += kStepsPerSuper * kChunkRowsBytes;
+            hi_at += kStepsPerSuper * kChunkRowsBytes;
+            scales_at += 1024;
+            zeros_at += kStepsPerSuper * 4;
+            digits_at += kStepsPerSuper * 4 * kBlock32Bytes;
+            table_at += kStepsPerSuper * 4 * 32;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          ptx::MbarArrive(&empty_bar[slot]);
+        }
+      }
+      if (!has_tile) {
+        continue;
+      }
+      float v = t == 0   ? fmaf(16384.0f, acc[0], 128.0f * acc[1])
+                : t == 1 ? fmaf(16384.0f, acc[3], acc[0])
+                : t == 2 ? fmaf(128.0f, acc[2], acc[3])
+                         : 0.0f;
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      const ResidentNode &node = p.node[at.node];
+      const std::int64_t row = static_cast<std::int64_t>(at.tile0 + member) * 8 + g;
+      if (!dead && t == 0 && row < node.w.n) {
+        const float bias = node.w.bias != nullptr ? __ldg(node.w.bias + row) : 0.0f;
+        StoreOutput(node.out, node.out.col_offset + row, fmaf(v, undo[0], bias));
+      }
+    }
+    finish_gathered_step();
+    return;
+  }
   // MMA row g is row `rho` of the tile: the two rows a quarter warp reads together then differ in
   // bit 2, and the 128-byte swizzle (16-byte unit ^ row) puts them on different halves of the banks
   const int rho = ((g & 1) << 2) | (g >> 1);
@@ -471,6 +638,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       StoreOutput(node.out, node.out.col_offset + row, fmaf(v, undo[0], bias));
     }
   }
+  finish_gathered_step();
 }
 
 bool EncodeWeightTileMap(CUtensorMap *map, const WeightView &w, int steps) {
@@ -504,11 +672,49 @@ bool EncodeWeightGroupMap(CUtensorMap *map, const WeightView &w, int steps, int 
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Scales of a node with blocks of 32: a row's scales seen as [chunks of 32][32 floats] (= four MMA
+// steps), fetched like the weights in 128-byte-swizzled boxes of eight rows.
+bool EncodeScaleTileMap32(CUtensorMap *map, const WeightView &w, int steps) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr) {
+    return false;
+  }
+  const cuuint64_t dims[3] = {32, static_cast<cuuint64_t>(w.n), static_cast<cuuint64_t>(w.n_blocks / 32)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(w.n_blocks) * 4, 128};
+  const cuuint32_t box[3] = {32, 8, static_cast<cuuint32_t>(steps / 4)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(w.scales), dims, strides, box,
+                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool EncodeScaleGroupMap32(CUtensorMap *map, const WeightView &w, int steps, int tiles_per_box) {
+  EncodeTiledFn encode = GetEncodeTiled();
+  if (encode == nullptr || (w.n % 8) != 0) {
+    return false;
+  }
+  const cuuint64_t row = static_cast<cuuint64_t>(w.n_blocks) * 4;
+  const cuuint64_t dims[4] = {32, 8, static_cast<cuuint64_t>(w.n_blocks / 32), static_cast<cuuint64_t>(w.n / 8)};
+  const cuuint64_t strides[3] = {row, 128, row * 8};
+  const cuuint32_t box[4] = {32, 8, static_cast<cuuint32_t>(steps / 4), static_cast<cuuint32_t>(tiles_per_box)};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(w.scales), dims, strides, box,
+                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 } // namespace
 
-// One token, 4-bit, block_size 128, whole 128-byte chunks per row in multiples of four (K a
-// multiple of 1024; of 2048 with zero points, whose prepared bytes must exist).
+// One token, 4-bit, block_size 128 or 32, whole 128-byte chunks per row in multiples of four (K a
+// multiple of 1024; of 2048 with zero points and block_size 128, whose prepared bytes must exist).
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m) {
+  if (m == 1 && w.bits == 4 && w.block_size == 32) {
+    // zero points come straight from the operator's packed nibbles: K / 64 bytes per row
+    return (w.k % 1024) == 0 && w.n_blocks * 32 == w.k &&
+           (w.zp == nullptr || (w.zp_row_bytes * 2 == w.n_blocks && (reinterpret_cast<std::uintptr_t>(w.zp) & 15u) == 0)) &&
+           (reinterpret_cast<std::uintptr_t>(w.b) & 15u) == 0 && (reinterpret_cast<std::uintptr_t>(w.scales) & 15u) == 0 &&
+           w.n < (std::int64_t{1} << 31);
+  }
   return m == 1 && w.bits == 4 && w.block_size == 128 && (w.n_blocks % (2 * kStepsPerSuper)) == 0 &&
          (w.zp == nullptr || (w.zp16 != nullptr && (w.n_blocks % 16) == 0)) &&
          (reinterpret_cast<std::uintptr_t>(w.b) & 15u) == 0 &&
@@ -559,8 +765,9 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
   const WeightView &w = nodes[0];  // K, block size and the presence of zero points are the group's
   p.nodes = count;
   p.k = static_cast<int>(w.k);
-  p.segs = w.n_blocks;
-  p.table_ints = (p.segs / 2) * 8;
+  const int bps = 128 / w.block_size;  // quantization blocks per 128-k segment: 1 or 4
+  p.segs = static_cast<int>((w.k + 127) / 128);  // the last one may be part padding (block_size 128 only)
+  p.table_ints = (p.segs / 2) * 8 * bps;
   std::int64_t tiles = 0;
   for (int i = 0; i < count; ++i) {
     p.node[i].w = nodes[i];
@@ -576,8 +783,9 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
                        (kMaxTokens + kMaxTokens * kMaxWarps) * sizeof(float) +
                        2 * kMaxGroupSlots * sizeof(std::uint64_t) + 1024;  // + alignment slack
   const size_t limit = 227 * 1024;
-  const size_t per_step = kChunkRowsBytes + 64 + (w.zp != nullptr ? 16 : 0);  // per tile and chunk
-  const int min_steps = w.zp != nullptr ? 8 : 4;  // the zero-point box needs 16 bytes per row
+  // per tile and chunk: weights, scales, zero points (prepared bytes, or packed nibbles with blocks of 32)
+  const size_t per_step = kChunkRowsBytes + 64 * bps + (w.zp != nullptr ? (bps == 1 ? 16 : 32) : 0);
+  const int min_steps = (w.zp != nullptr && bps == 1) ? 8 : 4;  // the zero-point box needs 16 bytes per row
   auto fits = [&](int warps, int slots, int s) {
     return fixed + static_cast<size_t>(warps) * slots * s * per_step <= limit;
   };
@@ -655,6 +863,12 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
       maps.w_group = maps.w_tile;
     }
     auto rows_map = [&](CUtensorMap *map, bool zero_points, int rows) {
+      if (zero_points && bps == 4) {
+        return EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, node.zp, static_cast<std::uint64_t>(node.zp_row_bytes),
+                           static_cast<std::uint64_t>(node.n), static_cast<std::uint64_t>(node.zp_row_bytes),
+                           static_cast<std::uint32_t>(4 * steps), static_cast<std::uint32_t>(rows),
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+      }
       return zero_points
                  ? EncodeMap2D(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, node.zp16,
                                static_cast<std::uint64_t>(node.n_blocks), static_cast<std::uint64_t>(node.n),
@@ -665,7 +879,16 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
                                static_cast<std::uint64_t>(node.n_blocks) * 4, static_cast<std::uint32_t>(2 * steps),
                                static_cast<std::uint32_t>(rows), CU_TENSOR_MAP_SWIZZLE_NONE);
     };
-    if (!rows_map(&maps.s_tile, false, 8) || !rows_map(&maps.s_group, false, 8 * group_tiles)) {
+    if (bps == 4) {
+      if (!EncodeScaleTileMap32(&maps.s_tile, node, steps)) {
+        return false;
+      }
+      if (p.node[i].group_boxes == 0 || !EncodeScaleGroupMap32(&maps.s_group, node, steps, group_tiles)) {
+        p.node[i].group_boxes = 0;
+        maps.w_group = maps.w_tile;
+        maps.s_group = maps.s_tile;
+      }
+    } else if (!rows_map(&maps.s_tile, false, 8) || !rows_map(&maps.s_group, false, 8 * group_tiles)) {
       return false;
     }
     maps.z_tile = maps.s_tile;
@@ -682,10 +905,16 @@ bool BuildPlan(const WeightView *nodes, int count, int sms, ResidentPlan *plan) 
   // The function attribute belongs to the kernel, not to the node: it is raised to the most any
   // plan can ask for, so that plans of different sizes do not undo one another.
   const int most = static_cast<int>(limit);
-  const cudaError_t err =
-      w.zp != nullptr
-          ? cudaFuncSetAttribute(nbits_decode_resident_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most)
-          : cudaFuncSetAttribute(nbits_decode_resident_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+  cudaError_t err = cudaErrorInvalidValue;
+  if (bps == 4) {
+    err = w.zp != nullptr
+              ? cudaFuncSetAttribute(nbits_decode_resident_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most)
+              : cudaFuncSetAttribute(nbits_decode_resident_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+  } else {
+    err = w.zp != nullptr
+              ? cudaFuncSetAttribute(nbits_decode_resident_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most)
+              : cudaFuncSetAttribute(nbits_decode_resident_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+  }
   return err == cudaSuccess;
 }
 
@@ -739,7 +968,7 @@ bool DecodeResidentGroupSupports(const WeightView *nodes, int count, std::int64_
     return false;
   }
   for (int i = 0; i < count; ++i) {
-    if (!DecodeResidentSupports(nodes[i], m) || nodes[i].k != nodes[0].k ||
+    if (!DecodeResidentSupports(nodes[i], m) || nodes[i].k != nodes[0].k || nodes[i].block_size != nodes[0].block_size ||
         (nodes[i].zp != nullptr) != (nodes[0].zp != nullptr)) {
       return false;
     }
@@ -748,8 +977,9 @@ bool DecodeResidentGroupSupports(const WeightView *nodes, int count, std::int64_
 }
 
 const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView *outs, int count, const float *a,
-                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count) {
-  if (!DecodeResidentGroupSupports(nodes, count, m)) {
+                                      std::int64_t m, int *status_word, cudaStream_t stream, int sm_count,
+                                      const GatherTail *tail) {
+  if (!DecodeResidentGroupSupports(nodes, count, m) || (tail != nullptr && count != 1)) {
     return nullptr;
   }
   const ResidentPlan *plan = PlanFor(nodes, count, sm_count > 0 ? sm_count : 148);
@@ -764,6 +994,7 @@ const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView 
   }
   p.a = a;
   p.status = status_word;
+  p.tail = tail != nullptr ? *tail : GatherTail{};
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(plan->ctas), 1, 1);
   config.blockDim = dim3(static_cast<unsigned>(plan->threads), 1, 1);
@@ -774,9 +1005,14 @@ const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView 
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  const cudaError_t err = nodes[0].zp != nullptr
-                              ? cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<true>, plan->maps, p)
-                              : cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<false>, plan->maps, p);
+  cudaError_t err = cudaErrorInvalidValue;
+  if (nodes[0].block_size == 32) {
+    err = nodes[0].zp != nullptr ? cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<true, 4>, plan->maps, p)
+                                 : cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<false, 4>, plan->maps, p);
+  } else {
+    err = nodes[0].zp != nullptr ? cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<true, 1>, plan->maps, p)
+                                 : cudaLaunchKernelEx(&config, nbits_decode_resident_kernel<false, 1>, plan->maps, p);
+  }
   if (err != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
@@ -786,8 +1022,8 @@ const char *LaunchDecodeResidentGroup(const WeightView *nodes, const OutputView 
 }
 
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
-                                 cudaStream_t stream, int sm_count) {
-  return LaunchDecodeResidentGroup(&w, &out, 1, a, m, status_word, stream, sm_count);
+                                 cudaStream_t stream, int sm_count, const GatherTail *tail) {
+  return LaunchDecodeResidentGroup(&w, &out, 1, a, m, status_word, stream, sm_count, tail);
 }
 
 } // namespace mnb

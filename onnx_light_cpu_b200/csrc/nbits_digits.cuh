@@ -117,7 +117,15 @@ __device__ __forceinline__ int ChunkOffset(int seg, int token, int digit, int ch
 // the balanced digits of n plus 64, 64 and 128. One fused multiply-add and one conversion per
 // value; u << 1 and u << 2 put the middle and high digit on byte boundaries.
 // sums[d] receives the sum of the eight digits d.
-template <bool ROWPAIR>
+//
+// BLOCK32 (row-pair mode, quantization blocks of 32): the digits are kept block by block instead,
+// for MMAs that take one 32-k block each. A block is four words; (step, block u of the segment,
+// MMA column c = 3 * (segment & 1) + digit, word t) holds eight bytes: the digits of the word's four
+// even k, then of its four odd k, which is what lane t of a quad feeds into k slots 4t.. and
+// 16 + 4t.. of the MMA. 192 bytes per (step, u).
+constexpr int kBlock32Bytes = 6 * 32;
+
+template <bool ROWPAIR, bool BLOCK32 = false>
 __device__ __forceinline__ void ConvertWord(const float (&x)[8], float lift, float up, int word, int token,
                                             unsigned char *digits, int chunk_stride, int (&sums)[kDigits]) {
   std::uint32_t u0[8], u1[8], u2[8];
@@ -148,6 +156,14 @@ __device__ __forceinline__ void ConvertWord(const float (&x)[8], float lift, flo
   const int seg = word >> 4;
   const int quad_lane = (word >> 2) & 3;
   const int word_in_lane = word & 3;
+  if constexpr (BLOCK32) {
+    unsigned char *at = digits + ((seg >> 1) * 4 + quad_lane) * kBlock32Bytes + (seg & 1) * kDigits * 32 + word_in_lane * 8;
+#pragma unroll
+    for (int d = 0; d < kDigits; ++d) {
+      *reinterpret_cast<uint2 *>(at + d * 32) = make_uint2(packed[d][0], packed[d][1]);
+    }
+    return;
+  }
   // the three chunks of a (segment, token) are 128 bytes apart and their swizzle bits alternate
   int swizzle;
   unsigned char *chunk = digits + ChunkOffset<ROWPAIR>(seg, token, 0, chunk_stride, &swizzle);
@@ -195,7 +211,7 @@ struct DigitGeometry {
   int table_ints;    // ints of the digit-sum table
 };
 
-template <bool ROWPAIR, typename Sync, typename IssueRest>
+template <bool ROWPAIR, bool BLOCK32 = false, typename Sync, typename IssueRest>
 __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const float *a_rows, int tokens,
                                             int column_tiles, unsigned char *digits, int *table, float *undo,
                                             float *red, int tid, int threads, Sync &&sync, IssueRest &&issue_rest) {
@@ -276,7 +292,25 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
       const bool valid = word < words_pad;  // the same for the sixteen lanes of a segment
       int sums[kDigits] = {0, 0, 0};
       if (valid) {
-        ConvertWord<ROWPAIR>(held[j], lift, up, word, 0, digits, geo.chunk_stride, sums);
+        ConvertWord<ROWPAIR, BLOCK32>(held[j], lift, up, word, 0, digits, geo.chunk_stride, sums);
+      }
+      if constexpr (BLOCK32) {
+        // a 32-k block is four words = four neighbouring lanes
+#pragma unroll
+        for (int offset = 2; offset > 0; offset >>= 1) {
+#pragma unroll
+          for (int d = 0; d < kDigits; ++d) {
+            sums[d] += __shfl_xor_sync(0xffffffffu, sums[d], offset);
+          }
+        }
+        if (valid && (lane & 3) == 0) {
+          const int seg = word >> 4;
+          int *entry = table + ((seg >> 1) * 4 + ((word >> 2) & 3)) * 8 + (seg & 1) * kDigits;
+          entry[0] = -sums[0];
+          entry[1] = -sums[1];
+          entry[2] = -sums[2];
+        }
+        continue;
       }
 #pragma unroll
       for (int offset = 8; offset > 0; offset >>= 1) {
@@ -333,7 +367,7 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
         float x[8];
         load_word(src, word, x);
         int unused[kDigits];
-        ConvertWord<ROWPAIR>(x, lift, up, word, token, digits, geo.chunk_stride, unused);
+        ConvertWord<ROWPAIR, BLOCK32>(x, lift, up, word, token, digits, geo.chunk_stride, unused);
       }
     }
   }
@@ -342,6 +376,23 @@ __device__ __forceinline__ void StageDigits(const DigitGeometry &geo, const floa
   // that step (0 for the unused columns)
   for (int entry = tid; entry < geo.table_ints; entry += threads) {
     const int column = entry & 7;
+    if constexpr (BLOCK32) {
+      // entry ((step, u), column): the 32 digits of that block and column
+      int sum = 0;
+      if (column < 2 * kDigits) {
+        const uint4 *bytes = reinterpret_cast<const uint4 *>(digits + (entry >> 3) * kBlock32Bytes + column * 32);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint4 q = bytes[i];
+          sum = __dp4a(static_cast<int>(q.x), 0x01010101, sum);
+          sum = __dp4a(static_cast<int>(q.y), 0x01010101, sum);
+          sum = __dp4a(static_cast<int>(q.z), 0x01010101, sum);
+          sum = __dp4a(static_cast<int>(q.w), 0x01010101, sum);
+        }
+      }
+      table[entry] = -sum;
+      continue;
+    }
     int seg, token, digit;
     bool used = column < 2 * kDigits;
     digit = column % kDigits;

@@ -48,6 +48,8 @@ RESIDENT = "nbits_decode_resident_kernel"
 def resident_takes(case):
     """Shapes AUTO sends to the one-token kernel that asks for all of its weights at kernel start."""
     blocks = -(-case.k // case.block_size)
+    if case.bits == 4 and case.block_size == 32 and case.m == 1:
+        return case.k % 1024 == 0      # blocks of 32: whole chunks of 32 scales per row
     return (case.bits == 4 and case.block_size == 128 and case.m == 1 and blocks % 8 == 0 and
             (case.zero_points is None or blocks % 16 == 0))
 
@@ -92,9 +94,12 @@ def test_dequant_integers_bit_exact(cuda_device, bits, bs, k, n, zp):
 def test_config1_single_node(cuda_device):
     case = syn.config1()
     y, kernel = run_device(case)
-    assert kernel == "nbits_gemv_mma_kernel", kernel
+    assert kernel == RESIDENT, kernel      # one token, blocks of 32: one integer MMA per block
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, None, None, case.n, case.k, 4, 32)) <= TOL_FP32
+    y1, kernel1 = run_device(case, path=_capi.PATH_GEMV_MMA)
+    assert kernel1 == "nbits_gemv_mma_kernel", kernel1
+    assert rel_err(y1, oracle_f64(case)) <= TOL_FP32
     y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
     assert kernel2.startswith("nbits_gemv_stream_kernel<4,1,"), kernel2
     assert rel_err(y2, oracle_f64(case)) <= TOL_FP32
@@ -357,6 +362,55 @@ def test_decode_resident_path(cuda_device, k, n, zp, bias):
     assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
     y_direct, _ = run_device(case, path=_capi.PATH_GEMV_DIRECT)   # same digits, same block sums
     assert rel_err(y, y_direct) <= 1e-6
+
+
+# the same kernel with blocks of 32 (one MMA per block): (k, n, zp, bias)
+RESIDENT_BLOCK32_CASES = [
+    (4096, 96, True, True),          # zero points straight from the operator's packed nibbles
+    (4096, 77, False, False),        # ragged last tile, default zero point
+    (1024, 50, False, True),         # one chunk of 32 scales per row
+    (2048, 8, True, False),          # a single tile
+    (3072, 272, True, True),         # three chunks of scales per row
+    (8192, 520, False, True),        # wide K: tasks of part of a row
+    (4096, 1001, False, False),      # N not a multiple of eight: tile by tile copies
+    (4096, 4096, False, False),      # cfg1 at full size
+    (4096, 16032, True, False),      # one of eight column shards of the large-N projection
+]
+
+
+@pytest.mark.parametrize("k,n,zp,bias", RESIDENT_BLOCK32_CASES)
+def test_decode_resident_path_block32(cuda_device, k, n, zp, bias):
+    case = syn.make_case("resident32", 1, k, n, 4, 32, seed=k + n + 32, zero_points=zp, bias=bias)
+    y, kernel = run_device(case, path=_capi.PATH_GEMV_RESIDENT)
+    assert kernel == RESIDENT
+    if n > 4096:
+        columns = np.random.default_rng(7).choice(n, size=512, replace=False)
+        ref = o.matmul_f64(case.a, case.b.reshape(n, -1)[columns].reshape(-1), case.scales.reshape(n, -1)[columns].reshape(-1),
+                           None if case.zero_points is None else case.zero_points.reshape(n, -1)[columns].reshape(-1),
+                           None if case.bias is None else case.bias[columns], len(columns), k, 4, 32)
+        assert rel_err(y[:, columns], ref) <= TOL_FP32
+    else:
+        assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    y_auto, kernel_auto = run_device(case)
+    assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    y_mma, name = run_device(case, path=_capi.PATH_GEMV_MMA)   # the fp16 two-piece kernel on the same node
+    assert name == "nbits_gemv_mma_kernel"
+    assert rel_err(y, y_mma) <= TOL_FP32
+
+
+def test_decode_resident_block32_special_rows(cuda_device):
+    for value, expect_nan in ((np.nan, True), (np.inf, True), (0.0, False)):
+        case = syn.make_case("resident32_special", 1, 4096, 64, 4, 32, seed=3, bias=True)
+        if value == 0.0:
+            case.a[:] = 0.0
+        else:
+            case.a[0, 4000] = value
+        y, kernel = run_device(case, path=_capi.PATH_GEMV_RESIDENT)
+        assert kernel == RESIDENT
+        if expect_nan:
+            assert np.isnan(y).all()
+        else:
+            assert np.array_equal(y[0], case.bias)
 
 
 def test_decode_resident_path_special_rows_and_rejections(cuda_device):
