@@ -368,14 +368,20 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       return;
     }
     asm volatile("bar.sync 4, %0;" ::"r"(consumer_threads) : "memory");
+    // (single node) the CTA's tile groups are cta, cta + grid, ...: G * 8 consecutive rows each; all of
+    // them in one pass over the consumer threads, consecutive lanes on consecutive rows
     const ResidentNode &node = p.node[0];
-    for (int local_group = 0; local_group < my_groups; ++local_group) {
-      const GroupPlace at = place_of(local_group);
-      const std::int64_t row0 = static_cast<std::int64_t>(at.tile0) * 8;
-      std::int64_t row1 = row0 + static_cast<std::int64_t>(at.count) * 8;
-      row1 = row1 < node.w.n ? row1 : node.w.n;
-      if (row1 > row0) {
-        PushRowsToPeers(node.out, p.tail, 0, 1, row0, row1, tid, consumer_threads);
+    const int rows_per_group = G * 8;
+    const float *local = node.out.y + node.out.col_offset;
+    for (int item = tid; item < my_groups * rows_per_group && p.tail.n_peers > 0; item += consumer_threads) {
+      const int local_group = item / rows_per_group;
+      const std::int64_t row = static_cast<std::int64_t>(cta + local_group * grid) * rows_per_group +
+                               (item - local_group * rows_per_group);
+      if (row < node.w.n) {
+        const float v = __ldcg(local + row);
+        for (int r = 0; r < p.tail.n_peers; ++r) {
+          p.tail.peers[r][node.out.col_offset + row] = v;
+        }
       }
     }
     PublishWhenGridDone(p.tail, tid, consumer_threads, 4, gridDim.x, p.status);
