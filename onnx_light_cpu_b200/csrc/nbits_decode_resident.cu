@@ -363,8 +363,12 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   // Gathered step: the arithmetic stores locally only; once all consumer warps of the CTA are done,
   // the rows of its tile groups go to the same place of every peer's buffer and the CTA counts
   // itself in; the last CTA of the grid publishes this rank's flags.
-  auto finish_gathered_step = [&]() {
+  auto finish_gathered_step = [&](bool rows_already_pushed) {
     if (p.tail.ranks <= 0) {
+      return;
+    }
+    if (rows_already_pushed) {
+      PublishWhenGridDone(p.tail, tid, consumer_threads, 4, gridDim.x, p.status);
       return;
     }
     asm volatile("bar.sync 4, %0;" ::"r"(consumer_threads) : "memory");
@@ -499,12 +503,40 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       const ResidentNode &node = p.node[at.node];
       const std::int64_t row = static_cast<std::int64_t>(at.tile0 + member) * 8 + g;
+      float result = 0.0f;
       if (!dead && t == 0 && row < node.w.n) {
         const float bias = node.w.bias != nullptr ? __ldg(node.w.bias + row) : 0.0f;
-        StoreOutput(node.out, node.out.col_offset + row, fmaf(v, undo[0], bias));
+        result = fmaf(v, undo[0], bias);
+        StoreOutput(node.out, node.out.col_offset + row, result);
+      }
+      if (p.tail.ranks > 0 && p.tail.n_peers > 0) {
+        // gathered step: the tile's eight outputs go to the peers right away, from one lane, as two
+        // 16-byte stores per peer where the place allows it (the copies are long done when the CTA
+        // counts itself in at the end)
+        float out8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          out8[j] = __shfl_sync(0xffffffffu, result, 4 * j);
+        }
+        const std::int64_t row0 = static_cast<std::int64_t>(at.tile0 + member) * 8;
+        const std::int64_t at0 = node.out.col_offset + row0;
+        if (lane == 0 && !dead) {
+          const bool whole = row0 + 8 <= node.w.n;
+          for (int r = 0; r < p.tail.n_peers; ++r) {
+            float *dst = p.tail.peers[r] + at0;
+            if (whole && (reinterpret_cast<std::uintptr_t>(dst) & 15u) == 0) {
+              reinterpret_cast<float4 *>(dst)[0] = make_float4(out8[0], out8[1], out8[2], out8[3]);
+              reinterpret_cast<float4 *>(dst)[1] = make_float4(out8[4], out8[5], out8[6], out8[7]);
+            } else {
+              for (int j = 0; j < 8 && row0 + j < node.w.n; ++j) {
+                dst[j] = out8[j];
+              }
+            }
+          }
+        }
       }
     }
-    finish_gathered_step();
+    finish_gathered_step(true);
     return;
   }
   // MMA row g is row `rho` of the tile: the two rows a quarter warp reads together then differ in
@@ -644,7 +676,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       StoreOutput(node.out, node.out.col_offset + row, fmaf(v, undo[0], bias));
     }
   }
-  finish_gathered_step();
+  finish_gathered_step(false);
 }
 
 bool EncodeWeightTileMap(CUtensorMap *map, const WeightView &w, int steps) {
