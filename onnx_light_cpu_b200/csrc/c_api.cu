@@ -342,7 +342,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     // holds 4 / 2 / 1 tokens for block_size >= 128 / 64 / 32; more tokens go to the kernel that
     // shares a pass over the weights between several column tiles.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m == 1 && path == MNB_PATH_AUTO) {
+    if (m == 1 && path == MNB_PATH_AUTO && mnb::DecodeResidentPreferred(w)) {
       // one token: the whole share of each SM is asked for at kernel start
       name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
@@ -833,7 +833,7 @@ int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const char *name = nullptr;
   // Bounded waits of a grouped launch report through the first node's status word.
-  if (accuracy_level == 0 && m == 1) {
+  if (accuracy_level == 0 && m == 1 && mnb::DecodeResidentPreferred(nodes[0])) {
     // one launch: the nodes' tiles form one sequence behind activations staged once
     name = mnb::LaunchDecodeResidentGroup(nodes, outs, count, a_dev, m, first->status_dev, s, first->sm_count);
   } else if (accuracy_level == 4 && count > 1) {
@@ -1078,7 +1078,7 @@ int mnb_matmul_device_gather_ex(mnb_weights *h, const float *a_dev, int64_t m, i
     // The tensor-core decode kernels push each CTA's rows to the peers as the CTA finishes, and the
     // last CTA to finish publishes the flags: one launch per node, no pass over the result.
     const int per_pass = w.block_size >= 128 ? 4 : (w.block_size == 64 ? 2 : 1);
-    if (m == 1 && mnb::DecodeResidentSupports(w, m)) {
+    if (m == 1 && mnb::DecodeResidentSupports(w, m) && mnb::DecodeResidentPreferred(w)) {
       // one token: the kernel that asks for each SM's whole share of the weights at its start
       name = mnb::LaunchDecodeResident(w, a_dev, m, out, h->status_dev, stream, h->sm_count, &fused_tail);
       if (name == nullptr) {

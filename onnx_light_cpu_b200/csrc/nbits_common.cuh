@@ -274,6 +274,10 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
 // block_size 128 or 32. `tail` (single node): the CTAs push their rows to the peers of a gathered
 // step and the last one publishes the flags.
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
+// Rows of up to 4096 k: a whole row of a tile fits a slot with ten or more warps at work. Longer
+// rows leave the tile-per-warp structure with few warps (K = 14336: 18.7 us against 11.9 on the
+// direct kernel, K = 8192: 10.0-11.3 against 9.5-10.0 on the fp16 kernel), so AUTO sends them elsewhere.
+bool DecodeResidentPreferred(const WeightView &w);
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
                                  cudaStream_t stream, int sm_count, const GatherTail *tail = nullptr);
 // Up to kMaxGroupedNodes nodes that take the same activations (same K, zero points in all or in

@@ -48,6 +48,8 @@ RESIDENT = "nbits_decode_resident_kernel"
 def resident_takes(case):
     """Shapes AUTO sends to the one-token kernel that asks for all of its weights at kernel start."""
     blocks = -(-case.k // case.block_size)
+    if case.k > 4096:
+        return False                   # longer rows leave the tile-per-warp kernel too few warps
     if case.bits == 4 and case.block_size == 32 and case.m == 1:
         return case.k % 1024 == 0      # blocks of 32: whole chunks of 32 scales per row
     return (case.bits == 4 and case.block_size == 128 and case.m == 1 and blocks % 8 == 0 and
@@ -359,7 +361,10 @@ def test_decode_resident_path(cuda_device, k, n, zp, bias):
     assert kernel == RESIDENT
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     y_auto, kernel_auto = run_device(case)
-    assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    if resident_takes(case):
+        assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    else:
+        assert kernel_auto == DIRECT and rel_err(y, y_auto) <= 1e-6
     y_direct, _ = run_device(case, path=_capi.PATH_GEMV_DIRECT)   # same digits, same block sums
     assert rel_err(y, y_direct) <= 1e-6
 
@@ -392,7 +397,10 @@ def test_decode_resident_path_block32(cuda_device, k, n, zp, bias):
     else:
         assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     y_auto, kernel_auto = run_device(case)
-    assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    if resident_takes(case):
+        assert kernel_auto == RESIDENT and np.array_equal(y, y_auto)
+    else:
+        assert kernel_auto == "nbits_gemv_mma_kernel"
     y_mma, name = run_device(case, path=_capi.PATH_GEMV_MMA)   # the fp16 two-piece kernel on the same node
     assert name == "nbits_gemv_mma_kernel"
     assert rel_err(y, y_mma) <= TOL_FP32
