@@ -350,6 +350,12 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // shapes the resident kernel does not take: every warp streams its own tile
       name = mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true);
     }
+    if (name == nullptr && m == 2 && path == MNB_PATH_AUTO && (w.k <= 2048 || (w.k >= 8192 && w.n >= 8192))) {
+      // two tokens, long rows on a wide node or short rows: every warp streams its own tile (K = 14336,
+      // N = 14336: 28.6 against 37.6 us on the integer-digit kernel below; K = 8192: 19.3 against 20.6;
+      // K = 2048: 8.4 against 9.5 at N = 14336, 4.6 against 5.5 at N = 1024)
+      name = mnb::LaunchDecodeDirect(w, a_dev, m, out, stream, h->sm_count, true);
+    }
     if (name == nullptr && m <= kImmaAutoTokens && path == MNB_PATH_AUTO) {
       // one or two tokens, block_size >= 128: the integer-digit kernel (fewest instructions per code)
       name = mnb::LaunchGemvImma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
@@ -833,7 +839,7 @@ int mnb_matmul_device_group(mnb_weights *const *handles, int count, const float 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const char *name = nullptr;
   // Bounded waits of a grouped launch report through the first node's status word.
-  if (accuracy_level == 0 && m == 1 && mnb::DecodeResidentPreferred(nodes[0])) {
+  if (accuracy_level == 0 && m == 1 && mnb::DecodeResidentGroupPreferred(nodes, count)) {
     // one launch: the nodes' tiles form one sequence behind activations staged once
     name = mnb::LaunchDecodeResidentGroup(nodes, outs, count, a_dev, m, first->status_dev, s, first->sm_count);
   } else if (accuracy_level == 4 && count > 1) {

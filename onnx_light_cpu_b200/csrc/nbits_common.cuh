@@ -276,8 +276,12 @@ const char *LaunchDecodeDirect(const WeightView &w, const float *a, std::int64_t
 bool DecodeResidentSupports(const WeightView &w, std::int64_t m);
 // Rows of up to 4096 k: a whole row of a tile fits a slot with ten or more warps at work. Longer
 // rows leave the tile-per-warp structure with few warps (K = 14336: 18.7 us against 11.9 on the
-// direct kernel, K = 8192: 10.0-11.3 against 9.5-10.0 on the fp16 kernel), so AUTO sends them elsewhere.
+// direct kernel, K = 8192: 10.0-11.3 against 9.5-10.0 on the fp16 kernel), and so do nodes of fewer
+// than four tiles per CTA (K = 4096, block 128: N = 1024 7.6 against 3.5 us, N = 4096 6.2 against 5.6
+// on the direct kernel; block 32, N = 1024: 8.0 against 6.1 on the fp16 kernel), so AUTO sends those
+// elsewhere. A group of sibling nodes in one launch is judged by its rows only.
 bool DecodeResidentPreferred(const WeightView &w);
+bool DecodeResidentGroupPreferred(const WeightView *nodes, int count);
 const char *LaunchDecodeResident(const WeightView &w, const float *a, std::int64_t m, OutputView out, int *status_word,
                                  cudaStream_t stream, int sm_count, const GatherTail *tail = nullptr);
 // Up to kMaxGroupedNodes nodes that take the same activations (same K, zero points in all or in

@@ -760,7 +760,18 @@ bool DecodeResidentSupports(const WeightView &w, std::int64_t m) {
          w.n < (std::int64_t{1} << 31);
 }
 
-bool DecodeResidentPreferred(const WeightView &w) { return w.row_bytes / 128 <= 16; }
+bool DecodeResidentPreferred(const WeightView &w) {
+  // at least four eight-row tiles per CTA of a 148-SM part: with fewer, most of its warps have no tile
+  // and a tile is a long chain of steps on one warp; rows of up to 2048 k are short enough for that
+  // not to matter (block 32: N = 4096 3.7 against 6.3 us on the fp16 kernel, N = 1024 5.1 against
+  // 5.7; block 128: N = 4096 3.4-3.6 against 3.9 us on the direct kernel, N = 1024 4.7 against 3.0)
+  const int chunks = w.row_bytes / 128;
+  return chunks <= 16 && (w.n >= 4736 || (chunks <= 8 && (w.block_size == 32 || w.n >= 4096)));
+}
+
+bool DecodeResidentGroupPreferred(const WeightView *nodes, int count) {
+  return count >= 1 && nodes[0].row_bytes / 128 <= 16;
+}
 
 namespace {
 

@@ -35,7 +35,7 @@ def upload(cases):
                                    block_size=c.block_size) for c in cases]
 
 
-def run_group(cases, accuracy_level=0):
+def run_group(cases, accuracy_level=0, single_path=_capi.PATH_AUTO):
     import torch
 
     nodes = upload(cases)
@@ -50,7 +50,7 @@ def run_group(cases, accuracy_level=0):
     assert all(node.poll_status() == 0 for node in nodes)
     singles = [torch.full((c.m, c.n), float("nan"), device="cuda") for c in cases]
     for node, y in zip(nodes, singles):
-        node.matmul_device(a, y, accuracy_level=accuracy_level)
+        node.matmul_device(a, y, accuracy_level=accuracy_level, path=single_path)
     torch.cuda.synchronize()
     out = [y.cpu().numpy() for y in ys]
     alone = [y.cpu().numpy() for y in singles]
@@ -67,7 +67,8 @@ def run_group(cases, accuracy_level=0):
 ])
 def test_one_token_group_is_one_resident_launch(cuda_device, shapes, k, zp, bias):
     cases = make_nodes(shapes, k, 128, zero_points=zp, bias=bias, m=1, seed=9100 + len(shapes) + k)
-    out, alone, kernel, launches = run_group(cases)
+    # (alone: the same kernel on request; AUTO would send the narrow nodes to the direct kernel)
+    out, alone, kernel, launches = run_group(cases, single_path=_capi.PATH_GEMV_RESIDENT)
     assert kernel == "nbits_decode_resident_kernel", kernel
     assert launches == 1
     for case, y, y1 in zip(cases, out, alone):

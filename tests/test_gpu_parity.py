@@ -48,8 +48,9 @@ RESIDENT = "nbits_decode_resident_kernel"
 def resident_takes(case):
     """Shapes AUTO sends to the one-token kernel that asks for all of its weights at kernel start."""
     blocks = -(-case.k // case.block_size)
-    if case.k > 4096:
-        return False                   # longer rows leave the tile-per-warp kernel too few warps
+    # long rows, or few tiles per CTA with rows that are not short, leave the tile-per-warp kernel too few warps
+    if case.k > 4096 or not (case.n >= 4736 or (case.k <= 2048 and (case.block_size == 32 or case.n >= 4096))):
+        return False
     if case.bits == 4 and case.block_size == 32 and case.m == 1:
         return case.k % 1024 == 0      # blocks of 32: whole chunks of 32 scales per row
     return (case.bits == 4 and case.block_size == 128 and case.m == 1 and blocks % 8 == 0 and
@@ -96,11 +97,11 @@ def test_dequant_integers_bit_exact(cuda_device, bits, bs, k, n, zp):
 def test_config1_single_node(cuda_device):
     case = syn.config1()
     y, kernel = run_device(case)
-    assert kernel == RESIDENT, kernel      # one token, blocks of 32: one integer MMA per block
+    assert kernel == "nbits_gemv_mma_kernel", kernel   # fewer than four tiles per CTA: the fp16 two-piece kernel
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
     assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, None, None, case.n, case.k, 4, 32)) <= TOL_FP32
-    y1, kernel1 = run_device(case, path=_capi.PATH_GEMV_MMA)
-    assert kernel1 == "nbits_gemv_mma_kernel", kernel1
+    y1, kernel1 = run_device(case, path=_capi.PATH_GEMV_RESIDENT)
+    assert kernel1 == RESIDENT, kernel1    # on request: one integer MMA per block of 32
     assert rel_err(y1, oracle_f64(case)) <= TOL_FP32
     y2, kernel2 = run_device(case, path=_capi.PATH_GEMV)
     assert kernel2.startswith("nbits_gemv_stream_kernel<4,1,"), kernel2
