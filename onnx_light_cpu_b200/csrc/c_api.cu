@@ -308,7 +308,11 @@ bool DigitSlicesWanted(const WeightView &w, std::int64_t m) {
   if (w.bits != 4 || m > 16) {
     return false;
   }
-  return m >= 5;
+  // from five tokens on; from three on rows of 8192 k and more, where the fp16 kernels need several
+  // passes or do not fit (K = 14336, M = 3 / 4, us per node: block 32 N = 4096 25.2 / 25.5 against
+  // 31.5 / 33.2, N = 14336 62.3 / 62.5 against 82.3 / 83.6; block 128 N = 14336 49.6 / 50.1 against 68.9
+  // and, at M = 4, no tensor-core kernel at all: 1.8 ms on the generic one)
+  return m >= 5 || (m >= 3 && w.k >= 8192);
 }
 
 // Core dispatch. The caller holds h->mutex and has made h->device current.
@@ -407,6 +411,22 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       // shapes the CUDA-core kernel cannot stage (very long K with several tokens): many passes of
       // the tensor-core kernel still beat the generic one by a wide margin
       name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
+    }
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && w.bits == 4) {
+      // nothing above took the shape: the one-pass digit kernel, whatever the token count, before the
+      // generic kernel (two to three orders of magnitude slower)
+      const std::size_t need = mnb::DigitSlicesScratchBytes(w, m);
+      if (need != 0) {
+        const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+        if (rc != MNB_OK) {
+          return rc;
+        }
+        name = mnb::LaunchDigitSlicesGroup(&w, &out, 1, a_dev, m, static_cast<unsigned char *>(h->scratch_a),
+                                           h->status_dev, stream, h->sm_count);
+        if (name == nullptr) {
+          cudaGetLastError();
+        }
+      }
     }
     if (name == nullptr) {
       name = mnb::LaunchGemvGeneric(w, a_dev, m, out, stream);

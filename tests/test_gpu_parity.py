@@ -65,10 +65,11 @@ def direct_takes(case):
 
 
 def sliced_digits_take(case):
-    """Shapes AUTO sends to the one-pass digit kernel: five to sixteen tokens, 4-bit, packed rows that
-    are whole 128-byte units."""
+    """Shapes AUTO sends to the one-pass digit kernel: five to sixteen tokens (three and four too on
+    rows of 8192 k and more), 4-bit, packed rows that are whole 128-byte units."""
     m, bs = case.m, case.block_size
-    return case.bits == 4 and 5 <= m <= 16 and (case.k // 2) % 128 == 0 and 32 <= bs <= 1024
+    enough_tokens = 5 <= m <= 16 or (3 <= m <= 16 and case.k >= 8192)   # long rows: from three tokens on
+    return case.bits == 4 and enough_tokens and (case.k // 2) % 128 == 0 and 32 <= bs <= 1024
 
 
 SLICED = "nbits_digits_mma_kernel"
@@ -688,6 +689,17 @@ def test_prefill_split_k(cuda_device, m, k, n, bs, zp, bias):
     whole, name = run_device(case, path=_capi.PATH_TCGEN05)
     assert name.startswith("nbits_gemm_tcgen05_kernel"), name
     assert rel_err(y, whole) <= 1e-5
+
+
+def test_four_tokens_on_long_rows_stay_on_tensor_cores(cuda_device):
+    """M = 4, block 128, K = 14336: the fp16 kernels cannot stage four tokens of that length, and the
+    product used to fall through to the scalar kernel (1.8 ms for the square node). AUTO takes the
+    one-pass digit kernel from three tokens on for rows of 8192 k and more."""
+    for m in (3, 4):
+        case = syn.make_case("long_rows", m, 14336, 264, 4, 128, seed=77 + m, zero_points=True, bias=True)
+        y, kernel = run_device(case)
+        assert kernel == SLICED, kernel
+        assert rel_err(y, oracle_f64(case)) <= TOL_FP32
 
 
 def test_prefill_kernels_agree_on_random_shapes(cuda_device):
