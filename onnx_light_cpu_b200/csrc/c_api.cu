@@ -562,8 +562,8 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     }
     if (name == nullptr) {
       return Fail(MNB_ERR_UNSUPPORTED,
-                  "MatMulNBits: accuracy_level 4 needs 16-byte aligned rows and block_size >= 32 "
-                  "for 4-bit weights.");
+                  "MatMulNBits: accuracy_level 4 needs packed rows and a weight base aligned to eight codes "
+                  "(4 bytes for 4-bit, 8 bytes for 8-bit weights).");
     }
     break;
   }
@@ -1483,8 +1483,8 @@ int mnb_matmul_int8_static(mnb_weights *h, const float *a_dev, int64_t m, float 
   }
   if (name == nullptr) {
     return Fail(MNB_ERR_UNSUPPORTED,
-                "mnb_matmul_int8_static: needs 16-byte aligned weight rows and block_size >= 32 for "
-                "4-bit weights.");
+                "mnb_matmul_int8_static: needs packed rows and a weight base aligned to eight codes (4 bytes "
+                "for 4-bit, 8 bytes for 8-bit weights).");
   }
   mnb::t_last_kernel = name;
   return MNB_OK;

@@ -471,6 +471,345 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Word-wise kernels for the shapes no staged kernel takes (block_size 16, 8-bit rows too long for
+// whole-row stages, row sizes outside the chunked layouts). The unit is a group of eight consecutive
+// codes, 4 bytes of a 4-bit row or 8 of an 8-bit one, read straight from global memory, so every
+// weight byte is read once per pass of MT tokens. A group never straddles a quantization block
+// (block_size >= 16). Arithmetic: codes as exact floats, fp32 FMAs.
+template <int BITS> struct GroupWord;
+template <> struct GroupWord<4> {
+  using Type = std::uint32_t;
+};
+template <> struct GroupWord<8> {
+  using Type = uint2;
+};
+
+// The eight codes of a group minus the block's zero point, as floats: 2^23 + code assembled in the
+// mantissa, minus (2^23 + zp), which is exact and needs no integer-to-float conversion. `magic` (the
+// bits of 2^23) arrives as a kernel argument: with the constant visible the compiler turns the pair
+// back into conversions, which run at a fraction of the FMA rate (55 % of the conversion pipe, and
+// that the limit, on an 8-bit M = 1 node). `neg_offset` = -(2^23 + zp) = -as_float(magic | zp).
+template <int BITS>
+__device__ __forceinline__ void DecodeEightCodes(typename GroupWord<BITS>::Type q, std::uint32_t magic,
+                                                 float neg_offset, float (&code)[8]) {
+  if constexpr (BITS == 4) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      code[e] = __uint_as_float(((q >> (4 * e)) & 0x0fu) | magic) + neg_offset;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      code[e] = __uint_as_float(((q.x >> (8 * e)) & 0xffu) | magic) + neg_offset;
+      code[4 + e] = __uint_as_float(((q.y >> (8 * e)) & 0xffu) | magic) + neg_offset;
+    }
+  }
+}
+
+// Eight activations of token row `src` from column k0 on; zeros beyond K (padding codes meet zeros).
+__device__ __forceinline__ void LoadEightActivations(const float *src, int k0, int k, bool vector, float (&av)[8]) {
+  if (vector && k0 + 8 <= k) {
+    const float4 lo = __ldg(reinterpret_cast<const float4 *>(src + k0));
+    const float4 hi = __ldg(reinterpret_cast<const float4 *>(src + k0) + 1);
+    av[0] = lo.x, av[1] = lo.y, av[2] = lo.z, av[3] = lo.w;
+    av[4] = hi.x, av[5] = hi.y, av[6] = hi.z, av[7] = hi.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      av[e] = k0 + e < k ? __ldg(src + k0 + e) : 0.0f;
+    }
+  }
+}
+
+// One and two tokens: one warp per output column, lanes stride over the groups of the row (the
+// loads of a warp are contiguous), four groups per lane at a time with the words of the next four
+// requested before these are used. acc += scale * sum a * (code - zp).
+template <int BITS, int MT>
+__global__ void __launch_bounds__(256)
+    nbits_gemv_words_kernel(const WeightView w, const float *a, int m_total, OutputView out, int block_shift,
+                            int a_vector, std::uint32_t magic) {
+  using Word = typename GroupWord<BITS>::Type;
+  constexpr int kBatch = 4;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::int64_t col = static_cast<std::int64_t>(blockIdx.x) * 8 + warp;
+  const int m_base = blockIdx.y * MT;
+  if (col >= w.n) {
+    return;
+  }
+  float acc[MT];
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) {
+    acc[mi] = 0.0f;
+  }
+  const Word *row = reinterpret_cast<const Word *>(w.b + col * w.row_bytes);
+  const float *scales = w.scales + col * w.n_blocks;
+  const std::uint8_t *zero_points = w.zp != nullptr ? w.zp + col * w.zp_row_bytes : nullptr;
+  const float *token[MT];
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) {
+    // a token beyond M repeats the last one; its sum is not written
+    token[mi] = a + static_cast<std::int64_t>(m_base + mi < m_total ? m_base + mi : m_total - 1) * w.k;
+  }
+  const int k = static_cast<int>(w.k);
+  const int groups = (k + 7) / 8; // groups with at least one code below K
+  const bool vector = a_vector != 0;
+
+  auto consume = [&](int g, Word q) {
+    const int k0 = g * 8;
+    const int block = k0 >> block_shift;
+    std::uint32_t zp = 1u << (BITS - 1);
+    if (zero_points != nullptr) {
+      if constexpr (BITS == 8) {
+        zp = __ldg(zero_points + block);
+      } else {
+        zp = (__ldg(zero_points + (block >> 1)) >> ((block & 1) * 4)) & 0x0fu;
+      }
+    }
+    const float scale = __ldg(scales + block);
+    float code[8];
+    DecodeEightCodes<BITS>(q, magic, -__uint_as_float(magic | zp), code);
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi) {
+      float av[8];
+      LoadEightActivations(token[mi], k0, k, vector, av);
+      float even = av[0] * code[0];
+      float odd = av[1] * code[1];
+#pragma unroll
+      for (int e = 2; e < 8; e += 2) {
+        even = fmaf(av[e], code[e], even);
+        odd = fmaf(av[e + 1], code[e + 1], odd);
+      }
+      acc[mi] = fmaf(scale, even + odd, acc[mi]);
+    }
+  };
+
+  // batches of four groups per lane; the words of the next batch are requested before this one is used
+  const int batches = groups / (32 * kBatch);
+  Word ahead[kBatch];
+  if (batches > 0) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      ahead[u] = __ldg(row + lane + 32 * u);
+    }
+  }
+#pragma unroll 1
+  for (int batch = 0; batch < batches; ++batch) {
+    const int g = batch * 32 * kBatch + lane;
+    Word now[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      now[u] = ahead[u];
+    }
+    if (batch + 1 < batches) {
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        ahead[u] = __ldg(row + g + 32 * (kBatch + u));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      consume(g + 32 * u, now[u]);
+    }
+  }
+  for (int g = batches * 32 * kBatch + lane; g < groups; g += 32) {
+    consume(g, __ldg(row + g));
+  }
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) {
+    float v = acc[mi];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      v += __shfl_xor_sync(0xffffffffu, v, offset);
+    }
+    if (lane == 0 && m_base + mi < m_total) {
+      const float bias = w.bias != nullptr ? __ldg(w.bias + col) : 0.0f;
+      out.y[static_cast<std::int64_t>(m_base + mi) * out.ld + out.col_offset + col] = v + bias;
+    }
+  }
+}
+
+// Three and more tokens: a lane per output column, so that the activations of a group are one
+// address for the whole warp (with lanes along K every lane loads its own eight activations per
+// token: one load per FMA). A CTA takes 32 columns; its eight warps take alternate chunks of 16
+// groups (128 codes) of K. Per chunk a warp copies into a tile of shared memory of its own, with
+// loads that run along K: the words of its 32 columns, their scales and zero points, and the
+// chunk's activations of up to eight tokens. It then reads the words back one column per lane and
+// the activations as broadcast loads, four tokens at a time so that four dot products are in
+// flight. The partial sums of the warps meet in shared memory at the end. No CTA-wide barrier in
+// the loop.
+constexpr int kColumnsWarps = 8;
+constexpr int kColumnsChunk = 16;      // groups per chunk
+constexpr int kColumnsWordStride = 17; // words of a column in the tile, padded
+constexpr int kColumnsMetaStride = 9;  // up to 8 blocks per chunk (block_size 16), padded
+constexpr int kColumnsTokens = 8;      // tokens per pass
+
+template <int BITS> __host__ __device__ constexpr int ColumnsWordBytes() { return 32 * kColumnsWordStride * BITS; }
+constexpr int kColumnsMetaBytes = 32 * kColumnsMetaStride * 8;
+template <int BITS, int MT> __host__ __device__ constexpr int ColumnsWarpBytes() {
+  return ColumnsWordBytes<BITS>() + kColumnsMetaBytes + MT * kColumnsChunk * 8 * 4;
+}
+
+template <int BITS, int MT>
+__global__ void __launch_bounds__(kColumnsWarps * 32)
+    nbits_gemv_columns_kernel(const WeightView w, const float *a, int m_total, OutputView out, int block_shift,
+                              int a_vector, std::uint32_t magic) {
+  static_assert(MT % 4 == 0, "tokens are taken four at a time");
+  using Word = typename GroupWord<BITS>::Type;
+  extern __shared__ __align__(16) unsigned char columns_smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::int64_t col0 = static_cast<std::int64_t>(blockIdx.x) * 32;
+  const int m_base = blockIdx.y * MT;
+  const int tokens = m_total - m_base < MT ? m_total - m_base : MT;
+  unsigned char *mine = columns_smem + warp * ColumnsWarpBytes<BITS, MT>();
+  Word *words = reinterpret_cast<Word *>(mine);
+  float2 *meta = reinterpret_cast<float2 *>(mine + ColumnsWordBytes<BITS>());
+  float *acts = reinterpret_cast<float *>(mine + ColumnsWordBytes<BITS>() + kColumnsMetaBytes); // [MT][128]
+
+  float acc[MT];
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) {
+    acc[mi] = 0.0f;
+  }
+  constexpr int kChunkCodes = kColumnsChunk * 8;
+  const int groups = static_cast<int>((w.k + 7) / 8);
+  const int chunks = (groups + kColumnsChunk - 1) / kColumnsChunk;
+  // quantization blocks a chunk touches (one for block_size >= 128)
+  const int blocks_per_chunk = (kChunkCodes >> block_shift) > 0 ? (kChunkCodes >> block_shift) : 1;
+  const int columns_here = w.n - col0 < 32 ? static_cast<int>(w.n - col0) : 32;
+
+  for (int chunk = warp; chunk < chunks; chunk += kColumnsWarps) {
+    const int g0 = chunk * kColumnsChunk;
+    const std::int64_t k_first = static_cast<std::int64_t>(g0) * 8;
+    const int first_block = static_cast<int>(k_first >> block_shift);
+    __syncwarp(); // the tiles of the chunk before have been read
+    // words: two columns per step, sixteen lanes along K each; columns beyond N repeat the last one
+    {
+      const int gl = lane & 15;
+#pragma unroll 8
+      for (int step = 0; step < 16; ++step) {
+        const int c = 2 * step + (lane >> 4);
+        const std::int64_t col = col0 + (c < columns_here ? c : columns_here - 1);
+        Word q{};
+        if (g0 + gl < groups) {
+          q = __ldg(reinterpret_cast<const Word *>(w.b + col * w.row_bytes) + g0 + gl);
+        }
+        words[c * kColumnsWordStride + gl] = q;
+      }
+    }
+    // {scale, -(2^23 + zp)} of every (column, block of the chunk)
+    for (int item = lane; item < 32 * blocks_per_chunk; item += 32) {
+      const int c = item / blocks_per_chunk;
+      const int b = item - c * blocks_per_chunk;
+      const std::int64_t col = col0 + (c < columns_here ? c : columns_here - 1);
+      const int block = first_block + b;
+      if (block < w.n_blocks) {
+        meta[c * kColumnsMetaStride + b] =
+            make_float2(__ldg(w.scales + col * w.n_blocks + block),
+                        -__uint_as_float(magic | static_cast<std::uint32_t>(ZeroPointOf(w, col, block))));
+      }
+    }
+    // activations of the chunk: 128 per token, four per lane; zeros beyond K and beyond M
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi) {
+      const std::int64_t kk = k_first + 4 * lane;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (mi < tokens) {
+        const float *src = a + static_cast<std::int64_t>(m_base + mi) * w.k;
+        if (a_vector != 0 && kk + 4 <= w.k) {
+          v = __ldg(reinterpret_cast<const float4 *>(src + kk));
+        } else {
+          v.x = kk + 0 < w.k ? __ldg(src + kk + 0) : 0.0f;
+          v.y = kk + 1 < w.k ? __ldg(src + kk + 1) : 0.0f;
+          v.z = kk + 2 < w.k ? __ldg(src + kk + 2) : 0.0f;
+          v.w = kk + 3 < w.k ? __ldg(src + kk + 3) : 0.0f;
+        }
+      }
+      reinterpret_cast<float4 *>(acts + mi * kChunkCodes)[lane] = v;
+    }
+    __syncwarp();
+    const int here = groups - g0 < kColumnsChunk ? groups - g0 : kColumnsChunk;
+#pragma unroll 2
+    for (int gi = 0; gi < here; ++gi) {
+      const int block = static_cast<int>((k_first + gi * 8) >> block_shift) - first_block;
+      const float2 sz = meta[lane * kColumnsMetaStride + block];
+      float code[8]; // code - zp: small integers, exact
+      DecodeEightCodes<BITS>(words[lane * kColumnsWordStride + gi], magic, sz.y, code);
+#pragma unroll
+      for (int quad = 0; quad < MT; quad += 4) {
+        float4 lo[4];
+        float4 hi[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float4 *src = reinterpret_cast<const float4 *>(acts + (quad + t) * kChunkCodes + gi * 8);
+          lo[t] = src[0];
+          hi[t] = src[1];
+        }
+        float dot[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = lo[t].x * code[0];
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(lo[t].y, code[1], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(lo[t].z, code[2], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(lo[t].w, code[3], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(hi[t].x, code[4], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(hi[t].y, code[5], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(hi[t].z, code[6], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          dot[t] = fmaf(hi[t].w, code[7], dot[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          acc[quad + t] = fmaf(sz.x, dot[t], acc[quad + t]);
+        }
+      }
+    }
+  }
+  // sum over the warps: [warp][token][column] in the shared memory the tiles used
+  __syncthreads();
+  float *partial = reinterpret_cast<float *>(columns_smem);
+#pragma unroll
+  for (int mi = 0; mi < MT; ++mi) {
+    partial[(warp * MT + mi) * 32 + lane] = acc[mi];
+  }
+  __syncthreads();
+  for (int item = threadIdx.x; item < tokens * 32; item += kColumnsWarps * 32) {
+    const int mi = item >> 5;
+    const int c = item & 31;
+    if (c < columns_here) {
+      float total = 0.0f;
+#pragma unroll
+      for (int wi = 0; wi < kColumnsWarps; ++wi) {
+        total += partial[(wi * MT + mi) * 32 + c];
+      }
+      const float bias = w.bias != nullptr ? __ldg(w.bias + col0 + c) : 0.0f;
+      out.y[static_cast<std::int64_t>(m_base + mi) * out.ld + out.col_offset + col0 + c] = total + bias;
+    }
+  }
+}
+
 int Log2Exact(int v) {
   int l = 0;
   while ((1 << l) < v) {
@@ -582,11 +921,83 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
   return name;
 }
 
+namespace {
+
+template <int BITS, int MT>
+cudaError_t LaunchWordsInstance(const WeightView &w, const float *a, std::int64_t m, OutputView out, int a_vector,
+                                cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>((w.n + 7) / 8), static_cast<unsigned>((m + MT - 1) / MT), 1);
+  nbits_gemv_words_kernel<BITS, MT>
+      <<<grid, 256, 0, stream>>>(w, a, static_cast<int>(m), out, Log2Exact(w.block_size), a_vector, kMagicBits);
+  return cudaGetLastError();
+}
+
+template <int BITS, int MT>
+cudaError_t LaunchColumnsInstance(const WeightView &w, const float *a, std::int64_t m, OutputView out, int a_vector,
+                                  cudaStream_t stream) {
+  auto kernel = nbits_gemv_columns_kernel<BITS, MT>;
+  constexpr int kSmem = kColumnsWarps * ColumnsWarpBytes<BITS, MT>();
+  static_assert(kSmem >= kColumnsWarps * MT * 32 * 4, "the partial sums reuse the tiles");
+  const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  if (attr != cudaSuccess) {
+    return attr;
+  }
+  dim3 grid(static_cast<unsigned>((w.n + 31) / 32), static_cast<unsigned>((m + MT - 1) / MT), 1);
+  kernel<<<grid, kColumnsWarps * 32, kSmem, stream>>>(w, a, static_cast<int>(m), out, Log2Exact(w.block_size),
+                                                      a_vector, kMagicBits);
+  return cudaGetLastError();
+}
+
+template <int BITS>
+cudaError_t LaunchWordsBits(const WeightView &w, const float *a, std::int64_t m, OutputView out, int a_vector,
+                            cudaStream_t stream, const char **name) {
+  *name = "nbits_gemv_words_kernel";
+  if (m == 1) {
+    return LaunchWordsInstance<BITS, 1>(w, a, m, out, a_vector, stream);
+  }
+  if (m == 2) {
+    return LaunchWordsInstance<BITS, 2>(w, a, m, out, a_vector, stream);
+  }
+  *name = "nbits_gemv_columns_kernel";
+  if (m <= 4) {
+    return LaunchColumnsInstance<BITS, 4>(w, a, m, out, a_vector, stream);
+  }
+  return LaunchColumnsInstance<BITS, kColumnsTokens>(w, a, m, out, a_vector, stream); // more tokens: passes of eight
+}
+
+} // namespace
+
+const char *LaunchGemvWords(const WeightView &w, const float *a, std::int64_t m, OutputView out,
+                            cudaStream_t stream) {
+  if (m < 1 || w.n < 1 || w.k < 1 || w.k > (std::int64_t{1} << 30) || (w.bits != 4 && w.bits != 8) ||
+      w.block_size < 16) {
+    return nullptr;
+  }
+  // a group of eight codes is one aligned 4-byte (4-bit) or 8-byte (8-bit) load
+  const std::uintptr_t group_bytes = static_cast<std::uintptr_t>(w.bits);
+  if ((reinterpret_cast<std::uintptr_t>(w.b) % group_bytes) != 0 || (w.row_bytes % group_bytes) != 0) {
+    return nullptr;
+  }
+  const int a_vector = (w.k % 4) == 0 && (reinterpret_cast<std::uintptr_t>(a) & 15u) == 0 ? 1 : 0;
+  const char *name = nullptr;
+  const cudaError_t err = w.bits == 4 ? LaunchWordsBits<4>(w, a, m, out, a_vector, stream, &name)
+                                      : LaunchWordsBits<8>(w, a, m, out, a_vector, stream, &name);
+  if (err != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  return name;
+}
+
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                               cudaStream_t stream) {
   if (m < 1 || w.n < 1) {
     return nullptr;
   }
+  if (const char *words = LaunchGemvWords(w, a, m, out, stream)) {
+    return words;
+  }
+  cudaGetLastError();
   dim3 grid(static_cast<unsigned>((w.n + 7) / 8),
             static_cast<unsigned>((m + kGenericMaxM - 1) / kGenericMaxM), 1);
   nbits_gemv_generic_kernel<<<grid, 256, 0, stream>>>(w, a, static_cast<int>(m), out);

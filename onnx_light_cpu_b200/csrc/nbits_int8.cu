@@ -182,6 +182,73 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same product for rows the 16-byte chunks do not fit (4-bit weights with block_size 16, where a
+// chunk would span two blocks, and packed rows that are not a multiple of 16 bytes): lanes stride
+// over groups of eight codes, 4 bytes of a 4-bit row or 8 of an 8-bit one, against 8 bytes of `aq`.
+template <int BITS>
+__global__ void __launch_bounds__(256)
+    nbits_int8_words_kernel(const WeightView w, const std::int8_t *aq, std::int64_t aq_ld, const float *a_scales,
+                            int m_total, OutputView out, int block_shift) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::int64_t col = static_cast<std::int64_t>(blockIdx.x) * 8 + warp;
+  const int m_base = blockIdx.y * kInt8Mt;
+  if (col >= w.n) {
+    return;
+  }
+  float acc[kInt8Mt];
+#pragma unroll
+  for (int mi = 0; mi < kInt8Mt; ++mi) {
+    acc[mi] = 0.0f;
+  }
+  const int groups = w.row_bytes / BITS;
+  const unsigned char *row = w.b + col * w.row_bytes;
+  for (int g = lane; g < groups; g += 32) {
+    std::uint32_t q_lo;
+    std::uint32_t q_hi = 0;
+    if constexpr (BITS == 4) {
+      q_lo = __ldg(reinterpret_cast<const std::uint32_t *>(row) + g);
+    } else {
+      const uint2 q = __ldg(reinterpret_cast<const uint2 *>(row) + g);
+      q_lo = q.x;
+      q_hi = q.y;
+    }
+    const int block = (g * 8) >> block_shift;
+    const float scale = w.scales[col * w.n_blocks + block];
+    const int zp = ZeroPointOf(w, col, block);
+#pragma unroll
+    for (int mi = 0; mi < kInt8Mt; ++mi) {
+      const int m = m_base + mi;
+      if (m < m_total) {
+        const uint2 av = *reinterpret_cast<const uint2 *>(aq + static_cast<std::int64_t>(m) * aq_ld +
+                                                          static_cast<std::int64_t>(g) * 8);
+        int dot;
+        if constexpr (BITS == 4) {
+          dot = Dot8Nibbles(q_lo, av.x, av.y);
+        } else {
+          asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(dot) : "r"(av.x), "r"(q_lo), "r"(0));
+          asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(dot) : "r"(av.y), "r"(q_hi), "r"(dot));
+        }
+        const int exact = dot - zp * (Sum4(av.x) + Sum4(av.y)); // sum aq * (q - zp) over this group
+        const float sa = a_scales[static_cast<std::int64_t>(m) * w.n_blocks + block];
+        acc[mi] = fmaf(sa * scale, static_cast<float>(exact), acc[mi]);
+      }
+    }
+  }
+#pragma unroll
+  for (int mi = 0; mi < kInt8Mt; ++mi) {
+    float v = acc[mi];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      v += __shfl_xor_sync(0xffffffffu, v, offset);
+    }
+    if (lane == 0 && m_base + mi < m_total) {
+      const float bias = w.bias != nullptr ? w.bias[col] : 0.0f;
+      out.y[static_cast<std::int64_t>(m_base + mi) * out.ld + out.col_offset + col] = v + bias;
+    }
+  }
+}
+
 int Log2Of(int v) {
   int l = 0;
   while ((1 << l) < v) {
@@ -229,15 +296,33 @@ const char *LaunchInt8BlockDots(const WeightView &w, const std::int8_t *aq, std:
 const char *LaunchInt8Matmul(const WeightView &w, const std::int8_t *aq, const float *a_scales,
                              std::int64_t m, OutputView out, cudaStream_t stream, int sm_count) {
   (void)sm_count;
-  if (m < 1 || (w.row_bytes % 16) != 0 || (reinterpret_cast<std::uintptr_t>(w.b) & 15u) != 0) {
-    return nullptr;
-  }
-  if (w.bits == 4 && w.block_size < 32) {
+  if (m < 1 || (w.bits != 4 && w.bits != 8) || w.block_size < 16) {
     return nullptr;
   }
   const std::int64_t aq_ld = static_cast<std::int64_t>(w.n_blocks) * w.block_size;
   dim3 grid(static_cast<unsigned>((w.n + 7) / 8), static_cast<unsigned>((m + kInt8Mt - 1) / kInt8Mt), 1);
   const int shift = Log2Of(w.block_size);
+  const bool chunked = (w.row_bytes % 16) == 0 && (reinterpret_cast<std::uintptr_t>(w.b) & 15u) == 0 &&
+                       !(w.bits == 4 && w.block_size < 32);
+  if (!chunked) {
+    // groups of eight codes: one aligned 4-byte (4-bit) or 8-byte (8-bit) load each; `aq` rows are a
+    // multiple of 16 bytes in the padded layout
+    const std::uintptr_t group_bytes = static_cast<std::uintptr_t>(w.bits);
+    if ((reinterpret_cast<std::uintptr_t>(w.b) % group_bytes) != 0 || (w.row_bytes % group_bytes) != 0 ||
+        (reinterpret_cast<std::uintptr_t>(aq) & 7u) != 0) {
+      return nullptr;
+    }
+    if (w.bits == 4) {
+      nbits_int8_words_kernel<4><<<grid, 256, 0, stream>>>(w, aq, aq_ld, a_scales, static_cast<int>(m), out, shift);
+    } else {
+      nbits_int8_words_kernel<8><<<grid, 256, 0, stream>>>(w, aq, aq_ld, a_scales, static_cast<int>(m), out, shift);
+    }
+    if (cudaGetLastError() != cudaSuccess) {
+      return nullptr;
+    }
+    CountLaunch();
+    return w.bits == 4 ? "nbits_int8_words_kernel<4>" : "nbits_int8_words_kernel<8>";
+  }
   if (w.bits == 4) {
     nbits_int8_matmul_kernel<4><<<grid, 256, 0, stream>>>(w, aq, aq_ld, a_scales, static_cast<int>(m), out, shift);
   } else {

@@ -46,6 +46,11 @@ SHAPES = (
     ("mid_cfg2_m256", 256, 4096, 14336, 4, 128, True, True, 0),
     ("mid_cfg3_m64", 64, 4096, 4096, 4, 64, True, False, 0),
     ("mid_cfg3_m256", 256, 4096, 4096, 4, 64, True, False, 0),
+    # shapes outside the staged kernels: 8-bit rows too long for whole-row stages, blocks of sixteen
+    ("down8_m1", 1, 14336, 4096, 8, 128, True, False, 0),
+    ("down8_m8", 8, 14336, 4096, 8, 128, True, False, 0),
+    ("block16_m1", 1, 4096, 14336, 4, 16, True, False, 0),
+    ("block16_m8", 8, 4096, 14336, 4, 16, True, False, 0),
 )
 
 

@@ -133,8 +133,8 @@ DECODE_EDGES = [
     (1, 4096, 77, 8, 32, True, True),       # 8-bit
     (7, 4096, 50, 8, 128, False, False),
     (16, 2048, 31, 8, 16, True, True),
-    (1, 4000, 33, 4, 32, True, True),       # K not a multiple of the chunk: generic kernel
-    (2, 96, 5, 4, 16, True, False),         # block 16: generic kernel
+    (1, 4000, 33, 4, 32, True, True),       # K not a multiple of the chunk: word-wise kernel
+    (2, 96, 5, 4, 16, True, False),         # block 16: word-wise kernel
     (1, 40, 3, 8, 32, True, True),          # partial last block
     (16, 4096, 2, 4, 128, True, True),
 ]
@@ -549,15 +549,47 @@ def test_generic_kernel_matches_stream_kernel(cuda_device):
     a = torch.from_numpy(case.a).cuda()
     y1 = torch.empty((2, 513), device="cuda")
     weights.matmul_device(a, y1, path=_capi.PATH_GEMV)
-    # block_size 16 is outside what the stream kernel takes, so it runs on the generic one
+    # block_size 16 is outside what the stream kernel takes, so it runs on the word-wise one
     case2 = syn.make_case("cross", 2, 4096, 513, 4, 16, seed=42, bias=True)
     torch.cuda.synchronize()
     assert _capi.last_kernel().startswith("nbits_gemv_stream")
     y_ref = oracle_f64(case)
     assert rel_err(y1.cpu().numpy(), y_ref) <= TOL_FP32
     y2, kernel2 = run_device(case2)
-    assert kernel2 == "nbits_gemv_generic_kernel"
+    assert kernel2 == "nbits_gemv_words_kernel"
     assert rel_err(y2, oracle_f64(case2)) <= TOL_FP32
+
+
+# Shapes no staged kernel takes: block_size 16, 8-bit rows too long for whole-row stages, K that is
+# not a multiple of eight (scalar activation loads), ragged N, more tokens than one pass takes.
+WORDS_CASES = [
+    # m, k, n, bits, block, zp, bias
+    (1, 4096, 515, 4, 16, True, True),
+    (2, 1024, 33, 4, 16, False, False),
+    (3, 8192, 70, 4, 16, True, False),
+    (7, 4096, 129, 4, 16, True, True),
+    (16, 2048, 31, 4, 16, False, True),
+    (1, 14336, 257, 8, 128, True, True),
+    (2, 14336, 64, 8, 32, False, False),
+    (5, 14336, 100, 8, 64, True, False),
+    (16, 14336, 37, 8, 256, True, True),
+    (4, 8192, 50, 8, 16, True, False),
+    (20, 1024, 45, 8, 16, True, True),       # three passes of eight tokens
+    (40, 512, 19, 4, 16, True, False),       # five passes
+    (3, 1003, 21, 4, 16, True, True),        # K odd: scalar activation loads, a partly filled last group
+    (18, 72, 5, 8, 16, False, True),         # partial last block
+    (9, 14336, 40, 8, 512, True, True),      # a block longer than a chunk of 256 codes
+    (19, 264, 300, 8, 16, True, False),      # a last chunk of one group, more columns than one CTA
+]
+
+
+@pytest.mark.parametrize("m,k,n,bits,bs,zp,bias", WORDS_CASES)
+def test_word_wise_kernel(cuda_device, m, k, n, bits, bs, zp, bias):
+    case = syn.make_case("words", m, k, n, bits, bs, seed=m * 31 + n, zero_points=zp, bias=bias)
+    y, kernel = run_device(case)
+    # lanes along K for one and two tokens, a lane per output column from three tokens on
+    assert kernel == ("nbits_gemv_words_kernel" if m <= 2 else "nbits_gemv_columns_kernel"), kernel
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
 
 
 def test_strided_output_window(cuda_device):
@@ -773,6 +805,18 @@ def test_int8_block_dots_bit_exact(cuda_device, bits, bs, k, n):
     weights.int8_block_dots(torch.from_numpy(aq).cuda(), dots)
     torch.cuda.synchronize()
     assert np.array_equal(dots.cpu().numpy(), o.int8_block_dots(aq, case.b, case.zero_points, n, k, bits, bs))
+
+
+@pytest.mark.parametrize("m,k,n,bits,bs,zp", [(5, 80, 7, 4, 16, True), (16, 4096, 33, 4, 16, False),
+                                              (20, 1000, 12, 4, 16, True), (3, 72, 5, 8, 16, True)])
+def test_int8_path_block16(cuda_device, m, k, n, bits, bs, zp):
+    """accuracy_level 4 under AUTO with blocks of sixteen: groups of eight codes for 4-bit weights."""
+    case = syn.make_case("lvl4b16", m, k, n, bits, bs, seed=m + n, zero_points=zp, bias=True)
+    y, kernel = run_device(case, accuracy_level=4)
+    assert kernel == ("nbits_int8_words_kernel<4>" if bits == 4 else "nbits_int8_matmul_kernel<8>"), kernel
+    ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, bits, bs)
+    assert rel_err(y, ref) <= TOL_FP32
+    assert rel_err(y, oracle_f64(case)) <= 3e-2   # int8 activations vs exact
 
 
 @pytest.mark.parametrize("m,k,n,bits,bs,zp", [(16, 4096, 128, 4, 32, False), (1, 4096, 77, 4, 128, True),
