@@ -404,6 +404,15 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
         name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
       }
     }
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && w.bits == 8 &&
+        (m >= 8 || (m >= 3 && (w.n + 31) / 32 <= h->sm_count))) {
+      // 8-bit weights: the staged kernel below takes two tokens per pass over the weights, the
+      // lane-per-column kernel eight. Measured, us per call, staged against lane-per-column:
+      // K = 4096, N = 14336 M = 4 / 8 / 16: 51.8 / 97.1 / 189 against 56.0 / 81.3 / 148;
+      // K = 8192, N = 4096: M = 3 / 8 / 16 42.7 / 83.6 / 161 against 31.4 / 45.5 / 78.5 (a node of at
+      // most one 32-column CTA per SM runs sixteen warps along K).
+      name = mnb::LaunchGemvWords(w, a_dev, m, out, stream, h->sm_count);
+    }
     if (name == nullptr && m <= 16) {
       name = mnb::LaunchGemvStream(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
     }
@@ -429,7 +438,7 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       }
     }
     if (name == nullptr) {
-      name = mnb::LaunchGemvGeneric(w, a_dev, m, out, stream);
+      name = mnb::LaunchGemvGeneric(w, a_dev, m, out, stream, h->sm_count);
     }
     break;
   }

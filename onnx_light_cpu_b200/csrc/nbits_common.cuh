@@ -226,11 +226,12 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
 // Any geometry and any token count (passes of sixteen tokens): the word-wise kernel below when the
 // packed rows allow it, else one code at a time.
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                              cudaStream_t stream);
-// One warp per output column (two from three tokens on), lanes on groups of eight codes read straight from
-// global memory; needs rows and the base of B aligned to a group (4 bytes for 4-bit, 8 for 8-bit weights).
+                              cudaStream_t stream, int sm_count);
+// Groups of eight codes read straight from global memory: a warp per output column with lanes along K for
+// one and two tokens, a lane per column from three tokens on; needs rows and the base of B aligned to a
+// group (4 bytes for 4-bit, 8 for 8-bit weights).
 const char *LaunchGemvWords(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                            cudaStream_t stream);
+                            cudaStream_t stream, int sm_count);
 // Prepared side array used by the MMA decode kernel: per (8-row half tile, task slice) one
 // record {float scale[8][scale_row_floats]; uint8 zp[8][bpt] (only with zero points)}. bytes == 0 means
 // the geometry is outside what that kernel takes.

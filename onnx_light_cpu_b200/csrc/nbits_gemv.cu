@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(256)
 // the activations as broadcast loads, four tokens at a time so that four dot products are in
 // flight. The partial sums of the warps meet in shared memory at the end. No CTA-wide barrier in
 // the loop.
-constexpr int kColumnsWarps = 8;
+constexpr int kColumnsWarps = 8;      // sixteen when the node has no more 32-column CTAs than the GPU has SMs
 constexpr int kColumnsChunk = 16;      // groups per chunk
 constexpr int kColumnsWordStride = 17; // words of a column in the tile, padded
 constexpr int kColumnsMetaStride = 9;  // up to 8 blocks per chunk (block_size 16), padded
@@ -652,7 +652,7 @@ template <int BITS, int MT> __host__ __device__ constexpr int ColumnsWarpBytes()
 }
 
 template <int BITS, int MT>
-__global__ void __launch_bounds__(kColumnsWarps * 32)
+__global__ void __launch_bounds__(2 * kColumnsWarps * 32)
     nbits_gemv_columns_kernel(const WeightView w, const float *a, int m_total, OutputView out, int block_shift,
                               int a_vector, std::uint32_t magic) {
   static_assert(MT % 4 == 0, "tokens are taken four at a time");
@@ -663,6 +663,7 @@ __global__ void __launch_bounds__(kColumnsWarps * 32)
   const std::int64_t col0 = static_cast<std::int64_t>(blockIdx.x) * 32;
   const int m_base = blockIdx.y * MT;
   const int tokens = m_total - m_base < MT ? m_total - m_base : MT;
+  const int warps = static_cast<int>(blockDim.x >> 5);
   unsigned char *mine = columns_smem + warp * ColumnsWarpBytes<BITS, MT>();
   Word *words = reinterpret_cast<Word *>(mine);
   float2 *meta = reinterpret_cast<float2 *>(mine + ColumnsWordBytes<BITS>());
@@ -680,7 +681,7 @@ __global__ void __launch_bounds__(kColumnsWarps * 32)
   const int blocks_per_chunk = (kChunkCodes >> block_shift) > 0 ? (kChunkCodes >> block_shift) : 1;
   const int columns_here = w.n - col0 < 32 ? static_cast<int>(w.n - col0) : 32;
 
-  for (int chunk = warp; chunk < chunks; chunk += kColumnsWarps) {
+  for (int chunk = warp; chunk < chunks; chunk += warps) {
     const int g0 = chunk * kColumnsChunk;
     const std::int64_t k_first = static_cast<std::int64_t>(g0) * 8;
     const int first_block = static_cast<int>(k_first >> block_shift);
@@ -795,13 +796,12 @@ __global__ void __launch_bounds__(kColumnsWarps * 32)
     partial[(warp * MT + mi) * 32 + lane] = acc[mi];
   }
   __syncthreads();
-  for (int item = threadIdx.x; item < tokens * 32; item += kColumnsWarps * 32) {
+  for (int item = threadIdx.x; item < tokens * 32; item += warps * 32) {
     const int mi = item >> 5;
     const int c = item & 31;
     if (c < columns_here) {
       float total = 0.0f;
-#pragma unroll
-      for (int wi = 0; wi < kColumnsWarps; ++wi) {
+      for (int wi = 0; wi < warps; ++wi) {
         total += partial[(wi * MT + mi) * 32 + c];
       }
       const float bias = w.bias != nullptr ? __ldg(w.bias + col0 + c) : 0.0f;
@@ -934,23 +934,27 @@ cudaError_t LaunchWordsInstance(const WeightView &w, const float *a, std::int64_
 
 template <int BITS, int MT>
 cudaError_t LaunchColumnsInstance(const WeightView &w, const float *a, std::int64_t m, OutputView out, int a_vector,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, int sm_count) {
   auto kernel = nbits_gemv_columns_kernel<BITS, MT>;
-  constexpr int kSmem = kColumnsWarps * ColumnsWarpBytes<BITS, MT>();
-  static_assert(kSmem >= kColumnsWarps * MT * 32 * 4, "the partial sums reuse the tiles");
-  const cudaError_t attr = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+  static_assert(ColumnsWarpBytes<BITS, MT>() >= MT * 32 * 4, "the partial sums reuse the tiles");
+  dim3 grid(static_cast<unsigned>((w.n + 31) / 32), static_cast<unsigned>((m + MT - 1) / MT), 1);
+  // a narrow node in one pass leaves SMs with one CTA or none: twice the warps along K then
+  const int warps = static_cast<std::int64_t>(grid.x) * grid.y <= (sm_count > 0 ? sm_count : 148) ? 2 * kColumnsWarps
+                                                                                                  : kColumnsWarps;
+  const int smem = warps * ColumnsWarpBytes<BITS, MT>();
+  const cudaError_t attr =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kColumnsWarps * ColumnsWarpBytes<BITS, MT>());
   if (attr != cudaSuccess) {
     return attr;
   }
-  dim3 grid(static_cast<unsigned>((w.n + 31) / 32), static_cast<unsigned>((m + MT - 1) / MT), 1);
-  kernel<<<grid, kColumnsWarps * 32, kSmem, stream>>>(w, a, static_cast<int>(m), out, Log2Exact(w.block_size),
+  kernel<<<grid, warps * 32, smem, stream>>>(w, a, static_cast<int>(m), out, Log2Exact(w.block_size),
                                                       a_vector, kMagicBits);
   return cudaGetLastError();
 }
 
 template <int BITS>
 cudaError_t LaunchWordsBits(const WeightView &w, const float *a, std::int64_t m, OutputView out, int a_vector,
-                            cudaStream_t stream, const char **name) {
+                            cudaStream_t stream, int sm_count, const char **name) {
   *name = "nbits_gemv_words_kernel";
   if (m == 1) {
     return LaunchWordsInstance<BITS, 1>(w, a, m, out, a_vector, stream);
@@ -960,15 +964,15 @@ cudaError_t LaunchWordsBits(const WeightView &w, const float *a, std::int64_t m,
   }
   *name = "nbits_gemv_columns_kernel";
   if (m <= 4) {
-    return LaunchColumnsInstance<BITS, 4>(w, a, m, out, a_vector, stream);
+    return LaunchColumnsInstance<BITS, 4>(w, a, m, out, a_vector, stream, sm_count);
   }
-  return LaunchColumnsInstance<BITS, kColumnsTokens>(w, a, m, out, a_vector, stream); // more tokens: passes of eight
+  return LaunchColumnsInstance<BITS, kColumnsTokens>(w, a, m, out, a_vector, stream, sm_count); // more tokens: passes of eight
 }
 
 } // namespace
 
 const char *LaunchGemvWords(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int sm_count) {
   if (m < 1 || w.n < 1 || w.k < 1 || w.k > (std::int64_t{1} << 30) || (w.bits != 4 && w.bits != 8) ||
       w.block_size < 16) {
     return nullptr;
@@ -980,8 +984,8 @@ const char *LaunchGemvWords(const WeightView &w, const float *a, std::int64_t m,
   }
   const int a_vector = (w.k % 4) == 0 && (reinterpret_cast<std::uintptr_t>(a) & 15u) == 0 ? 1 : 0;
   const char *name = nullptr;
-  const cudaError_t err = w.bits == 4 ? LaunchWordsBits<4>(w, a, m, out, a_vector, stream, &name)
-                                      : LaunchWordsBits<8>(w, a, m, out, a_vector, stream, &name);
+  const cudaError_t err = w.bits == 4 ? LaunchWordsBits<4>(w, a, m, out, a_vector, stream, sm_count, &name)
+                                      : LaunchWordsBits<8>(w, a, m, out, a_vector, stream, sm_count, &name);
   if (err != cudaSuccess) {
     return nullptr;
   }
@@ -990,11 +994,11 @@ const char *LaunchGemvWords(const WeightView &w, const float *a, std::int64_t m,
 }
 
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, int sm_count) {
   if (m < 1 || w.n < 1) {
     return nullptr;
   }
-  if (const char *words = LaunchGemvWords(w, a, m, out, stream)) {
+  if (const char *words = LaunchGemvWords(w, a, m, out, stream, sm_count)) {
     return words;
   }
   cudaGetLastError();

@@ -583,6 +583,21 @@ WORDS_CASES = [
 ]
 
 
+@pytest.mark.parametrize("m,k,n,bs,expected", [
+    (2, 4096, 200, 32, "nbits_gemv_stream_kernel"),        # two tokens: one pass of the staged kernel
+    (3, 4096, 200, 32, "nbits_gemv_columns_kernel"),       # a narrow node from three tokens on
+    (8, 4096, 5000, 128, "nbits_gemv_columns_kernel"),     # any node from eight tokens on
+    (7, 4096, 5000, 128, "nbits_gemv_stream_kernel"),      # a wide node below that
+    (16, 8192, 333, 64, "nbits_gemv_columns_kernel"),
+])
+def test_eight_bit_tokens_take_the_lane_per_column_kernel(cuda_device, m, k, n, bs, expected):
+    """8-bit weights under AUTO: the kernel that reads the weights once per eight tokens where it is faster."""
+    case = syn.make_case("u8tokens", m, k, n, 8, bs, seed=m + n, zero_points=True, bias=True)
+    y, kernel = run_device(case)
+    assert kernel.startswith(expected), kernel
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+
+
 @pytest.mark.parametrize("m,k,n,bits,bs,zp,bias", WORDS_CASES)
 def test_word_wise_kernel(cuda_device, m, k, n, bits, bs, zp, bias):
     case = syn.make_case("words", m, k, n, bits, bs, seed=m * 31 + n, zero_points=zp, bias=bias)
