@@ -24,6 +24,7 @@ CUDA_SOURCES = [
     "csrc/nbits_gemv_mma.cu",
     "csrc/nbits_gemv_mma_multi.cu",
     "csrc/nbits_gemv_imma.cu",
+    "csrc/nbits_gemv_u8_mma.cu",
     "csrc/nbits_decode_direct.cu",
     "csrc/nbits_decode_resident.cu",
     "csrc/nbits_int8.cu",

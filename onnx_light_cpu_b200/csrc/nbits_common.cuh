@@ -227,6 +227,13 @@ const char *LaunchGemvStream(const WeightView &w, const float *a, std::int64_t m
 // packed rows allow it, else one code at a time.
 const char *LaunchGemvGeneric(const WeightView &w, const float *a, std::int64_t m, OutputView out,
                               cudaStream_t stream, int sm_count);
+// 8-bit weights, up to sixteen tokens: activations as three base-128 digit columns of an integer MMA whose
+// other operand is the codes as they lie in B (blocks of 32 ... 256, B 16-byte aligned, K <= 32768). Two
+// launches (digits, multiply); `scratch` holds the digits, their block sums and the row factors.
+bool GemvU8MmaSupports(const WeightView &w, std::int64_t m);
+std::size_t GemvU8MmaScratchBytes(const WeightView &w, std::int64_t m);
+const char *LaunchGemvU8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch, OutputView out,
+                            cudaStream_t stream, int sm_count);
 // Groups of eight codes read straight from global memory: a warp per output column with lanes along K for
 // one and two tokens, a lane per column from three tokens on; needs rows and the base of B aligned to a
 // group (4 bytes for 4-bit, 8 for 8-bit weights).

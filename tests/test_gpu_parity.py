@@ -571,8 +571,8 @@ WORDS_CASES = [
     (16, 2048, 31, 4, 16, False, True),
     (1, 14336, 257, 8, 128, True, True),
     (2, 14336, 64, 8, 32, False, False),
-    (5, 14336, 100, 8, 64, True, False),
-    (16, 14336, 37, 8, 256, True, True),
+    (4, 14336, 100, 8, 64, True, False),
+    (16, 14336, 37, 8, 512, True, True),
     (4, 8192, 50, 8, 16, True, False),
     (20, 1024, 45, 8, 16, True, True),       # three passes of eight tokens
     (40, 512, 19, 4, 16, True, False),       # five passes
@@ -585,17 +585,65 @@ WORDS_CASES = [
 
 @pytest.mark.parametrize("m,k,n,bs,expected", [
     (2, 4096, 200, 32, "nbits_gemv_stream_kernel"),        # two tokens: one pass of the staged kernel
-    (3, 4096, 200, 32, "nbits_gemv_columns_kernel"),       # a narrow node from three tokens on
-    (8, 4096, 5000, 128, "nbits_gemv_columns_kernel"),     # any node from eight tokens on
-    (7, 4096, 5000, 128, "nbits_gemv_stream_kernel"),      # a wide node below that
-    (16, 8192, 333, 64, "nbits_gemv_columns_kernel"),
+    (3, 4096, 200, 32, "nbits_gemv_columns_kernel"),       # a narrow node, three and four tokens
+    (4, 4096, 5000, 128, "nbits_gemv_stream_kernel"),      # a wide node, three and four tokens
+    (5, 4096, 5000, 128, "nbits_gemv_u8_mma_kernel"),      # five tokens and more: integer tensor cores
+    (16, 8192, 333, 64, "nbits_gemv_u8_mma_kernel"),
+    (8, 4096, 200, 512, "nbits_gemv_columns_kernel"),      # blocks the tensor-core kernel does not take
 ])
-def test_eight_bit_tokens_take_the_lane_per_column_kernel(cuda_device, m, k, n, bs, expected):
-    """8-bit weights under AUTO: the kernel that reads the weights once per eight tokens where it is faster."""
+def test_eight_bit_decode_kernels_under_auto(cuda_device, m, k, n, bs, expected):
     case = syn.make_case("u8tokens", m, k, n, 8, bs, seed=m + n, zero_points=True, bias=True)
     y, kernel = run_device(case)
     assert kernel.startswith(expected), kernel
     assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+
+
+# 8-bit weights on integer tensor cores: every block size it takes, with and without zero points and
+# bias, one and two column tiles of tokens, ragged N (a last row tile that is partly filled, fewer rows
+# than one tile), K that is not a multiple of the block (padding codes meet zero digits), rows long
+# enough for several tiles of weights per warp and short enough for less than one.
+U8_MMA_CASES = [
+    # m, k, n, block, zp, bias
+    (5, 4096, 77, 32, True, True),
+    (8, 4096, 149, 64, True, False),
+    (8, 1024, 300, 128, False, True),
+    (9, 8192, 40, 256, True, True),
+    (16, 14336, 37, 32, True, True),
+    (5, 4000, 33, 32, True, True),
+    (16, 4096, 1000, 128, True, False),
+    (6, 40, 3, 32, True, True),
+    (13, 14336, 260, 128, False, False),
+    (7, 96, 16, 32, True, False),
+    (16, 2048, 2100, 64, True, True),
+]
+
+
+@pytest.mark.parametrize("m,k,n,bs,zp,bias", U8_MMA_CASES)
+def test_eight_bit_tensor_core_decode(cuda_device, m, k, n, bs, zp, bias):
+    case = syn.make_case("u8mma", m, k, n, 8, bs, seed=3 * m + n, zero_points=zp, bias=bias)
+    y, kernel = run_device(case)
+    assert kernel == "nbits_gemv_u8_mma_kernel", kernel
+    assert rel_err(y, oracle_f64(case)) <= TOL_FP32
+    assert rel_err(y, o.matmul_f32(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 8, bs)) <= TOL_FP32
+
+
+def test_eight_bit_tensor_core_decode_special_rows(cuda_device):
+    """A token of zeros gives the bias; a NaN in a token reaches all of that token's outputs and no other;
+    a token 2^40 times larger than the others keeps its relative error (each token has its own factor)."""
+    case = syn.make_case("u8rows", 6, 1024, 70, 8, 64, seed=11, zero_points=True, bias=True)
+    case.a[1] = 0.0
+    case.a[3, 17] = np.nan
+    case.a[4] *= np.float32(2.0 ** 40)
+    case.a[5] *= np.float32(2.0 ** -110)
+    y, kernel = run_device(case)
+    assert kernel == "nbits_gemv_u8_mma_kernel", kernel
+    assert np.array_equal(y[1], case.bias)
+    assert np.isnan(y[3]).all()
+    ref = oracle_f64(case)
+    for token in (0, 2, 4):
+        assert rel_err(y[token], ref[token]) <= TOL_FP32, token
+    assert not np.isnan(y[5]).any()
+    assert np.abs(y[5] - case.bias).max() <= 1e-20
 
 
 @pytest.mark.parametrize("m,k,n,bits,bs,zp,bias", WORDS_CASES)
