@@ -35,7 +35,9 @@ typedef enum mnb_status {
   MNB_ERR_DEVICE_TIMEOUT = 4    /* a bounded device-side wait gave up; context still usable */
 } mnb_status;
 
-/* Which kernel family runs. AUTO picks by M and accuracy_level. */
+/* Which kernel family runs. AUTO picks by M, bits, block_size and accuracy_level and always finds a kernel
+ * for a valid node: shapes none of the families below takes (block_size 16, rows of any length, odd sizes)
+ * run on word-wise CUDA-core kernels; 8-bit weights with 5 <= M <= 16 run on integer tensor cores. */
 typedef enum mnb_path {
   MNB_PATH_AUTO = 0,
   MNB_PATH_GEMV = 1,    /* CUDA-core fused unpack-dequant GEMV, fp32 accumulate (decode) */
@@ -50,7 +52,7 @@ typedef enum mnb_path {
   MNB_PATH_GEMV_DIRECT = 10, /* decode on integer MMA with the weights streamed from global memory straight into each warp
                                (no staging ring), M <= 2, block_size 128; AUTO's choice for M = 1 where the resident kernel does not fit */
   MNB_PATH_GEMV_RESIDENT = 11 /* decode of one token on integer MMA: a producer warp asks the TMA unit for the CTA's whole
-                                 share of the weights at kernel start; block_size 128; AUTO's first choice for M = 1 */
+                                 share of the weights at kernel start; block_size 128 or 32; AUTO's first choice for M = 1 */
 } mnb_path;
 
 /* Device-resident, immutable weights of one MatMulNBits node. Plays the role the reference
