@@ -187,7 +187,6 @@ struct U8Params {
   int m_total;
   int parts;            // warps that share a row tile, each on a run of quantization blocks
   int blocks_per_part;
-  int step_shift;       // log2(32-k steps per quantization block)
   int steps;
   int tiles;
 };
@@ -196,9 +195,13 @@ constexpr int kU8Super = 8;                              // 32-k steps per tile 
 constexpr int kU8TileRowBytes = kU8Super * 32 + 32;      // 256 bytes of a row, padded: fragment reads hit 32 banks
 constexpr int kU8TileBytes = 16 * kU8TileRowBytes;
 
-template <int NTOK>
+// SPB = 32-k steps per quantization block (1, 2, 4, 8): a part of K starts on a block and tiles are eight steps,
+// so where a block starts and ends inside a tile is known at compile time (a fresh accumulator there, no
+// clearing, no test per step).
+template <int NTOK, int SPB>
 __global__ void __launch_bounds__(kU8Warps * 32)
     nbits_gemv_u8_mma_kernel(const U8Params p) {
+  static_assert(SPB == 1 || SPB == 2 || SPB == 4 || SPB == 8, "blocks of 32 ... 256");
   constexpr int NT = kDigits * NTOK;   // MMA column tiles
   constexpr int kCols = NT * 8;
   __shared__ __align__(16) unsigned char tiles[kU8Warps][kU8TileBytes];
@@ -243,9 +246,8 @@ __global__ void __launch_bounds__(kU8Warps * 32)
   if (!live || block_begin > block_end) {
     block_begin = block_end = 0;
   }
-  const int s_begin = block_begin << p.step_shift;
-  const int s_end = (block_end << p.step_shift) < p.steps ? (block_end << p.step_shift) : p.steps;
-  const int block_mask = (1 << p.step_shift) - 1;
+  const int s_begin = block_begin * SPB;
+  const int s_end = block_end * SPB < p.steps ? block_end * SPB : p.steps;
 
   uint4 next[kU8Super];
   auto request = [&](int s_first) {
@@ -266,13 +268,7 @@ __global__ void __launch_bounds__(kU8Warps * 32)
   // the digits come from the kernel launched just before; the weights above do not depend on it
   ptx::GridDependencyWait();
   int d[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      d[nt][i] = 0;
-    }
-  }
+  const ZeroQuad zero = MakeZeroQuad();
 #pragma unroll 1
   for (int s0 = s_begin; s0 < s_end; s0 += kU8Super) {
     __syncwarp(); // the tile before has been read
@@ -285,12 +281,12 @@ __global__ void __launch_bounds__(kU8Warps * 32)
       request(s0 + kU8Super);
     }
     // the digits of a step are asked for one step ahead (a step beyond the part reads the last one again)
-    uint2 bq_next[NT];
+    uint2 bq[2][NT];
     {
       const unsigned char *digit_step = digit_lane + s0 * (kCols * 32);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        bq_next[nt] = __ldg(reinterpret_cast<const uint2 *>(digit_step + nt * 256));
+        bq[0][nt] = __ldg(reinterpret_cast<const uint2 *>(digit_step + nt * 256));
       }
     }
 #pragma unroll
@@ -299,27 +295,26 @@ __global__ void __launch_bounds__(kU8Warps * 32)
       if (s < s_end) {
         const uint2 lo = *reinterpret_cast<const uint2 *>(frag_lo + u * 32);
         const uint2 hi = *reinterpret_cast<const uint2 *>(frag_hi + u * 32);
-        uint2 bq[NT];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          bq[nt] = bq_next[nt];
-        }
         if (u + 1 < kU8Super) {
           const int ahead = s + 1 < s_end ? s + 1 : s;
           const unsigned char *digit_step = digit_lane + ahead * (kCols * 32);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            bq_next[nt] = __ldg(reinterpret_cast<const uint2 *>(digit_step + nt * 256));
+            bq[(u + 1) & 1][nt] = __ldg(reinterpret_cast<const uint2 *>(digit_step + nt * 256));
           }
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           // k slots 4 t ... of the MMA: bytes 8 t ... 8 t + 3 of the step; slots 16 + 4 t ...: bytes 8 t + 4 ...
-          ImmaAdd(d[nt], lo.x, hi.x, lo.y, hi.y, bq[nt].x, bq[nt].y);
+          if (u % SPB == 0) {
+            ImmaFresh(d[nt], lo.x, hi.x, lo.y, hi.y, bq[u & 1][nt].x, bq[u & 1][nt].y, zero);
+          } else {
+            ImmaAdd(d[nt], lo.x, hi.x, lo.y, hi.y, bq[u & 1][nt].x, bq[u & 1][nt].y);
+          }
         }
-        if (((s + 1) & block_mask) == 0 || s + 1 == s_end) {
+        if ((u + 1) % SPB == 0) {
           // a quantization block is complete
-          const int block = s >> p.step_shift;
+          const int block = s / SPB;
           const float ws_lo = __ldg(scale_lo + block);
           const float ws_hi = __ldg(scale_hi + block);
           const int z_lo = zp_lo != nullptr ? static_cast<int>(__ldg(zp_lo + block)) : 128;
@@ -337,10 +332,6 @@ __global__ void __launch_bounds__(kU8Warps * 32)
               f[1] = fmaf(weight, static_cast<float>(d[nt][1] - z_lo * sd.y), f[1]);
               f[2] = fmaf(weight, static_cast<float>(d[nt][2] - z_hi * sd.x), f[2]);
               f[3] = fmaf(weight, static_cast<float>(d[nt][3] - z_hi * sd.y), f[3]);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                d[nt][i] = 0;
-              }
             }
             acc[j][0] = fmaf(ws_lo, f[0], acc[j][0]);
             acc[j][1] = fmaf(ws_lo, f[1], acc[j][1]);
@@ -382,14 +373,6 @@ __global__ void __launch_bounds__(kU8Warps * 32)
   }
 }
 
-int Log2Floor(int v) {
-  int l = 0;
-  while ((2 << l) <= v) {
-    ++l;
-  }
-  return l;
-}
-
 } // namespace
 
 bool GemvU8MmaSupports(const WeightView &w, std::int64_t m) {
@@ -429,7 +412,6 @@ const char *LaunchGemvU8Mma(const WeightView &w, const float *a, std::int64_t m,
   p.undo = reinterpret_cast<const float *>(scratch + layout.undo_offset);
   p.out = out;
   p.m_total = static_cast<int>(m);
-  p.step_shift = Log2Floor(steps_per_block);
   p.steps = layout.steps;
   p.tiles = static_cast<int>((w.n + 15) / 16);
   // warps per row tile: towards sixteen warps per SM, every part at least four blocks
@@ -453,8 +435,24 @@ const char *LaunchGemvU8Mma(const WeightView &w, const float *a, std::int64_t m,
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = 1;
-  const cudaError_t launched = ntok == 1 ? cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<1>, p)
-                                         : cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<2>, p);
+  cudaError_t launched = cudaErrorInvalidValue;
+  if (ntok == 1) {
+    switch (steps_per_block) {
+    case 1: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<1, 1>, p); break;
+    case 2: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<1, 2>, p); break;
+    case 4: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<1, 4>, p); break;
+    case 8: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<1, 8>, p); break;
+    default: break;
+    }
+  } else {
+    switch (steps_per_block) {
+    case 1: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<2, 1>, p); break;
+    case 2: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<2, 2>, p); break;
+    case 4: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<2, 4>, p); break;
+    case 8: launched = cudaLaunchKernelEx(&config, nbits_gemv_u8_mma_kernel<2, 8>, p); break;
+    default: break;
+    }
+  }
   if (launched != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
