@@ -404,11 +404,13 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
         name = mnb::LaunchGemvMma(w, a_dev, m, out, h->status_dev, stream, h->sm_count);
       }
     }
-    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && w.bits == 8 && m >= 5) {
-      // 8-bit weights, five tokens and more: digit columns on integer tensor cores, one pass over the weights
-      // whatever the token count (us per call against the CUDA-core kernels below, K = 4096: N = 16032 block
-      // 32 57 for M = 1 ... 8 against 54 at M = 4 and 95 at M = 8; N = 14336 block 128 46 against 52 / 81;
-      // N = 4096 block 64 21 against 17 / 23, M = 16 31 against 41; below five tokens those are ahead)
+    if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && w.bits == 8 &&
+        (m >= 5 || (m >= 3 && (w.n + 31) / 32 > h->sm_count))) {
+      // 8-bit weights, five tokens and more (three and more on nodes wider than one 32-column CTA per SM):
+      // digit columns on integer tensor cores, one pass over the weights and one duration for one to eight
+      // tokens (us per call against the CUDA-core kernels below, K = 4096: N = 16032 block 32 45 against 29 at
+      // M = 2, 53 at M = 3, 54 at M = 4 and 95 at M = 8; N = 4096 block 64 21 against 17 at M = 3, 4 and
+      // 23 / 41 at M = 8 / 16)
       const std::size_t need = mnb::GemvU8MmaScratchBytes(w, m);
       if (need != 0) {
         const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);

@@ -6,8 +6,8 @@
 // digits of the tokens are signed-byte MMA columns (digit-major: column tile d * NTOK + j holds digit
 // d of tokens 8 j ... 8 j + 7, so the three digits of a token meet in one lane and register). Per
 // quantization block the three int32 sums are exact (< 2^24 for blocks of up to 256); the zero point
-// leaves as e_d - zp * (sum of the block's digits d) in int32, the digits are combined in fp32 as
-// 16384 f0 + 128 f1 + f2 and one FFMA applies the block's scale. The row factor max / 2e6 and the bias
+// leaves as e - zp * (sum of the block's digits) in int32, for the high digit on its own and for
+// 128 e1 + e2 together; 16384 f0 + f12 in fp32 and one FFMA applies the block's scale. The row factor max / 2e6 and the bias
 // are applied at the end.
 //
 // Two launches: a small kernel writes the digit bytes, the per-block digit sums and the row factors
@@ -42,15 +42,16 @@ U8Layout LayoutFor(const WeightView &w, int ntok) {
   l.cols = kDigits * 8 * ntok;
   const std::size_t digits = static_cast<std::size_t>(l.steps) * l.cols * 32;
   l.sums_offset = (digits + 255) & ~std::size_t{255};
-  const std::size_t sums = static_cast<std::size_t>(w.n_blocks) * l.cols * sizeof(int);
+  const std::size_t sums = static_cast<std::size_t>(w.n_blocks) * 2 * 8 * ntok * sizeof(int);
   l.undo_offset = (l.sums_offset + sums + 255) & ~std::size_t{255};
   l.total = l.undo_offset + 8 * ntok * sizeof(float);
   return l;
 }
 
 // One CTA of 1024 threads per token slot (tokens beyond M get zeros), a thread per four consecutive k.
-// Digits: [step][column][32 k] signed bytes, column = digit * tokens_pad + token. Sums: [block][column]
-// int32. undo: [token].
+// Digits: [step][column][32 k] signed bytes, column = digit * tokens_pad + token. Sums: [block][2][token]
+// int32: the block's sum of the high digits, and 128 * (sum of the middle digits) + (sum of the low ones).
+// undo: [token].
 constexpr int kU8DigitThreads = 1024;
 
 __global__ void __launch_bounds__(kU8DigitThreads)
@@ -162,10 +163,8 @@ __global__ void __launch_bounds__(kU8DigitThreads)
         }
       }
     }
-#pragma unroll
-    for (int d = 0; d < kDigits; ++d) {
-      sums[static_cast<std::size_t>(block) * cols + d * tokens_pad + token] = total[d];
-    }
+    sums[static_cast<std::size_t>(block) * 2 * tokens_pad + token] = total[0];
+    sums[static_cast<std::size_t>(block) * 2 * tokens_pad + tokens_pad + token] = 128 * total[1] + total[2];
   }
 }
 
@@ -319,24 +318,28 @@ __global__ void __launch_bounds__(kU8Warps * 32)
           const float ws_hi = __ldg(scale_hi + block);
           const int z_lo = zp_lo != nullptr ? static_cast<int>(__ldg(zp_lo + block)) : 128;
           const int z_hi = zp_hi != nullptr ? static_cast<int>(__ldg(zp_hi + block)) : 128;
-          const int *sum_block = sum_lane + block * kCols;
+          const int *sum_block = sum_lane + block * (2 * 8 * NTOK);
 #pragma unroll
           for (int j = 0; j < NTOK; ++j) {
-            float f[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int digit = 0; digit < kDigits; ++digit) {
-              const int nt = digit * NTOK + j;
-              const int2 sd = __ldg(reinterpret_cast<const int2 *>(sum_block + nt * 8));
-              const float weight = digit == 0 ? 16384.0f : (digit == 1 ? 128.0f : 1.0f);
-              f[0] = fmaf(weight, static_cast<float>(d[nt][0] - z_lo * sd.x), f[0]);
-              f[1] = fmaf(weight, static_cast<float>(d[nt][1] - z_lo * sd.y), f[1]);
-              f[2] = fmaf(weight, static_cast<float>(d[nt][2] - z_hi * sd.x), f[2]);
-              f[3] = fmaf(weight, static_cast<float>(d[nt][3] - z_hi * sd.y), f[3]);
-            }
-            acc[j][0] = fmaf(ws_lo, f[0], acc[j][0]);
-            acc[j][1] = fmaf(ws_lo, f[1], acc[j][1]);
-            acc[j][2] = fmaf(ws_hi, f[2], acc[j][2]);
-            acc[j][3] = fmaf(ws_hi, f[3], acc[j][3]);
+            // high digit on its own, middle and low digit combined in int32 (|128 e1 + e2| < 2^30 for blocks
+            // of up to 256), the zero point out of both in int32, then 16384 f0 + f12 in fp32
+            const int2 s_high = __ldg(reinterpret_cast<const int2 *>(sum_block + j * 8));
+            const int2 s_rest = __ldg(reinterpret_cast<const int2 *>(sum_block + (NTOK + j) * 8));
+            const int *e0 = d[j];
+            const int *e1 = d[NTOK + j];
+            const int *e2 = d[2 * NTOK + j];
+            const float f0 = fmaf(16384.0f, static_cast<float>(e0[0] - z_lo * s_high.x),
+                                  static_cast<float>(128 * e1[0] + e2[0] - z_lo * s_rest.x));
+            const float f1 = fmaf(16384.0f, static_cast<float>(e0[1] - z_lo * s_high.y),
+                                  static_cast<float>(128 * e1[1] + e2[1] - z_lo * s_rest.y));
+            const float f2 = fmaf(16384.0f, static_cast<float>(e0[2] - z_hi * s_high.x),
+                                  static_cast<float>(128 * e1[2] + e2[2] - z_hi * s_rest.x));
+            const float f3 = fmaf(16384.0f, static_cast<float>(e0[3] - z_hi * s_high.y),
+                                  static_cast<float>(128 * e1[3] + e2[3] - z_hi * s_rest.y));
+            acc[j][0] = fmaf(ws_lo, f0, acc[j][0]);
+            acc[j][1] = fmaf(ws_lo, f1, acc[j][1]);
+            acc[j][2] = fmaf(ws_hi, f2, acc[j][2]);
+            acc[j][3] = fmaf(ws_hi, f3, acc[j][3]);
           }
         }
       }

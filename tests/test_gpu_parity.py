@@ -586,8 +586,9 @@ WORDS_CASES = [
 @pytest.mark.parametrize("m,k,n,bs,expected", [
     (2, 4096, 200, 32, "nbits_gemv_stream_kernel"),        # two tokens: one pass of the staged kernel
     (3, 4096, 200, 32, "nbits_gemv_columns_kernel"),       # a narrow node, three and four tokens
-    (4, 4096, 5000, 128, "nbits_gemv_stream_kernel"),      # a wide node, three and four tokens
-    (5, 4096, 5000, 128, "nbits_gemv_u8_mma_kernel"),      # five tokens and more: integer tensor cores
+    (2, 4096, 5000, 128, "nbits_gemv_stream_kernel"),      # a wide node, two tokens
+    (3, 4096, 5000, 128, "nbits_gemv_u8_mma_kernel"),      # a wide node from three tokens on: integer tensor cores
+    (5, 4096, 200, 128, "nbits_gemv_u8_mma_kernel"),       # any node from five tokens on
     (16, 8192, 333, 64, "nbits_gemv_u8_mma_kernel"),
     (8, 4096, 200, 512, "nbits_gemv_columns_kernel"),      # blocks the tensor-core kernel does not take
 ])
