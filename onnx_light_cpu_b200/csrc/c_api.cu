@@ -405,8 +405,9 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
       }
     }
     if (name == nullptr && m <= 16 && path == MNB_PATH_AUTO && w.bits == 8 &&
-        (m >= 5 || (m >= 3 && (w.n + 31) / 32 > h->sm_count))) {
-      // 8-bit weights, five tokens and more (three and more on nodes wider than one 32-column CTA per SM):
+        (m >= 5 || (m >= 3 && ((w.n + 31) / 32 > h->sm_count || w.k > 4096)))) {
+      // 8-bit weights, five tokens and more (three and more on nodes wider than one 32-column CTA per SM and
+      // on rows of more than 4096 k, where the lane-per-column kernel takes 52 us at K = 14336, N = 4096, M = 4):
       // digit columns on integer tensor cores, one pass over the weights and one duration for one to eight
       // tokens (us per call against the CUDA-core kernels below, K = 4096: N = 16032 block 32 45 against 29 at
       // M = 2, 53 at M = 3, 54 at M = 4 and 95 at M = 8; N = 4096 block 64 21 against 17 at M = 3, 4 and
@@ -451,6 +452,21 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
         }
         name = mnb::LaunchDigitSlicesGroup(&w, &out, 1, a_dev, m, static_cast<unsigned char *>(h->scratch_a),
                                            h->status_dev, stream, h->sm_count);
+        if (name == nullptr) {
+          cudaGetLastError();
+        }
+      }
+    }
+    if (name == nullptr && m >= 2 && m <= 16 && path == MNB_PATH_AUTO && w.bits == 8) {
+      // 8-bit rows too long for the staged kernel, two to four tokens: the tensor-core kernel before the
+      // word-wise ones (K = 14336, N = 4096, M = 2: 33 against 42 us)
+      const std::size_t need = mnb::GemvU8MmaScratchBytes(w, m);
+      if (need != 0) {
+        const int rc = Grow(&h->scratch_a, &h->scratch_a_bytes, need);
+        if (rc != MNB_OK) {
+          return rc;
+        }
+        name = mnb::LaunchGemvU8Mma(w, a_dev, m, static_cast<unsigned char *>(h->scratch_a), out, stream, h->sm_count);
         if (name == nullptr) {
           cudaGetLastError();
         }

@@ -570,8 +570,8 @@ WORDS_CASES = [
     (7, 4096, 129, 4, 16, True, True),
     (16, 2048, 31, 4, 16, False, True),
     (1, 14336, 257, 8, 128, True, True),
-    (2, 14336, 64, 8, 32, False, False),
-    (4, 14336, 100, 8, 64, True, False),
+    (2, 14336, 64, 8, 512, False, False),
+    (4, 14336, 100, 8, 512, True, False),
     (16, 14336, 37, 8, 512, True, True),
     (4, 8192, 50, 8, 16, True, False),
     (20, 1024, 45, 8, 16, True, True),       # three passes of eight tokens
@@ -616,6 +616,8 @@ U8_MMA_CASES = [
     (13, 14336, 260, 128, False, False),
     (7, 96, 16, 32, True, False),
     (16, 2048, 2100, 64, True, True),
+    (2, 14336, 64, 32, False, False),        # rows too long for the staged kernel, two tokens
+    (4, 14336, 100, 64, True, False),
 ]
 
 
