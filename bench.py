@@ -450,6 +450,33 @@ def main() -> None:
             del iw, ys_i8
             torch.cuda.empty_cache()
 
+            # ---- 8-bit weights, M = 8: one column shard of the large-N projection, digit columns on integer MMA ----
+            ucfg = {"k": 4096, "n": 16032, "bits": 8, "block_size": 32}
+            ucopies = 4
+            uw = device_weights(torch, pkg, ucfg, ucopies, seed=1501, zp=True, bias=False)
+            a_u8 = torch.randn(8, ucfg["k"], device="cuda")
+            ys_u8 = [torch.empty(8, ucfg["n"], device="cuda") for _ in range(ucopies)]
+
+            def u8_step():
+                for w, y in zip(uw, ys_u8):
+                    w.matmul_device(a_u8, y)
+
+            u8_step()
+            torch.cuda.synchronize()
+            uname = _capi.last_kernel()
+            ustatus = max(w.poll_status() for w in uw)
+            rep, _ = capture_graph(torch, u8_step)
+            sec = time_steps(torch, dist, rep, isteps, 3, 1)
+            ubytes = uw[0].algorithmic_bytes(8)
+            ugbs = ubytes * ucopies * isteps / sec / 1e9
+            extras["u8_shard_m8"] = {
+                "workload": "cfg5 column shard M=8 K=4096 N=16032 bits=8 block=32 zp, accuracy_level=0",
+                "gbs": ugbs, "frac_of_hbm_peak": ugbs / peaks["hbm_gbs"], "us_per_call": sec / (ucopies * isteps) * 1e6,
+                "kernel": uname, "device_status": ustatus,
+                "includes": "digit kernel + integer-MMA kernel (dependent launch)"}
+            del uw, ys_u8
+            torch.cuda.empty_cache()
+
             # ---- sibling nodes in one call: gate + up of the decode workload, M = 1, one launch per pair ----
             from onnx_light_cpu_b200.matmul_nbits import matmul_device_group
             pairs = 4
