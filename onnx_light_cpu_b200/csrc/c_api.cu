@@ -592,13 +592,27 @@ int Dispatch(mnb_weights *h, const float *a_dev, std::int64_t m, int accuracy_le
     if (rc != MNB_OK) {
       return rc;
     }
-    rc = Grow(&h->scratch_s, &h->scratch_s_bytes, static_cast<std::size_t>(m) * w.n_blocks * sizeof(float));
+    // activation scales, and behind them room for the per-block sums of the 8-bit tensor-core kernel
+    const std::size_t scale_count = static_cast<std::size_t>(m) * w.n_blocks;
+    rc = Grow(&h->scratch_s, &h->scratch_s_bytes, scale_count * (sizeof(float) + sizeof(int)));
     if (rc != MNB_OK) {
       return rc;
     }
     name = mnb::LaunchQuantizeAPadded(a_dev, m, w.k, w.block_size,
                                       static_cast<std::int8_t *>(h->scratch_a),
                                       static_cast<float *>(h->scratch_s), stream);
+    if (name != nullptr && path == MNB_PATH_AUTO && mnb::GemvU8MmaSupports(w, m)) {
+      // 8-bit weights, up to sixteen tokens: the quantized activations as columns of an integer MMA
+      const char *mma = mnb::LaunchGemvU8Int8Mma(w, static_cast<const std::int8_t *>(h->scratch_a),
+                                                 static_cast<const float *>(h->scratch_s), m,
+                                                 reinterpret_cast<int *>(static_cast<float *>(h->scratch_s) + scale_count), out,
+                                                 stream, h->sm_count);
+      if (mma != nullptr) {
+        name = mma;
+        break;
+      }
+      cudaGetLastError();
+    }
     if (name != nullptr) {
       name = mnb::LaunchInt8Matmul(w, static_cast<const std::int8_t *>(h->scratch_a),
                                    static_cast<const float *>(h->scratch_s), m, out, stream,

@@ -234,6 +234,10 @@ bool GemvU8MmaSupports(const WeightView &w, std::int64_t m);
 std::size_t GemvU8MmaScratchBytes(const WeightView &w, std::int64_t m);
 const char *LaunchGemvU8Mma(const WeightView &w, const float *a, std::int64_t m, unsigned char *scratch, OutputView out,
                             cudaStream_t stream, int sm_count);
+// The same shapes at accuracy_level 4: `aq` / `a_scales` in the padded layout of LaunchQuantizeAPadded
+// (16-byte aligned), `sums` room for m * n_blocks ints. The quantized activations are the MMA columns.
+const char *LaunchGemvU8Int8Mma(const WeightView &w, const std::int8_t *aq, const float *a_scales, std::int64_t m,
+                                int *sums, OutputView out, cudaStream_t stream, int sm_count);
 // Groups of eight codes read straight from global memory: a warp per output column with lanes along K for
 // one and two tokens, a lane per column from three tokens on; needs rows and the base of B aligned to a
 // group (4 bytes for 4-bit, 8 for 8-bit weights).

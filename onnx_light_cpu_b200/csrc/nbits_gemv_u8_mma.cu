@@ -376,7 +376,257 @@ __global__ void __launch_bounds__(kU8Warps * 32)
   }
 }
 
+// ---- accuracy_level 4 on the same structure -----------------------------------------------------------
+// The quantized activations (signed bytes, one scale per token and block) are the MMA columns themselves:
+// one column tile per eight tokens, e - zp * (sum of the block's quantized activations) in int32, one
+// conversion and one FFMA with activation scale x weight scale per output and block.
+
+// sums[token][block] of the quantized activations; aq rows are zero beyond K.
+__global__ void __launch_bounds__(256)
+    nbits_u8_aq_sums_kernel(const signed char *aq, int m_total, int n_blocks, int block_size, std::int64_t aq_ld,
+                            int *sums) {
+  const int item = blockIdx.x * 256 + threadIdx.x;
+  if (item >= m_total * n_blocks) {
+    return;
+  }
+  const int token = item / n_blocks;
+  const int block = item - token * n_blocks;
+  const uint4 *src = reinterpret_cast<const uint4 *>(aq + token * aq_ld + static_cast<std::int64_t>(block) * block_size);
+  int total = 0;
+  for (int i = 0; i < block_size / 16; ++i) {
+    const uint4 v = __ldg(src + i);
+    total = __dp4a(static_cast<int>(v.x), 0x01010101, total);
+    total = __dp4a(static_cast<int>(v.y), 0x01010101, total);
+    total = __dp4a(static_cast<int>(v.z), 0x01010101, total);
+    total = __dp4a(static_cast<int>(v.w), 0x01010101, total);
+  }
+  sums[item] = total;
+}
+
+struct U8Int8Params {
+  WeightView w;
+  const signed char *aq;   // [m][aq_ld], aq_ld = n_blocks * block_size
+  std::int64_t aq_ld;
+  const float *a_scales;   // [m][n_blocks]
+  const int *sums;         // [m][n_blocks]
+  OutputView out;
+  int m_total;
+  int parts;
+  int blocks_per_part;
+  int steps;
+  int tiles;
+};
+
+template <int NTOK, int SPB>
+__global__ void __launch_bounds__(kU8Warps * 32)
+    nbits_gemv_u8_int8_mma_kernel(const U8Int8Params p) {
+  static_assert(SPB == 1 || SPB == 2 || SPB == 4 || SPB == 8, "blocks of 32 ... 256");
+  __shared__ __align__(16) unsigned char tiles[kU8Warps][kU8TileBytes];
+  __shared__ float meet[kU8Warps][NTOK * 4][32];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int part = warp % p.parts;
+  const int tile = blockIdx.x * (kU8Warps / p.parts) + warp / p.parts;
+  const bool live = tile < p.tiles;
+  const std::int64_t row0 = static_cast<std::int64_t>(live ? tile : 0) * 16;
+  const std::int64_t r_lo = row0 + g < p.w.n ? row0 + g : p.w.n - 1;
+  const std::int64_t r_hi = row0 + g + 8 < p.w.n ? row0 + g + 8 : p.w.n - 1;
+  const float *scale_lo = p.w.scales + r_lo * p.w.n_blocks;
+  const float *scale_hi = p.w.scales + r_hi * p.w.n_blocks;
+  const std::uint8_t *zp_lo = p.w.zp != nullptr ? p.w.zp + r_lo * p.w.zp_row_bytes : nullptr;
+  const std::uint8_t *zp_hi = p.w.zp != nullptr ? p.w.zp + r_hi * p.w.zp_row_bytes : nullptr;
+  // MMA column g of tile j is token 8 j + g; outputs of this lane are tokens 8 j + 2 t and 8 j + 2 t + 1.
+  // Tokens beyond M repeat the last one; their sums are not written.
+  const signed char *act_lane[NTOK];
+  int token_a[NTOK], token_b[NTOK];
+#pragma unroll
+  for (int j = 0; j < NTOK; ++j) {
+    const int column = 8 * j + g < p.m_total ? 8 * j + g : p.m_total - 1;
+    act_lane[j] = p.aq + column * p.aq_ld + 8 * t;
+    token_a[j] = 8 * j + 2 * t < p.m_total ? 8 * j + 2 * t : p.m_total - 1;
+    token_b[j] = 8 * j + 2 * t + 1 < p.m_total ? 8 * j + 2 * t + 1 : p.m_total - 1;
+  }
+  unsigned char *my_tile = tiles[warp];
+  const int copy_row = lane >> 4;
+  const int copy_byte = (lane & 15) * 16;
+  const unsigned char *frag_lo = my_tile + g * kU8TileRowBytes + 8 * t;
+  const unsigned char *frag_hi = frag_lo + 8 * kU8TileRowBytes;
+
+  float acc[NTOK][4];
+#pragma unroll
+  for (int j = 0; j < NTOK; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[j][i] = 0.0f;
+    }
+  }
+  int block_begin = part * p.blocks_per_part;
+  int block_end = block_begin + p.blocks_per_part < p.w.n_blocks ? block_begin + p.blocks_per_part : p.w.n_blocks;
+  if (!live || block_begin > block_end) {
+    block_begin = block_end = 0;
+  }
+  const int s_begin = block_begin * SPB;
+  const int s_end = block_end * SPB < p.steps ? block_end * SPB : p.steps;
+
+  uint4 next[kU8Super];
+  auto request = [&](int s_first) {
+    const int byte = s_first * 32 + copy_byte;
+    const bool inside = byte + 16 <= s_end * 32;
+#pragma unroll
+    for (int i = 0; i < kU8Super; ++i) {
+      const std::int64_t row = row0 + 2 * i + copy_row < p.w.n ? row0 + 2 * i + copy_row : p.w.n - 1;
+      next[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (inside) {
+        next[i] = LoadStreaming16(p.w.b + row * p.w.row_bytes + byte);
+      }
+    }
+  };
+  if (s_begin < s_end) {
+    request(s_begin);
+  }
+  int d[NTOK][4];
+  const ZeroQuad zero = MakeZeroQuad();
+#pragma unroll 1
+  for (int s0 = s_begin; s0 < s_end; s0 += kU8Super) {
+    __syncwarp(); // the tile before has been read
+#pragma unroll
+    for (int i = 0; i < kU8Super; ++i) {
+      *reinterpret_cast<uint4 *>(my_tile + (2 * i + copy_row) * kU8TileRowBytes + copy_byte) = next[i];
+    }
+    __syncwarp();
+    if (s0 + kU8Super < s_end) {
+      request(s0 + kU8Super);
+    }
+#pragma unroll
+    for (int u = 0; u < kU8Super; ++u) {
+      const int s = s0 + u;
+      if (s < s_end) {
+        const uint2 lo = *reinterpret_cast<const uint2 *>(frag_lo + u * 32);
+        const uint2 hi = *reinterpret_cast<const uint2 *>(frag_hi + u * 32);
+#pragma unroll
+        for (int j = 0; j < NTOK; ++j) {
+          const uint2 bq = __ldg(reinterpret_cast<const uint2 *>(act_lane[j] + s * 32));
+          if (u % SPB == 0) {
+            ImmaFresh(d[j], lo.x, hi.x, lo.y, hi.y, bq.x, bq.y, zero);
+          } else {
+            ImmaAdd(d[j], lo.x, hi.x, lo.y, hi.y, bq.x, bq.y);
+          }
+        }
+        if ((u + 1) % SPB == 0) {
+          // a quantization block is complete
+          const int block = s / SPB;
+          const float ws_lo = __ldg(scale_lo + block);
+          const float ws_hi = __ldg(scale_hi + block);
+          const int z_lo = zp_lo != nullptr ? static_cast<int>(__ldg(zp_lo + block)) : 128;
+          const int z_hi = zp_hi != nullptr ? static_cast<int>(__ldg(zp_hi + block)) : 128;
+#pragma unroll
+          for (int j = 0; j < NTOK; ++j) {
+            const float sa_a = __ldg(p.a_scales + token_a[j] * p.w.n_blocks + block);
+            const float sa_b = __ldg(p.a_scales + token_b[j] * p.w.n_blocks + block);
+            const int sum_a = __ldg(p.sums + token_a[j] * p.w.n_blocks + block);
+            const int sum_b = __ldg(p.sums + token_b[j] * p.w.n_blocks + block);
+            acc[j][0] = fmaf(sa_a * ws_lo, static_cast<float>(d[j][0] - z_lo * sum_a), acc[j][0]);
+            acc[j][1] = fmaf(sa_b * ws_lo, static_cast<float>(d[j][1] - z_lo * sum_b), acc[j][1]);
+            acc[j][2] = fmaf(sa_a * ws_hi, static_cast<float>(d[j][2] - z_hi * sum_a), acc[j][2]);
+            acc[j][3] = fmaf(sa_b * ws_hi, static_cast<float>(d[j][3] - z_hi * sum_b), acc[j][3]);
+          }
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < NTOK; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      meet[warp][j * 4 + i][lane] = acc[j][i];
+    }
+  }
+  __syncthreads();
+  if (live && part == 0) {
+#pragma unroll
+    for (int j = 0; j < NTOK; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float total = acc[j][i];
+        for (int other = 1; other < p.parts; ++other) {
+          total += meet[warp + other][j * 4 + i][lane];
+        }
+        const int token = 8 * j + 2 * t + (i & 1);
+        const std::int64_t row = row0 + g + (i >> 1) * 8;
+        if (token < p.m_total && row < p.w.n) {
+          const float bias = p.w.bias != nullptr ? __ldg(p.w.bias + row) : 0.0f;
+          p.out.y[static_cast<std::int64_t>(token) * p.out.ld + p.out.col_offset + row] = total + bias;
+        }
+      }
+    }
+  }
+}
+
+// Warps per row tile: towards sixteen warps per SM, every part at least four blocks.
+int PartsFor(const WeightView &w, int tiles, int sm_count) {
+  const std::int64_t wanted = std::int64_t{16} * (sm_count > 0 ? sm_count : 148);
+  int parts = 1;
+  while (parts < kU8Warps && static_cast<std::int64_t>(tiles) * parts < wanted && w.n_blocks >= 8 * parts) {
+    parts *= 2;
+  }
+  return parts;
+}
+
+template <int NTOK>
+cudaError_t LaunchU8Int8(const U8Int8Params &p, int steps_per_block, unsigned grid, cudaStream_t stream) {
+  switch (steps_per_block) {
+  case 1: nbits_gemv_u8_int8_mma_kernel<NTOK, 1><<<grid, kU8Warps * 32, 0, stream>>>(p); break;
+  case 2: nbits_gemv_u8_int8_mma_kernel<NTOK, 2><<<grid, kU8Warps * 32, 0, stream>>>(p); break;
+  case 4: nbits_gemv_u8_int8_mma_kernel<NTOK, 4><<<grid, kU8Warps * 32, 0, stream>>>(p); break;
+  case 8: nbits_gemv_u8_int8_mma_kernel<NTOK, 8><<<grid, kU8Warps * 32, 0, stream>>>(p); break;
+  default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
 } // namespace
+
+const char *LaunchGemvU8Int8Mma(const WeightView &w, const std::int8_t *aq, const float *a_scales, std::int64_t m,
+                                int *sums, OutputView out, cudaStream_t stream, int sm_count) {
+  if (!GemvU8MmaSupports(w, m) || sums == nullptr || (reinterpret_cast<std::uintptr_t>(aq) & 15u) != 0) {
+    return nullptr;
+  }
+  const std::int64_t aq_ld = static_cast<std::int64_t>(w.n_blocks) * w.block_size;
+  const int items = static_cast<int>(m) * w.n_blocks;
+  nbits_u8_aq_sums_kernel<<<(items + 255) / 256, 256, 0, stream>>>(reinterpret_cast<const signed char *>(aq),
+                                                                   static_cast<int>(m), w.n_blocks, w.block_size, aq_ld,
+                                                                   sums);
+  if (cudaGetLastError() != cudaSuccess) {
+    return nullptr;
+  }
+  CountLaunch();
+  U8Int8Params p{};
+  p.w = w;
+  p.aq = reinterpret_cast<const signed char *>(aq);
+  p.aq_ld = aq_ld;
+  p.a_scales = a_scales;
+  p.sums = sums;
+  p.out = out;
+  p.m_total = static_cast<int>(m);
+  p.steps = w.row_bytes / 32;
+  p.tiles = static_cast<int>((w.n + 15) / 16);
+  p.parts = PartsFor(w, p.tiles, sm_count);
+  p.blocks_per_part = (w.n_blocks + p.parts - 1) / p.parts;
+  const int tiles_per_cta = kU8Warps / p.parts;
+  const unsigned grid = static_cast<unsigned>((p.tiles + tiles_per_cta - 1) / tiles_per_cta);
+  const cudaError_t launched = m <= 8 ? LaunchU8Int8<1>(p, w.block_size / 32, grid, stream)
+                                      : LaunchU8Int8<2>(p, w.block_size / 32, grid, stream);
+  if (launched != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  CountLaunch();
+  return "nbits_gemv_u8_int8_mma_kernel";
+}
 
 bool GemvU8MmaSupports(const WeightView &w, std::int64_t m) {
   return w.bits == 8 && m >= 1 && m <= 16 && w.block_size >= 32 && w.block_size <= 256 && w.n >= 1 && w.k >= 1 &&
@@ -417,12 +667,7 @@ const char *LaunchGemvU8Mma(const WeightView &w, const float *a, std::int64_t m,
   p.m_total = static_cast<int>(m);
   p.steps = layout.steps;
   p.tiles = static_cast<int>((w.n + 15) / 16);
-  // warps per row tile: towards sixteen warps per SM, every part at least four blocks
-  const std::int64_t wanted = std::int64_t{16} * (sm_count > 0 ? sm_count : 148);
-  int parts = 1;
-  while (parts < kU8Warps && static_cast<std::int64_t>(p.tiles) * parts < wanted && w.n_blocks >= 8 * parts) {
-    parts *= 2;
-  }
+  const int parts = PartsFor(w, p.tiles, sm_count);
   p.parts = parts;
   p.blocks_per_part = (w.n_blocks + parts - 1) / parts;
   const int tiles_per_cta = kU8Warps / parts;

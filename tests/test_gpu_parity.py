@@ -885,6 +885,18 @@ def test_int8_path_block16(cuda_device, m, k, n, bits, bs, zp):
     assert rel_err(y, oracle_f64(case)) <= 3e-2   # int8 activations vs exact
 
 
+@pytest.mark.parametrize("m,k,n,bs,zp", [(16, 4096, 200, 32, True), (8, 1024, 50, 64, False), (5, 4000, 33, 32, True),
+                                         (9, 14336, 40, 128, True), (1, 4096, 77, 256, True), (3, 96, 7, 32, True)])
+def test_int8_path_eight_bit_weights_on_integer_mma(cuda_device, m, k, n, bs, zp):
+    """accuracy_level 4 under AUTO with 8-bit weights: the quantized activations as MMA columns."""
+    case = syn.make_case("lvl4u8", m, k, n, 8, bs, seed=2 * m + n, zero_points=zp, bias=True)
+    y, kernel = run_device(case, accuracy_level=4)
+    assert kernel == "nbits_gemv_u8_int8_mma_kernel", kernel
+    ref = o.matmul_int8(case.a, case.b, case.scales, case.zero_points, case.bias, n, k, 8, bs)
+    assert rel_err(y, ref) <= TOL_FP32   # same integers, fp32 scaling in a different order
+    assert rel_err(y, oracle_f64(case)) <= 3e-2   # int8 activations vs exact
+
+
 @pytest.mark.parametrize("m,k,n,bits,bs,zp", [(16, 4096, 128, 4, 32, False), (1, 4096, 77, 4, 128, True),
                                               (9, 1024, 50, 8, 32, True), (16, 4064, 31, 4, 32, True)])
 def test_int8_path_outputs(cuda_device, m, k, n, bits, bs, zp):
