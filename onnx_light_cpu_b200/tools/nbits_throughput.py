@@ -39,6 +39,7 @@ SHAPES = (
     ("cfg5_shard8_m256", 256, 4096, 16032, 4, 32, True, False, 0),
     ("cfg5_shard8_m8_8bit", 8, 4096, 16032, 8, 32, True, False, 0),
     ("cfg5_shard8_m256_8bit", 256, 4096, 16032, 8, 32, True, False, 0),
+    ("cfg5_shard8_m8_8bit_level4", 8, 4096, 16032, 8, 32, True, False, 4),
     # between decode and prefill: 17 <= M <= 256 on the decode geometry and the prefill geometry
     ("mid_cfg2_m32", 32, 4096, 14336, 4, 128, True, True, 0),
     ("mid_cfg2_m64", 64, 4096, 14336, 4, 128, True, True, 0),
