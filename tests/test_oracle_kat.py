@@ -97,3 +97,33 @@ def test_config_shapes():
     shard = syn.shard_columns(c5, 4, 1)
     assert shard.n == 32 and shard.meta["col_offset"] == 32
     assert np.array_equal(shard.scales, c5.scales.reshape(128, 128)[32:64].reshape(-1))
+
+
+def test_digit_split_invariants_of_the_integer_mma_decode_kernels():
+    """The integer-MMA decode kernels (csrc/nbits_digits.cuh, csrc/nbits_gemv_u8_mma.cu) write an activation
+    row as n = round(a / max|a| * 2e6) = 16384 d0 + 128 d1 + d2 with balanced base-128 digits taken from the
+    plain digits of the biased integer n + 64 + 64 * 128 + 128 * 16384. Restated here in numpy: the identity,
+    the signed-byte ranges, the int32 / 2^24 bounds the per-block sums rely on, and the accuracy of a product
+    rebuilt from the digits against the float64 product."""
+    rng = np.random.default_rng(2026)
+    k, block = 4096, 256
+    a = (rng.standard_normal(k) * np.exp(rng.uniform(-3, 3, size=k))).astype(np.float32)
+    amax = np.abs(a).max()
+    n = np.rint(a.astype(np.float64) / amax * 2.0e6).astype(np.int64)
+    bias = 64 + 64 * 128 + 128 * 16384
+    u = n + bias
+    assert u.min() > 0 and u.max() < 2 ** 22
+    d0, d1, d2 = (u >> 14) - 128, ((u >> 7) & 127) - 64, (u & 127) - 64
+    assert np.array_equal(16384 * d0 + 128 * d1 + d2, n)
+    assert np.abs(d0).max() <= 123 and d1.min() >= -64 and d1.max() <= 63 and d2.min() >= -64 and d2.max() <= 63
+    # exact int32 block sums: 8-bit codes against digits, blocks of up to 256
+    assert 255 * 123 * block < 2 ** 24
+    # middle and low digit combined before the conversion, zero point taken out in int32
+    worst = 128 * (255 * 64 * block) + 255 * 64 * block + 255 * (128 * 64 * block + 64 * block)
+    assert worst < 2 ** 31
+    # a product rebuilt from the digits is within 1e-5 of the float64 product (codes minus zero point)
+    w = rng.integers(0, 256, size=k).astype(np.int64) - 128
+    rebuilt = float((w * (16384 * d0 + 128 * d1 + d2)).sum()) * (float(amax) / 2.0e6)
+    exact = float((w.astype(np.float64) * a.astype(np.float64)).sum())
+    scale = float(np.abs(w.astype(np.float64) * a.astype(np.float64)).sum())
+    assert abs(rebuilt - exact) <= 1e-6 * scale
